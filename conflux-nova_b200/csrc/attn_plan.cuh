@@ -1,0 +1,113 @@
+// attn_plan.cuh — device-side stream-K partition of a decode-attention launch.
+//
+// Rows of one layer: r = s * n_groups + g (session s, kv-head group g); their page counts are
+// prefix-summed into shared memory once per CTA.  The launch-wide page line has
+// P = n_layers * P_layer entries and CTA c owns [c*P/C, (c+1)*P/C).  Everything below is
+// computed redundantly (and identically) by every thread from that prefix array, so the
+// host never has to build or upload a work list and the same launch can be replayed from a
+// CUDA graph while n_past grows on the device.
+#pragma once
+#include "common.cuh"
+
+namespace novab {
+
+struct PlanView {
+    const int* prefix;     // shared memory, rows_per_layer + 1 entries
+    int rows_per_layer;    // S * n_groups
+    int n_groups;
+    int64_t pages_per_layer;
+    int64_t pages_total;   // n_layers * pages_per_layer
+    int n_ctas;
+};
+
+struct Segment {
+    int layer_local;   // 0 .. n_layers-1
+    int row;           // row within the layer
+    int session;
+    int group;
+    int64_t row_id;    // layer_local * rows_per_layer + row
+    int page_first;    // first page of this segment, relative to the row's first page
+    int page_count;
+    int c_first;       // first and last CTA that touch this row
+    int c_last;
+};
+
+__device__ __forceinline__ int plan_session_keys(const AttnLaunch& a, int s) {
+    return a.n_past ? (a.n_past[s] + a.keys_add) : a.keys_imm;
+}
+
+// First logical page and page count of session s inside the launch's page window.
+__device__ __forceinline__ void plan_session_pages(const AttnLaunch& a, int s, int& first, int& count) {
+    const int n_keys = plan_session_keys(a, s);
+    int64_t total = n_keys > 0 ? (((int64_t)n_keys + kKvBlock - 1) >> kKvShift) : 0;
+    if (total > a.table_stride) total = a.table_stride;   // never walk past the table
+    int64_t lo = a.page_lo > 0 ? a.page_lo : 0;
+    int64_t hi = (a.page_hi >= 0 && a.page_hi < total) ? a.page_hi : total;
+    if (lo > hi) lo = hi;
+    first = (int)lo;
+    count = (int)(hi - lo);
+}
+
+// Fills prefix[0..rows] (shared memory) with a warp scan; call from all threads of the CTA.
+__device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n_groups) {
+    const int rows = a.n_sessions * n_groups;
+    if (threadIdx.x < 32) {
+        const int lane = (int)threadIdx.x;
+        int carry = 0;
+        if (lane == 0) prefix[0] = 0;
+        for (int base = 0; base < rows; base += 32) {
+            const int r = base + lane;
+            int v = 0;
+            if (r < rows) {
+                int first, count;
+                plan_session_pages(a, r / n_groups, first, count);
+                v = count;
+            }
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += t;
+            }
+            if (r < rows) prefix[r + 1] = carry + v;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ int plan_owner(const PlanView& p, int64_t page) {
+    return (int)((((page + 1) * (int64_t)p.n_ctas) - 1) / p.pages_total);
+}
+
+__device__ __forceinline__ int64_t plan_cta_begin(const PlanView& p, int c) {
+    return ((int64_t)c * p.pages_total) / p.n_ctas;
+}
+
+// Segment that starts at launch-wide page `pos` and ends at the row's end or at `hi`.
+__device__ inline Segment plan_segment(const PlanView& p, int64_t pos, int64_t hi) {
+    Segment sg;
+    sg.layer_local = (int)(pos / p.pages_per_layer);
+    const int64_t layer_base = (int64_t)sg.layer_local * p.pages_per_layer;
+    const int r = (int)(pos - layer_base);
+    int lo = 0, up = p.rows_per_layer;           // find row with prefix[row] <= r < prefix[row+1]
+    while (up - lo > 1) {
+        const int mid = (lo + up) >> 1;
+        if (p.prefix[mid] <= r) lo = mid; else up = mid;
+    }
+    // rows with zero pages share a prefix value with their successor: move to the last one
+    while (lo + 1 < p.rows_per_layer && p.prefix[lo + 1] <= r) ++lo;
+    sg.row = lo;
+    sg.session = lo / p.n_groups;
+    sg.group = lo - sg.session * p.n_groups;
+    sg.row_id = (int64_t)sg.layer_local * p.rows_per_layer + lo;
+    const int64_t row_begin = layer_base + p.prefix[lo];
+    const int64_t row_end = layer_base + p.prefix[lo + 1];
+    const int64_t end = row_end < hi ? row_end : hi;
+    sg.page_first = (int)(pos - row_begin);
+    sg.page_count = (int)(end - pos);
+    sg.c_first = plan_owner(p, row_begin);
+    sg.c_last = plan_owner(p, row_end - 1);
+    return sg;
+}
+
+}  // namespace novab

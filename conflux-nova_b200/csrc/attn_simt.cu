@@ -1,0 +1,404 @@
+// attn_simt.cu — paged split-K decode attention, SIMT form, for every session of a batch
+// (and optionally every layer) in ONE launch.  Replaces fa_split_paged_kernel +
+// fa_combine_kernel (src/kernel/attn.cu:197-289,163-191) and the per-session launch loop of
+// Engine::decode_batch (src/model.cpp:286-290).
+//
+// One warp per kv head: the G = NH/NKV query heads that share it are packed, so every K and
+// V row is read from HBM once (the reference reads it G times).  Each lane owns 4 of the 128
+// dims; a key costs G 4-term dot partials, one transposing butterfly (9 shuffles + G
+// broadcasts instead of 5G), an online softmax in the exp2 domain and 4G fp32 FMAs on V.
+// Pages are walked straight from global memory with 8/16-byte loads, two keys in flight.
+// Work is cut stream-K style over pages (attn_plan.cuh); the last CTA to arrive at a row
+// merges its partials — no spinning anywhere.
+//
+// This is the fp32-accumulating reference form of the product: it serves fp32 pools (the
+// reference's own format) and is the correctness anchor for the tensor-core kernel.
+#include "attn_plan.cuh"
+
+namespace novab {
+namespace {
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void load4(const float* p, float (&x)[4]) {
+    const float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+    x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __half* p, float (&x)[4]) {
+    const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+}
+
+// Sum v[g] over the 32 lanes for up to 8 values at once: after three exchange-and-halve
+// steps each lane holds one value's partial for head (lane>>2)&7, two more steps finish it.
+template <int G>
+__device__ __forceinline__ void reduce_heads(float (&v)[8], float (&out)[G], int lane) {
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float snd = b4 ? v[j] : v[j + 4];
+        const float kp = b4 ? v[j + 4] : v[j];
+        v[j] = kp + __shfl_xor_sync(0xffffffffu, snd, 16);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const float snd = b3 ? v[j] : v[j + 2];
+        const float kp = b3 ? v[j + 2] : v[j];
+        v[j] = kp + __shfl_xor_sync(0xffffffffu, snd, 8);
+    }
+    {
+        const float snd = b2 ? v[0] : v[1];
+        const float kp = b2 ? v[1] : v[0];
+        v[0] = kp + __shfl_xor_sync(0xffffffffu, snd, 4);
+    }
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 2);
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], 1);
+#pragma unroll
+    for (int g = 0; g < G; ++g) out[g] = __shfl_sync(0xffffffffu, v[0], 4 * g);
+}
+
+template <int G>
+struct HeadState {
+    float m[G], l[G], acc[G][4];
+    __device__ __forceinline__ void reset() {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            m[g] = -INFINITY;
+            l[g] = 0.f;
+#pragma unroll
+            for (int d = 0; d < 4; ++d) acc[g][d] = 0.f;
+        }
+    }
+};
+
+// Merge the partial rows of slots [c_first .. c_last] for one head (fixed order), then
+// either normalise into `out` or leave (m, l, acc) in `out_part`.
+__device__ __forceinline__ void merge_head(const float* part, int heads_per_row, int head_in_row, int64_t row_id,
+                                           int c_first, int c_last, int lane, float* out, float* out_part) {
+    float M = -INFINITY;
+    for (int c = c_first; c <= c_last; ++c) {
+        const float* pr = part + ((size_t)(c + row_id) * heads_per_row + head_in_row) * kPartW;
+        if (pr[1] > 0.f) M = fmaxf(M, pr[0]);
+    }
+    float L = 0.f, A[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = c_first; c <= c_last; ++c) {
+        const float* pr = part + ((size_t)(c + row_id) * heads_per_row + head_in_row) * kPartW;
+        const float lc = pr[1];
+        if (lc > 0.f) {
+            const float w = __expf(pr[0] - M);
+            L = fmaf(lc, w, L);
+            // a row is 130 floats, so acc (at pr+2) is only 8-byte aligned: two float2 loads
+            const float2 a0 = *reinterpret_cast<const float2*>(pr + 2 + 4 * lane);
+            const float2 a1 = *reinterpret_cast<const float2*>(pr + 4 + 4 * lane);
+            A[0] = fmaf(a0.x, w, A[0]); A[1] = fmaf(a0.y, w, A[1]);
+            A[2] = fmaf(a1.x, w, A[2]); A[3] = fmaf(a1.y, w, A[3]);
+        }
+    }
+    if (out_part) {
+        if (lane == 0) { out_part[0] = M; out_part[1] = L; }
+#pragma unroll
+        for (int d = 0; d < 4; ++d) out_part[2 + 4 * lane + d] = A[d];
+    } else {
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        *reinterpret_cast<float4*>(out + 4 * lane) = make_float4(A[0] * inv, A[1] * inv, A[2] * inv, A[3] * inv);
+    }
+}
+
+template <typename KvT, int G>
+__global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
+    __shared__ int s_prefix[kMaxRowsSmem + 1];
+    __shared__ int s_last;
+
+    const int lane = (int)threadIdx.x & 31;
+    const int warp = (int)threadIdx.x >> 5;
+    const int KVG = a.kv_group;
+    const int n_groups = a.n_kv_heads / KVG;
+    const int NKV = a.n_kv_heads, NH = a.n_heads, S = a.n_sessions;
+    const int heads_per_row = KVG * G;
+
+    plan_build_prefix(a, s_prefix, n_groups);
+    PlanView pv;
+    pv.prefix = s_prefix;
+    pv.rows_per_layer = S * n_groups;
+    pv.n_groups = n_groups;
+    pv.pages_per_layer = s_prefix[pv.rows_per_layer];
+    pv.pages_total = pv.pages_per_layer * a.n_layers;
+    pv.n_ctas = (int)gridDim.x;
+
+    // Rows without any page in the window get their "nothing attended" result here.
+    {
+        const int64_t rows_total = (int64_t)pv.rows_per_layer * a.n_layers;
+        for (int64_t v = blockIdx.x; v < rows_total; v += gridDim.x) {
+            const int row = (int)(v % pv.rows_per_layer);
+            if (s_prefix[row + 1] != s_prefix[row]) continue;
+            const int ll = (int)(v / pv.rows_per_layer);
+            const int s = row / n_groups, g = row - s * n_groups;
+            const int kvh = g * KVG + warp;
+            for (int h = 0; h < G; ++h) {
+                const int64_t head = ((int64_t)ll * S + s) * NH + (int64_t)kvh * G + h;
+                if (a.write_partial_only) {
+                    float* op = a.out_part + head * kPartW;
+                    if (lane == 0) { op[0] = -INFINITY; op[1] = 0.f; }
+                    for (int d = 0; d < 4; ++d) op[2 + 4 * lane + d] = 0.f;
+                } else if (a.fused_combine) {
+                    *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+        }
+    }
+    if (pv.pages_total == 0) return;
+
+    const int64_t lo = plan_cta_begin(pv, (int)blockIdx.x);
+    const int64_t hi = plan_cta_begin(pv, (int)blockIdx.x + 1);
+    const KvT* pool_k = static_cast<const KvT*>(a.pool_k);
+    const KvT* pool_v = static_cast<const KvT*>(a.pool_v);
+    const int64_t row_elems = (int64_t)NKV * kHeadDim;
+    constexpr float kQScale = kAttnScale * kLog2e;
+
+    for (int64_t pos = lo; pos < hi;) {
+        const Segment sg = plan_segment(pv, pos, hi);
+        pos += sg.page_count;
+        const int s = sg.session;
+        const int kvh = sg.group * KVG + warp;
+        const int layer = a.layer0 + sg.layer_local;
+        const int n_keys = plan_session_keys(a, s);
+        int first_page, n_pages_row;
+        plan_session_pages(a, s, first_page, n_pages_row);
+        const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
+        const int64_t head0 = ((int64_t)sg.layer_local * S + s) * NH + (int64_t)kvh * G;
+
+        float qr[G][4];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float4 t = *reinterpret_cast<const float4*>(a.q + (head0 + g) * kHeadDim + 4 * lane);
+            qr[g][0] = t.x * kQScale; qr[g][1] = t.y * kQScale; qr[g][2] = t.z * kQScale; qr[g][3] = t.w * kQScale;
+        }
+        HeadState<G> st;
+        st.reset();
+
+        for (int pg = 0; pg < sg.page_count; ++pg) {
+            const int page = first_page + sg.page_first + pg;
+            const int phys = __ldg(table + page);
+            if (phys < 0 || phys >= a.nb) {
+                if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
+                continue;
+            }
+            int kcount = n_keys - page * kKvBlock;
+            if (kcount > kKvBlock) kcount = kKvBlock;
+            const int64_t base = (((int64_t)layer * a.nb + phys) * kKvBlock) * row_elems + (int64_t)kvh * kHeadDim + 4 * lane;
+            const KvT* kp = pool_k + base;
+            const KvT* vp = pool_v + base;
+            for (int slot = 0; slot < kcount; slot += 2) {
+                const bool two = slot + 1 < kcount;
+                float k0[4], k1[4] = {0.f, 0.f, 0.f, 0.f}, v0[4], v1[4] = {0.f, 0.f, 0.f, 0.f};
+                load4(kp + (int64_t)slot * row_elems, k0);
+                load4(vp + (int64_t)slot * row_elems, v0);
+                if (two) {
+                    load4(kp + (int64_t)(slot + 1) * row_elems, k1);
+                    load4(vp + (int64_t)(slot + 1) * row_elems, v1);
+                }
+                float d0[8], d1[8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    if (g < G) {
+                        d0[g] = fmaf(qr[g][3], k0[3], fmaf(qr[g][2], k0[2], fmaf(qr[g][1], k0[1], qr[g][0] * k0[0])));
+                        d1[g] = fmaf(qr[g][3], k1[3], fmaf(qr[g][2], k1[2], fmaf(qr[g][1], k1[1], qr[g][0] * k1[0])));
+                    } else {
+                        d0[g] = 0.f;
+                        d1[g] = 0.f;
+                    }
+                }
+                float s0[G], s1[G];
+                reduce_heads<G>(d0, s0, lane);
+                reduce_heads<G>(d1, s1, lane);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float sc1 = two ? s1[g] : -INFINITY;
+                    const float mn = fmaxf(st.m[g], fmaxf(s0[g], sc1));
+                    const float corr = ex2(st.m[g] - mn);
+                    const float p0 = ex2(s0[g] - mn);
+                    const float p1 = ex2(sc1 - mn);
+                    st.l[g] = fmaf(st.l[g], corr, p0 + p1);
+#pragma unroll
+                    for (int d = 0; d < 4; ++d)
+                        st.acc[g][d] = fmaf(p1, v1[d], fmaf(p0, v0[d], st.acc[g][d] * corr));
+                    st.m[g] = mn;
+                }
+            }
+        }
+
+        const int n_contrib = sg.c_last - sg.c_first + 1;
+        const bool direct = a.fused_combine && n_contrib == 1;
+        if (direct) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                if (a.write_partial_only) {
+                    float* op = a.out_part + (head0 + g) * kPartW;
+                    if (lane == 0) { op[0] = st.m[g] * (1.f / kLog2e); op[1] = st.l[g]; }
+#pragma unroll
+                    for (int d = 0; d < 4; ++d) op[2 + 4 * lane + d] = st.acc[g][d];
+                } else {
+                    const float inv = st.l[g] > 0.f ? 1.f / st.l[g] : 0.f;
+                    *reinterpret_cast<float4*>(a.out + (head0 + g) * kHeadDim + 4 * lane) =
+                        make_float4(st.acc[g][0] * inv, st.acc[g][1] * inv, st.acc[g][2] * inv, st.acc[g][3] * inv);
+                }
+            }
+            continue;
+        }
+        // partial slot (cta + row): rows [heads_per_row][130], m in natural-log units
+        {
+            float* slot_base = a.part + (size_t)((int64_t)blockIdx.x + sg.row_id) * heads_per_row * kPartW;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float* pr = slot_base + (size_t)(warp * G + g) * kPartW;
+                if (lane == 0) { pr[0] = st.m[g] * (1.f / kLog2e); pr[1] = st.l[g]; }
+                *reinterpret_cast<float2*>(pr + 2 + 4 * lane) = make_float2(st.acc[g][0], st.acc[g][1]);
+                *reinterpret_cast<float2*>(pr + 4 + 4 * lane) = make_float2(st.acc[g][2], st.acc[g][3]);
+            }
+        }
+        if (!a.fused_combine) continue;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            const unsigned old = atomicAdd(a.tickets + sg.row_id, 1u);
+            s_last = (old == (unsigned)(n_contrib - 1));
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+                merge_head(a.part, heads_per_row, warp * G + g, sg.row_id, sg.c_first, sg.c_last, lane,
+                           a.write_partial_only ? nullptr : a.out + (head0 + g) * kHeadDim,
+                           a.write_partial_only ? a.out_part + (head0 + g) * kPartW : nullptr);
+            if (threadIdx.x == 0) a.tickets[sg.row_id] = 0u;
+        }
+        __syncthreads();   // s_last is rewritten by the next segment
+    }
+}
+
+// Separate merge for launches without tickets (caller-provided scratch): one CTA per row.
+template <int G>
+__global__ void __launch_bounds__(128) part_merge_kernel(AttnLaunch a, int n_ctas_split) {
+    __shared__ int s_prefix[kMaxRowsSmem + 1];
+    const int lane = (int)threadIdx.x & 31;
+    const int warp = (int)threadIdx.x >> 5;
+    const int KVG = a.kv_group;
+    const int n_groups = a.n_kv_heads / KVG;
+    plan_build_prefix(a, s_prefix, n_groups);
+    PlanView pv;
+    pv.prefix = s_prefix;
+    pv.rows_per_layer = a.n_sessions * n_groups;
+    pv.n_groups = n_groups;
+    pv.pages_per_layer = s_prefix[pv.rows_per_layer];
+    pv.pages_total = pv.pages_per_layer * a.n_layers;
+    pv.n_ctas = n_ctas_split;
+    const int64_t rows_total = (int64_t)pv.rows_per_layer * a.n_layers;
+    for (int64_t v = blockIdx.x; v < rows_total; v += gridDim.x) {
+        const int row = (int)(v % pv.rows_per_layer);
+        const int ll = (int)(v / pv.rows_per_layer);
+        const int s = row / n_groups, g = row - s * n_groups;
+        const int kvh = g * KVG + warp;
+        const int64_t head0 = ((int64_t)ll * a.n_sessions + s) * a.n_heads + (int64_t)kvh * G;
+        if (s_prefix[row + 1] == s_prefix[row]) {
+            for (int h = 0; h < G; ++h)
+                *reinterpret_cast<float4*>(a.out + (head0 + h) * kHeadDim + 4 * lane) = make_float4(0.f, 0.f, 0.f, 0.f);
+            continue;
+        }
+        const int64_t row_begin = (int64_t)ll * pv.pages_per_layer + s_prefix[row];
+        const int64_t row_end = (int64_t)ll * pv.pages_per_layer + s_prefix[row + 1];
+        const int c_first = plan_owner(pv, row_begin), c_last = plan_owner(pv, row_end - 1);
+        for (int h = 0; h < G; ++h)
+            merge_head(a.part, KVG * G, warp * G + h, v, c_first, c_last, lane, a.out + (head0 + h) * kHeadDim, nullptr);
+    }
+}
+
+// LSE merge of n_parts stacked partial buffers [n_parts][n_rows][130] -> out [n_rows][128],
+// parts taken in index order (fa_combine_kernel's arithmetic, src/kernel/attn.cu:169-190).
+__global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restrict__ parts, int n_parts, int n_rows,
+                                                          float* __restrict__ out) {
+    const int row = (int)blockIdx.x;
+    const int d = (int)threadIdx.x;
+    if (row >= n_rows) return;
+    float M = -INFINITY;
+    for (int p = 0; p < n_parts; ++p) {
+        const float* pr = parts + ((size_t)p * n_rows + row) * kPartW;
+        if (pr[1] > 0.f) M = fmaxf(M, pr[0]);
+    }
+    float L = 0.f, A = 0.f;
+    for (int p = 0; p < n_parts; ++p) {
+        const float* pr = parts + ((size_t)p * n_rows + row) * kPartW;
+        if (pr[1] > 0.f) {
+            const float w = __expf(pr[0] - M);
+            L = fmaf(pr[1], w, L);
+            A = fmaf(pr[2 + d], w, A);
+        }
+    }
+    out[(size_t)row * kHeadDim + d] = L > 0.f ? A / L : 0.f;
+}
+
+template <typename KvT>
+int launch_simt_g(const AttnLaunch& a, int G, int n_ctas, cudaStream_t s) {
+    const unsigned threads = 32u * (unsigned)a.kv_group;
+    switch (G) {
+#define NOVA_CASE(g) case g: attn_simt_kernel<KvT, g><<<(unsigned)n_ctas, threads, 0, s>>>(a); break;
+        NOVA_CASE(1) NOVA_CASE(2) NOVA_CASE(4) NOVA_CASE(5) NOVA_CASE(6) NOVA_CASE(7) NOVA_CASE(8)
+#undef NOVA_CASE
+        default: return NOVA_ERR_UNSUPPORTED;
+    }
+    return NOVA_OK;
+}
+
+}  // namespace
+
+int attn_default_ctas_simt(int n_kv_heads) {
+    // 128-thread (or smaller) CTAs, 16 warps per SM resident: enough loads in flight without smem.
+    const int kvg = n_kv_heads < 4 ? n_kv_heads : 4;
+    return 148 * (16 / kvg);
+}
+
+int launch_attn_simt(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
+    if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
+    if (a.n_heads % a.n_kv_heads || a.kv_group < 1 || a.kv_group > 4 || a.n_kv_heads % a.kv_group)
+        return NOVA_ERR_INVALID;
+    if ((int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
+    if (n_ctas <= 0) n_ctas = attn_default_ctas_simt(a.n_kv_heads);
+    const int G = a.n_heads / a.n_kv_heads;
+    int rc;
+    if (kv_dtype == NOVA_KV_F16) rc = launch_simt_g<__half>(a, G, n_ctas, s);
+    else if (kv_dtype == NOVA_KV_F32) rc = launch_simt_g<float>(a, G, n_ctas, s);
+    else return NOVA_ERR_UNSUPPORTED;
+    if (rc != NOVA_OK) return rc;
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+int launch_part_merge(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
+    const int G = a.n_heads / a.n_kv_heads;
+    const int64_t rows = (int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) * a.n_layers;
+    const unsigned grid = (unsigned)(rows < 148 * 8 ? rows : 148 * 8);
+    const unsigned threads = 32u * (unsigned)a.kv_group;
+    switch (G) {
+#define NOVA_CASE(g) case g: part_merge_kernel<g><<<grid, threads, 0, s>>>(a, n_ctas_split); break;
+        NOVA_CASE(1) NOVA_CASE(2) NOVA_CASE(4) NOVA_CASE(5) NOVA_CASE(6) NOVA_CASE(7) NOVA_CASE(8)
+#undef NOVA_CASE
+        default: return NOVA_ERR_UNSUPPORTED;
+    }
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s) {
+    if (n_rows <= 0 || n_parts <= 0) return NOVA_OK;
+    lse_combine_kernel<<<(unsigned)n_rows, kHeadDim, 0, s>>>(parts, n_parts, n_rows, out);
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+}  // namespace novab

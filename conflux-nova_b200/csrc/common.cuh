@@ -1,0 +1,123 @@
+// common.cuh — shared declarations of the sm_100a paged-KV decode library.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/nova_b200.h"
+
+namespace novab {
+
+constexpr int kHeadDim = 128;   // the only head_dim built (every model of the reference uses 128)
+constexpr int kKvBlock = 16;    // tokens per page (the reference's default NOVA_KV_BLOCK)
+constexpr int kKvShift = 4;
+constexpr int kPartW = kHeadDim + 2;   // partial row: m, l, acc[128]  (src/kernel/attn.cu:150-158)
+// 1/sqrt(128), the literal the reference uses (src/kernel/attn.cu:21)
+constexpr float kAttnScale = 0.08838834764831845f;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ---- error plumbing -------------------------------------------------------------------
+void set_cuda_error(cudaError_t e, const char* what);
+void count_launch(int n = 1);
+
+#define NOVA_CUDA_TRY(expr)                                   \
+    do {                                                      \
+        cudaError_t _e = (expr);                              \
+        if (_e != cudaSuccess) {                              \
+            ::novab::set_cuda_error(_e, #expr);               \
+            return NOVA_ERR_CUDA;                             \
+        }                                                     \
+    } while (0)
+
+#define NOVA_LAUNCH_CHECK()                                   \
+    do {                                                      \
+        cudaError_t _e = cudaGetLastError();                  \
+        if (_e != cudaSuccess) {                              \
+            ::novab::set_cuda_error(_e, "kernel launch");     \
+            return NOVA_ERR_CUDA;                             \
+        }                                                     \
+        ::novab::count_launch();                              \
+    } while (0)
+
+// ---- KV element access ----------------------------------------------------------------
+template <typename T> struct KvTraits;
+template <> struct KvTraits<float> {
+    static constexpr int kDtype = NOVA_KV_F32;
+    __device__ static __forceinline__ float load(const float* p) { return *p; }
+    __device__ static __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct KvTraits<__half> {
+    static constexpr int kDtype = NOVA_KV_F16;
+    __device__ static __forceinline__ float load(const __half* p) { return __half2float(*p); }
+    __device__ static __forceinline__ void store(__half* p, float v) { *p = __float2half_rn(v); }
+};
+
+// ---- attention launch description (shared by the SIMT and tensor-core kernels) ---------
+//
+// Work is cut stream-K style.  A "row" is one (layer, session, kv-head group): its pages
+// are ceil(n_keys/16).  All pages of all rows of the launch form one line of P pages; CTA c
+// owns [floor(c*P/C), floor((c+1)*P/C)).  A CTA whose range crosses a row boundary produces
+// one partial per row it touches; the (CTA, row) pairs form a chain, so `c + row` names a
+// unique partial slot.  The CTA that is last to arrive at a row (atomic ticket) merges the
+// row's partials in CTA order and writes the normalised output.
+struct AttnLaunch {
+    const void* pool_k;          // [L][NB][16][NKV][128]
+    const void* pool_v;
+    const int32_t* table_base;   // device block tables, one per slice
+    int64_t table_stride;        // entries per slice table (nblocks)
+    const int32_t* slice_ids;    // [S] slice of each batch entry; nullptr: entry s uses table_base + s*stride
+    const int32_t* n_past;       // [S] device; n_keys = n_past[s] + keys_add; nullptr: n_keys = keys_imm
+    int32_t keys_add;
+    int32_t keys_imm;
+    const float* q;              // [layers][S][NH][128] fp32, already rotated
+    float* out;                  // [layers][S][NH][128]
+    float* part;                 // partial slots [(C + rows)][heads_per_row][130]
+    unsigned int* tickets;       // [rows], zero before the first launch; self-resetting
+    int32_t* status;             // device status word (0 ok)
+    int32_t n_sessions;
+    int32_t layer0;              // first layer of the pools this launch reads
+    int32_t n_layers;            // layers covered by this launch (1 = per-layer call)
+    int32_t nb;                  // physical pages per layer
+    int32_t n_heads, n_kv_heads;
+    int32_t kv_group;            // kv heads handled by one CTA (<= 4)
+    int32_t fused_combine;       // 1: last arriver merges; 0: every partial is left in `part`
+    int64_t page_lo, page_hi;    // restrict every session to logical pages [lo, hi) (multi-GPU split); hi<0: all
+    int32_t write_partial_only;  // 1: leave un-normalised (m,l,acc) rows in `out_part` instead of `out`
+    float* out_part;             // [layers][S][NH][130]
+};
+
+constexpr int kMaxRowsSmem = 2048;   // (sessions x kv groups) prefix entries kept in shared memory
+
+// Launchers (defined in attn_simt.cu / attn_mma.cu).  n_ctas == 0 picks a default.
+int launch_attn_simt(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s);
+int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s);
+int attn_default_ctas_simt(int n_kv_heads);
+int attn_default_ctas_mma();
+int launch_part_merge(const AttnLaunch& a, int n_ctas, cudaStream_t s);
+int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s);
+
+// rope / append / page utilities (rope_append.cu)
+int launch_rope_table(float* cs, float* sn, int64_t n_pos, int theta, cudaStream_t s);
+struct AppendLaunch {
+    void* pool_k; void* pool_v;
+    const int32_t* table_base; int64_t table_stride;
+    const int32_t* slice_ids;     // [S] or nullptr (see AttnLaunch)
+    const int32_t* n_past;        // [S] device write positions, or nullptr: pos_imm
+    int64_t pos_imm;
+    float* q; float* k; const float* v;   // [layers][S][n_tok][NH|NKV][128]
+    const float* cs; const float* sn; int64_t rope_rows;
+    int32_t* status;
+    int32_t n_sessions, n_tok, layer0, n_layers, nb, n_heads, n_kv_heads, neox, kv_dtype;
+};
+int launch_rope_append(const AppendLaunch& a, cudaStream_t s);
+struct CowEvent { int32_t src, dst; int32_t* table_entry; };
+int launch_cow_copy(void* pool_k, void* pool_v, int n_layers, int nb, size_t page_bytes,
+                    const CowEvent* ev, int n_events, cudaStream_t s);
+int launch_zero_pages(void* pool_k, void* pool_v, int n_layers, int nb, size_t page_bytes,
+                      const int32_t* table_dev, int n_pages, cudaStream_t s);
+int launch_advance(int32_t* n_past, int n, cudaStream_t s);
+int launch_synth_normal(float* dst, size_t n, uint64_t key, uint64_t first_index, cudaStream_t s);
+
+}  // namespace novab

@@ -1,0 +1,801 @@
+// engine.cu — the engine-side glue of the paged-KV decode path behind the C ABI: page pools,
+// block tables and RoPE tables in device memory (Engine, include/nova/model.h:117-179 and
+// src/model.cpp:93-96,115-119 of the reference), sessions with their own streams
+// (SessionManager, code/session.h:74-150), the copy-on-write guard (src/model.cpp:171-191),
+// the raw launcher entry points (include/nova/kernel.h:44-49,62-64) and the batched
+// per-layer / all-layer decode calls that replace the per-session loop of
+// Engine::decode_batch (src/model.cpp:281-290).
+#include <cstring>
+#include <limits>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "handles.hpp"
+
+using namespace novab;
+
+namespace {
+struct SessionRec {
+    bool used = false;
+    int slice = -1;
+    cudaStream_t stream = nullptr;
+};
+constexpr int kMaxSplitCtas = 148 * 8;   // upper bound of CTAs of any attention launch (partial slots)
+}  // namespace
+
+struct nova_engine {
+    nova_engine_desc d{};
+    nova_pool pool;
+    void* pool_k = nullptr;
+    void* pool_v = nullptr;
+    int32_t* tables = nullptr;       // [n_slices][nblocks]
+    float* cs = nullptr;
+    float* sn = nullptr;
+    int32_t* status = nullptr;       // device status word shared by all launches of this engine
+    size_t page_bytes = 0;
+    size_t elem_bytes = 0;
+    int nb = 0, nblocks = 0;
+    int kv_group = 0;
+    std::vector<SessionRec> sess;
+    std::mutex mu;
+};
+
+struct nova_batch {
+    nova_engine* e = nullptr;
+    int n = 0;
+    std::vector<int> sessions, slices;
+    int32_t* d_slices = nullptr;
+    int32_t* d_n_past = nullptr;
+    int32_t* h_n_past = nullptr;     // pinned staging
+    float* part = nullptr;
+    unsigned int* tickets = nullptr;
+    int kernel = 0;                  // 0 SIMT, 1 tensor-core
+    // staging for the host-buffer step and the graph replay
+    float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
+    cudaGraphExec_t graph = nullptr;   // one per-layer decode step on the staging buffers
+    int graph_kernel = -1;
+    std::vector<cudaEvent_t> ev;       // event pool for per-launch timing
+};
+
+namespace {
+
+int check_desc(const nova_engine_desc& d) {
+    if (d.n_layers <= 0 || d.n_heads <= 0 || d.n_kv_heads <= 0 || d.n_slices <= 0 || d.ctx <= 0) return NOVA_ERR_INVALID;
+    if (d.n_heads % d.n_kv_heads) return NOVA_ERR_INVALID;
+    if (d.head_dim != kHeadDim || d.kv_block != kKvBlock) return NOVA_ERR_UNSUPPORTED;
+    if (d.kv_dtype != NOVA_KV_F32 && d.kv_dtype != NOVA_KV_F16) return NOVA_ERR_UNSUPPORTED;
+    const int g = d.n_heads / d.n_kv_heads;
+    if (!(g == 1 || g == 2 || (g >= 4 && g <= 8))) return NOVA_ERR_UNSUPPORTED;
+    const int kvg = d.n_kv_heads < 4 ? d.n_kv_heads : 4;
+    if (d.n_kv_heads % kvg) return NOVA_ERR_UNSUPPORTED;
+    return NOVA_OK;
+}
+
+int kv_group_of(int n_kv_heads) { return n_kv_heads < 4 ? n_kv_heads : 4; }
+
+SessionRec* session_of(nova_engine* e, int id) {
+    if (!e || id < 0 || id >= (int)e->sess.size() || !e->sess[(size_t)id].used) return nullptr;
+    return &e->sess[(size_t)id];
+}
+const SessionRec* session_of(const nova_engine* e, int id) {
+    if (!e || id < 0 || id >= (int)e->sess.size() || !e->sess[(size_t)id].used) return nullptr;
+    return &e->sess[(size_t)id];
+}
+
+int upload_table(nova_engine* e, int slice, cudaStream_t s) {
+    const SliceState* st = e->pool.p.find(slice);
+    if (!st) return NOVA_ERR_INVALID;
+    NOVA_CUDA_TRY(cudaMemcpyAsync(e->tables + (size_t)slice * e->nblocks, st->table.data(),
+                                  (size_t)e->nblocks * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    return NOVA_OK;
+}
+
+// KvPool::cow_slice for every logical block of [pos0, pos0+n), collecting the device copies.
+int collect_cow(nova_engine* e, int slice, int64_t pos0, int n, std::vector<CowEvent>& ev) {
+    if (n <= 0) return NOVA_OK;
+    PagePool& pp = e->pool.p;
+    const int b0 = pp.block_index(pos0), b1 = pp.block_index(pos0 + n - 1);
+    for (int b = b0; b <= b1; ++b) {
+        const int fresh = pp.cow(slice, (int64_t)b * pp.kv_block());
+        if (fresh == -2) return NOVA_ERR_POOL_FULL;
+        if (fresh < 0) continue;
+        SliceState* st = pp.find(slice);
+        CowEvent c;
+        c.src = st->copy_from;
+        c.dst = fresh;
+        c.table_entry = e->tables + (size_t)slice * e->nblocks + b;
+        st->copy_from = -1;                       // one-shot request consumed (src/model.cpp:175-176)
+        ev.push_back(c);
+    }
+    return NOVA_OK;
+}
+
+void fill_attn(const nova_batch* b, AttnLaunch& a) {
+    const nova_engine* e = b->e;
+    std::memset(&a, 0, sizeof(a));
+    a.pool_k = e->pool_k;
+    a.pool_v = e->pool_v;
+    a.table_base = e->tables;
+    a.table_stride = e->nblocks;
+    a.slice_ids = b->d_slices;
+    a.n_past = b->d_n_past;
+    a.keys_add = 1;
+    a.part = b->part;
+    a.tickets = b->tickets;
+    a.status = e->status;
+    a.n_sessions = b->n;
+    a.nb = e->nb;
+    a.n_heads = e->d.n_heads;
+    a.n_kv_heads = e->d.n_kv_heads;
+    a.kv_group = e->kv_group;
+    a.fused_combine = 1;
+    a.page_lo = 0;
+    a.page_hi = -1;
+}
+
+int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
+    if (b->kernel == 1) return launch_attn_mma(a, b->e->d.kv_dtype, 0, s);
+    return launch_attn_simt(a, b->e->d.kv_dtype, 0, s);
+}
+
+void fill_append(const nova_batch* b, AppendLaunch& a) {
+    const nova_engine* e = b->e;
+    std::memset(&a, 0, sizeof(a));
+    a.pool_k = e->pool_k;
+    a.pool_v = e->pool_v;
+    a.table_base = e->tables;
+    a.table_stride = e->nblocks;
+    a.slice_ids = b->d_slices;
+    a.n_past = b->d_n_past;
+    a.cs = e->cs;
+    a.sn = e->sn;
+    a.rope_rows = e->d.rope_positions;
+    a.status = e->status;
+    a.n_sessions = b->n;
+    a.n_tok = 1;
+    a.nb = e->nb;
+    a.n_heads = e->d.n_heads;
+    a.n_kv_heads = e->d.n_kv_heads;
+    a.neox = e->d.rope_neox;
+    a.kv_dtype = e->d.kv_dtype;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nova_engine_create(const nova_engine_desc* desc, nova_engine** out) {
+    if (!desc || !out) return NOVA_ERR_INVALID;
+    *out = nullptr;
+    nova_engine_desc d = *desc;
+    if (d.max_sessions <= 0 || d.max_sessions > d.n_slices) d.max_sessions = d.n_slices;
+    if (d.rope_positions <= 0) d.rope_positions = d.ctx;
+    const int rc = check_desc(d);
+    if (rc != NOVA_OK) return rc;
+    NOVA_CUDA_TRY(cudaSetDevice(d.device));
+
+    nova_engine* e = new (std::nothrow) nova_engine();
+    if (!e) return NOVA_ERR_INVALID;
+    e->d = d;
+    e->pool.p.set_block(d.kv_block);
+    const int64_t nblocks = (d.ctx + d.kv_block - 1) / d.kv_block;
+    if (nblocks * d.n_slices > 0x7fffffffLL) { delete e; return NOVA_ERR_TOO_LARGE; }
+    e->pool.p.init(d.n_slices, d.ctx);
+    e->nblocks = e->pool.p.nblocks();
+    e->nb = e->pool.p.nb_total();
+    e->elem_bytes = d.kv_dtype == NOVA_KV_F16 ? 2 : 4;
+    e->page_bytes = (size_t)d.kv_block * d.n_kv_heads * d.head_dim * e->elem_bytes;
+    e->kv_group = kv_group_of(d.n_kv_heads);
+    e->sess.resize((size_t)d.max_sessions);
+
+    const size_t pool_bytes = (size_t)d.n_layers * (size_t)e->nb * e->page_bytes;
+    const size_t rope_bytes = (size_t)d.rope_positions * (kHeadDim / 2) * sizeof(float);
+    cudaError_t ce = cudaSuccess;
+    if (ce == cudaSuccess) ce = cudaMalloc(&e->pool_k, pool_bytes);
+    if (ce == cudaSuccess) ce = cudaMalloc(&e->pool_v, pool_bytes);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&e->tables, (size_t)d.n_slices * e->nblocks * sizeof(int32_t));
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&e->cs, rope_bytes);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&e->sn, rope_bytes);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&e->status, sizeof(int32_t));
+    if (ce == cudaSuccess) ce = cudaMemset(e->status, 0, sizeof(int32_t));
+    if (ce == cudaSuccess) ce = cudaMemset(e->tables, 0xff, (size_t)d.n_slices * e->nblocks * sizeof(int32_t));
+    if (ce != cudaSuccess) {
+        set_cuda_error(ce, "engine allocation");
+        nova_engine_destroy(e);
+        return NOVA_ERR_CUDA;
+    }
+    int r = launch_rope_table(e->cs, e->sn, d.rope_positions, d.rope_theta, 0);   // Kernel::rope_table, model.cpp:119
+    if (r == NOVA_OK && cudaDeviceSynchronize() != cudaSuccess) r = NOVA_ERR_CUDA;
+    if (r != NOVA_OK) {
+        nova_engine_destroy(e);
+        return r;
+    }
+    *out = e;
+    return NOVA_OK;
+}
+
+void nova_engine_destroy(nova_engine* e) {
+    if (!e) return;
+    cudaSetDevice(e->d.device);
+    for (auto& s : e->sess)
+        if (s.used && s.stream) cudaStreamDestroy(s.stream);
+    cudaFree(e->pool_k);
+    cudaFree(e->pool_v);
+    cudaFree(e->tables);
+    cudaFree(e->cs);
+    cudaFree(e->sn);
+    cudaFree(e->status);
+    delete e;
+}
+
+int nova_engine_desc_get(const nova_engine* e, nova_engine_desc* out) {
+    if (!e || !out) return NOVA_ERR_INVALID;
+    *out = e->d;
+    return NOVA_OK;
+}
+
+void* nova_kv_k_base(const nova_engine* e) { return e ? e->pool_k : nullptr; }
+void* nova_kv_v_base(const nova_engine* e) { return e ? e->pool_v : nullptr; }
+int32_t* nova_kv_table_slot(const nova_engine* e, int slice) {
+    if (!e || slice < 0 || slice >= e->d.n_slices) return nullptr;
+    return e->tables + (size_t)slice * e->nblocks;
+}
+int nova_kv_nb(const nova_engine* e) { return e ? e->nb : 0; }
+int nova_kv_nblocks(const nova_engine* e) { return e ? e->nblocks : 0; }
+int nova_kv_width(const nova_engine* e) { return e ? e->d.n_kv_heads * e->d.head_dim : 0; }
+size_t nova_kv_page_bytes(const nova_engine* e) { return e ? e->page_bytes : 0; }
+const float* nova_rope_cos(const nova_engine* e) { return e ? e->cs : nullptr; }
+const float* nova_rope_sin(const nova_engine* e) { return e ? e->sn : nullptr; }
+nova_pool* nova_engine_pool(nova_engine* e) { return e ? &e->pool : nullptr; }
+
+int nova_session_create(nova_engine* e) {
+    if (!e) return NOVA_ERR_INVALID;
+    std::lock_guard<std::mutex> lk(e->mu);
+    int slot = -1;
+    for (size_t i = 0; i < e->sess.size(); ++i)
+        if (!e->sess[i].used) { slot = (int)i; break; }
+    if (slot < 0) return NOVA_ERR_NO_SESSION;
+    NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    const int slice = e->pool.p.acquire();
+    if (slice < 0) return NOVA_ERR_NO_SLICE;
+    cudaStream_t st = nullptr;
+    cudaError_t ce = cudaStreamCreate(&st);
+    if (ce != cudaSuccess) {
+        set_cuda_error(ce, "cudaStreamCreate");
+        e->pool.p.release(slice);
+        return NOVA_ERR_CUDA;
+    }
+    SessionRec& r = e->sess[(size_t)slot];
+    r.used = true;
+    r.slice = slice;
+    r.stream = st;
+    int rc = upload_table(e, slice, st);
+    if (rc == NOVA_OK && e->d.zero_pages)
+        rc = launch_zero_pages(e->pool_k, e->pool_v, e->d.n_layers, e->nb, e->page_bytes,
+                               e->tables + (size_t)slice * e->nblocks, e->nblocks, st);
+    if (rc == NOVA_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = NOVA_ERR_CUDA;
+    if (rc != NOVA_OK) return rc;
+    return slot;
+}
+
+int nova_session_destroy(nova_engine* e, int session) {
+    if (!e) return NOVA_ERR_INVALID;
+    std::lock_guard<std::mutex> lk(e->mu);
+    SessionRec* r = session_of(e, session);
+    if (!r) return NOVA_ERR_INVALID;
+    cudaStreamDestroy(r->stream);
+    e->pool.p.release(r->slice);
+    *r = SessionRec{};
+    return NOVA_OK;
+}
+
+int nova_session_live_count(nova_engine* e) {
+    if (!e) return 0;
+    std::lock_guard<std::mutex> lk(e->mu);
+    int n = 0;
+    for (const auto& s : e->sess) n += s.used ? 1 : 0;
+    return n;
+}
+int nova_session_slice(const nova_engine* e, int session) {
+    const SessionRec* r = session_of(e, session);
+    return r ? r->slice : NOVA_ERR_INVALID;
+}
+nova_stream_t nova_session_stream(const nova_engine* e, int session) {
+    const SessionRec* r = session_of(e, session);
+    return r ? (nova_stream_t)r->stream : nullptr;
+}
+int64_t nova_session_n_past(const nova_engine* e, int session) {
+    const SessionRec* r = session_of(e, session);
+    if (!r) return -1;
+    const SliceState* st = e->pool.p.find(r->slice);
+    return st ? st->n_past : -1;
+}
+int nova_session_set_n_past(nova_engine* e, int session, int64_t n_past) {
+    SessionRec* r = session_of(e, session);
+    if (!r || n_past < 0) return NOVA_ERR_INVALID;
+    SliceState* st = e->pool.p.find(r->slice);
+    if (!st) return NOVA_ERR_INVALID;
+    st->n_past = n_past;
+    return NOVA_OK;
+}
+
+int nova_session_attach(nova_engine* e, int dst, int src, int k) {
+    SessionRec *d = session_of(e, dst), *s = session_of(e, src);
+    if (!d || !s) return NOVA_ERR_INVALID;
+    if (!e->pool.p.attach(d->slice, s->slice, k)) return NOVA_ERR_INVALID;
+    NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    const int rc = upload_table(e, d->slice, d->stream);
+    if (rc != NOVA_OK) return rc;
+    NOVA_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    return NOVA_OK;
+}
+
+int nova_session_attach_prefix(nova_engine* e, int dst, int src, int64_t n_tokens) {
+    SessionRec *d = session_of(e, dst), *s = session_of(e, src);
+    if (!d || !s) return NOVA_ERR_INVALID;
+    if (!e->pool.p.attach_prefix(d->slice, s->slice, n_tokens)) return NOVA_ERR_INVALID;
+    NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    const int rc = upload_table(e, d->slice, d->stream);
+    if (rc != NOVA_OK) return rc;
+    NOVA_CUDA_TRY(cudaStreamSynchronize(d->stream));
+    return NOVA_OK;
+}
+
+int nova_session_cow_on(nova_engine* e, int session, int64_t pos0, int n, nova_stream_t stream) {
+    SessionRec* r = session_of(e, session);
+    if (!r || pos0 < 0) return NOVA_ERR_INVALID;
+    std::vector<CowEvent> ev;
+    const int rc = collect_cow(e, r->slice, pos0, n, ev);
+    if (!ev.empty()) {
+        NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+        const int lrc = launch_cow_copy(e->pool_k, e->pool_v, e->d.n_layers, e->nb, e->page_bytes, ev.data(),
+                                        (int)ev.size(), (cudaStream_t)stream);
+        if (lrc != NOVA_OK) return lrc;
+    }
+    return rc != NOVA_OK ? rc : (int)ev.size();
+}
+
+int nova_session_cow(nova_engine* e, int session, int64_t pos0, int n) {
+    const SessionRec* r = session_of(e, session);
+    if (!r) return NOVA_ERR_INVALID;
+    return nova_session_cow_on(e, session, pos0, n, (nova_stream_t)r->stream);
+}
+
+int nova_session_permute_pages(nova_engine* e, int session, const int32_t* perm, int n) {
+    SessionRec* r = session_of(e, session);
+    if (!r || !perm || n != e->nblocks) return NOVA_ERR_INVALID;
+    std::vector<char> seen((size_t)n, 0);
+    for (int i = 0; i < n; ++i) {
+        if (perm[i] < 0 || perm[i] >= n || seen[(size_t)perm[i]]) return NOVA_ERR_INVALID;
+        seen[(size_t)perm[i]] = 1;
+    }
+    SliceState* st = e->pool.p.find(r->slice);
+    const int first = r->slice * e->nblocks;
+    for (int i = 0; i < n; ++i) {
+        // only a table that still maps onto the slice's own pages may be permuted
+        const int cur = st->table[(size_t)i];
+        if (cur < first || cur >= first + n) return NOVA_ERR_INVALID;
+    }
+    for (int i = 0; i < n; ++i) st->table[(size_t)i] = first + perm[i];
+    return nova_session_sync_table(e, session);
+}
+
+int nova_session_sync_table(nova_engine* e, int session) {
+    SessionRec* r = session_of(e, session);
+    if (!r) return NOVA_ERR_INVALID;
+    NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    const int rc = upload_table(e, r->slice, r->stream);
+    if (rc != NOVA_OK) return rc;
+    NOVA_CUDA_TRY(cudaStreamSynchronize(r->stream));
+    return NOVA_OK;
+}
+
+/* ------------------------------------------------------------- raw launchers */
+
+int nova_launch_rope_table(float* cs, float* sn, int64_t n_pos, int32_t head_dim, int32_t theta, nova_stream_t s) {
+    if (head_dim != kHeadDim) return NOVA_ERR_UNSUPPORTED;
+    return launch_rope_table(cs, sn, n_pos, theta, (cudaStream_t)s);
+}
+
+int nova_launch_rope_append_paged(const nova_kv_shape* sh, void* pool_k, void* pool_v, const int32_t* table,
+                                  int layer, int nb, int n, int64_t pos0, float* q, float* k, const float* v,
+                                  const float* cs, const float* sn, nova_stream_t s) {
+    if (!sh || !pool_k || !pool_v || !table || !k || !v || !cs || !sn || layer < 0 || nb <= 0 || pos0 < 0)
+        return NOVA_ERR_INVALID;
+    if (sh->head_dim != kHeadDim || sh->kv_block != kKvBlock) return NOVA_ERR_UNSUPPORTED;
+    AppendLaunch a;
+    std::memset(&a, 0, sizeof(a));
+    a.pool_k = pool_k; a.pool_v = pool_v;
+    a.table_base = table;
+    a.table_stride = std::numeric_limits<int32_t>::max();   // the caller vouches for the table length, as in the reference
+    a.pos_imm = pos0;
+    a.q = q; a.k = k; a.v = v; a.cs = cs; a.sn = sn;
+    a.rope_rows = std::numeric_limits<int64_t>::max();
+    a.n_sessions = 1; a.n_tok = n; a.layer0 = layer; a.n_layers = 1; a.nb = nb;
+    a.n_heads = sh->n_heads; a.n_kv_heads = sh->n_kv_heads; a.neox = sh->rope_neox; a.kv_dtype = sh->kv_dtype;
+    return launch_rope_append(a, (cudaStream_t)s);
+}
+
+size_t nova_attn_scratch_floats(const nova_kv_shape* sh) {
+    return sh ? (size_t)sh->n_heads * 32 * (size_t)(sh->head_dim + 2) : 0;
+}
+
+int nova_launch_attn_decode_paged(const nova_kv_shape* sh, const float* q, const void* pool_k, const void* pool_v,
+                                  const int32_t* table, int layer, int nb, int n_keys, float* o, float* scratch,
+                                  nova_stream_t s) {
+    if (!sh || !q || !pool_k || !pool_v || !table || !o || !scratch || layer < 0 || nb <= 0) return NOVA_ERR_INVALID;
+    if (sh->head_dim != kHeadDim || sh->kv_block != kKvBlock) return NOVA_ERR_UNSUPPORTED;
+    if (sh->n_kv_heads <= 0 || sh->n_heads % sh->n_kv_heads) return NOVA_ERR_INVALID;
+    AttnLaunch a;
+    std::memset(&a, 0, sizeof(a));
+    a.pool_k = pool_k; a.pool_v = pool_v;
+    a.table_base = table;
+    a.table_stride = std::numeric_limits<int32_t>::max();
+    a.keys_imm = n_keys;
+    a.q = q; a.out = o; a.part = scratch;
+    a.n_sessions = 1; a.layer0 = layer; a.n_layers = 1; a.nb = nb;
+    a.n_heads = sh->n_heads; a.n_kv_heads = sh->n_kv_heads;
+    a.kv_group = kv_group_of(sh->n_kv_heads);
+    a.fused_combine = 0;      // the caller's scratch is not zeroed: separate merge, no tickets
+    a.page_lo = 0; a.page_hi = -1;
+    // The scratch holds NH*32 partial rows = 32*NH/(kv_group*G) slots; slot index = cta + row.
+    const int heads_per_row = a.kv_group * (sh->n_heads / sh->n_kv_heads);
+    const int rows = sh->n_kv_heads / a.kv_group;
+    int ctas = (sh->n_heads * 32) / heads_per_row - rows;
+    const int want = attn_default_ctas_simt(sh->n_kv_heads);
+    if (ctas > want) ctas = want;
+    if (ctas < 1) return NOVA_ERR_UNSUPPORTED;
+    int rc = launch_attn_simt(a, sh->kv_dtype, ctas, (cudaStream_t)s);
+    if (rc != NOVA_OK) return rc;
+    return launch_part_merge(a, ctas, (cudaStream_t)s);
+}
+
+int nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim, float* out, nova_stream_t s) {
+    if (!parts || !out || head_dim != kHeadDim) return NOVA_ERR_INVALID;
+    return launch_lse_combine(parts, n_parts, n_rows, out, (cudaStream_t)s);
+}
+
+uint64_t nova_synth_key(uint64_t seed, uint64_t tensor, uint64_t session, uint64_t layer) {
+    auto mix = [](uint64_t x) {
+        x += 0x9E3779B97F4A7C15ull;
+        x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+        x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+        return x ^ (x >> 31);
+    };
+    uint64_t k = mix(seed);
+    k = mix(k ^ (tensor * 0xD6E8FEB86659FD93ull));
+    k = mix(k ^ (session * 0xA0761D6478BD642Full));
+    k = mix(k ^ (layer * 0xE7037ED1A0B428DBull));
+    return k;
+}
+
+int nova_synth_normal(float* dst_dev, size_t n, uint64_t key, uint64_t first_index, nova_stream_t s) {
+    if (!dst_dev && n) return NOVA_ERR_INVALID;
+    return launch_synth_normal(dst_dev, n, key, first_index, (cudaStream_t)s);
+}
+
+/* ------------------------------------------------------------------- batches */
+
+int nova_batch_create(nova_engine* e, const int32_t* sessions, int n, nova_batch** out) {
+    if (!e || !sessions || n <= 0 || !out) return NOVA_ERR_INVALID;
+    *out = nullptr;
+    if ((int64_t)n * (e->d.n_kv_heads / e->kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
+    nova_batch* b = new (std::nothrow) nova_batch();
+    if (!b) return NOVA_ERR_INVALID;
+    b->e = e;
+    b->n = n;
+    for (int i = 0; i < n; ++i) {
+        const SessionRec* r = session_of(e, sessions[i]);
+        if (!r) { delete b; return NOVA_ERR_INVALID; }
+        b->sessions.push_back(sessions[i]);
+        b->slices.push_back(r->slice);
+    }
+    NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    const int64_t rows = (int64_t)e->d.n_layers * n * (e->d.n_kv_heads / e->kv_group);
+    const int heads_per_row = e->kv_group * (e->d.n_heads / e->d.n_kv_heads);
+    const size_t part_floats = (size_t)(rows + kMaxSplitCtas) * heads_per_row * kPartW;
+    cudaError_t ce = cudaSuccess;
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->d_slices, (size_t)n * sizeof(int32_t));
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->d_n_past, (size_t)n * sizeof(int32_t));
+    if (ce == cudaSuccess) ce = cudaMallocHost((void**)&b->h_n_past, (size_t)n * sizeof(int32_t));
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->part, part_floats * sizeof(float));
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->tickets, (size_t)rows * sizeof(unsigned int));
+    if (ce == cudaSuccess) ce = cudaMemset(b->tickets, 0, (size_t)rows * sizeof(unsigned int));
+    if (ce == cudaSuccess)
+        ce = cudaMemcpy(b->d_slices, b->slices.data(), (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) {
+        set_cuda_error(ce, "batch allocation");
+        nova_batch_destroy(b);
+        return NOVA_ERR_CUDA;
+    }
+    const int rc = nova_batch_sync_positions(b, nullptr);
+    if (rc != NOVA_OK || cudaDeviceSynchronize() != cudaSuccess) {
+        nova_batch_destroy(b);
+        return rc != NOVA_OK ? rc : NOVA_ERR_CUDA;
+    }
+    *out = b;
+    return NOVA_OK;
+}
+
+void nova_batch_destroy(nova_batch* b) {
+    if (!b) return;
+    cudaSetDevice(b->e->d.device);
+    cudaFree(b->d_slices);
+    cudaFree(b->d_n_past);
+    cudaFreeHost(b->h_n_past);
+    cudaFree(b->part);
+    cudaFree(b->tickets);
+    cudaFree(b->dq);
+    cudaFree(b->dk);
+    cudaFree(b->dv);
+    cudaFree(b->dout);
+    if (b->graph) cudaGraphExecDestroy(b->graph);
+    for (cudaEvent_t e : b->ev) cudaEventDestroy(e);
+    delete b;
+}
+
+int nova_batch_size(const nova_batch* b) { return b ? b->n : 0; }
+
+int nova_batch_sync_positions(nova_batch* b, nova_stream_t s) {
+    if (!b) return NOVA_ERR_INVALID;
+    for (int i = 0; i < b->n; ++i) {
+        const SliceState* st = b->e->pool.p.find(b->slices[(size_t)i]);
+        if (!st || st->n_past > 0x7ffffff0LL) return NOVA_ERR_INVALID;
+        b->h_n_past[i] = (int32_t)st->n_past;
+    }
+    NOVA_CUDA_TRY(cudaMemcpyAsync(b->d_n_past, b->h_n_past, (size_t)b->n * sizeof(int32_t), cudaMemcpyHostToDevice,
+                                  (cudaStream_t)s));
+    return NOVA_OK;
+}
+
+int nova_batch_set_kernel(nova_batch* b, int which) {
+    if (!b || which < 0 || which > 1) return NOVA_ERR_INVALID;
+    if (which == 1 && b->e->d.kv_dtype != NOVA_KV_F16) return NOVA_ERR_UNSUPPORTED;
+    b->kernel = which;
+    return NOVA_OK;
+}
+int nova_batch_get_kernel(const nova_batch* b) { return b ? b->kernel : NOVA_ERR_INVALID; }
+
+int nova_batch_cow(nova_batch* b, nova_stream_t s) {
+    if (!b) return NOVA_ERR_INVALID;
+    nova_engine* e = b->e;
+    std::vector<CowEvent> ev;
+    int rc = NOVA_OK;
+    for (int i = 0; i < b->n && rc == NOVA_OK; ++i) {
+        const SliceState* st = e->pool.p.find(b->slices[(size_t)i]);
+        rc = collect_cow(e, b->slices[(size_t)i], st->n_past, 1, ev);
+    }
+    if (!ev.empty()) {
+        const int lrc = launch_cow_copy(e->pool_k, e->pool_v, e->d.n_layers, e->nb, e->page_bytes, ev.data(),
+                                        (int)ev.size(), (cudaStream_t)s);
+        if (lrc != NOVA_OK) return lrc;
+    }
+    return rc != NOVA_OK ? rc : (int)ev.size();
+}
+
+int nova_batch_append(nova_batch* b, int layer, float* q, float* k, const float* v, nova_stream_t s) {
+    if (!b || !q || !k || !v || layer < 0 || layer >= b->e->d.n_layers) return NOVA_ERR_INVALID;
+    AppendLaunch a;
+    fill_append(b, a);
+    a.q = q; a.k = k; a.v = v;
+    a.layer0 = layer; a.n_layers = 1;
+    return launch_rope_append(a, (cudaStream_t)s);
+}
+
+int nova_batch_attn(nova_batch* b, int layer, const float* q, float* out, nova_stream_t s) {
+    if (!b || !q || !out || layer < 0 || layer >= b->e->d.n_layers) return NOVA_ERR_INVALID;
+    AttnLaunch a;
+    fill_attn(b, a);
+    a.q = q; a.out = out;
+    a.layer0 = layer; a.n_layers = 1;
+    return run_attn(b, a, (cudaStream_t)s);
+}
+
+int nova_batch_advance(nova_batch* b, nova_stream_t s) {
+    if (!b) return NOVA_ERR_INVALID;
+    for (int i = 0; i < b->n; ++i) {
+        SliceState* st = b->e->pool.p.find(b->slices[(size_t)i]);
+        if (st) st->n_past += 1;
+    }
+    return launch_advance(b->d_n_past, b->n, (cudaStream_t)s);
+}
+
+int nova_batch_step_all_layers(nova_batch* b, float* q, float* k, const float* v, float* out, nova_stream_t s) {
+    if (!b || !q || !k || !v || !out) return NOVA_ERR_INVALID;
+    AppendLaunch ap;
+    fill_append(b, ap);
+    ap.q = q; ap.k = k; ap.v = v;
+    ap.layer0 = 0; ap.n_layers = b->e->d.n_layers;
+    int rc = launch_rope_append(ap, (cudaStream_t)s);
+    if (rc != NOVA_OK) return rc;
+    AttnLaunch at;
+    fill_attn(b, at);
+    at.q = q; at.out = out;
+    at.layer0 = 0; at.n_layers = b->e->d.n_layers;
+    return run_attn(b, at, (cudaStream_t)s);
+}
+
+static int ensure_staging(nova_batch* b);
+
+int nova_batch_decode_step_host(nova_batch* b, const float* q, const float* k, const float* v, float* out,
+                                int per_layer_launch, nova_stream_t s) {
+    if (!b || !q || !k || !v || !out) return NOVA_ERR_INVALID;
+    nova_engine* e = b->e;
+    cudaStream_t st = (cudaStream_t)s;
+    const size_t L = (size_t)e->d.n_layers, S = (size_t)b->n;
+    const size_t q_elems = L * S * e->d.n_heads * kHeadDim, kv_elems = L * S * e->d.n_kv_heads * kHeadDim;
+    int rc = ensure_staging(b);
+    if (rc != NOVA_OK) return rc;
+    rc = nova_batch_cow(b, s);
+    if (rc < 0) return rc;
+    NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq, q, q_elems * 4, cudaMemcpyHostToDevice, st));
+    NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk, k, kv_elems * 4, cudaMemcpyHostToDevice, st));
+    NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv, v, kv_elems * 4, cudaMemcpyHostToDevice, st));
+    if (per_layer_launch) {
+        const size_t qs = S * e->d.n_heads * kHeadDim, ks = S * e->d.n_kv_heads * kHeadDim;
+        for (int l = 0; l < e->d.n_layers; ++l) {
+            rc = nova_batch_append(b, l, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, s);
+            if (rc != NOVA_OK) return rc;
+            rc = nova_batch_attn(b, l, b->dq + l * qs, b->dout + l * qs, s);
+            if (rc != NOVA_OK) return rc;
+        }
+    } else {
+        rc = nova_batch_step_all_layers(b, b->dq, b->dk, b->dv, b->dout, s);
+        if (rc != NOVA_OK) return rc;
+    }
+    NOVA_CUDA_TRY(cudaMemcpyAsync(out, b->dout, q_elems * 4, cudaMemcpyDeviceToHost, st));
+    rc = nova_batch_advance(b, s);
+    if (rc != NOVA_OK) return rc;
+    NOVA_CUDA_TRY(cudaStreamSynchronize(st));
+    return NOVA_OK;
+}
+
+static int ensure_staging(nova_batch* b) {
+    if (b->dq) return NOVA_OK;
+    const nova_engine* e = b->e;
+    const size_t L = (size_t)e->d.n_layers, S = (size_t)b->n;
+    const size_t q_elems = L * S * e->d.n_heads * kHeadDim, kv_elems = L * S * e->d.n_kv_heads * kHeadDim;
+    cudaError_t ce = cudaMalloc((void**)&b->dq, q_elems * 4);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dk, kv_elems * 4);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dv, kv_elems * 4);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dout, q_elems * 4);
+    if (ce != cudaSuccess) { set_cuda_error(ce, "step staging"); return NOVA_ERR_CUDA; }
+    return NOVA_OK;
+}
+
+// One decode step as per-layer launches on the staging buffers (everything but the COW guard).
+static int issue_layers(nova_batch* b, float* q, float* k, const float* v, float* out, cudaStream_t st,
+                        std::vector<cudaEvent_t>* ev, size_t* ev_used) {
+    const nova_engine* e = b->e;
+    const size_t S = (size_t)b->n;
+    const size_t qs = S * e->d.n_heads * kHeadDim, ks = S * e->d.n_kv_heads * kHeadDim;
+    for (int l = 0; l < e->d.n_layers; ++l) {
+        int rc = nova_batch_append(b, l, q + l * qs, k + l * ks, v + l * ks, (nova_stream_t)st);
+        if (rc != NOVA_OK) return rc;
+        if (ev) NOVA_CUDA_TRY(cudaEventRecord((*ev)[(*ev_used)++], st));
+        rc = nova_batch_attn(b, l, q + l * qs, out + l * qs, (nova_stream_t)st);
+        if (rc != NOVA_OK) return rc;
+        if (ev) NOVA_CUDA_TRY(cudaEventRecord((*ev)[(*ev_used)++], st));
+    }
+    return NOVA_OK;
+}
+
+int nova_batch_run_steps(nova_batch* b, int n_steps, float* q, float* k, const float* v, float* out,
+                         size_t q_stride, size_t kv_stride, int mode, float* attn_ms, nova_stream_t s) {
+    if (!b || n_steps < 0 || !q || !k || !v || !out || mode < 0 || mode > 2) return NOVA_ERR_INVALID;
+    if (attn_ms && mode == 2) return NOVA_ERR_INVALID;
+    nova_engine* e = b->e;
+    cudaStream_t st = (cudaStream_t)s;
+    NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    const size_t L = (size_t)e->d.n_layers, S = (size_t)b->n;
+    const size_t q_elems = L * S * e->d.n_heads * kHeadDim, kv_elems = L * S * e->d.n_kv_heads * kHeadDim;
+    size_t ev_used = 0;
+    if (attn_ms) {
+        const size_t need = (size_t)n_steps * (mode == 0 ? 2 : 2 * L);
+        while (b->ev.size() < need) {
+            cudaEvent_t ce = nullptr;
+            NOVA_CUDA_TRY(cudaEventCreate(&ce));
+            b->ev.push_back(ce);
+        }
+    }
+    if (mode == 2) {
+        int rc = ensure_staging(b);
+        if (rc != NOVA_OK) return rc;
+        if (!st) return NOVA_ERR_INVALID;   // stream capture needs a real stream
+        if (!b->graph || b->graph_kernel != b->kernel) {
+            if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+            cudaGraph_t g = nullptr;
+            NOVA_CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            rc = issue_layers(b, b->dq, b->dk, b->dv, b->dout, st, nullptr, nullptr);
+            if (rc == NOVA_OK) rc = launch_advance(b->d_n_past, b->n, st);
+            const cudaError_t ce = cudaStreamEndCapture(st, &g);
+            if (rc != NOVA_OK) { if (g) cudaGraphDestroy(g); return rc; }
+            if (ce != cudaSuccess) { set_cuda_error(ce, "cudaStreamEndCapture"); return NOVA_ERR_CUDA; }
+            const cudaError_t ie = cudaGraphInstantiate(&b->graph, g, 0);
+            cudaGraphDestroy(g);
+            if (ie != cudaSuccess) { set_cuda_error(ie, "cudaGraphInstantiate"); return NOVA_ERR_CUDA; }
+            b->graph_kernel = b->kernel;
+        }
+    }
+    for (int i = 0; i < n_steps; ++i) {
+        float* qi = q + (size_t)i * q_stride;
+        float* ki = k + (size_t)i * kv_stride;
+        const float* vi = v + (size_t)i * kv_stride;
+        float* oi = out + (size_t)i * q_stride;
+        int rc = nova_batch_cow(b, s);
+        if (rc < 0) return rc;
+        if (mode == 0) {
+            AppendLaunch ap;
+            fill_append(b, ap);
+            ap.q = qi; ap.k = ki; ap.v = vi;
+            ap.layer0 = 0; ap.n_layers = e->d.n_layers;
+            rc = launch_rope_append(ap, st);
+            if (rc != NOVA_OK) return rc;
+            if (attn_ms) NOVA_CUDA_TRY(cudaEventRecord(b->ev[ev_used++], st));
+            AttnLaunch at;
+            fill_attn(b, at);
+            at.q = qi; at.out = oi;
+            at.layer0 = 0; at.n_layers = e->d.n_layers;
+            rc = run_attn(b, at, st);
+            if (rc != NOVA_OK) return rc;
+            if (attn_ms) NOVA_CUDA_TRY(cudaEventRecord(b->ev[ev_used++], st));
+            rc = nova_batch_advance(b, s);
+            if (rc != NOVA_OK) return rc;
+        } else if (mode == 1) {
+            rc = issue_layers(b, qi, ki, vi, oi, st, attn_ms ? &b->ev : nullptr, &ev_used);
+            if (rc != NOVA_OK) return rc;
+            rc = nova_batch_advance(b, s);
+            if (rc != NOVA_OK) return rc;
+        } else {
+            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq, qi, q_elems * 4, cudaMemcpyDeviceToDevice, st));
+            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk, ki, kv_elems * 4, cudaMemcpyDeviceToDevice, st));
+            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv, vi, kv_elems * 4, cudaMemcpyDeviceToDevice, st));
+            NOVA_CUDA_TRY(cudaGraphLaunch(b->graph, st));
+            count_launch(2 * e->d.n_layers + 1);
+            NOVA_CUDA_TRY(cudaMemcpyAsync(qi, b->dq, q_elems * 4, cudaMemcpyDeviceToDevice, st));   // q rotated in place
+            NOVA_CUDA_TRY(cudaMemcpyAsync(oi, b->dout, q_elems * 4, cudaMemcpyDeviceToDevice, st));
+            for (int j = 0; j < b->n; ++j) {
+                SliceState* sl = e->pool.p.find(b->slices[(size_t)j]);
+                if (sl) sl->n_past += 1;
+            }
+        }
+    }
+    if (attn_ms) {
+        NOVA_CUDA_TRY(cudaStreamSynchronize(st));
+        float total = 0.f;
+        for (size_t j = 0; j + 1 < ev_used; j += 2) {
+            float ms = 0.f;
+            NOVA_CUDA_TRY(cudaEventElapsedTime(&ms, b->ev[j], b->ev[j + 1]));
+            total += ms;
+        }
+        *attn_ms = total;
+    }
+    return NOVA_OK;
+}
+
+int nova_batch_device_status(nova_batch* b) {
+    if (!b) return NOVA_ERR_INVALID;
+    int32_t v = 0;
+    NOVA_CUDA_TRY(cudaMemcpy(&v, b->e->status, sizeof(v), cudaMemcpyDeviceToHost));
+    if (v != 0) cudaMemset(b->e->status, 0, sizeof(v));
+    return v;
+}
+
+int nova_batch_attn_partial(nova_batch* b, int layer, const float* q, int64_t page0, int64_t page1, float* part,
+                            nova_stream_t s) {
+    if (!b || !q || !part || layer < 0 || layer >= b->e->d.n_layers || page0 < 0 || page1 < page0)
+        return NOVA_ERR_INVALID;
+    AttnLaunch a;
+    fill_attn(b, a);
+    a.q = q;
+    a.out_part = part;
+    a.write_partial_only = 1;
+    a.page_lo = page0;
+    a.page_hi = page1;
+    a.layer0 = layer; a.n_layers = 1;
+    return run_attn(b, a, (cudaStream_t)s);
+}
+
+}  // extern "C"

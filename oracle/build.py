@@ -1,0 +1,105 @@
+"""Build recipe of the checker (TEST INFRASTRUCTURE; nothing here is product code).
+
+  oracle/_build/libpaged_decode_oracle.so   the CPU restatement (paged_decode_oracle.c)
+  oracle/_ref/libnova_ref_host.so           the reference's own host headers behind a C shim
+  oracle/_ref/libnova_ref_gpu_<model>.so    the reference's own CUDA kernels for this path,
+                                            compiled unmodified for sm_100a
+
+The two `_ref` libraries are compiled from the reference tree where it lies (directory named
+by $NOVA_REFERENCE_DIR, default: `reference` beside the repository); where that tree is
+absent (a GPU box) the prebuilt files are used as they are.  No reference source is copied.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REPO = os.path.dirname(HERE)
+BUILD = os.path.join(HERE, "_build")
+REF_OUT = os.path.join(HERE, "_ref")
+
+ORACLE_SO = os.path.join(BUILD, "libpaged_decode_oracle.so")
+REF_HOST_SO = os.path.join(REF_OUT, "libnova_ref_host.so")
+REF_GPU_MODELS = {"qwen25_7b": "NOVA_MODEL_QWEN25_7B", "qwen25_1p5b": "NOVA_MODEL_QWEN25_1P5B"}
+
+
+def ref_gpu_so(model: str) -> str:
+    return os.path.join(REF_OUT, f"libnova_ref_gpu_{model}.so")
+
+
+def reference_dir() -> str | None:
+    d = os.environ.get("NOVA_REFERENCE_DIR") or os.path.join(os.path.dirname(REPO), "reference")
+    return d if os.path.isdir(os.path.join(d, "src", "kernel")) else None
+
+
+def _newer(out: str, srcs: list[str]) -> bool:
+    if not os.path.exists(out):
+        return False
+    t = os.path.getmtime(out)
+    return all(os.path.getmtime(s) <= t for s in srcs if os.path.exists(s))
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+        raise RuntimeError(f"build failed: {cmd[0]}")
+
+
+def build_oracle(force: bool = False) -> str:
+    src = os.path.join(HERE, "paged_decode_oracle.c")
+    if not force and _newer(ORACLE_SO, [src]):
+        return ORACLE_SO
+    os.makedirs(BUILD, exist_ok=True)
+    _run(["gcc", "-O2", "-std=c11", "-fopenmp", "-ffp-contract=off", "-fno-fast-math", "-shared", "-fPIC",
+          src, "-o", ORACLE_SO, "-lm"])
+    return ORACLE_SO
+
+
+def build_ref_host(force: bool = False) -> str | None:
+    ref = reference_dir()
+    src = os.path.join(HERE, "ref_host_shim.cpp")
+    if ref is None:
+        return REF_HOST_SO if os.path.exists(REF_HOST_SO) else None
+    if not force and _newer(REF_HOST_SO, [src]):
+        return REF_HOST_SO
+    os.makedirs(REF_OUT, exist_ok=True)
+    _run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", f"-I{ref}/code", f"-I{ref}/include", src, "-o", REF_HOST_SO])
+    return REF_HOST_SO
+
+
+def build_ref_gpu(force: bool = False) -> dict[str, str]:
+    ref = reference_dir()
+    out: dict[str, str] = {}
+    shim = os.path.join(HERE, "ref_gpu_shim.cu")
+    for model, macro in REF_GPU_MODELS.items():
+        so = ref_gpu_so(model)
+        if ref is None or shutil.which("nvcc") is None:
+            if os.path.exists(so):
+                out[model] = so
+            continue
+        if force or not _newer(so, [shim]):
+            os.makedirs(REF_OUT, exist_ok=True)
+            _run(["nvcc", "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+                  f"-D{macro}", f"-I{ref}/include", f"-I{ref}/code", "-Xcompiler", "-fPIC", "-shared", "-w",
+                  shim, f"{ref}/src/kernel/rope.cu", f"{ref}/src/kernel/elem.cu", f"{ref}/src/kernel/attn.cu",
+                  "-o", so])
+        out[model] = so
+    return out
+
+
+def build_all(force: bool = False) -> None:
+    build_oracle(force)
+    build_ref_host(force)
+    build_ref_gpu(force)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv)
+    print("oracle:", ORACLE_SO, os.path.exists(ORACLE_SO))
+    print("ref host:", REF_HOST_SO, os.path.exists(REF_HOST_SO))
+    for m in REF_GPU_MODELS:
+        print("ref gpu:", ref_gpu_so(m), os.path.exists(ref_gpu_so(m)))

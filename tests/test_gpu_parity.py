@@ -1,0 +1,468 @@
+"""GPU parity (tiers T1/T2): every CUDA entry point of the path, called through the C ABI, against
+the CPU oracle on the same seeded inputs, and against the reference's own CUDA kernels recompiled
+for sm_100a where that library is present.  Bars: pages / tables / rotated q,k bit-exact; attention
+within rel-L2 <= 2e-3 and max-abs <= 1e-2 (the tolerance the north-star states)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL, ABS_TOL = 2e-3, 1e-2
+SHAPES = {"qwen25_1p5b": (12, 2), "qwen25_7b": (28, 4), "qwen25_14b": (40, 8)}
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def assert_attn_close(got, want, what=""):
+    r, m = rel_l2(got, want), float(np.abs(got - want).max())
+    assert r <= REL_TOL and m <= ABS_TOL, (what, r, m)
+    return r, m
+
+
+def bits(a):
+    return a.view(np.uint16 if a.dtype == np.float16 else np.uint32)
+
+
+def kernels_for(nv, kv_dtype):
+    return [0, 1] if kv_dtype == nv.KV_F16 else [0]
+
+
+def try_set_kernel(nv, batch, which):
+    rc = nv.lib.nova_batch_set_kernel(batch.h, which)
+    if rc == nv.ERR_UNSUPPORTED:
+        pytest.skip("kernel not built for this dtype")
+    assert rc == 0
+
+
+# --------------------------------------------------------------------------------------------
+def test_synth_matches_oracle(nv, ob):
+    key = nv.synth_key(0x5EED0002, 2, 5, 9)
+    assert key == ob.synth_key(0x5EED0002, 2, 5, 9)
+    n = 100_003
+    d = nv.DevBuf(n * 4)
+    nv.check(nv.lib.nova_synth_normal(d.ptr, n, key, 12345, None))
+    nv.check(nv.lib.dev_sync())
+    assert np.array_equal(bits(d.download(np.float32)), bits(ob.synth_normal(n, key, 12345)))
+
+
+def test_hal_roundtrip(nv):
+    x = np.arange(1000, dtype=np.float32)
+    d = nv.to_device(x)
+    assert np.array_equal(d.download(np.float32), x)
+    d.zero()
+    assert not d.download(np.float32).any()
+    assert nv.lib.dev_alloc(0) is None
+    assert nv.lib.dev_max_alloc() > (1 << 30)
+    assert nv.lib.dev_count() >= 1
+    s = C.c_void_p()
+    assert nv.lib.dev_stream_create(C.byref(s)) == 0 and nv.lib.dev_stream_sync(s) == 0
+    assert nv.lib.dev_stream_destroy(s) == 0
+
+
+def test_rope_table(nv, ob):
+    eng = nv.Engine(1, 12, 2, ctx=8448, n_slices=1, kv_dtype=nv.KV_F32)
+    cs, sn = eng.rope_tables()
+    assert cs.shape == (8448, 64) and cs[0, 0] == 1.0 and sn[0, 0] == 0.0        # tests/gpu_misc.cu:22
+    i = np.arange(64, dtype=np.float64)
+    ang = np.arange(8448, dtype=np.float64)[:, None] * (1e6 ** (-i / 64.0))[None, :]
+    # fp32 angle rounding dominates: |d angle| <= ~2^-24 * pos
+    assert np.abs(cs - np.cos(ang)).max() < 2e-3 and np.abs(sn - np.sin(ang)).max() < 2e-3
+    assert np.abs(cs[:64] - np.cos(ang[:64])).max() < 1e-5
+    g = ob.ref_gpu("qwen25_7b")
+    if g is not None:   # the reference's rope_table_kernel, rows 0..kCtx-1, bit for bit
+        n = g.ref_gpu_kctx() * 64
+        rc, rs = nv.DevBuf(n * 4), nv.DevBuf(n * 4)
+        g.ref_gpu_rope_table(rc.ptr, rs.ptr, None)
+        nv.check(nv.lib.dev_sync())
+        assert np.array_equal(bits(rc.download(np.float32)), bits(cs[: g.ref_gpu_kctx()].ravel()))
+        assert np.array_equal(bits(rs.download(np.float32)), bits(sn[: g.ref_gpu_kctx()].ravel()))
+    eng.close()
+
+
+@pytest.mark.parametrize("model", list(SHAPES))
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+def test_append_bit_exact_vs_oracle(nv, ob, model, dtype):
+    NH, NKV = SHAPES[model]
+    kvd = nv.KV_F16 if dtype == "f16" else nv.KV_F32
+    L, ctx = 3, 160
+    eng = nv.Engine(L, NH, NKV, ctx=ctx, n_slices=3, kv_dtype=kvd)
+    rng = np.random.default_rng(11)
+    ss = [eng.session_create() for _ in range(3)]
+    for s in ss:
+        eng.permute_pages(s, rng.permutation(eng.nblocks))
+    cs, sn = eng.rope_tables()
+    sh = ob.shape(L, NH, NKV, kvd)
+    pk, pv = ob.new_pools(sh, eng.nb)
+    shp = eng.shape()
+    # multi-token appends that start mid-page and cross page boundaries, in every layer
+    for s, (pos0, n) in zip(ss, [(0, 37), (5, 16), (15, 70)]):
+        table = eng.pool.table(eng.session_slice(s))
+        for layer in range(L):
+            q = rng.standard_normal((n, NH, 128)).astype(np.float32)
+            k = rng.standard_normal((n, NKV, 128)).astype(np.float32)
+            v = rng.standard_normal((n, NKV, 128)).astype(np.float32)
+            dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+            nv.check(nv.lib.nova_launch_rope_append_paged(
+                C.byref(shp), eng.k_base, eng.v_base, nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(s)),
+                layer, eng.nb, n, pos0, dq.ptr, dk.ptr, dv.ptr, nv.lib.nova_rope_cos(eng.h),
+                nv.lib.nova_rope_sin(eng.h), None))
+            nv.check(nv.lib.dev_sync())
+            ob.rope_append_paged(sh, pk, pv, table, layer, eng.nb, n, pos0, q, k, v, cs, sn)
+            assert np.array_equal(bits(dq.download(np.float32)), bits(q.ravel())), "rotated q"
+            assert np.array_equal(bits(dk.download(np.float32)), bits(k.ravel())), "rotated k"
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    eng.close()
+
+
+@pytest.mark.parametrize("model", ["qwen25_1p5b", "qwen25_7b"])
+def test_append_vs_reference_kernels(nv, ob, model):
+    """rope_batch_kernel + kv_store_paged_kernel of the reference (fp32 pools) against the fused
+    kernel: fp32 pages identical, fp16 pages == round-to-nearest-even of the reference's."""
+    g = ob.ref_gpu(model)
+    if g is None:
+        pytest.skip("reference CUDA library not built")
+    NH, NKV = SHAPES[model]
+    L, ctx, n, pos0, layer = 2, 4096, 300, 1000, 1
+    rng = np.random.default_rng(5)
+    q = rng.standard_normal((n, NH, 128)).astype(np.float32)
+    k = rng.standard_normal((n, NKV, 128)).astype(np.float32)
+    v = rng.standard_normal((n, NKV, 128)).astype(np.float32)
+    res = {}
+    for kvd in (nv.KV_F32, nv.KV_F16):
+        eng = nv.Engine(L, NH, NKV, ctx=ctx, n_slices=1, kv_dtype=kvd, rope_positions=4096)
+        s = eng.session_create()
+        perm = np.random.default_rng(6).permutation(eng.nblocks)
+        eng.permute_pages(s, perm)
+        tab = nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(s))
+        dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+        shp = eng.shape()
+        nv.check(nv.lib.nova_launch_rope_append_paged(C.byref(shp), eng.k_base, eng.v_base, tab, layer, eng.nb, n, pos0,
+                                                      dq.ptr, dk.ptr, dv.ptr, nv.lib.nova_rope_cos(eng.h),
+                                                      nv.lib.nova_rope_sin(eng.h), None))
+        nv.check(nv.lib.dev_sync())
+        res[kvd] = (eng.read_pools(), dq.download(np.float32), dk.download(np.float32))
+        if kvd == nv.KV_F32:
+            # the reference on its own tables and an fp32 pool of the same geometry
+            rcs, rsn = nv.DevBuf(4096 * 64 * 4), nv.DevBuf(4096 * 64 * 4)
+            g.ref_gpu_rope_table(rcs.ptr, rsn.ptr, None)
+            rpk = nv.DevBuf(L * eng.nb * eng.page_bytes).zero()
+            rpv = nv.DevBuf(L * eng.nb * eng.page_bytes).zero()
+            rq, rk, rv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+            g.ref_gpu_rope_batch(rq.ptr, rk.ptr, n, pos0, rcs.ptr, rsn.ptr, None)
+            g.ref_gpu_kv_store_paged(rpk.ptr, rpv.ptr, tab, layer, eng.nb, n, pos0, rk.ptr, rv.ptr, None)
+            nv.check(nv.lib.dev_sync())
+            assert g.ref_gpu_last_error() == 0
+            ref = (rpk.download(np.float32), rpv.download(np.float32), rq.download(np.float32), rk.download(np.float32))
+        eng.close()
+    (k32, v32), q32, kk32 = res[nv.KV_F32]
+    assert np.array_equal(bits(q32), bits(ref[2])) and np.array_equal(bits(kk32), bits(ref[3]))
+    assert np.array_equal(bits(k32.ravel()), bits(ref[0])) and np.array_equal(bits(v32.ravel()), bits(ref[1]))
+    (k16, v16), _, _ = res[nv.KV_F16]
+    assert np.array_equal(bits(k16.ravel()), bits(ref[0].astype(np.float16)))
+    assert np.array_equal(bits(v16.ravel()), bits(ref[1].astype(np.float16)))
+
+
+def build_case(nv, ob, model, kvd, ctx_lens, L=2, seed=21, spare=0):
+    """Engine + sessions with permuted tables and random cached context, mirrored in numpy pools."""
+    NH, NKV = SHAPES[model]
+    ctx = ((max(ctx_lens) + 40 + 15) // 16) * 16
+    eng = nv.Engine(L, NH, NKV, ctx=ctx, n_slices=len(ctx_lens) + spare, kv_dtype=kvd)
+    rng = np.random.default_rng(seed)
+    sh = ob.shape(L, NH, NKV, kvd)
+    pk, pv = ob.new_pools(sh, eng.nb)
+    cs, sn = eng.rope_tables()
+    shp = eng.shape()
+    ss = []
+    for n in ctx_lens:
+        s = eng.session_create()
+        ss.append(s)
+        eng.permute_pages(s, rng.permutation(eng.nblocks))
+        if n == 0:
+            continue
+        table = eng.pool.table(eng.session_slice(s))
+        for layer in range(L):
+            k = rng.standard_normal((n, NKV, 128)).astype(np.float32)
+            v = rng.standard_normal((n, NKV, 128)).astype(np.float32)
+            dk, dv = nv.to_device(k), nv.to_device(v)
+            nv.check(nv.lib.nova_launch_rope_append_paged(
+                C.byref(shp), eng.k_base, eng.v_base, nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(s)), layer,
+                eng.nb, n, 0, None, dk.ptr, dv.ptr, nv.lib.nova_rope_cos(eng.h), nv.lib.nova_rope_sin(eng.h), None))
+            qd = np.zeros((n, NH, 128), np.float32)
+            ob.rope_append_paged(sh, pk, pv, table, layer, eng.nb, n, 0, qd, k, v, cs, sn)
+        eng.set_n_past(s, n)
+    nv.check(nv.lib.dev_sync())
+    return eng, ss, sh, pk, pv, cs, sn, rng
+
+
+@pytest.mark.parametrize("kernel", [0, 1])
+@pytest.mark.parametrize("model,dtype", [("qwen25_1p5b", "f16"), ("qwen25_7b", "f16"), ("qwen25_14b", "f16"),
+                                         ("qwen25_7b", "f32"), ("qwen25_1p5b", "f32")])
+def test_decode_steps_vs_oracle(nv, ob, model, dtype, kernel):
+    """Sessions of ragged lengths (a fresh one, page-boundary cases, a long one), three decode steps
+    per-layer and all-layers: pages bit-exact, attention within tolerance of the exact softmax."""
+    kvd = nv.KV_F16 if dtype == "f16" else nv.KV_F32
+    if kernel == 1 and kvd != nv.KV_F16:
+        pytest.skip("tensor-core kernel is fp16-KV only")
+    ctx_lens = [0, 1, 15, 16, 17, 31, 33, 100, 255, 1024, 1500]
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, kvd, ctx_lens)
+    NH, NKV, L, S = eng.NH, eng.NKV, eng.L, len(ss)
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
+    batch = eng.batch(ss)
+    try_set_kernel(nv, batch, kernel)
+    pos = list(ctx_lens)
+    out_d = nv.DevBuf(L * S * NH * 128 * 4)
+    for step in range(3):
+        q = rng.standard_normal((L, S, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+        assert batch.cow() == 0
+        if step % 2 == 0:
+            batch.step_all_layers(dq.ptr, dk.ptr, dv.ptr, out_d.ptr)
+        else:
+            qs, ks = S * NH * 128 * 4, S * NKV * 128 * 4
+            for layer in range(L):
+                batch.append(layer, dq.ptr + layer * qs, dk.ptr + layer * ks, dv.ptr + layer * ks)
+                batch.attn(layer, dq.ptr + layer * qs, out_d.ptr + layer * qs)
+        batch.advance()
+        nv.check(nv.lib.dev_sync())
+        assert batch.device_status() == 0
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)
+        got = out_d.download(np.float32).reshape(L, S, NH, 128)
+        assert np.array_equal(bits(dq.download(np.float32)), bits(q.ravel())), "q rotated in place"
+        for i in range(S):
+            assert_attn_close(got[:, i], want[:, i], f"step {step} session {i} n_keys {pos[i] + 1}")
+        pos = [p + 1 for p in pos]
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    assert [eng.n_past(s) for s in ss] == pos
+    batch.close()
+    eng.close()
+
+
+@pytest.mark.parametrize("model", ["qwen25_1p5b", "qwen25_7b"])
+def test_attention_vs_reference_kernels(nv, ob, model):
+    """fa_split_paged_kernel + fa_combine_kernel of the reference on an fp32 pool holding
+    float(half(x)), against this library on the fp16 pool with the same values (both kernels)."""
+    g = ob.ref_gpu(model)
+    if g is None:
+        pytest.skip("reference CUDA library not built")
+    for n_ctx in (1, 33, 700, 2047):
+        eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, nv.KV_F16, [n_ctx], L=2, seed=n_ctx)
+        NH = eng.NH
+        rk, rv = nv.to_device(pk.astype(np.float32)), nv.to_device(pv.astype(np.float32))
+        q = rng.standard_normal((1, NH, 128)).astype(np.float32)
+        dq = nv.to_device(q)
+        tab = nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(ss[0]))
+        ro, scr = nv.DevBuf(NH * 128 * 4), nv.DevBuf(NH * 32 * 130 * 4)
+        layer = 1
+        g.ref_gpu_attn_decode_paged(dq.ptr, rk.ptr, rv.ptr, tab, layer, eng.nb, n_ctx, ro.ptr, scr.ptr, None)
+        nv.check(nv.lib.dev_sync())
+        assert g.ref_gpu_last_error() == 0
+        ref = ro.download(np.float32).reshape(NH, 128)
+        # the oracle's order-faithful restatement should sit within float noise of the real kernels
+        orc = ob.attn_decode_paged(sh, q[0], pk, pv, eng.pool.table(eng.session_slice(ss[0])), layer, eng.nb, n_ctx)
+        assert rel_l2(orc, ref) < 2e-6
+        # raw launcher (caller scratch, separate merge)
+        shp = eng.shape()
+        o = nv.DevBuf(NH * 128 * 4)
+        nv.check(nv.lib.nova_launch_attn_decode_paged(C.byref(shp), dq.ptr, eng.k_base, eng.v_base, tab, layer, eng.nb,
+                                                      n_ctx, o.ptr, scr.ptr, None))
+        nv.check(nv.lib.dev_sync())
+        assert_attn_close(o.download(np.float32).reshape(NH, 128), ref, f"raw n={n_ctx}")
+        # batched path, both kernels; n_keys = n_past + 1 so step back by one
+        eng.set_n_past(ss[0], n_ctx - 1)
+        batch = eng.batch(ss)
+        for kernel in (0, 1):
+            if nv.lib.nova_batch_set_kernel(batch.h, kernel) != 0:
+                continue
+            o.zero()
+            batch.attn(layer, dq.ptr, o.ptr)
+            nv.check(nv.lib.dev_sync())
+            assert_attn_close(o.download(np.float32).reshape(NH, 128), ref, f"kernel {kernel} n={n_ctx}")
+        batch.close()
+        eng.close()
+
+
+def test_gpu_misc_known_answers(nv):
+    """tests/gpu_misc.cu of the reference: RoPE at position 0 is the identity; one key -> V[0]."""
+    eng = nv.Engine(1, 12, 2, ctx=64, n_slices=1, kv_dtype=nv.KV_F32)
+    s = eng.session_create()
+    q = np.sin(np.arange(12 * 128, dtype=np.float32)).reshape(1, 1, 12, 128)
+    k = np.cos(np.arange(2 * 128, dtype=np.float32)).reshape(1, 1, 2, 128)
+    v = np.sin(np.arange(2 * 128, dtype=np.float32) * 0.001).reshape(1, 1, 2, 128)
+    dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+    out = nv.DevBuf(12 * 128 * 4)
+    b = eng.batch([s])
+    b.step_all_layers(dq.ptr, dk.ptr, dv.ptr, out.ptr)
+    nv.check(nv.lib.dev_sync())
+    assert np.abs(dq.download(np.float32) - q.ravel()).max() <= 1e-6
+    assert np.abs(dk.download(np.float32) - k.ravel()).max() <= 1e-6
+    o = out.download(np.float32).reshape(12, 128)
+    for h in range(12):
+        assert np.abs(o[h] - v[0, 0, h // 6]).max() <= 1e-6
+    b.close()
+    eng.close()
+
+
+@pytest.mark.parametrize("kernel", [0, 1])
+def test_partial_and_lse_combine(nv, ob, kernel):
+    """Split-K over page ranges (the multi-GPU cut) + nova_lse_combine == whole attention."""
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, "qwen25_7b", nv.KV_F16, [999, 40], L=1, seed=3)
+    NH, S = eng.NH, 2
+    batch = eng.batch(ss)
+    try_set_kernel(nv, batch, kernel)
+    for s in ss:
+        eng.set_n_past(s, eng.n_past(s) - 1)
+    batch.sync_positions()
+    q = rng.standard_normal((S, NH, 128)).astype(np.float32)
+    dq = nv.to_device(q)
+    ranges = [(0, 20), (20, 21), (21, 50), (50, 70)]
+    parts = nv.DevBuf(len(ranges) * S * NH * 130 * 4)
+    for i, (a, b) in enumerate(ranges):
+        batch.attn_partial(0, dq.ptr, a, b, parts.ptr + i * S * NH * 130 * 4)
+    out = nv.DevBuf(S * NH * 128 * 4)
+    nv.check(nv.lib.nova_lse_combine(parts.ptr, len(ranges), S * NH, 128, out.ptr, None))
+    nv.check(nv.lib.dev_sync())
+    got = out.download(np.float32).reshape(S, NH, 128)
+    gp = parts.download(np.float32).reshape(len(ranges), S, NH, 130)
+    for i, s in enumerate(ss):
+        tab = eng.pool.table(eng.session_slice(s))
+        want = ob.attn_decode_paged(sh, q[i], pk, pv, tab, 0, eng.nb, [999, 40][i], exact=True)
+        assert_attn_close(got[i], want, f"session {i}")
+        for j, (a, b) in enumerate(ranges):
+            wp = ob.attn_partial(sh, q[i], pk, pv, tab, 0, eng.nb, [999, 40][i], a, b)
+            if wp[0, 1] == 0:      # this range holds no key of the session
+                assert np.isneginf(gp[j, i, :, 0]).all() and not gp[j, i, :, 1:].any()
+            else:                  # compare normalised partial outputs
+                assert_attn_close(gp[j, i, :, 2:] / gp[j, i, :, 1:2], wp[:, 2:] / wp[:, 1:2], f"part {j}")
+    # the oracle's merge of the GPU partials agrees with the GPU merge
+    assert rel_l2(ob.lse_combine(gp.reshape(len(ranges), S * NH, 130)), got.reshape(S * NH, 128)) < 1e-5
+    batch.close()
+    eng.close()
+
+
+def test_cow_shared_prefix(nv, ob):
+    """Config-3 in miniature: sessions share a donor's prefix whose tail page is partly filled; the
+    first append of each un-shares that page exactly once (tests/cow_e2e_demo.cpp:87-105,
+    tests/reuse_demo.cpp:72-81).  Pages and attention against the oracle; the host bookkeeping itself is
+    diffed against the reference's KvPool in test_host_state.py."""
+    model, kvd, L, P, n_fork = "qwen25_7b", nv.KV_F16, 2, 37, 5
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, kvd, [P], L=L, seed=8, spare=n_fork + 1)
+    donor = ss[0]
+    forks = []
+    for _ in range(n_fork):
+        f = eng.session_create()
+        forks.append(f)
+        eng.attach_prefix(f, donor, P)
+    tail = eng.pool.table(eng.session_slice(donor))[(P - 1) >> 4]
+    assert eng.pool.refcnt(tail) == n_fork + 1
+    donor_tail_before = eng.read_page("k", 1, tail).copy()
+    batch = eng.batch(forks)
+    NH, NKV, S = eng.NH, eng.NKV, n_fork
+    out_d = nv.DevBuf(L * S * NH * 128 * 4)
+    pos = [P] * S
+    cows = []
+    for step in range(4):
+        q = rng.standard_normal((L, S, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        before = {f: eng.pool.table(eng.session_slice(f)).copy() for f in forks}
+        n_cow = batch.cow()
+        cows.append(n_cow)
+        for f in forks:      # oracle: same page copies, in the same order
+            after = eng.pool.table(eng.session_slice(f))
+            for lb in np.nonzero(after != before[f])[0]:
+                ob.cow_copy(sh, pk, pv, eng.nb, int(before[f][lb]), int(after[lb]))
+        dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+        batch.step_all_layers(dq.ptr, dk.ptr, dv.ptr, out_d.ptr)
+        batch.advance()
+        nv.check(nv.lib.dev_sync())
+        tables = np.stack([eng.pool.table(eng.session_slice(f)) for f in forks])
+        for f, row in zip(forks, tables):      # device mirror follows the host table
+            assert np.array_equal(eng.device_table(eng.session_slice(f)), row)
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)
+        assert_attn_close(out_d.download(np.float32).reshape(want.shape), want, f"step {step}")
+        pos = [p + 1 for p in pos]
+    assert cows == [n_fork, 0, 0, 0]                                   # exactly once each, never again
+    assert eng.pool.cow_count() == n_fork
+    assert eng.pool.refcnt(tail) == 1                                  # donor owns its tail page again
+    assert np.array_equal(bits(eng.read_page("k", 1, tail)), bits(donor_tail_before))   # donor untouched
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    # pool exhaustion is an error code, not an abort (src/model.cpp:173 aborts)
+    eng2 = nv.Engine(1, 12, 2, ctx=32, n_slices=2, kv_dtype=kvd)
+    a, b = eng2.session_create(), eng2.session_create()
+    eng2.set_n_past(a, 20)
+    eng2.attach_prefix(b, a, 20)
+    assert nv.lib.nova_session_cow(eng2.h, b, 20, 1) == nv.ERR_POOL_FULL
+    eng2.close()
+    batch.close()
+    eng.close()
+
+
+def test_sessions_follow_reference_manager(nv):
+    """SessionManager semantics (code/session.h:84-142): lowest free slot, slice ids LIFO, errors
+    as codes; zeroing of a new session's pages."""
+    eng = nv.Engine(2, 12, 2, ctx=64, n_slices=3, kv_dtype=nv.KV_F16, max_sessions=3)
+    a, b, c = eng.session_create(), eng.session_create(), eng.session_create()
+    assert (a, b, c) == (0, 1, 2)
+    assert nv.lib.nova_session_create(eng.h) == nv.ERR_NO_SESSION
+    assert [eng.session_slice(x) for x in (a, b, c)] == [0, 1, 2]
+    eng.session_destroy(a)
+    eng.session_destroy(c)
+    d = eng.session_create()
+    assert d == 0 and eng.session_slice(d) == 2          # slot: lowest free; slice: last released first
+    assert np.array_equal(eng.device_table(2), eng.pool.table(2))
+    assert nv.lib.nova_session_live_count(eng.h) == 2
+    assert eng.session_stream(d) is not None and eng.session_stream(1) != eng.session_stream(d)
+    k, v = eng.read_pools()
+    assert not k.any() and not v.any()
+    assert nv.lib.nova_session_destroy(eng.h, 7) == nv.ERR_INVALID
+    eng.close()
+
+
+def test_bad_table_entry_is_reported_not_followed(nv):
+    """A block-table entry outside [0, NB) is checked before it is used: the launch skips the page
+    and leaves NOVA_ERR_BAD_TABLE in the status word."""
+    eng = nv.Engine(1, 12, 2, ctx=64, n_slices=1, kv_dtype=nv.KV_F16)
+    s = eng.session_create()
+    eng.set_n_past(s, 20)
+    bad = eng.pool.table(eng.session_slice(s)).copy()
+    bad[1] = eng.nb + 5
+    nv.check(nv.lib.dev_upload(nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(s)), bad.ctypes.data, bad.nbytes))
+    b = eng.batch([s])
+    q = nv.to_device(np.zeros((12, 128), np.float32))
+    o = nv.DevBuf(12 * 128 * 4)
+    b.attn(0, q.ptr, o.ptr)
+    nv.check(nv.lib.dev_sync())
+    assert b.device_status() == nv.ERR_BAD_TABLE
+    assert b.device_status() == 0          # reading clears it
+    b.close()
+    eng.close()
+
+
+def test_decode_step_from_host_buffers(nv, ob):
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, "qwen25_1p5b", nv.KV_F16, [50, 7], L=3, seed=13)
+    L, S, NH, NKV = eng.L, 2, eng.NH, eng.NKV
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
+    batch = eng.batch(ss)
+    pos = [50, 7]
+    for step, per_layer in enumerate((1, 0, 1)):
+        q = rng.standard_normal((L, S, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        out = np.empty_like(q)
+        batch.decode_step_host(q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data, per_layer)
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q.copy(), k.copy(), v, cs, sn, exact=True)
+        assert_attn_close(out, want, f"step {step}")
+        pos = [p + 1 for p in pos]
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    batch.close()
+    eng.close()
