@@ -1,0 +1,382 @@
+"""Benchmark of the paged-KV decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+
+One decode step = for every session of the workload and every layer: copy-on-write guard,
+fused RoPE+append of the step's K/V at n_past, paged decode attention over n_past+1 keys;
+then n_past += 1.  The metric counts session-steps (one session advanced by one token through
+all layers) per second, so that it aggregates over sessions and GPUs.
+
+Timed on the device with CUDA events on the launching stream after >= 3 warm-up steps; at N > 1
+(one process per GPU, sessions sharded by GPU, no collective on the data path) the time is the
+maximum over ranks.  One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import __graft_entry__ as graft  # noqa: E402
+
+# name -> (model, sessions, (ctx_lo, ctx_hi), seed offset); BASELINE.json configs
+WORKLOADS = {
+    "c1": dict(model="qwen25_1p5b", sessions=1, ctx=(1024, 1024), cfg=0,
+               text="Qwen2.5-1.5B-shaped KV, 1 session x 1024 cached tokens, permuted pages"),
+    "c2": dict(model="qwen25_7b", sessions=8, ctx=(2048, 8192), cfg=1,
+               text="Qwen2.5-7B-shaped KV, 8 sessions, contexts uniform in [2048, 8192], permuted pages"),
+    "c4": dict(model="qwen25_14b", sessions=64, ctx=(8192, 8192), cfg=3,
+               text="Qwen2.5-14B-shaped KV, 64 sessions x 8192 cached tokens, permuted pages"),
+}
+BASE_SEED = 0x5EED0000
+METRIC, UNIT = "decode_steps_per_s", "session-steps/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# --------------------------------------------------------------------------------------------
+def run_ours(args):
+    rank, local_rank, world = dist_env()
+    nv = graft.load_package()          # ImportError if libnova_b200.so is missing: no fallback
+    import conflux_nova_b200.workloads as wl
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    nv.check(nv.lib.dev_select(local_rank))
+
+    w = WORKLOADS[args.workload]
+    seed = BASE_SEED + w["cfg"] + 1000 * rank          # every GPU holds its own sessions
+    lens = wl.context_lengths(seed, w["sessions"], *w["ctx"])
+    K, W, KE = args.steps, args.warmup, args.e2e_steps
+    total_steps = 5 * (W + K) + (W + KE) + 8
+    work = wl.Workload(w["model"], lens, seed=seed, steps=total_steps, device=local_rank)
+    eng, batch = work.eng, work.batch
+    kernel = args.kernel
+    if kernel < 0:
+        kernel = 1 if nv.lib.nova_batch_set_kernel(batch.h, 1) == nv.OK else 0
+    batch.set_kernel(kernel)
+    stream = nv.Stream()
+    nq, nk = work.step_input_sizes()
+    S, L = len(work.sessions), eng.L
+
+    # step inputs resident in HBM before any timed region: a ring of 4 input sets
+    ring = 4
+    dq, dk, dv = nv.DevBuf(ring * nq * 4), nv.DevBuf(ring * nk * 4), nv.DevBuf(ring * nk * 4)
+    dout = nv.DevBuf(ring * nq * 4)
+    for i in range(ring):
+        a, b, c = work.device_step_inputs(i)
+        for dst, src, n in ((dq, a, nq), (dk, b, nk), (dv, c, nk)):
+            host = src.download(np.float32)
+            dst.upload(host, i * n * 4)
+            src.free()
+
+    def barrier():
+        nv.check(nv.lib.dev_sync())
+        if dist is not None:
+            dist.barrier()
+        nv.check(nv.lib.dev_sync())
+
+    def timed(mode, steps, warm, time_attn=False):
+        """Run `warm` + `steps` decode steps in `ring`-sized groups; returns (ms, attn_ms, kv_bytes)."""
+        def go(n, measure):
+            attn = 0.0
+            done = 0
+            while done < n:
+                m = min(ring, n - done)
+                r = batch.run_steps(m, dq.ptr, dk.ptr, dv.ptr, dout.ptr, nq, nk, mode, stream.h,
+                                    time_attn=measure and time_attn)
+                attn += r or 0.0
+                done += m
+            return attn
+        go(warm, False)
+        barrier()
+        n0 = [eng.n_past(s) for s in work.sessions]
+        kv_bytes = sum(work.kv_bytes_per_step([n + i for n in n0]) for i in range(steps))
+        e0, e1 = nv.Event(), nv.Event()
+        e0.record(stream)
+        attn_ms = go(steps, True)
+        e1.record(stream)
+        e1.sync()
+        ms = e0.elapsed_ms(e1)
+        barrier()
+        return ms, attn_ms, kv_bytes
+
+    launches0 = nv.lib.nova_launch_count()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    mode = {"layer": 1, "graph": 2, "fused": 0}[args.launch]
+    ms_main, _, kv_main = timed(mode, K, W)
+    launches = int(nv.lib.nova_launch_count() - launches0) * K // (K + W)
+    # the same K steps again with an event pair around every attention launch: the dominant kernel's own time
+    ms_evt, attn_ms, kv_evt = timed(1 if mode == 2 else mode, K, W, time_attn=True)
+    # all layers in one launch (the isolated path; legal because layer inputs are independent here)
+    other = {}
+    for name, m in (("fused", 0), ("layer", 1), ("graph", 2)):
+        if m != mode:
+            ms_o, _, kv_o = timed(m, K, W)
+            other[name] = dict(ms_per_step=ms_o / K, kv_gbs=kv_o / ms_o / 1e6)
+    ms_f, attn_f, kv_f = timed(0, K, W, time_attn=True)
+
+    # end to end through the host-buffer call: pinned host q/k/v in, out back, every step
+    hq, hk, hv = nv.lib.dev_host_alloc(nq * 4), nv.lib.dev_host_alloc(nk * 4), nv.lib.dev_host_alloc(nk * 4)
+    ho = nv.lib.dev_host_alloc(nq * 4)
+    nv.check(nv.lib.dev_download(hq, dq.ptr, nq * 4))
+    nv.check(nv.lib.dev_download(hk, dk.ptr, nk * 4))
+    nv.check(nv.lib.dev_download(hv, dv.ptr, nk * 4))
+    for _ in range(W):
+        batch.decode_step_host(hq, hk, hv, ho, 1 if mode else 0, stream.h)
+    barrier()
+    e0, e1 = nv.Event(), nv.Event()
+    e0.record(stream)
+    t0 = time.perf_counter()
+    for _ in range(KE):
+        batch.decode_step_host(hq, hk, hv, ho, 1 if mode else 0, stream.h)
+    e1.record(stream)
+    e1.sync()
+    ms_e2e = max(e0.elapsed_ms(e1), (time.perf_counter() - t0) * 1e3)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    status = batch.device_status()
+    if status != 0:
+        raise RuntimeError(f"device status {status} after the timed regions")
+
+    # max over ranks
+    vals = np.array([ms_main, ms_e2e, ms_evt, attn_ms, ms_f, attn_f], dtype=np.float64)
+    sums = np.array([kv_main, kv_evt, kv_f], dtype=np.float64)
+    if dist is not None:
+        import torch
+        t = torch.tensor(vals, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        vals = t.cpu().numpy()
+        u = torch.tensor(sums, device="cuda")
+        dist.all_reduce(u, op=dist.ReduceOp.SUM)
+        sums = u.cpu().numpy()
+    ms_main, ms_e2e, ms_evt, attn_ms, ms_f, attn_f = [float(x) for x in vals]
+    kv_main_all, kv_evt_all, kv_f_all = [float(x) for x in sums]
+
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        cpu = cpu_baseline_sample(nv, work, lens, seed)
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        n_attn = K * (1 if mode == 0 else L)
+        per_launch_bytes = kv_evt / n_attn
+        achieved = per_launch_bytes / (attn_ms / n_attn) / 1e6 if attn_ms > 0 else 0.0
+        line = {
+            "metric": METRIC, "value": world * S * K / (ms_main / 1e3), "unit": UNIT,
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_main / K,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['text']}; per GPU", "sessions_per_gpu": S,
+                       "context_tokens": lens, "layers": L, "kv_dtype": "fp16", "page_tokens": 16,
+                       "launch": args.launch, "attention_kernel": "mma" if kernel == 1 else "simt",
+                       "l2": "inputs larger than L2 (KV read per step >> 126 MB)"},
+            "batch_steps_per_s": K / (ms_main / 1e3),
+            "kv_gbs": kv_main_all / ms_main / 1e6,
+            "kv_bytes_per_step": kv_main / K,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "attention (%s)" % ("all layers per launch" if mode == 0 else "one layer per launch"),
+                         "launch_us": attn_ms / n_attn * 1e3, "algorithmic_bytes_per_launch": per_launch_bytes,
+                         "all_layers_one_launch": {"achieved": kv_f / K / (attn_f / K) / 1e6 if attn_f > 0 else 0.0,
+                                                   "frac": (kv_f / K / (attn_f / K) / 1e6) / peak if attn_f > 0 else 0.0,
+                                                   "launch_us": attn_f / K * 1e3}},
+            "other_launch_modes": other,
+            "e2e": {"value": world * S * KE / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": (nq + 2 * nk) * 4,
+                    "d2h_bytes_per_step": nq * 4, "ms_per_step": ms_e2e / KE, "steps": KE},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def cpu_baseline_sample(nv, work, lens, seed):
+    """The CPU restatement of the reference's path (oracle/, the checker) timed on this box's cores on
+    a bounded sample of the same workload: one decode step of `sample_layers` layers, scaled to all."""
+    from oracle import binding as ob
+    eng = work.eng
+    L, S = eng.L, len(work.sessions)
+    sample_layers = 1
+    sh = ob.shape(sample_layers, eng.NH, eng.NKV, ob.KV_F16)
+    n = eng.nb * eng.page_bytes // 2
+    shp = (sample_layers, eng.nb, 16, eng.NKV, eng.HD)
+    pk = nv.download_ptr(eng.k_base, np.float16, n).reshape(shp)
+    pv = nv.download_ptr(eng.v_base, np.float16, n).reshape(shp)
+    cs, sn = eng.rope_tables()
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in work.sessions])
+    pos = [eng.n_past(s) for s in work.sessions]
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((sample_layers, S, eng.NH, eng.HD)).astype(np.float32)
+    k = rng.standard_normal((sample_layers, S, eng.NKV, eng.HD)).astype(np.float32)
+    v = rng.standard_normal((sample_layers, S, eng.NKV, eng.HD)).astype(np.float32)
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q.copy(), k.copy(), v, cs, sn)
+        reps += 1
+        if time.perf_counter() - t0 > 8.0 or reps >= 5:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": S / (dt * L / sample_layers), "unit": UNIT, "cores": ob.num_threads(), "kind": "port",
+            "sample": f"{reps} x (1 decode step of {sample_layers} of {L} layers, all {S} sessions at their full "
+                      f"context), time scaled by {L}/{sample_layers}; order-faithful fp32 restatement of "
+                      "fa_split_paged/fa_combine + rope/kv_store, OpenMP over layer x session"}
+
+
+# --------------------------------------------------------------------------------------------
+def run_reference(args):
+    """The reference arm: the reference has no CPU implementation of the attention itself (its only
+    implementations are CUDA and SYCL kernels), so this times the CPU restatement of its algorithm
+    (oracle/, kind "port") with every host thread, on the same workload, same metric."""
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from oracle import binding as ob
+    graft.load_package()       # workload definitions (context lengths, page permutations) use the library's hashing
+    import conflux_nova_b200.workloads as from_wl
+    w = WORKLOADS[args.workload]
+    seed = BASE_SEED + w["cfg"]
+    lens = from_wl.context_lengths(seed, w["sessions"], *w["ctx"])
+    Lfull, NH, NKV = from_wl.SHAPES[w["model"]]
+    S = len(lens)
+    sample_layers = 1
+    sh = ob.shape(sample_layers, NH, NKV, ob.KV_F16)
+    nblocks = (max(lens) + args.steps + args.warmup + 16 + 15) // 16
+    nb = nblocks * S
+    pk, pv = ob.new_pools(sh, nb)
+    cs, sn = ob.rope_table(nblocks * 16)
+    tables = np.stack([s * nblocks + from_wl.page_permutation(seed, s, nblocks) for s in range(S)]).astype(np.int32)
+    row = NKV * 128
+    for s in range(S):          # cached context through the oracle's append, same seeded values
+        n = lens[s]
+        k = ob.synth_normal(n * row, ob.synth_key(seed, 1, s, 0)).reshape(n, NKV, 128)
+        v = ob.synth_normal(n * row, ob.synth_key(seed, 2, s, 0)).reshape(n, NKV, 128)
+        qd = np.zeros((n, NH, 128), np.float32)
+        ob.rope_append_paged(sh, pk, pv, tables[s], 0, nb, n, 0, qd, k, v, cs, sn)
+    pos = list(lens)
+    rng = np.random.default_rng(1)
+
+    def one_step():
+        q = rng.standard_normal((sample_layers, S, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((sample_layers, S, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((sample_layers, S, NKV, 128)).astype(np.float32)
+        ob.decode_step(sh, pk, pv, tables, nb, pos, q, k, v, cs, sn)
+        for i in range(S):
+            pos[i] += 1
+
+    for _ in range(args.warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one_step()
+    dt = time.perf_counter() - t0
+    ms_step = dt / args.steps * 1e3 * (Lfull / sample_layers)
+    value = S / (ms_step / 1e3)
+    sample = (f"each step = 1 decode step of {sample_layers} of {Lfull} layers over all {S} sessions at full context; "
+              f"time scaled by {Lfull}/{sample_layers}")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {w['text']}", "sessions_per_gpu": S, "context_tokens": lens,
+                   "layers": Lfull, "kv_dtype": "fp16", "page_tokens": 16},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": ob.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--e2e-steps", type=int, default=16)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--launch", default="graph", choices=["layer", "graph", "fused"],
+                    help="layer: 2 launches per layer; graph: the same, replayed from a CUDA graph; fused: all layers per launch")
+    ap.add_argument("--kernel", type=int, default=-1, help="-1 best available, 0 SIMT, 1 tensor-core")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    _, _, world = dist_env()
+    if args.gpus != world and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -410,7 +410,7 @@ class Engine:
 
     def read_page(self, which: str, layer: int, phys: int) -> np.ndarray:
         base = self.k_base if which == "k" else self.v_base
-        off = (layer * self.nb + phys) * self.page_bytes
+        off = (int(layer) * self.nb + int(phys)) * self.page_bytes
         n = self.page_bytes // np.dtype(self.kv_np).itemsize
         return download_ptr(base + off, self.kv_np, n).reshape(self.desc.kv_block, self.NKV, self.HD)
 

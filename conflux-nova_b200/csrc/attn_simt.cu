@@ -129,7 +129,10 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
     pv.n_groups = n_groups;
     pv.pages_per_layer = s_prefix[pv.rows_per_layer];
     pv.pages_total = pv.pages_per_layer * a.n_layers;
-    pv.n_ctas = (int)gridDim.x;
+    // With fewer pages than CTAs only the first `pages_total` CTAs take part, so that every
+    // participating CTA owns at least one page and a row's contributors are exactly
+    // c_first .. c_last.
+    pv.n_ctas = pv.pages_total < (int64_t)gridDim.x ? (int)pv.pages_total : (int)gridDim.x;
 
     // Rows without any page in the window get their "nothing attended" result here.
     {
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
             }
         }
     }
-    if (pv.pages_total == 0) return;
+    if (pv.pages_total == 0 || (int)blockIdx.x >= pv.n_ctas) return;
 
     const int64_t lo = plan_cta_begin(pv, (int)blockIdx.x);
     const int64_t hi = plan_cta_begin(pv, (int)blockIdx.x + 1);
@@ -298,7 +301,7 @@ __global__ void __launch_bounds__(128) part_merge_kernel(AttnLaunch a, int n_cta
     pv.n_groups = n_groups;
     pv.pages_per_layer = s_prefix[pv.rows_per_layer];
     pv.pages_total = pv.pages_per_layer * a.n_layers;
-    pv.n_ctas = n_ctas_split;
+    pv.n_ctas = pv.pages_total < (int64_t)n_ctas_split ? (int)pv.pages_total : n_ctas_split;
     const int64_t rows_total = (int64_t)pv.rows_per_layer * a.n_layers;
     for (int64_t v = blockIdx.x; v < rows_total; v += gridDim.x) {
         const int row = (int)(v % pv.rows_per_layer);

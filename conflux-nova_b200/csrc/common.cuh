@@ -95,6 +95,7 @@ int launch_attn_simt(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s);
 int attn_default_ctas_simt(int n_kv_heads);
 int attn_default_ctas_mma();
+bool attn_mma_built();
 int launch_part_merge(const AttnLaunch& a, int n_ctas, cudaStream_t s);
 int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s);
 

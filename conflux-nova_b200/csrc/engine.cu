@@ -552,7 +552,7 @@ int nova_batch_sync_positions(nova_batch* b, nova_stream_t s) {
 
 int nova_batch_set_kernel(nova_batch* b, int which) {
     if (!b || which < 0 || which > 1) return NOVA_ERR_INVALID;
-    if (which == 1 && b->e->d.kv_dtype != NOVA_KV_F16) return NOVA_ERR_UNSUPPORTED;
+    if (which == 1 && (b->e->d.kv_dtype != NOVA_KV_F16 || !attn_mma_built())) return NOVA_ERR_UNSUPPORTED;
     b->kernel = which;
     return NOVA_OK;
 }
