@@ -1,8 +1,493 @@
-// attn_mma.cu — tensor-core form of the paged decode attention (placeholder until built).
-#include "common.cuh"
+// attn_mma.cu — paged split-K decode attention for fp16 pools, tensor-core form.
+// Same contract as attn_simt.cu (replaces fa_split_paged_kernel + fa_combine_kernel,
+// src/kernel/attn.cu:197-289,163-191 of the reference, for all sessions / layers of a launch),
+// built for the B200 memory system:
+//
+//   * One persistent CTA per SM (two for 2-kv-head models).  A producer warp walks the CTA's
+//     stream-K page range and brings WHOLE pages into shared memory with TMA tensor copies
+//     (cp.async.bulk.tensor, no multicast): a page of one pool is [16 slots][NKV][128] fp16 and
+//     is fetched as two boxes [64 dims][16 slots][kv group] with the 128-byte swizzle, so that
+//     each kv head's 16 key rows sit in 16 consecutive 128-byte lines.  A ring of
+//     kStages page sets (K+V, 32 KiB each at 4 kv heads) keeps ~190 KiB per SM in flight.
+//   * One consumer warp per kv head.  The G = NH/NKV query heads of that kv head are the rows
+//     of an m16n8k16 tile: S = Q.K^T and O += P.V run on mma.sync (fp16 inputs, fp32
+//     accumulate) with bank-conflict-free ldmatrix reads; q is split into fp16 hi + lo parts so
+//     the scores keep fp32-level accuracy; the online softmax (exp2 domain) and all sums are
+//     fp32.  A scalar fp32 version cannot keep up with HBM here: at G = 7 it needs ~3600 FMAs per
+//     512 bytes of KV, more than the SM's FP32 pipes deliver at 20+ B/clk.
+//   * Full/empty mbarriers hand the stages over; every wait is bounded by a wall-clock limit and
+//     reports NOVA_ERR_TIMEOUT through the status word instead of spinning forever.
+//   * Work split and partial slots are those of attn_plan.cuh; the warp that arrives last at a
+//     (row, kv head) ticket merges that head group's partials - no CTA-wide barrier, no spinning.
+#include <cuda.h>
+
+#include "attn_plan.cuh"
 
 namespace novab {
-bool attn_mma_built() { return false; }
+namespace {
+
+constexpr int kStages = 6;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s per barrier wait
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false after kWaitLimitNs (or as soon as another thread of the CTA gave up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const unsigned long long t0 = now_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (now_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+
+// m16n8k16, rows 8..15 of A are zero padding (G <= 8 query heads per kv head): a1 = a3 = 0 and
+// the accumulator rows 8..15 (c2, c3) stay zero and are dropped.
+__device__ __forceinline__ void mma_top(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1,
+                                        float c0, float c1) {
+    float x2, x3;
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d0), "=f"(d1), "=f"(x2), "=f"(x3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(0.f), "f"(0.f));
+    (void)x2;
+    (void)x3;
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int KVG>
+struct MmaCfg {
+    static constexpr int kBoxBytes = KVG * 16 * 128;          // one [64 dims][16 slots][KVG] box
+    static constexpr int kStageBytes = 4 * kBoxBytes;          // K lo/hi dims + V lo/hi dims
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+    static constexpr int kThreads = 32 * (KVG + 1);
+    static constexpr int kCtasPerSm = 4 / KVG >= 1 ? 4 / KVG : 1;
+};
+
+template <int KVG>
+__global__ void __launch_bounds__(MmaCfg<KVG>::kThreads, MmaCfg<KVG>::kCtasPerSm)
+attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv) {
+    using Cfg = MmaCfg<KVG>;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ int s_prefix[kMaxRowsSmem + 1];
+    __shared__ __align__(8) unsigned long long s_full[kStages];
+    __shared__ __align__(8) unsigned long long s_empty[kStages];
+    __shared__ int s_kcount[kStages];
+    __shared__ int s_abort;
+
+    const int lane = (int)threadIdx.x & 31;
+    const int warp = (int)threadIdx.x >> 5;
+    const int G = a.n_heads / a.n_kv_heads;
+    const int n_groups = a.n_kv_heads / KVG;
+    const int NH = a.n_heads, S = a.n_sessions;
+    const int heads_per_row = KVG * G;
+    const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(smem_u32(&s_full[i]), 1);
+            mbar_init(smem_u32(&s_empty[i]), KVG);
+        }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    plan_build_prefix(a, s_prefix, n_groups);   // ends with __syncthreads()
+
+    PlanView pv;
+    pv.prefix = s_prefix;
+    pv.rows_per_layer = S * n_groups;
+    pv.n_groups = n_groups;
+    pv.pages_per_layer = s_prefix[pv.rows_per_layer];
+    pv.pages_total = pv.pages_per_layer * a.n_layers;
+    pv.n_ctas = pv.pages_total < (int64_t)gridDim.x ? (int)pv.pages_total : (int)gridDim.x;
+
+    const int g = lane >> 2, t = lane & 3;   // fragment row (query head within the kv head) / quad lane
+
+    // Rows without any page in the window: "nothing attended".
+    if (warp < KVG) {
+        const int64_t rows_total = (int64_t)pv.rows_per_layer * a.n_layers;
+        for (int64_t v = blockIdx.x; v < rows_total; v += gridDim.x) {
+            const int row = (int)(v % pv.rows_per_layer);
+            if (s_prefix[row + 1] != s_prefix[row]) continue;
+            const int ll = (int)(v / pv.rows_per_layer);
+            const int s = row / n_groups, grp = row - s * n_groups;
+            const int kvh = grp * KVG + warp;
+            if (g < G) {
+                const int64_t head = ((int64_t)ll * S + s) * NH + (int64_t)kvh * G + g;
+                if (a.write_partial_only) {
+                    float* op = a.out_part + head * kPartW;
+                    if (t == 0) { op[0] = -INFINITY; op[1] = 0.f; }
+                    for (int j = 0; j < 16; ++j)
+                        *reinterpret_cast<float2*>(op + 2 + 8 * j + 2 * t) = make_float2(0.f, 0.f);
+                } else {
+                    float* op = a.out + head * kHeadDim;
+                    for (int j = 0; j < 16; ++j)
+                        *reinterpret_cast<float2*>(op + 8 * j + 2 * t) = make_float2(0.f, 0.f);
+                }
+            }
+        }
+    }
+    if (pv.pages_total == 0 || (int)blockIdx.x >= pv.n_ctas) return;
+
+    const int64_t lo = plan_cta_begin(pv, (int)blockIdx.x);
+    const int64_t hi = plan_cta_begin(pv, (int)blockIdx.x + 1);
+
+    // ------------------------------------------------------------------ producer warp
+    if (warp == KVG) {
+        if (lane != 0) return;
+        uint32_t it = 0;
+        for (int64_t pos = lo; pos < hi;) {
+            const Segment sg = plan_segment(pv, pos, hi);
+            pos += sg.page_count;
+            const int s = sg.session;
+            const int n_keys = plan_session_keys(a, s);
+            int first_page, n_pages_row;
+            plan_session_pages(a, s, first_page, n_pages_row);
+            const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
+            const int layer = a.layer0 + sg.layer_local;
+            for (int pg = 0; pg < sg.page_count; ++pg, ++it) {
+                const int stage = (int)(it % kStages);
+                const uint32_t round = it / kStages;
+                if (round > 0 && !mbar_wait(smem_u32(&s_empty[stage]), (round - 1) & 1, &s_abort)) {
+                    if (a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
+                    return;
+                }
+                const int page = first_page + sg.page_first + pg;
+                int phys = __ldg(table + page);
+                int kcount = n_keys - page * kKvBlock;
+                if (kcount > kKvBlock) kcount = kKvBlock;
+                if (phys < 0 || phys >= a.nb) {      // never follow a bad entry: load page 0, use none of it
+                    if (a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
+                    phys = 0;
+                    kcount = 0;
+                }
+                s_kcount[stage] = kcount;
+                const uint32_t bar = smem_u32(&s_full[stage]);
+                const uint32_t dst = stage0 + (uint32_t)stage * Cfg::kStageBytes;
+                const int c1 = (int)(((int64_t)layer * a.nb + phys) * kKvBlock);
+                const int c2 = sg.group * KVG;
+                mbar_expect_tx(bar, Cfg::kStageBytes);
+                tma_load_3d(dst, &tmk, 0, c1, c2, bar);
+                tma_load_3d(dst + Cfg::kBoxBytes, &tmk, 64, c1, c2, bar);
+                tma_load_3d(dst + 2 * Cfg::kBoxBytes, &tmv, 0, c1, c2, bar);
+                tma_load_3d(dst + 3 * Cfg::kBoxBytes, &tmv, 64, c1, c2, bar);
+            }
+        }
+        return;
+    }
+
+    // ------------------------------------------------------------------ consumer warps
+    const int w = warp;                              // kv head within the group
+    const int lm = lane >> 3, lr = lane & 7;         // ldmatrix: matrix index / row within it
+    // K operand: matrices (keys 0-7 | 8-15) x (dims 16ks.. | 16ks+8..): key = (lm>>1)*8 + lr, chunk = 2ks + (lm&1)
+    const uint32_t k_row = (uint32_t)(w * 2048 + (((lm >> 1) << 3) + lr) * 128);
+    // V operand (transposed): matrices (keys 0-7 | 8-15) x (dims chunk c | c+1): key = (lm&1)*8 + lr, chunk = 2jp + (lm>>1)
+    const uint32_t v_row = (uint32_t)(w * 2048 + (((lm & 1) << 3) + lr) * 128);
+    constexpr float kQScale = kAttnScale * kLog2e;
+    uint32_t it = 0;
+
+    for (int64_t pos = lo; pos < hi;) {
+        const Segment sg = plan_segment(pv, pos, hi);
+        pos += sg.page_count;
+        const int s = sg.session;
+        const int kvh = sg.group * KVG + w;
+        const int64_t head0 = ((int64_t)sg.layer_local * S + s) * NH + (int64_t)kvh * G;
+
+        // q fragments of row g (zero for padding rows): hi + lo fp16 parts of q * scale * log2(e)
+        uint32_t qh[8][2], ql[8][2];
+        {
+            const float* qp = a.q + (head0 + (g < G ? g : 0)) * kHeadDim;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+                for (int hlf = 0; hlf < 2; ++hlf) {
+                    float2 x = make_float2(0.f, 0.f);
+                    if (g < G) x = *reinterpret_cast<const float2*>(qp + 16 * ks + 8 * hlf + 2 * t);
+                    x.x *= kQScale;
+                    x.y *= kQScale;
+                    const __half2 h = __floats2half2_rn(x.x, x.y);
+                    const float2 hf = __half22float2(h);
+                    qh[ks][hlf] = *reinterpret_cast<const uint32_t*>(&h);
+                    ql[ks][hlf] = pack_h2(x.x - hf.x, x.y - hf.y);
+                }
+        }
+        float m = -INFINITY, l = 0.f;
+        float o[16][2];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = 0.f;
+
+        for (int pg = 0; pg < sg.page_count; ++pg, ++it) {
+            const int stage = (int)(it % kStages);
+            const uint32_t round = it / kStages;
+            if (!mbar_wait(smem_u32(&s_full[stage]), round & 1, &s_abort)) {
+                if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
+                return;
+            }
+            const int kcount = s_kcount[stage];
+            const uint32_t sk = stage0 + (uint32_t)stage * Cfg::kStageBytes;
+            const uint32_t sv = sk + 2 * Cfg::kBoxBytes;
+
+            if (kcount > 0) {
+                if (kcount < kKvBlock) {
+                    // Rows past the last key hold whatever the page held before: P is 0 there, but
+                    // 0 * (Inf/NaN bit patterns) would poison O, so clear those V rows first.
+                    for (int i = lane; i < (kKvBlock - kcount) * 16; i += 32) {
+                        const int row = kcount + (i >> 4), c = i & 15;
+                        const uint32_t addr = sv + (uint32_t)((c >> 3) * Cfg::kBoxBytes + w * 2048 + row * 128 + ((c & 7) << 4));
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
+                    }
+                    __syncwarp();
+                }
+                // S = Q K^T for the 16 keys of the page: two n-tiles of 8 keys, hi and lo parts of q
+                float sh[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, sl[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    uint32_t b[4];
+                    const uint32_t chunk = (uint32_t)((2 * ks + (lm & 1)) & 7);
+                    ldsm_x4(b, sk + (uint32_t)((ks >> 2) * Cfg::kBoxBytes) + k_row + ((chunk ^ (uint32_t)lr) << 4));
+                    mma_top(sh[0][0], sh[0][1], qh[ks][0], qh[ks][1], b[0], b[1], sh[0][0], sh[0][1]);
+                    mma_top(sh[1][0], sh[1][1], qh[ks][0], qh[ks][1], b[2], b[3], sh[1][0], sh[1][1]);
+                    mma_top(sl[0][0], sl[0][1], ql[ks][0], ql[ks][1], b[0], b[1], sl[0][0], sl[0][1]);
+                    mma_top(sl[1][0], sl[1][1], ql[ks][0], ql[ks][1], b[2], b[3], sl[1][0], sl[1][1]);
+                }
+                float sc[4] = {sh[0][0] + sl[0][0], sh[0][1] + sl[0][1], sh[1][0] + sl[1][0], sh[1][1] + sl[1][1]};
+                if (kcount < kKvBlock) {   // keys 2t, 2t+1, 8+2t, 9+2t of the page
+                    if (2 * t >= kcount) sc[0] = -INFINITY;
+                    if (2 * t + 1 >= kcount) sc[1] = -INFINITY;
+                    if (8 + 2 * t >= kcount) sc[2] = -INFINITY;
+                    if (9 + 2 * t >= kcount) sc[3] = -INFINITY;
+                }
+                float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float mn = fmaxf(m, mx);
+                const float corr = ex2(m - mn);
+                m = mn;
+                const uint32_t p0 = pack_h2(ex2(sc[0] - mn), ex2(sc[1] - mn));
+                const uint32_t p1 = pack_h2(ex2(sc[2] - mn), ex2(sc[3] - mn));
+                {   // the row sum uses the fp16-rounded weights that multiply V
+                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&p0));
+                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&p1));
+                    l = fmaf(l, corr, (f0.x + f0.y) + (f1.x + f1.y));
+                }
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        o[j][0] *= corr;
+                        o[j][1] *= corr;
+                    }
+                }
+                // O += P V : n-tiles of 8 dims, two per ldmatrix
+#pragma unroll
+                for (int jp = 0; jp < 8; ++jp) {
+                    uint32_t b[4];
+                    const uint32_t chunk = (uint32_t)((2 * jp + (lm >> 1)) & 7);
+                    ldsm_x4_t(b, sv + (uint32_t)((jp >> 2) * Cfg::kBoxBytes) + v_row + ((chunk ^ (uint32_t)lr) << 4));
+                    mma_top(o[2 * jp][0], o[2 * jp][1], p0, p1, b[0], b[1], o[2 * jp][0], o[2 * jp][1]);
+                    mma_top(o[2 * jp + 1][0], o[2 * jp + 1][1], p0, p1, b[2], b[3], o[2 * jp + 1][0], o[2 * jp + 1][1]);
+                }
+                if (kcount < kKvBlock) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
+        }
+
+        // ---- segment done: row sums, then direct output or partial + ticket
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int n_contrib = sg.c_last - sg.c_first + 1;
+        if (n_contrib == 1) {
+            if (g < G) {
+                if (a.write_partial_only) {
+                    float* op = a.out_part + (head0 + g) * kPartW;
+                    if (t == 0) { op[0] = m * (1.f / kLog2e); op[1] = l; }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        *reinterpret_cast<float2*>(op + 2 + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+                } else {
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
+                    float* op = a.out + (head0 + g) * kHeadDim;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        *reinterpret_cast<float2*>(op + 8 * j + 2 * t) = make_float2(o[j][0] * inv, o[j][1] * inv);
+                }
+            }
+            continue;
+        }
+        if (g < G) {
+            float* pr = a.part + ((size_t)((int64_t)blockIdx.x + sg.row_id) * heads_per_row + (size_t)(w * G + g)) * kPartW;
+            if (t == 0) { pr[0] = m * (1.f / kLog2e); pr[1] = l; }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                *reinterpret_cast<float2*>(pr + 2 + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+        }
+        // Each kv head's rows are merged by the LAST WARP to arrive for them: a ticket per
+        // (row, kv head in group), no CTA-wide barrier.
+        __threadfence();
+        __syncwarp();
+        unsigned old = 0;
+        if (lane == 0) old = atomicAdd(a.tickets + sg.row_id * KVG + w, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == (unsigned)(n_contrib - 1)) {
+            __threadfence();
+            if (g < G) {
+                float M = -INFINITY;
+                for (int c = sg.c_first; c <= sg.c_last; ++c) {
+                    const float* pr = a.part + ((size_t)(c + sg.row_id) * heads_per_row + (size_t)(w * G + g)) * kPartW;
+                    if (pr[1] > 0.f) M = fmaxf(M, pr[0]);
+                }
+                float L = 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = 0.f;
+                for (int c = sg.c_first; c <= sg.c_last; ++c) {
+                    const float* pr = a.part + ((size_t)(c + sg.row_id) * heads_per_row + (size_t)(w * G + g)) * kPartW;
+                    const float lc = pr[1];
+                    if (lc > 0.f) {
+                        const float wt = __expf(pr[0] - M);
+                        L = fmaf(lc, wt, L);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float2 x = *reinterpret_cast<const float2*>(pr + 2 + 8 * j + 2 * t);
+                            o[j][0] = fmaf(x.x, wt, o[j][0]);
+                            o[j][1] = fmaf(x.y, wt, o[j][1]);
+                        }
+                    }
+                }
+                if (a.write_partial_only) {
+                    float* op = a.out_part + (head0 + g) * kPartW;
+                    if (t == 0) { op[0] = M; op[1] = L; }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        *reinterpret_cast<float2*>(op + 2 + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+                } else {
+                    const float inv = L > 0.f ? 1.f / L : 0.f;
+                    float* op = a.out + (head0 + g) * kHeadDim;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        *reinterpret_cast<float2*>(op + 8 * j + 2 * t) = make_float2(o[j][0] * inv, o[j][1] * inv);
+                }
+            }
+            if (lane == 0) a.tickets[sg.row_id * KVG + w] = 0u;
+        }
+    }
+}
+
+template <int KVG>
+int launch_kvg(const AttnLaunch& a, int n_ctas, cudaStream_t s) {
+    using Cfg = MmaCfg<KVG>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<KVG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           Cfg::kSmemBytes));
+        attr_set = true;
+    }
+    if (n_ctas <= 0) n_ctas = 148 * Cfg::kCtasPerSm;
+    const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k);
+    const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v);
+    attn_mma_kernel<KVG><<<(unsigned)n_ctas, Cfg::kThreads, Cfg::kSmemBytes, s>>>(a, *tk, *tv);
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace
+
+bool attn_mma_built() { return true; }
 int attn_default_ctas_mma() { return 148; }
-int launch_attn_mma(const AttnLaunch&, int, int, cudaStream_t) { return NOVA_ERR_UNSUPPORTED; }
+size_t attn_tmap_bytes() { return sizeof(CUtensorMap); }
+
+// Tensor map over one fp16 pool [rows = L*NB*16][NKV][128]: dim0 = 128 dims, dim1 = slot rows
+// (stride NKV*256 B), dim2 = kv head (stride 256 B); box = [64][16][kv_group], 128-byte swizzle.
+int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        cudaDriverEntryPointQueryResult q;
+        void* fn = nullptr;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            set_cuda_error(e == cudaSuccess ? cudaErrorNotSupported : e, "cuTensorMapEncodeTiled entry point");
+            return NOVA_ERR_CUDA;
+        }
+        encode = (EncodeTiledFn)fn;
+    }
+    if (slot_rows <= 0 || slot_rows > 0x7fffffffLL) return NOVA_ERR_TOO_LARGE;
+    const cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)slot_rows, (cuuint64_t)n_kv_heads};
+    const cuuint64_t strides[2] = {(cuuint64_t)n_kv_heads * kHeadDim * 2, (cuuint64_t)kHeadDim * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)kKvBlock, (cuuint32_t)kv_group};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = encode(static_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pool, dims, strides,
+                              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+        return NOVA_ERR_CUDA;
+    }
+    return NOVA_OK;
+}
+
+int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
+    if (kv_dtype != NOVA_KV_F16 || !a.tmap_k || !a.tmap_v) return NOVA_ERR_UNSUPPORTED;
+    if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
+    if (a.n_heads % a.n_kv_heads || a.n_kv_heads % a.kv_group) return NOVA_ERR_INVALID;
+    if (a.n_heads / a.n_kv_heads > 8) return NOVA_ERR_UNSUPPORTED;
+    if ((int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
+    switch (a.kv_group) {
+        case 4: return launch_kvg<4>(a, n_ctas, s);
+        case 2: return launch_kvg<2>(a, n_ctas, s);
+        case 1: return launch_kvg<1>(a, n_ctas, s);
+        default: return NOVA_ERR_UNSUPPORTED;
+    }
+}
+
 }  // namespace novab

@@ -74,7 +74,7 @@ struct AttnLaunch {
     const float* q;              // [layers][S][NH][128] fp32, already rotated
     float* out;                  // [layers][S][NH][128]
     float* part;                 // partial slots [(C + rows)][heads_per_row][130]
-    unsigned int* tickets;       // [rows], zero before the first launch; self-resetting
+    unsigned int* tickets;       // [rows * kv_group], zero before the first launch; self-resetting
     int32_t* status;             // device status word (0 ok)
     int32_t n_sessions;
     int32_t layer0;              // first layer of the pools this launch reads
@@ -86,6 +86,8 @@ struct AttnLaunch {
     int64_t page_lo, page_hi;    // restrict every session to logical pages [lo, hi) (multi-GPU split); hi<0: all
     int32_t write_partial_only;  // 1: leave un-normalised (m,l,acc) rows in `out_part` instead of `out`
     float* out_part;             // [layers][S][NH][130]
+    const void* tmap_k;          // host pointers to the CUtensorMap of each pool (tensor-core kernel only)
+    const void* tmap_v;
 };
 
 constexpr int kMaxRowsSmem = 2048;   // (sessions x kv groups) prefix entries kept in shared memory
@@ -96,6 +98,7 @@ int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t 
 int attn_default_ctas_simt(int n_kv_heads);
 int attn_default_ctas_mma();
 bool attn_mma_built();
+int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group);
 int launch_part_merge(const AttnLaunch& a, int n_ctas, cudaStream_t s);
 int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s);
 

@@ -38,6 +38,9 @@ struct nova_engine {
     size_t elem_bytes = 0;
     int nb = 0, nblocks = 0;
     int kv_group = 0;
+    alignas(128) unsigned char tmap_k[128];   // CUtensorMap of each fp16 pool (tensor-core attention)
+    alignas(128) unsigned char tmap_v[128];
+    bool tmaps_ok = false;
     std::vector<SessionRec> sess;
     std::mutex mu;
 };
@@ -133,6 +136,8 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.fused_combine = 1;
     a.page_lo = 0;
     a.page_hi = -1;
+    a.tmap_k = e->tmaps_ok ? e->tmap_k : nullptr;
+    a.tmap_v = e->tmaps_ok ? e->tmap_v : nullptr;
 }
 
 int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
@@ -205,6 +210,11 @@ int nova_engine_create(const nova_engine_desc* desc, nova_engine** out) {
         set_cuda_error(ce, "engine allocation");
         nova_engine_destroy(e);
         return NOVA_ERR_CUDA;
+    }
+    if (d.kv_dtype == NOVA_KV_F16 && attn_mma_built()) {
+        const int64_t slot_rows = (int64_t)d.n_layers * e->nb * kKvBlock;
+        e->tmaps_ok = attn_make_tmap(e->tmap_k, e->pool_k, slot_rows, d.n_kv_heads, e->kv_group) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_v, e->pool_v, slot_rows, d.n_kv_heads, e->kv_group) == NOVA_OK;
     }
     int r = launch_rope_table(e->cs, e->sn, d.rope_positions, d.rope_theta, 0);   // Kernel::rope_table, model.cpp:119
     if (r == NOVA_OK && cudaDeviceSynchronize() != cudaSuccess) r = NOVA_ERR_CUDA;
@@ -501,8 +511,9 @@ int nova_batch_create(nova_engine* e, const int32_t* sessions, int n, nova_batch
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->d_n_past, (size_t)n * sizeof(int32_t));
     if (ce == cudaSuccess) ce = cudaMallocHost((void**)&b->h_n_past, (size_t)n * sizeof(int32_t));
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->part, part_floats * sizeof(float));
-    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->tickets, (size_t)rows * sizeof(unsigned int));
-    if (ce == cudaSuccess) ce = cudaMemset(b->tickets, 0, (size_t)rows * sizeof(unsigned int));
+    const size_t n_tickets = (size_t)rows * (size_t)e->kv_group;
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->tickets, n_tickets * sizeof(unsigned int));
+    if (ce == cudaSuccess) ce = cudaMemset(b->tickets, 0, n_tickets * sizeof(unsigned int));
     if (ce == cudaSuccess)
         ce = cudaMemcpy(b->d_slices, b->slices.data(), (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice);
     if (ce != cudaSuccess) {
@@ -552,7 +563,7 @@ int nova_batch_sync_positions(nova_batch* b, nova_stream_t s) {
 
 int nova_batch_set_kernel(nova_batch* b, int which) {
     if (!b || which < 0 || which > 1) return NOVA_ERR_INVALID;
-    if (which == 1 && (b->e->d.kv_dtype != NOVA_KV_F16 || !attn_mma_built())) return NOVA_ERR_UNSUPPORTED;
+    if (which == 1 && (b->e->d.kv_dtype != NOVA_KV_F16 || !b->e->tmaps_ok)) return NOVA_ERR_UNSUPPORTED;
     b->kernel = which;
     return NOVA_OK;
 }
