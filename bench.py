@@ -173,6 +173,11 @@ def run_ours(args):
     mode = {"layer": 1, "graph": 2, "fused": 0}[args.launch]
     ms_main, _, kv_main = timed(mode, K, W)
     launches = int(nv.lib.nova_launch_count() - launches0) * K // (K + W)
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"quick": True, "launch": args.launch, "ms_per_step": ms_main / K,
+                              "kv_gbs": kv_main / ms_main / 1e6, "gpu_launches": launches}))
+        return
     # the same K steps again with an event pair around every attention launch: the dominant kernel's own time
     ms_evt, attn_ms, kv_evt = timed(1 if mode == 2 else mode, K, W, time_attn=True)
     # all layers in one launch (the isolated path; legal because layer inputs are independent here)
@@ -367,6 +372,8 @@ def main():
                     help="layer: 2 launches per layer; graph: the same, replayed from a CUDA graph; fused: all layers per launch")
     ap.add_argument("--kernel", type=int, default=-1, help="-1 best available, 0 SIMT, 1 tensor-core")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true",
+                    help="only the main timed region (for profiler captures): no other modes, e2e or CPU baseline")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     _, _, world = dist_env()

@@ -100,6 +100,7 @@ SIGNATURES = {
     "nova_synth_key": (u64, [u64, u64, u64, u64]), "nova_synth_normal": (i32, [vp, sz, u64, u64, vp]),
     "nova_batch_create": (i32, [vp, c_i32p, i32, C.POINTER(vp)]), "nova_batch_destroy": (None, [vp]),
     "nova_batch_size": (i32, [vp]), "nova_batch_sync_positions": (i32, [vp, vp]),
+    "nova_batch_set_timeline": (i32, [vp, vp]),
     "nova_batch_set_kernel": (i32, [vp, i32]), "nova_batch_get_kernel": (i32, [vp]),
     "nova_batch_cow": (i32, [vp, vp]), "nova_batch_append": (i32, [vp, i32, vp, vp, vp, vp]),
     "nova_batch_attn": (i32, [vp, i32, vp, vp, vp]), "nova_batch_advance": (i32, [vp, vp]),

@@ -1,0 +1,156 @@
+// attn_combine.cu — log-sum-exp merge of split-K partials.  Replaces fa_combine_kernel
+// (src/kernel/attn.cu:163-191 of the reference): m = max m_c, l = sum l_c e^{m_c - m},
+// O = sum acc_c e^{m_c - m} / l, zero when l == 0, contributors taken in a fixed order.
+//
+// attn_combine_kernel follows either split kernel: one WARP per (row, query head) recomputes from
+// the work split (attn_plan.cuh) which CTAs contributed, loads all their (m, l) pairs at once
+// (one lane per contributor), then streams the partial accumulators with 16-byte loads that do
+// not depend on each other, so the whole merge costs a few L2 round trips instead of one per
+// contributor.  Rows covered by a single CTA were already written by the split kernel.
+#include "attn_plan.cuh"
+
+namespace novab {
+namespace {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__global__ void __launch_bounds__(128) attn_combine_kernel(AttnLaunch a, int n_ctas_split) {
+    __shared__ int s_prefix[kMaxRowsSmem + 1];
+    const int lane = (int)threadIdx.x & 31;
+    const int warp = (int)threadIdx.x >> 5;
+    const int KVG = a.kv_group;
+    const int G = a.n_heads / a.n_kv_heads;
+    const int n_groups = a.n_kv_heads / KVG;
+    const int heads_per_row = KVG * G;
+    plan_build_prefix(a, s_prefix, n_groups);
+    PlanView pv;
+    pv.prefix = s_prefix;
+    pv.rows_per_layer = a.n_sessions * n_groups;
+    pv.n_groups = n_groups;
+    pv.pages_per_layer = s_prefix[pv.rows_per_layer];
+    pv.pages_total = pv.pages_per_layer * a.n_layers;
+    pv.n_ctas = pv.pages_total < (int64_t)n_ctas_split ? (int)pv.pages_total : n_ctas_split;
+    if (pv.pages_total == 0) return;
+
+    const int64_t units = (int64_t)pv.rows_per_layer * a.n_layers * heads_per_row;
+    const size_t stride_c = (size_t)heads_per_row * kSlotW;
+    for (int64_t u = (int64_t)blockIdx.x * 4 + warp; u < units; u += (int64_t)gridDim.x * 4) {
+        const int64_t v = u / heads_per_row;
+        const int hr = (int)(u - v * heads_per_row);            // kv head in group * G + query head
+        const int row = (int)(v % pv.rows_per_layer);
+        if (s_prefix[row + 1] == s_prefix[row]) continue;        // no pages: written by the split kernel
+        const int ll = (int)(v / pv.rows_per_layer);
+        const int64_t row_begin = (int64_t)ll * pv.pages_per_layer + s_prefix[row];
+        const int64_t row_end = (int64_t)ll * pv.pages_per_layer + s_prefix[row + 1];
+        const int c_first = plan_owner(pv, row_begin), c_last = plan_owner(pv, row_end - 1);
+        const int n = c_last - c_first + 1;
+        if (n == 1) continue;                                     // written by the split kernel
+        const int s = row / n_groups, grp = row - s * n_groups;
+        const int64_t head = ((int64_t)ll * a.n_sessions + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
+        const float* base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
+
+        float M = -INFINITY;
+        for (int c0 = 0; c0 < n; c0 += 32) {
+            const int idx = c0 + lane;
+            if (idx < n) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)idx * stride_c));
+                if (ml.y > 0.f) M = fmaxf(M, ml.x);
+            }
+        }
+        M = warp_max(M);
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c0 = 0; c0 < n; c0 += 32) {
+            const int idx = c0 + lane;
+            float w = 0.f;
+            if (idx < n) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)idx * stride_c));
+                if (ml.y > 0.f) {
+                    w = __expf(ml.x - M);
+                    L = fmaf(ml.y, w, L);
+                }
+            }
+            const int cnt = n - c0 < 32 ? n - c0 : 32;
+            const float* src = base + (size_t)c0 * stride_c + 4 + 4 * lane;
+#pragma unroll 8
+            for (int i = 0; i < cnt; ++i) {
+                const float wi = __shfl_sync(0xffffffffu, w, i);
+                const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * stride_c));
+                acc.x = fmaf(x.x, wi, acc.x);
+                acc.y = fmaf(x.y, wi, acc.y);
+                acc.z = fmaf(x.z, wi, acc.z);
+                acc.w = fmaf(x.w, wi, acc.w);
+            }
+        }
+        L = warp_sum(L);
+        if (a.write_partial_only) {
+            float* op = a.out_part + head * kPartW;
+            if (lane == 0) { op[0] = M; op[1] = L; }
+            op[2 + 4 * lane + 0] = acc.x;
+            op[2 + 4 * lane + 1] = acc.y;
+            op[2 + 4 * lane + 2] = acc.z;
+            op[2 + 4 * lane + 3] = acc.w;
+        } else {
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =
+                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        }
+    }
+}
+
+// LSE merge of n_parts stacked caller-visible partial buffers [n_parts][n_rows][130] -> out
+// [n_rows][128], parts taken in index order (the multi-GPU merge after an all-gather).
+__global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restrict__ parts, int n_parts, int n_rows,
+                                                          float* __restrict__ out) {
+    const int row = (int)blockIdx.x;
+    const int d = (int)threadIdx.x;
+    if (row >= n_rows) return;
+    float M = -INFINITY;
+    for (int p = 0; p < n_parts; ++p) {
+        const float* pr = parts + ((size_t)p * n_rows + row) * kPartW;
+        if (pr[1] > 0.f) M = fmaxf(M, pr[0]);
+    }
+    float L = 0.f, A = 0.f;
+#pragma unroll 4
+    for (int p = 0; p < n_parts; ++p) {
+        const float* pr = parts + ((size_t)p * n_rows + row) * kPartW;
+        const float lp = pr[1], mp = pr[0], ap = pr[2 + d];
+        if (lp > 0.f) {
+            const float w = __expf(mp - M);
+            L = fmaf(lp, w, L);
+            A = fmaf(ap, w, A);
+        }
+    }
+    out[(size_t)row * kHeadDim + d] = L > 0.f ? A / L : 0.f;
+}
+
+}  // namespace
+
+int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
+    if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
+    const int G = a.n_heads / a.n_kv_heads;
+    const int64_t units = (int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) * a.n_layers * (int64_t)(a.kv_group * G);
+    int64_t ctas = (units + 3) / 4;
+    if (ctas > 148 * 8) ctas = 148 * 8;
+    attn_combine_kernel<<<(unsigned)ctas, 128, 0, s>>>(a, n_ctas_split);
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s) {
+    if (n_rows <= 0 || n_parts <= 0) return NOVA_OK;
+    lse_combine_kernel<<<(unsigned)n_rows, kHeadDim, 0, s>>>(parts, n_parts, n_rows, out);
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+}  // namespace novab

@@ -17,8 +17,8 @@
 //     512 bytes of KV, more than the SM's FP32 pipes deliver at 20+ B/clk.
 //   * Full/empty mbarriers hand the stages over; every wait is bounded by a wall-clock limit and
 //     reports NOVA_ERR_TIMEOUT through the status word instead of spinning forever.
-//   * Work split and partial slots are those of attn_plan.cuh; the warp that arrives last at a
-//     (row, kv head) ticket merges that head group's partials - no CTA-wide barrier, no spinning.
+//   * Work split and partial slots are those of attn_plan.cuh; rows shared by several CTAs are
+//     merged by the combine kernel that follows (attn_combine.cu) - no flags between CTAs.
 #include <cuda.h>
 
 #include "attn_plan.cuh"
@@ -131,6 +131,8 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const int heads_per_row = KVG * G;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
+    unsigned long long* tl = a.timeline ? a.timeline + (size_t)blockIdx.x * 8 : nullptr;
+    if (tl && threadIdx.x == 0) tl[0] = now_ns();
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(smem_u32(&s_full[i]), 1);
@@ -179,10 +181,13 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
 
     const int64_t lo = plan_cta_begin(pv, (int)blockIdx.x);
     const int64_t hi = plan_cta_begin(pv, (int)blockIdx.x + 1);
+    if (tl && threadIdx.x == 0) tl[1] = now_ns();
 
     // ------------------------------------------------------------------ producer warp
     if (warp == KVG) {
         if (lane != 0) return;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
         uint32_t it = 0;
         for (int64_t pos = lo; pos < hi;) {
             const Segment sg = plan_segment(pv, pos, hi);
@@ -219,8 +224,10 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                 tma_load_3d(dst + Cfg::kBoxBytes, &tmk, 64, c1, c2, bar);
                 tma_load_3d(dst + 2 * Cfg::kBoxBytes, &tmv, 0, c1, c2, bar);
                 tma_load_3d(dst + 3 * Cfg::kBoxBytes, &tmv, 64, c1, c2, bar);
+                if (tl && it == 0) tl[2] = now_ns();
             }
         }
+        if (tl) tl[3] = now_ns();
         return;
     }
 
@@ -271,6 +278,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                 if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
                 return;
             }
+            if (tl && threadIdx.x == 0 && it == 0) tl[4] = now_ns();
             const int kcount = s_kcount[stage];
             const uint32_t sk = stage0 + (uint32_t)stage * Cfg::kStageBytes;
             const uint32_t sv = sk + 2 * Cfg::kBoxBytes;
@@ -340,7 +348,8 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
         }
 
-        // ---- segment done: row sums, then direct output or partial + ticket
+        // ---- segment done: row sums, then direct output or a partial slot
+        if (tl && threadIdx.x == 0) tl[5] = now_ns();
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int n_contrib = sg.c_last - sg.c_first + 1;
@@ -362,74 +371,29 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             }
             continue;
         }
+        // several CTAs share this row: leave (m, l, acc) in this CTA's slot for the combine kernel
         if (g < G) {
-            float* pr = a.part + ((size_t)((int64_t)blockIdx.x + sg.row_id) * heads_per_row + (size_t)(w * G + g)) * kPartW;
-            if (t == 0) { pr[0] = m * (1.f / kLog2e); pr[1] = l; }
+            float* pr = a.part + ((size_t)((int64_t)blockIdx.x + sg.row_id) * heads_per_row + (size_t)(w * G + g)) * kSlotW;
+            if (t == 0) *reinterpret_cast<float2*>(pr) = make_float2(m * (1.f / kLog2e), l);
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-                *reinterpret_cast<float2*>(pr + 2 + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+                *reinterpret_cast<float2*>(pr + 4 + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
         }
-        // Each kv head's rows are merged by the LAST WARP to arrive for them: a ticket per
-        // (row, kv head in group), no CTA-wide barrier.
-        __threadfence();
-        __syncwarp();
-        unsigned old = 0;
-        if (lane == 0) old = atomicAdd(a.tickets + sg.row_id * KVG + w, 1u);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old == (unsigned)(n_contrib - 1)) {
-            __threadfence();
-            if (g < G) {
-                float M = -INFINITY;
-                for (int c = sg.c_first; c <= sg.c_last; ++c) {
-                    const float* pr = a.part + ((size_t)(c + sg.row_id) * heads_per_row + (size_t)(w * G + g)) * kPartW;
-                    if (pr[1] > 0.f) M = fmaxf(M, pr[0]);
-                }
-                float L = 0.f;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = 0.f;
-                for (int c = sg.c_first; c <= sg.c_last; ++c) {
-                    const float* pr = a.part + ((size_t)(c + sg.row_id) * heads_per_row + (size_t)(w * G + g)) * kPartW;
-                    const float lc = pr[1];
-                    if (lc > 0.f) {
-                        const float wt = __expf(pr[0] - M);
-                        L = fmaf(lc, wt, L);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float2 x = *reinterpret_cast<const float2*>(pr + 2 + 8 * j + 2 * t);
-                            o[j][0] = fmaf(x.x, wt, o[j][0]);
-                            o[j][1] = fmaf(x.y, wt, o[j][1]);
-                        }
-                    }
-                }
-                if (a.write_partial_only) {
-                    float* op = a.out_part + (head0 + g) * kPartW;
-                    if (t == 0) { op[0] = M; op[1] = L; }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        *reinterpret_cast<float2*>(op + 2 + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
-                } else {
-                    const float inv = L > 0.f ? 1.f / L : 0.f;
-                    float* op = a.out + (head0 + g) * kHeadDim;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        *reinterpret_cast<float2*>(op + 8 * j + 2 * t) = make_float2(o[j][0] * inv, o[j][1] * inv);
-                }
-            }
-            if (lane == 0) a.tickets[sg.row_id * KVG + w] = 0u;
-        }
+        if (tl && threadIdx.x == 0) tl[6] = now_ns();
     }
 }
 
 template <int KVG>
 int launch_kvg(const AttnLaunch& a, int n_ctas, cudaStream_t s) {
     using Cfg = MmaCfg<KVG>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {};          // the attribute is per device
+    int dev = 0;
+    NOVA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<KVG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            Cfg::kSmemBytes));
-        attr_set = true;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    if (n_ctas <= 0) n_ctas = 148 * Cfg::kCtasPerSm;
     const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k);
     const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v);
     attn_mma_kernel<KVG><<<(unsigned)n_ctas, Cfg::kThreads, Cfg::kSmemBytes, s>>>(a, *tk, *tv);
@@ -476,6 +440,12 @@ int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads,
     return NOVA_OK;
 }
 
+int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
+    if (n_ctas > 0) return n_ctas;
+    const int per_sm = a.kv_group >= 4 ? 1 : 4 / a.kv_group;
+    return 148 * per_sm;
+}
+
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
     if (kv_dtype != NOVA_KV_F16 || !a.tmap_k || !a.tmap_v) return NOVA_ERR_UNSUPPORTED;
     if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
@@ -483,9 +453,9 @@ int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t 
     if (a.n_heads / a.n_kv_heads > 8) return NOVA_ERR_UNSUPPORTED;
     if ((int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
     switch (a.kv_group) {
-        case 4: return launch_kvg<4>(a, n_ctas, s);
-        case 2: return launch_kvg<2>(a, n_ctas, s);
-        case 1: return launch_kvg<1>(a, n_ctas, s);
+        case 4: return launch_kvg<4>(a, attn_split_ctas_mma(a, n_ctas), s);
+        case 2: return launch_kvg<2>(a, attn_split_ctas_mma(a, n_ctas), s);
+        case 1: return launch_kvg<1>(a, attn_split_ctas_mma(a, n_ctas), s);
         default: return NOVA_ERR_UNSUPPORTED;
     }
 }

@@ -8,8 +8,8 @@
 // dims; a key costs G 4-term dot partials, one transposing butterfly (9 shuffles + G
 // broadcasts instead of 5G), an online softmax in the exp2 domain and 4G fp32 FMAs on V.
 // Pages are walked straight from global memory with 8/16-byte loads, two keys in flight.
-// Work is cut stream-K style over pages (attn_plan.cuh); the last CTA to arrive at a row
-// merges its partials — no spinning anywhere.
+// Work is cut stream-K style over pages (attn_plan.cuh); rows split over several CTAs leave
+// partials for the combine kernel (attn_combine.cu) — no flags, no spinning anywhere.
 //
 // This is the fp32-accumulating reference form of the product: it serves fp32 pools (the
 // reference's own format) and is the correctness anchor for the tensor-core kernel.
@@ -77,43 +77,9 @@ struct HeadState {
     }
 };
 
-// Merge the partial rows of slots [c_first .. c_last] for one head (fixed order), then
-// either normalise into `out` or leave (m, l, acc) in `out_part`.
-__device__ __forceinline__ void merge_head(const float* part, int heads_per_row, int head_in_row, int64_t row_id,
-                                           int c_first, int c_last, int lane, float* out, float* out_part) {
-    float M = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) {
-        const float* pr = part + ((size_t)(c + row_id) * heads_per_row + head_in_row) * kPartW;
-        if (pr[1] > 0.f) M = fmaxf(M, pr[0]);
-    }
-    float L = 0.f, A[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int c = c_first; c <= c_last; ++c) {
-        const float* pr = part + ((size_t)(c + row_id) * heads_per_row + head_in_row) * kPartW;
-        const float lc = pr[1];
-        if (lc > 0.f) {
-            const float w = __expf(pr[0] - M);
-            L = fmaf(lc, w, L);
-            // a row is 130 floats, so acc (at pr+2) is only 8-byte aligned: two float2 loads
-            const float2 a0 = *reinterpret_cast<const float2*>(pr + 2 + 4 * lane);
-            const float2 a1 = *reinterpret_cast<const float2*>(pr + 4 + 4 * lane);
-            A[0] = fmaf(a0.x, w, A[0]); A[1] = fmaf(a0.y, w, A[1]);
-            A[2] = fmaf(a1.x, w, A[2]); A[3] = fmaf(a1.y, w, A[3]);
-        }
-    }
-    if (out_part) {
-        if (lane == 0) { out_part[0] = M; out_part[1] = L; }
-#pragma unroll
-        for (int d = 0; d < 4; ++d) out_part[2 + 4 * lane + d] = A[d];
-    } else {
-        const float inv = L > 0.f ? 1.f / L : 0.f;
-        *reinterpret_cast<float4*>(out + 4 * lane) = make_float4(A[0] * inv, A[1] * inv, A[2] * inv, A[3] * inv);
-    }
-}
-
 template <typename KvT, int G>
 __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
     __shared__ int s_prefix[kMaxRowsSmem + 1];
-    __shared__ int s_last;
 
     const int lane = (int)threadIdx.x & 31;
     const int warp = (int)threadIdx.x >> 5;
@@ -149,7 +115,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
                     float* op = a.out_part + head * kPartW;
                     if (lane == 0) { op[0] = -INFINITY; op[1] = 0.f; }
                     for (int d = 0; d < 4; ++d) op[2 + 4 * lane + d] = 0.f;
-                } else if (a.fused_combine) {
+                } else {
                     *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
@@ -237,8 +203,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
         }
 
         const int n_contrib = sg.c_last - sg.c_first + 1;
-        const bool direct = a.fused_combine && n_contrib == 1;
-        if (direct) {
+        if (n_contrib == 1) {
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 if (a.write_partial_only) {
@@ -254,96 +219,17 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
             }
             continue;
         }
-        // partial slot (cta + row): rows [heads_per_row][130], m in natural-log units
+        // partial slot (cta + row): rows [heads_per_row][kSlotW], m in natural-log units
         {
-            float* slot_base = a.part + (size_t)((int64_t)blockIdx.x + sg.row_id) * heads_per_row * kPartW;
+            float* slot_base = a.part + (size_t)((int64_t)blockIdx.x + sg.row_id) * heads_per_row * kSlotW;
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                float* pr = slot_base + (size_t)(warp * G + g) * kPartW;
-                if (lane == 0) { pr[0] = st.m[g] * (1.f / kLog2e); pr[1] = st.l[g]; }
-                *reinterpret_cast<float2*>(pr + 2 + 4 * lane) = make_float2(st.acc[g][0], st.acc[g][1]);
-                *reinterpret_cast<float2*>(pr + 4 + 4 * lane) = make_float2(st.acc[g][2], st.acc[g][3]);
+                float* pr = slot_base + (size_t)(warp * G + g) * kSlotW;
+                if (lane == 0) *reinterpret_cast<float2*>(pr) = make_float2(st.m[g] * (1.f / kLog2e), st.l[g]);
+                *reinterpret_cast<float4*>(pr + 4 + 4 * lane) = make_float4(st.acc[g][0], st.acc[g][1], st.acc[g][2], st.acc[g][3]);
             }
         }
-        if (!a.fused_combine) continue;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence();
-            const unsigned old = atomicAdd(a.tickets + sg.row_id, 1u);
-            s_last = (old == (unsigned)(n_contrib - 1));
-        }
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-#pragma unroll
-            for (int g = 0; g < G; ++g)
-                merge_head(a.part, heads_per_row, warp * G + g, sg.row_id, sg.c_first, sg.c_last, lane,
-                           a.write_partial_only ? nullptr : a.out + (head0 + g) * kHeadDim,
-                           a.write_partial_only ? a.out_part + (head0 + g) * kPartW : nullptr);
-            if (threadIdx.x == 0) a.tickets[sg.row_id] = 0u;
-        }
-        __syncthreads();   // s_last is rewritten by the next segment
     }
-}
-
-// Separate merge for launches without tickets (caller-provided scratch): one CTA per row.
-template <int G>
-__global__ void __launch_bounds__(128) part_merge_kernel(AttnLaunch a, int n_ctas_split) {
-    __shared__ int s_prefix[kMaxRowsSmem + 1];
-    const int lane = (int)threadIdx.x & 31;
-    const int warp = (int)threadIdx.x >> 5;
-    const int KVG = a.kv_group;
-    const int n_groups = a.n_kv_heads / KVG;
-    plan_build_prefix(a, s_prefix, n_groups);
-    PlanView pv;
-    pv.prefix = s_prefix;
-    pv.rows_per_layer = a.n_sessions * n_groups;
-    pv.n_groups = n_groups;
-    pv.pages_per_layer = s_prefix[pv.rows_per_layer];
-    pv.pages_total = pv.pages_per_layer * a.n_layers;
-    pv.n_ctas = pv.pages_total < (int64_t)n_ctas_split ? (int)pv.pages_total : n_ctas_split;
-    const int64_t rows_total = (int64_t)pv.rows_per_layer * a.n_layers;
-    for (int64_t v = blockIdx.x; v < rows_total; v += gridDim.x) {
-        const int row = (int)(v % pv.rows_per_layer);
-        const int ll = (int)(v / pv.rows_per_layer);
-        const int s = row / n_groups, g = row - s * n_groups;
-        const int kvh = g * KVG + warp;
-        const int64_t head0 = ((int64_t)ll * a.n_sessions + s) * a.n_heads + (int64_t)kvh * G;
-        if (s_prefix[row + 1] == s_prefix[row]) {
-            for (int h = 0; h < G; ++h)
-                *reinterpret_cast<float4*>(a.out + (head0 + h) * kHeadDim + 4 * lane) = make_float4(0.f, 0.f, 0.f, 0.f);
-            continue;
-        }
-        const int64_t row_begin = (int64_t)ll * pv.pages_per_layer + s_prefix[row];
-        const int64_t row_end = (int64_t)ll * pv.pages_per_layer + s_prefix[row + 1];
-        const int c_first = plan_owner(pv, row_begin), c_last = plan_owner(pv, row_end - 1);
-        for (int h = 0; h < G; ++h)
-            merge_head(a.part, KVG * G, warp * G + h, v, c_first, c_last, lane, a.out + (head0 + h) * kHeadDim, nullptr);
-    }
-}
-
-// LSE merge of n_parts stacked partial buffers [n_parts][n_rows][130] -> out [n_rows][128],
-// parts taken in index order (fa_combine_kernel's arithmetic, src/kernel/attn.cu:169-190).
-__global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restrict__ parts, int n_parts, int n_rows,
-                                                          float* __restrict__ out) {
-    const int row = (int)blockIdx.x;
-    const int d = (int)threadIdx.x;
-    if (row >= n_rows) return;
-    float M = -INFINITY;
-    for (int p = 0; p < n_parts; ++p) {
-        const float* pr = parts + ((size_t)p * n_rows + row) * kPartW;
-        if (pr[1] > 0.f) M = fmaxf(M, pr[0]);
-    }
-    float L = 0.f, A = 0.f;
-    for (int p = 0; p < n_parts; ++p) {
-        const float* pr = parts + ((size_t)p * n_rows + row) * kPartW;
-        if (pr[1] > 0.f) {
-            const float w = __expf(pr[0] - M);
-            L = fmaf(pr[1], w, L);
-            A = fmaf(pr[2 + d], w, A);
-        }
-    }
-    out[(size_t)row * kHeadDim + d] = L > 0.f ? A / L : 0.f;
 }
 
 template <typename KvT>
@@ -366,40 +252,22 @@ int attn_default_ctas_simt(int n_kv_heads) {
     return 148 * (16 / kvg);
 }
 
+int attn_split_ctas_simt(const AttnLaunch& a, int n_ctas) {
+    return n_ctas > 0 ? n_ctas : attn_default_ctas_simt(a.n_kv_heads);
+}
+
 int launch_attn_simt(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
     if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
     if (a.n_heads % a.n_kv_heads || a.kv_group < 1 || a.kv_group > 4 || a.n_kv_heads % a.kv_group)
         return NOVA_ERR_INVALID;
     if ((int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
-    if (n_ctas <= 0) n_ctas = attn_default_ctas_simt(a.n_kv_heads);
+    n_ctas = attn_split_ctas_simt(a, n_ctas);
     const int G = a.n_heads / a.n_kv_heads;
     int rc;
     if (kv_dtype == NOVA_KV_F16) rc = launch_simt_g<__half>(a, G, n_ctas, s);
     else if (kv_dtype == NOVA_KV_F32) rc = launch_simt_g<float>(a, G, n_ctas, s);
     else return NOVA_ERR_UNSUPPORTED;
     if (rc != NOVA_OK) return rc;
-    NOVA_LAUNCH_CHECK();
-    return NOVA_OK;
-}
-
-int launch_part_merge(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
-    const int G = a.n_heads / a.n_kv_heads;
-    const int64_t rows = (int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) * a.n_layers;
-    const unsigned grid = (unsigned)(rows < 148 * 8 ? rows : 148 * 8);
-    const unsigned threads = 32u * (unsigned)a.kv_group;
-    switch (G) {
-#define NOVA_CASE(g) case g: part_merge_kernel<g><<<grid, threads, 0, s>>>(a, n_ctas_split); break;
-        NOVA_CASE(1) NOVA_CASE(2) NOVA_CASE(4) NOVA_CASE(5) NOVA_CASE(6) NOVA_CASE(7) NOVA_CASE(8)
-#undef NOVA_CASE
-        default: return NOVA_ERR_UNSUPPORTED;
-    }
-    NOVA_LAUNCH_CHECK();
-    return NOVA_OK;
-}
-
-int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s) {
-    if (n_rows <= 0 || n_parts <= 0) return NOVA_OK;
-    lse_combine_kernel<<<(unsigned)n_rows, kHeadDim, 0, s>>>(parts, n_parts, n_rows, out);
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }

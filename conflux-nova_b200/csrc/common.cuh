@@ -13,7 +13,8 @@ namespace novab {
 constexpr int kHeadDim = 128;   // the only head_dim built (every model of the reference uses 128)
 constexpr int kKvBlock = 16;    // tokens per page (the reference's default NOVA_KV_BLOCK)
 constexpr int kKvShift = 4;
-constexpr int kPartW = kHeadDim + 2;   // partial row: m, l, acc[128]  (src/kernel/attn.cu:150-158)
+constexpr int kPartW = kHeadDim + 2;   // partial row handed to callers: m, l, acc[128]  (src/kernel/attn.cu:150-158)
+constexpr int kSlotW = kHeadDim + 4;   // the same row inside the split-K scratch: m, l, 2 pad, acc[128] (acc 16-byte aligned)
 // 1/sqrt(128), the literal the reference uses (src/kernel/attn.cu:21)
 constexpr float kAttnScale = 0.08838834764831845f;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -60,8 +61,9 @@ template <> struct KvTraits<__half> {
 // are ceil(n_keys/16).  All pages of all rows of the launch form one line of P pages; CTA c
 // owns [floor(c*P/C), floor((c+1)*P/C)).  A CTA whose range crosses a row boundary produces
 // one partial per row it touches; the (CTA, row) pairs form a chain, so `c + row` names a
-// unique partial slot.  The CTA that is last to arrive at a row (atomic ticket) merges the
-// row's partials in CTA order and writes the normalised output.
+// unique partial slot.  A row that one CTA covers alone is normalised and written at once; the
+// others are merged, in CTA order, by the combine kernel that follows the split kernel
+// (the reference's split + combine pair, src/kernel/attn.cu:498-512).
 struct AttnLaunch {
     const void* pool_k;          // [L][NB][16][NKV][128]
     const void* pool_v;
@@ -73,8 +75,7 @@ struct AttnLaunch {
     int32_t keys_imm;
     const float* q;              // [layers][S][NH][128] fp32, already rotated
     float* out;                  // [layers][S][NH][128]
-    float* part;                 // partial slots [(C + rows)][heads_per_row][130]
-    unsigned int* tickets;       // [rows * kv_group], zero before the first launch; self-resetting
+    float* part;                 // partial slots [(C + rows)][heads_per_row][kSlotW]
     int32_t* status;             // device status word (0 ok)
     int32_t n_sessions;
     int32_t layer0;              // first layer of the pools this launch reads
@@ -82,12 +83,12 @@ struct AttnLaunch {
     int32_t nb;                  // physical pages per layer
     int32_t n_heads, n_kv_heads;
     int32_t kv_group;            // kv heads handled by one CTA (<= 4)
-    int32_t fused_combine;       // 1: last arriver merges; 0: every partial is left in `part`
     int64_t page_lo, page_hi;    // restrict every session to logical pages [lo, hi) (multi-GPU split); hi<0: all
     int32_t write_partial_only;  // 1: leave un-normalised (m,l,acc) rows in `out_part` instead of `out`
     float* out_part;             // [layers][S][NH][130]
     const void* tmap_k;          // host pointers to the CUtensorMap of each pool (tensor-core kernel only)
     const void* tmap_v;
+    unsigned long long* timeline;   // optional [n_ctas][8] globaltimer stamps (profiling aid), or nullptr
 };
 
 constexpr int kMaxRowsSmem = 2048;   // (sessions x kv groups) prefix entries kept in shared memory
@@ -99,7 +100,9 @@ int attn_default_ctas_simt(int n_kv_heads);
 int attn_default_ctas_mma();
 bool attn_mma_built();
 int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group);
-int launch_part_merge(const AttnLaunch& a, int n_ctas, cudaStream_t s);
+int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s);   // after either split kernel
+int attn_split_ctas_simt(const AttnLaunch& a, int n_ctas);
+int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas);
 int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s);
 
 // rope / append / page utilities (rope_append.cu)

@@ -53,12 +53,12 @@ struct nova_batch {
     int32_t* d_n_past = nullptr;
     int32_t* h_n_past = nullptr;     // pinned staging
     float* part = nullptr;
-    unsigned int* tickets = nullptr;
     int kernel = 0;                  // 0 SIMT, 1 tensor-core
     // staging for the host-buffer step and the graph replay
     float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
     cudaGraphExec_t graph = nullptr;   // one per-layer decode step on the staging buffers
     int graph_kernel = -1;
+    unsigned long long* timeline = nullptr;   // caller-owned profiling buffer, see nova_batch_set_timeline
     std::vector<cudaEvent_t> ev;       // event pool for per-launch timing
 };
 
@@ -126,23 +126,31 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.n_past = b->d_n_past;
     a.keys_add = 1;
     a.part = b->part;
-    a.tickets = b->tickets;
     a.status = e->status;
     a.n_sessions = b->n;
     a.nb = e->nb;
     a.n_heads = e->d.n_heads;
     a.n_kv_heads = e->d.n_kv_heads;
     a.kv_group = e->kv_group;
-    a.fused_combine = 1;
     a.page_lo = 0;
     a.page_hi = -1;
     a.tmap_k = e->tmaps_ok ? e->tmap_k : nullptr;
     a.tmap_v = e->tmaps_ok ? e->tmap_v : nullptr;
+    a.timeline = b->timeline;
 }
 
+// Split kernel, then the merge of the rows that more than one CTA worked on.
 int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
-    if (b->kernel == 1) return launch_attn_mma(a, b->e->d.kv_dtype, 0, s);
-    return launch_attn_simt(a, b->e->d.kv_dtype, 0, s);
+    int rc, ctas;
+    if (b->kernel == 1) {
+        ctas = attn_split_ctas_mma(a, 0);
+        rc = launch_attn_mma(a, b->e->d.kv_dtype, ctas, s);
+    } else {
+        ctas = attn_split_ctas_simt(a, 0);
+        rc = launch_attn_simt(a, b->e->d.kv_dtype, ctas, s);
+    }
+    if (rc != NOVA_OK) return rc;
+    return launch_attn_combine(a, ctas, s);
 }
 
 void fill_append(const nova_batch* b, AppendLaunch& a) {
@@ -448,18 +456,17 @@ int nova_launch_attn_decode_paged(const nova_kv_shape* sh, const float* q, const
     a.n_sessions = 1; a.layer0 = layer; a.n_layers = 1; a.nb = nb;
     a.n_heads = sh->n_heads; a.n_kv_heads = sh->n_kv_heads;
     a.kv_group = kv_group_of(sh->n_kv_heads);
-    a.fused_combine = 0;      // the caller's scratch is not zeroed: separate merge, no tickets
     a.page_lo = 0; a.page_hi = -1;
-    // The scratch holds NH*32 partial rows = 32*NH/(kv_group*G) slots; slot index = cta + row.
+    // The caller's scratch (NH*32*(HD+2) floats) holds so many partial slots; slot index = cta + row.
     const int heads_per_row = a.kv_group * (sh->n_heads / sh->n_kv_heads);
     const int rows = sh->n_kv_heads / a.kv_group;
-    int ctas = (sh->n_heads * 32) / heads_per_row - rows;
+    int ctas = (int)(nova_attn_scratch_floats(sh) / ((size_t)heads_per_row * kSlotW)) - rows;
     const int want = attn_default_ctas_simt(sh->n_kv_heads);
     if (ctas > want) ctas = want;
     if (ctas < 1) return NOVA_ERR_UNSUPPORTED;
     int rc = launch_attn_simt(a, sh->kv_dtype, ctas, (cudaStream_t)s);
     if (rc != NOVA_OK) return rc;
-    return launch_part_merge(a, ctas, (cudaStream_t)s);
+    return launch_attn_combine(a, ctas, (cudaStream_t)s);
 }
 
 int nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim, float* out, nova_stream_t s) {
@@ -505,15 +512,12 @@ int nova_batch_create(nova_engine* e, const int32_t* sessions, int n, nova_batch
     NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
     const int64_t rows = (int64_t)e->d.n_layers * n * (e->d.n_kv_heads / e->kv_group);
     const int heads_per_row = e->kv_group * (e->d.n_heads / e->d.n_kv_heads);
-    const size_t part_floats = (size_t)(rows + kMaxSplitCtas) * heads_per_row * kPartW;
+    const size_t part_floats = (size_t)(rows + kMaxSplitCtas) * heads_per_row * kSlotW;
     cudaError_t ce = cudaSuccess;
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->d_slices, (size_t)n * sizeof(int32_t));
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->d_n_past, (size_t)n * sizeof(int32_t));
     if (ce == cudaSuccess) ce = cudaMallocHost((void**)&b->h_n_past, (size_t)n * sizeof(int32_t));
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->part, part_floats * sizeof(float));
-    const size_t n_tickets = (size_t)rows * (size_t)e->kv_group;
-    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->tickets, n_tickets * sizeof(unsigned int));
-    if (ce == cudaSuccess) ce = cudaMemset(b->tickets, 0, n_tickets * sizeof(unsigned int));
     if (ce == cudaSuccess)
         ce = cudaMemcpy(b->d_slices, b->slices.data(), (size_t)n * sizeof(int32_t), cudaMemcpyHostToDevice);
     if (ce != cudaSuccess) {
@@ -537,7 +541,6 @@ void nova_batch_destroy(nova_batch* b) {
     cudaFree(b->d_n_past);
     cudaFreeHost(b->h_n_past);
     cudaFree(b->part);
-    cudaFree(b->tickets);
     cudaFree(b->dq);
     cudaFree(b->dk);
     cudaFree(b->dv);
@@ -565,6 +568,11 @@ int nova_batch_set_kernel(nova_batch* b, int which) {
     if (!b || which < 0 || which > 1) return NOVA_ERR_INVALID;
     if (which == 1 && (b->e->d.kv_dtype != NOVA_KV_F16 || !b->e->tmaps_ok)) return NOVA_ERR_UNSUPPORTED;
     b->kernel = which;
+    return NOVA_OK;
+}
+int nova_batch_set_timeline(nova_batch* b, void* dev_buf) {
+    if (!b) return NOVA_ERR_INVALID;
+    b->timeline = static_cast<unsigned long long*>(dev_buf);
     return NOVA_OK;
 }
 int nova_batch_get_kernel(const nova_batch* b) { return b ? b->kernel : NOVA_ERR_INVALID; }
@@ -764,7 +772,7 @@ int nova_batch_run_steps(nova_batch* b, int n_steps, float* q, float* k, const f
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk, ki, kv_elems * 4, cudaMemcpyDeviceToDevice, st));
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv, vi, kv_elems * 4, cudaMemcpyDeviceToDevice, st));
             NOVA_CUDA_TRY(cudaGraphLaunch(b->graph, st));
-            count_launch(2 * e->d.n_layers + 1);
+            count_launch(3 * e->d.n_layers + 1);
             NOVA_CUDA_TRY(cudaMemcpyAsync(qi, b->dq, q_elems * 4, cudaMemcpyDeviceToDevice, st));   // q rotated in place
             NOVA_CUDA_TRY(cudaMemcpyAsync(oi, b->dout, q_elems * 4, cudaMemcpyDeviceToDevice, st));
             for (int j = 0; j < b->n; ++j) {

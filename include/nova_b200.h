@@ -257,6 +257,11 @@ int  nova_batch_sync_positions(nova_batch* b, nova_stream_t s);
 /* Select the attention kernel: 0 = SIMT, 1 = tensor-core (mma + bulk-copy pipeline, fp16 KV). */
 int  nova_batch_set_kernel(nova_batch* b, int which);
 int  nova_batch_get_kernel(const nova_batch* b);
+/* Profiling aid (tensor-core kernel): dev_buf = 148*8 uint64 in device memory, or NULL to switch off.
+ * Every CTA of the next attention launches leaves %globaltimer stamps there: [0] start, [1] work split
+ * known, [2] first page requested, [3] last page requested, [4] first page landed, [5] last page
+ * consumed, [6] results/partials written. */
+int  nova_batch_set_timeline(nova_batch* b, void* dev_buf);
 
 /* For each session s of the batch: session_cow(s, n_past, 1).  One kernel copies
  * all pages that had to be un-shared.  Returns the number of COW copies. */
