@@ -122,6 +122,12 @@ def run_ours(args):
     if kernel < 0:
         kernel = 1 if nv.lib.nova_batch_set_kernel(batch.h, 1) == nv.OK else 0
     batch.set_kernel(kernel)
+    fused = bool(kernel == 1 and not args.no_fused_append)
+    if fused:
+        batch.set_fused_append(1)
+        batch.set_pdl(0 if args.no_pdl else 1)
+    if args.row_setup >= 0:
+        batch.set_row_setup_pages(args.row_setup)
     stream = nv.Stream()
     nq, nk = work.step_input_sizes()
     S, L = len(work.sessions), eng.L
@@ -175,7 +181,7 @@ def run_ours(args):
     launches = int(nv.lib.nova_launch_count() - launches0) * K // (K + W)
     if args.quick:
         if rank == 0:
-            print(json.dumps({"quick": True, "launch": args.launch, "ms_per_step": ms_main / K,
+            print(json.dumps({"quick": True, "launch": args.launch, "fused_append": fused, "pdl": bool(fused and not args.no_pdl), "ms_per_step": ms_main / K,
                               "kv_gbs": kv_main / ms_main / 1e6, "gpu_launches": launches}))
         return
     # the same K steps again with an event pair around every attention launch: the dominant kernel's own time
@@ -241,7 +247,7 @@ def run_ours(args):
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {w['text']}; per GPU", "sessions_per_gpu": S,
                        "context_tokens": lens, "layers": L, "kv_dtype": "fp16", "page_tokens": 16,
-                       "launch": args.launch, "attention_kernel": "mma" if kernel == 1 else "simt",
+                       "launch": args.launch, "attention_kernel": "mma" if kernel == 1 else "simt", "fused_append": fused, "pdl": bool(fused and not args.no_pdl),
                        "l2": "inputs larger than L2 (KV read per step >> 126 MB)"},
             "batch_steps_per_s": K / (ms_main / 1e3),
             "kv_gbs": kv_main_all / ms_main / 1e6,
@@ -371,6 +377,10 @@ def main():
     ap.add_argument("--launch", default="graph", choices=["layer", "graph", "fused"],
                     help="layer: 2 launches per layer; graph: the same, replayed from a CUDA graph; fused: all layers per launch")
     ap.add_argument("--kernel", type=int, default=-1, help="-1 best available, 0 SIMT, 1 tensor-core")
+    ap.add_argument("--no-fused-append", action="store_true",
+                    help="keep RoPE+append as its own launch instead of doing it inside the attention launch")
+    ap.add_argument("--row-setup", type=int, default=-1, help="work-split weight of a session start, in pages")
+    ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true",
                     help="only the main timed region (for profiler captures): no other modes, e2e or CPU baseline")

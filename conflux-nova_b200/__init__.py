@@ -101,6 +101,8 @@ SIGNATURES = {
     "nova_batch_create": (i32, [vp, c_i32p, i32, C.POINTER(vp)]), "nova_batch_destroy": (None, [vp]),
     "nova_batch_size": (i32, [vp]), "nova_batch_sync_positions": (i32, [vp, vp]),
     "nova_batch_set_timeline": (i32, [vp, vp]),
+    "nova_batch_set_pdl": (i32, [vp, i32]), "nova_batch_set_row_setup_pages": (i32, [vp, i32]),
+    "nova_batch_set_fused_append": (i32, [vp, i32]), "nova_batch_append_attn": (i32, [vp, i32, vp, vp, vp, vp, vp]),
     "nova_batch_set_kernel": (i32, [vp, i32]), "nova_batch_get_kernel": (i32, [vp]),
     "nova_batch_cow": (i32, [vp, vp]), "nova_batch_append": (i32, [vp, i32, vp, vp, vp, vp]),
     "nova_batch_attn": (i32, [vp, i32, vp, vp, vp]), "nova_batch_advance": (i32, [vp, vp]),
@@ -447,6 +449,11 @@ class Batch:
             self.close()
 
     def set_kernel(self, which): return check(lib.nova_batch_set_kernel(self.h, which), "set_kernel")
+    def set_fused_append(self, on): return check(lib.nova_batch_set_fused_append(self.h, int(on)), "set_fused_append")
+    def set_pdl(self, on): return check(lib.nova_batch_set_pdl(self.h, int(on)), "set_pdl")
+    def set_row_setup_pages(self, n): return check(lib.nova_batch_set_row_setup_pages(self.h, int(n)), "set_row_setup")
+    def append_attn(self, layer, q, k, v, out, stream=None):
+        return check(lib.nova_batch_append_attn(self.h, layer, q, k, v, out, stream), "append_attn")
     def sync_positions(self, stream=None): return check(lib.nova_batch_sync_positions(self.h, stream))
     def cow(self, stream=None): return check(lib.nova_batch_cow(self.h, stream), "batch_cow")
     def append(self, layer, q, k, v, stream=None):

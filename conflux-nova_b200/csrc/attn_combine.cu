@@ -3,10 +3,9 @@
 // O = sum acc_c e^{m_c - m} / l, zero when l == 0, contributors taken in a fixed order.
 //
 // attn_combine_kernel follows either split kernel: one WARP per (row, query head) recomputes from
-// the work split (attn_plan.cuh) which CTAs contributed, loads all their (m, l) pairs at once
-// (one lane per contributor), then streams the partial accumulators with 16-byte loads that do
-// not depend on each other, so the whole merge costs a few L2 round trips instead of one per
-// contributor.  Rows covered by a single CTA were already written by the split kernel.
+// the work split (attn_plan.cuh) which CTAs contributed and loads their (m, l) pairs (one lane per
+// contributor) and all their accumulators (16-byte loads) in one batch of independent loads, so
+// the merge costs one memory round trip per 32 contributors instead of two per contributor.  Rows covered by a single CTA were already written by the split kernel.
 #include "attn_plan.cuh"
 
 namespace novab {
@@ -27,11 +26,17 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(AttnLaunch a, int n_c
     __shared__ int s_prefix[kMaxRowsSmem + 1];
     const int lane = (int)threadIdx.x & 31;
     const int warp = (int)threadIdx.x >> 5;
+    // profiling aid: stamps of the first 148 CTAs go after the split kernel's 148 x 8 block
+    unsigned long long* tl = (a.timeline && blockIdx.x < 148) ? a.timeline + 148 * 8 + (size_t)blockIdx.x * 4 : nullptr;
+    if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[0]));
+    pdl_launch_dependents();
     const int KVG = a.kv_group;
     const int G = a.n_heads / a.n_kv_heads;
     const int n_groups = a.n_kv_heads / KVG;
     const int heads_per_row = KVG * G;
-    plan_build_prefix(a, s_prefix, n_groups);
+    plan_build_prefix(a, s_prefix, n_groups);     // n_past: not written by the split kernel before us
+    pdl_wait();                                   // the split kernel's partials are complete from here on
+    if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[1]));
     PlanView pv;
     pv.prefix = s_prefix;
     pv.rows_per_layer = a.n_sessions * n_groups;
@@ -58,40 +63,42 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(AttnLaunch a, int n_c
         const int64_t head = ((int64_t)ll * a.n_sessions + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
         const float* base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
 
-        float M = -INFINITY;
-        for (int c0 = 0; c0 < n; c0 += 32) {
-            const int idx = c0 + lane;
-            if (idx < n) {
-                const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)idx * stride_c));
-                if (ml.y > 0.f) M = fmaxf(M, ml.x);
-            }
-        }
-        M = warp_max(M);
-        float L = 0.f;
+        // Contributors are taken 32 at a time: lane i holds (m, l) of contributor c0 + i while every
+        // lane pulls its 4 dims of all 32 accumulators.  None of these loads depends on another, so a
+        // chunk costs ONE memory round trip (a round trip is ~1 us here; a row usually fits one chunk).
+        float M = -INFINITY, L = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int c0 = 0; c0 < n; c0 += 32) {
-            const int idx = c0 + lane;
-            float w = 0.f;
-            if (idx < n) {
-                const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)idx * stride_c));
-                if (ml.y > 0.f) {
-                    w = __expf(ml.x - M);
-                    L = fmaf(ml.y, w, L);
+            const int cnt = n - c0 < 32 ? n - c0 : 32;
+            const float* src = base + (size_t)c0 * stride_c;
+            float2 ml = make_float2(-INFINITY, 0.f);
+            if (lane < cnt) ml = __ldcg(reinterpret_cast<const float2*>(src + (size_t)lane * stride_c));
+            float4 x[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < cnt) x[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * stride_c + 4 + 4 * lane));
+            }
+            const float mc = warp_max(ml.y > 0.f ? ml.x : -INFINITY);
+            if (c0 == 0 && tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[2]));
+            const float Mn = fmaxf(M, mc);
+            if (Mn == -INFINITY) continue;                       // nothing attended in this chunk or before
+            const float corr = __expf(M - Mn);                   // 0 on the first chunk (M = -inf)
+            const float w = ml.y > 0.f ? __expf(ml.x - Mn) : 0.f;
+            L = fmaf(L, corr, warp_sum(ml.y * w));
+            acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float wi = __shfl_sync(0xffffffffu, w, i);
+                if (wi != 0.f) {     // a slot with l == 0 carries no accumulator (and may hold anything)
+                    acc.x = fmaf(x[i].x, wi, acc.x);
+                    acc.y = fmaf(x[i].y, wi, acc.y);
+                    acc.z = fmaf(x[i].z, wi, acc.z);
+                    acc.w = fmaf(x[i].w, wi, acc.w);
                 }
             }
-            const int cnt = n - c0 < 32 ? n - c0 : 32;
-            const float* src = base + (size_t)c0 * stride_c + 4 + 4 * lane;
-#pragma unroll 8
-            for (int i = 0; i < cnt; ++i) {
-                const float wi = __shfl_sync(0xffffffffu, w, i);
-                const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * stride_c));
-                acc.x = fmaf(x.x, wi, acc.x);
-                acc.y = fmaf(x.y, wi, acc.y);
-                acc.z = fmaf(x.z, wi, acc.z);
-                acc.w = fmaf(x.w, wi, acc.w);
-            }
+            M = Mn;
         }
-        L = warp_sum(L);
         if (a.write_partial_only) {
             float* op = a.out_part + head * kPartW;
             if (lane == 0) { op[0] = M; op[1] = L; }
@@ -105,6 +112,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(AttnLaunch a, int n_c
                 make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         }
     }
+    if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[3]));
 }
 
 // LSE merge of n_parts stacked caller-visible partial buffers [n_parts][n_rows][130] -> out
@@ -141,7 +149,12 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
     const int64_t units = (int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) * a.n_layers * (int64_t)(a.kv_group * G);
     int64_t ctas = (units + 3) / 4;
     if (ctas > 148 * 8) ctas = 148 * 8;
-    attn_combine_kernel<<<(unsigned)ctas, 128, 0, s>>>(a, n_ctas_split);
+    // Always a programmatic dependent of the split kernel launched just before it.
+    const cudaError_t le = launch_kernel_pdl(attn_combine_kernel, dim3((unsigned)ctas), dim3(128), 0, s, true, a, n_ctas_split);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "combine launch");
+        return NOVA_ERR_CUDA;
+    }
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }

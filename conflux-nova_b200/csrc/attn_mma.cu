@@ -121,6 +121,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     __shared__ __align__(8) unsigned long long s_full[kStages];
     __shared__ __align__(8) unsigned long long s_empty[kStages];
     __shared__ int s_kcount[kStages];
+    __shared__ int s_phys[kStages];
     __shared__ int s_abort;
 
     const int lane = (int)threadIdx.x & 31;
@@ -131,6 +132,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const int heads_per_row = KVG * G;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
+    pdl_launch_dependents();      // the combine kernel may be scheduled; it waits for this grid to finish
     unsigned long long* tl = a.timeline ? a.timeline + (size_t)blockIdx.x * 8 : nullptr;
     if (tl && threadIdx.x == 0) tl[0] = now_ns();
     if (threadIdx.x == 0) {
@@ -190,8 +192,8 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
         uint32_t it = 0;
         for (int64_t pos = lo; pos < hi;) {
-            const Segment sg = plan_segment(pv, pos, hi);
-            pos += sg.page_count;
+            const Segment sg = plan_segment(pv, pos, hi, a.row_setup_pages);
+            pos += sg.span;
             const int s = sg.session;
             const int n_keys = plan_session_keys(a, s);
             int first_page, n_pages_row;
@@ -215,6 +217,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     kcount = 0;
                 }
                 s_kcount[stage] = kcount;
+                s_phys[stage] = phys;
                 const uint32_t bar = smem_u32(&s_full[stage]);
                 const uint32_t dst = stage0 + (uint32_t)stage * Cfg::kStageBytes;
                 const int c1 = (int)(((int64_t)layer * a.nb + phys) * kKvBlock);
@@ -240,30 +243,63 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const uint32_t v_row = (uint32_t)(w * 2048 + (((lm & 1) << 3) + lr) * 128);
     constexpr float kQScale = kAttnScale * kLog2e;
     uint32_t it = 0;
+    // Everything the consumers read or write from here on (q, the new k/v, out, partial slots) may
+    // belong to the kernel before this one; the producer warp meanwhile prefetches pages, which it
+    // cannot be writing.
+    pdl_wait();
 
     for (int64_t pos = lo; pos < hi;) {
-        const Segment sg = plan_segment(pv, pos, hi);
-        pos += sg.page_count;
+        const Segment sg = plan_segment(pv, pos, hi, a.row_setup_pages);
+        pos += sg.span;
         const int s = sg.session;
         const int kvh = sg.group * KVG + w;
         const int64_t head0 = ((int64_t)sg.layer_local * S + s) * NH + (int64_t)kvh * G;
+        int first_page_c, n_pages_row_c;
+        plan_session_pages(a, s, first_page_c, n_pages_row_c);
 
-        // q fragments of row g (zero for padding rows): hi + lo fp16 parts of q * scale * log2(e)
+        // q fragments of row g (zero for padding rows): hi + lo fp16 parts of q * scale * log2(e).
+        // With the fused append q arrives un-rotated: dims d and d+64 of a NeoX pair sit in the same
+        // thread (k-steps ks and ks+4), so the rotation at n_past[s] is done here, in registers, with
+        // the same fused form as the append kernel.
         uint32_t qh[8][2], ql[8][2];
+        const int pos_new = a.fuse_append ? a.n_past[s] : -1;
         {
             const float* qp = a.q + (head0 + (g < G ? g : 0)) * kHeadDim;
+            float2 x[8][2];
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
 #pragma unroll
                 for (int hlf = 0; hlf < 2; ++hlf) {
-                    float2 x = make_float2(0.f, 0.f);
-                    if (g < G) x = *reinterpret_cast<const float2*>(qp + 16 * ks + 8 * hlf + 2 * t);
-                    x.x *= kQScale;
-                    x.y *= kQScale;
-                    const __half2 h = __floats2half2_rn(x.x, x.y);
+                    x[ks][hlf] = make_float2(0.f, 0.f);
+                    if (g < G) x[ks][hlf] = *reinterpret_cast<const float2*>(qp + 16 * ks + 8 * hlf + 2 * t);
+                }
+            if (a.fuse_append && pos_new >= 0 && pos_new < a.rope_rows) {
+                const float* cr = a.rope_cs + (int64_t)pos_new * (kHeadDim / 2);
+                const float* sr = a.rope_sn + (int64_t)pos_new * (kHeadDim / 2);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+                    for (int hlf = 0; hlf < 2; ++hlf) {
+                        const float2 c = *reinterpret_cast<const float2*>(cr + 16 * ks + 8 * hlf + 2 * t);
+                        const float2 sn = *reinterpret_cast<const float2*>(sr + 16 * ks + 8 * hlf + 2 * t);
+                        const float2 x0 = x[ks][hlf], x1 = x[ks + 4][hlf];
+                        x[ks][hlf].x = __fmaf_rn(x0.x, c.x, -__fmul_rn(x1.x, sn.x));
+                        x[ks][hlf].y = __fmaf_rn(x0.y, c.y, -__fmul_rn(x1.y, sn.y));
+                        x[ks + 4][hlf].x = __fmaf_rn(x0.x, sn.x, __fmul_rn(x1.x, c.x));
+                        x[ks + 4][hlf].y = __fmaf_rn(x0.y, sn.y, __fmul_rn(x1.y, c.y));
+                    }
+            } else if (a.fuse_append && lane == 0 && a.status) {
+                atomicCAS(a.status, 0, NOVA_ERR_INVALID);      // position beyond the RoPE table
+            }
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+                for (int hlf = 0; hlf < 2; ++hlf) {
+                    const float xs = x[ks][hlf].x * kQScale, ys = x[ks][hlf].y * kQScale;
+                    const __half2 h = __floats2half2_rn(xs, ys);
                     const float2 hf = __half22float2(h);
                     qh[ks][hlf] = *reinterpret_cast<const uint32_t*>(&h);
-                    ql[ks][hlf] = pack_h2(x.x - hf.x, x.y - hf.y);
+                    ql[ks][hlf] = pack_h2(xs - hf.x, ys - hf.y);
                 }
         }
         float m = -INFINITY, l = 0.f;
@@ -284,6 +320,46 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             const uint32_t sv = sk + 2 * Cfg::kBoxBytes;
 
             if (kcount > 0) {
+                bool patched = false;
+                if (a.fuse_append && pos_new >= 0 && pos_new < a.rope_rows &&
+                    (pos_new >> kKvShift) == first_page_c + sg.page_first + pg) {
+                    // This page receives the step's new token: rotate k, store k and v into the pool
+                    // (for later steps) and straight into the staged copy (for this one).  The TMA
+                    // copy of that slot may be old or new bytes; both are overwritten here.
+                    patched = true;
+                    const int slot = pos_new & (kKvBlock - 1);
+                    const int layer = a.layer0 + sg.layer_local;
+                    const int64_t tok = ((int64_t)sg.layer_local * S + s) * a.n_kv_heads + kvh;
+                    float* kn = a.k_new + tok * kHeadDim;
+                    const float* vn = a.v_new + tok * kHeadDim;
+                    const float* cr = a.rope_cs + (int64_t)pos_new * (kHeadDim / 2);
+                    const float* sr = a.rope_sn + (int64_t)pos_new * (kHeadDim / 2);
+                    const int64_t grow = (((int64_t)layer * a.nb + s_phys[stage]) * kKvBlock + slot) * (int64_t)a.n_kv_heads * kHeadDim +
+                                         (int64_t)kvh * kHeadDim;
+                    __half* gk = static_cast<__half*>(a.pool_k_w) + grow;
+                    __half* gv = static_cast<__half*>(a.pool_v_w) + grow;
+                    const uint32_t srow = (uint32_t)(w * 2048 + slot * 128);
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        const int i = lane + 32 * r;                 // pair (i, i + 64)
+                        const float c = cr[i], sn = sr[i];
+                        const float x0 = kn[i], x1 = kn[i + 64];
+                        const float r0 = __fmaf_rn(x0, c, -__fmul_rn(x1, sn));
+                        const float r1 = __fmaf_rn(x0, sn, __fmul_rn(x1, c));
+                        kn[i] = r0;
+                        kn[i + 64] = r1;
+                        const __half k0 = __float2half_rn(r0), k1 = __float2half_rn(r1);
+                        const __half v0 = __float2half_rn(vn[i]), v1 = __float2half_rn(vn[i + 64]);
+                        gk[i] = k0; gk[i + 64] = k1;
+                        gv[i] = v0; gv[i + 64] = v1;
+                        const uint32_t off = srow + ((((uint32_t)i >> 3) ^ (uint32_t)(slot & 7)) << 4) + (((uint32_t)i & 7) << 1);
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(sk + off), "h"(__half_as_ushort(k0)) : "memory");
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(sk + (uint32_t)Cfg::kBoxBytes + off), "h"(__half_as_ushort(k1)) : "memory");
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(sv + off), "h"(__half_as_ushort(v0)) : "memory");
+                        asm volatile("st.shared.u16 [%0], %1;" ::"r"(sv + (uint32_t)Cfg::kBoxBytes + off), "h"(__half_as_ushort(v1)) : "memory");
+                    }
+                    __syncwarp();
+                }
                 if (kcount < kKvBlock) {
                     // Rows past the last key hold whatever the page held before: P is 0 there, but
                     // 0 * (Inf/NaN bit patterns) would poison O, so clear those V rows first.
@@ -342,7 +418,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     mma_top(o[2 * jp][0], o[2 * jp][1], p0, p1, b[0], b[1], o[2 * jp][0], o[2 * jp][1]);
                     mma_top(o[2 * jp + 1][0], o[2 * jp + 1][1], p0, p1, b[2], b[3], o[2 * jp + 1][0], o[2 * jp + 1][1]);
                 }
-                if (kcount < kKvBlock) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (kcount < kKvBlock || patched) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
@@ -396,7 +472,12 @@ int launch_kvg(const AttnLaunch& a, int n_ctas, cudaStream_t s) {
     }
     const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k);
     const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v);
-    attn_mma_kernel<KVG><<<(unsigned)n_ctas, Cfg::kThreads, Cfg::kSmemBytes, s>>>(a, *tk, *tv);
+    const cudaError_t le = launch_kernel_pdl(attn_mma_kernel<KVG>, dim3((unsigned)n_ctas), dim3(Cfg::kThreads),
+                                             (size_t)Cfg::kSmemBytes, s, a.pdl != 0, a, *tk, *tv);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "attention launch");
+        return NOVA_ERR_CUDA;
+    }
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }
@@ -448,6 +529,8 @@ int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
 
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
     if (kv_dtype != NOVA_KV_F16 || !a.tmap_k || !a.tmap_v) return NOVA_ERR_UNSUPPORTED;
+    if (a.fuse_append && (!a.n_past || !a.k_new || !a.v_new || !a.rope_cs || !a.rope_sn || !a.pool_k_w || !a.pool_v_w))
+        return NOVA_ERR_INVALID;
     if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
     if (a.n_heads % a.n_kv_heads || a.n_kv_heads % a.kv_group) return NOVA_ERR_INVALID;
     if (a.n_heads / a.n_kv_heads > 8) return NOVA_ERR_UNSUPPORTED;

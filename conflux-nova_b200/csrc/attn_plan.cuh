@@ -26,8 +26,9 @@ struct Segment {
     int session;
     int group;
     int64_t row_id;    // layer_local * rows_per_layer + row
-    int page_first;    // first page of this segment, relative to the row's first page
-    int page_count;
+    int page_first;    // first REAL page of this segment, relative to the row's first page
+    int page_count;    // real pages in the segment (0: only the row's set-up weight fell to this CTA)
+    int span;          // how far the segment advances the launch-wide page line (set-up weight included)
     int c_first;       // first and last CTA that touch this row
     int c_last;
 };
@@ -61,7 +62,7 @@ __device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n
             if (r < rows) {
                 int first, count;
                 plan_session_pages(a, r / n_groups, first, count);
-                v = count;
+                v = count > 0 ? count + a.row_setup_pages : 0;
             }
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -84,7 +85,7 @@ __device__ __forceinline__ int64_t plan_cta_begin(const PlanView& p, int c) {
 }
 
 // Segment that starts at launch-wide page `pos` and ends at the row's end or at `hi`.
-__device__ inline Segment plan_segment(const PlanView& p, int64_t pos, int64_t hi) {
+__device__ inline Segment plan_segment(const PlanView& p, int64_t pos, int64_t hi, int setup) {
     Segment sg;
     sg.layer_local = (int)(pos / p.pages_per_layer);
     const int64_t layer_base = (int64_t)sg.layer_local * p.pages_per_layer;
@@ -103,8 +104,11 @@ __device__ inline Segment plan_segment(const PlanView& p, int64_t pos, int64_t h
     const int64_t row_begin = layer_base + p.prefix[lo];
     const int64_t row_end = layer_base + p.prefix[lo + 1];
     const int64_t end = row_end < hi ? row_end : hi;
-    sg.page_first = (int)(pos - row_begin);
-    sg.page_count = (int)(end - pos);
+    sg.span = (int)(end - pos);
+    // the first `setup` entries of a row on the page line are weight only
+    const int64_t r0 = pos - row_begin - setup, r1 = end - row_begin - setup;
+    sg.page_first = (int)(r0 > 0 ? r0 : 0);
+    sg.page_count = (int)((r1 > 0 ? r1 : 0) - sg.page_first);
     sg.c_first = plan_owner(p, row_begin);
     sg.c_last = plan_owner(p, row_end - 1);
     return sg;

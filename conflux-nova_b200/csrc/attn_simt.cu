@@ -131,8 +131,8 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
     constexpr float kQScale = kAttnScale * kLog2e;
 
     for (int64_t pos = lo; pos < hi;) {
-        const Segment sg = plan_segment(pv, pos, hi);
-        pos += sg.page_count;
+        const Segment sg = plan_segment(pv, pos, hi, a.row_setup_pages);
+        pos += sg.span;
         const int s = sg.session;
         const int kvh = sg.group * KVG + warp;
         const int layer = a.layer0 + sg.layer_local;

@@ -23,6 +23,29 @@ constexpr float kLog2e = 1.4426950408889634f;
 void set_cuda_error(cudaError_t e, const char* what);
 void count_launch(int n = 1);
 
+// Launch with or without the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                     bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Device side of the above (no-ops when the launch did not carry the attribute).
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 #define NOVA_CUDA_TRY(expr)                                   \
     do {                                                      \
         cudaError_t _e = (expr);                              \
@@ -88,6 +111,25 @@ struct AttnLaunch {
     float* out_part;             // [layers][S][NH][130]
     const void* tmap_k;          // host pointers to the CUtensorMap of each pool (tensor-core kernel only)
     const void* tmap_v;
+    // Fused RoPE + append (tensor-core kernel): when fuse_append != 0 the CTA that owns a session's
+    // last page rotates k_new at n_past[s], stores k_new/v_new into that page (pool and the staged copy)
+    // and every CTA rotates q on the fly; q itself is left as it was.
+    int32_t fuse_append;
+    void* pool_k_w;              // the pools again, writable
+    void* pool_v_w;
+    float* k_new;                // [layers][S][NKV][128], rotated in place
+    const float* v_new;          // [layers][S][NKV][128]
+    const float* rope_cs;        // [rope_rows][64]
+    const float* rope_sn;
+    int64_t rope_rows;
+    // Programmatic dependent launch: 1 = this launch may start while the kernel before it in the
+    // stream is still running.  The kernels then read only data that the previous kernel cannot be
+    // writing (pages of earlier steps, tables, n_past) before their griddepcontrol.wait.
+    int32_t pdl;
+    // Work-split weight of starting a row inside a CTA (q fetch, and with the fused append the new
+    // token's k/v fetch at the row end next to it), in pages: every row is treated as that many pages
+    // longer at its start, so a CTA whose range crosses a row boundary gets fewer real pages.
+    int32_t row_setup_pages;
     unsigned long long* timeline;   // optional [n_ctas][8] globaltimer stamps (profiling aid), or nullptr
 };
 

@@ -54,6 +54,9 @@ struct nova_batch {
     int32_t* h_n_past = nullptr;     // pinned staging
     float* part = nullptr;
     int kernel = 0;                  // 0 SIMT, 1 tensor-core
+    int fused = 0;                   // 1: RoPE+append done inside the tensor-core attention launch
+    int pdl = 0;                     // 1: layers after the first of a step launch as programmatic dependents
+    int row_setup = 2;               // work-split weight of a row start, in pages (see AttnLaunch)
     // staging for the host-buffer step and the graph replay
     float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
     cudaGraphExec_t graph = nullptr;   // one per-layer decode step on the staging buffers
@@ -134,6 +137,7 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.kv_group = e->kv_group;
     a.page_lo = 0;
     a.page_hi = -1;
+    a.row_setup_pages = b->row_setup;
     a.tmap_k = e->tmaps_ok ? e->tmap_k : nullptr;
     a.tmap_v = e->tmaps_ok ? e->tmap_v : nullptr;
     a.timeline = b->timeline;
@@ -151,6 +155,25 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
     }
     if (rc != NOVA_OK) return rc;
     return launch_attn_combine(a, ctas, s);
+}
+
+bool use_fused(const nova_batch* b) { return b->fused && b->kernel == 1 && b->e->d.rope_neox; }
+
+// RopeKvOp + AttnOp for layers [layer0, layer0 + n_layers) in one split launch (+ combine):
+// k rotated in place and appended with v, q read un-rotated and left as it is.
+int run_attn_fused(const nova_batch* b, int layer0, int n_layers, const float* q, float* k, const float* v,
+                   float* out, cudaStream_t s, bool pdl = false) {
+    const nova_engine* e = b->e;
+    AttnLaunch a;
+    fill_attn(b, a);
+    a.q = q; a.out = out;
+    a.layer0 = layer0; a.n_layers = n_layers;
+    a.fuse_append = 1;
+    a.pool_k_w = e->pool_k; a.pool_v_w = e->pool_v;
+    a.k_new = k; a.v_new = v;
+    a.rope_cs = e->cs; a.rope_sn = e->sn; a.rope_rows = e->d.rope_positions;
+    a.pdl = pdl ? 1 : 0;
+    return run_attn(b, a, s);
 }
 
 void fill_append(const nova_batch* b, AppendLaunch& a) {
@@ -568,12 +591,39 @@ int nova_batch_set_kernel(nova_batch* b, int which) {
     if (!b || which < 0 || which > 1) return NOVA_ERR_INVALID;
     if (which == 1 && (b->e->d.kv_dtype != NOVA_KV_F16 || !b->e->tmaps_ok)) return NOVA_ERR_UNSUPPORTED;
     b->kernel = which;
+    if (which != 1) b->fused = 0;
     return NOVA_OK;
 }
 int nova_batch_set_timeline(nova_batch* b, void* dev_buf) {
     if (!b) return NOVA_ERR_INVALID;
     b->timeline = static_cast<unsigned long long*>(dev_buf);
     return NOVA_OK;
+}
+int nova_batch_set_fused_append(nova_batch* b, int on) {
+    if (!b) return NOVA_ERR_INVALID;
+    if (on && (b->kernel != 1 || !b->e->d.rope_neox)) return NOVA_ERR_UNSUPPORTED;
+    b->fused = on ? 1 : 0;
+    if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+    return NOVA_OK;
+}
+int nova_batch_set_row_setup_pages(nova_batch* b, int pages) {
+    if (!b || pages < 0 || pages > 64) return NOVA_ERR_INVALID;
+    b->row_setup = pages;
+    if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+    return NOVA_OK;
+}
+int nova_batch_set_pdl(nova_batch* b, int on) {
+    if (!b) return NOVA_ERR_INVALID;
+    b->pdl = on ? 1 : 0;
+    if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+    return NOVA_OK;
+}
+int nova_batch_append_attn(nova_batch* b, int layer, float* q, float* k, const float* v, float* out, nova_stream_t s) {
+    if (!b || !q || !k || !v || !out || layer < 0 || layer >= b->e->d.n_layers) return NOVA_ERR_INVALID;
+    if (use_fused(b)) return run_attn_fused(b, layer, 1, q, k, v, out, (cudaStream_t)s);
+    const int rc = nova_batch_append(b, layer, q, k, v, s);
+    if (rc != NOVA_OK) return rc;
+    return nova_batch_attn(b, layer, q, out, s);
 }
 int nova_batch_get_kernel(const nova_batch* b) { return b ? b->kernel : NOVA_ERR_INVALID; }
 
@@ -623,6 +673,7 @@ int nova_batch_advance(nova_batch* b, nova_stream_t s) {
 
 int nova_batch_step_all_layers(nova_batch* b, float* q, float* k, const float* v, float* out, nova_stream_t s) {
     if (!b || !q || !k || !v || !out) return NOVA_ERR_INVALID;
+    if (use_fused(b)) return run_attn_fused(b, 0, b->e->d.n_layers, q, k, v, out, (cudaStream_t)s);
     AppendLaunch ap;
     fill_append(b, ap);
     ap.q = q; ap.k = k; ap.v = v;
@@ -655,9 +706,7 @@ int nova_batch_decode_step_host(nova_batch* b, const float* q, const float* k, c
     if (per_layer_launch) {
         const size_t qs = S * e->d.n_heads * kHeadDim, ks = S * e->d.n_kv_heads * kHeadDim;
         for (int l = 0; l < e->d.n_layers; ++l) {
-            rc = nova_batch_append(b, l, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, s);
-            if (rc != NOVA_OK) return rc;
-            rc = nova_batch_attn(b, l, b->dq + l * qs, b->dout + l * qs, s);
+            rc = nova_batch_append_attn(b, l, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, s);
             if (rc != NOVA_OK) return rc;
         }
     } else {
@@ -691,10 +740,18 @@ static int issue_layers(nova_batch* b, float* q, float* k, const float* v, float
     const size_t S = (size_t)b->n;
     const size_t qs = S * e->d.n_heads * kHeadDim, ks = S * e->d.n_kv_heads * kHeadDim;
     for (int l = 0; l < e->d.n_layers; ++l) {
-        int rc = nova_batch_append(b, l, q + l * qs, k + l * ks, v + l * ks, (nova_stream_t)st);
-        if (rc != NOVA_OK) return rc;
-        if (ev) NOVA_CUDA_TRY(cudaEventRecord((*ev)[(*ev_used)++], st));
-        rc = nova_batch_attn(b, l, q + l * qs, out + l * qs, (nova_stream_t)st);
+        int rc;
+        if (use_fused(b)) {
+            if (ev) NOVA_CUDA_TRY(cudaEventRecord((*ev)[(*ev_used)++], st));
+            // Layers after the first follow a combine kernel of this same step: nothing they read before
+            // their dependency wait (pages of earlier steps, tables, n_past) is written by it.
+            rc = run_attn_fused(b, l, 1, q + l * qs, k + l * ks, v + l * ks, out + l * qs, st, b->pdl && l > 0);
+        } else {
+            rc = nova_batch_append(b, l, q + l * qs, k + l * ks, v + l * ks, (nova_stream_t)st);
+            if (rc != NOVA_OK) return rc;
+            if (ev) NOVA_CUDA_TRY(cudaEventRecord((*ev)[(*ev_used)++], st));
+            rc = nova_batch_attn(b, l, q + l * qs, out + l * qs, (nova_stream_t)st);
+        }
         if (rc != NOVA_OK) return rc;
         if (ev) NOVA_CUDA_TRY(cudaEventRecord((*ev)[(*ev_used)++], st));
     }
@@ -746,18 +803,23 @@ int nova_batch_run_steps(nova_batch* b, int n_steps, float* q, float* k, const f
         int rc = nova_batch_cow(b, s);
         if (rc < 0) return rc;
         if (mode == 0) {
-            AppendLaunch ap;
-            fill_append(b, ap);
-            ap.q = qi; ap.k = ki; ap.v = vi;
-            ap.layer0 = 0; ap.n_layers = e->d.n_layers;
-            rc = launch_rope_append(ap, st);
-            if (rc != NOVA_OK) return rc;
-            if (attn_ms) NOVA_CUDA_TRY(cudaEventRecord(b->ev[ev_used++], st));
-            AttnLaunch at;
-            fill_attn(b, at);
-            at.q = qi; at.out = oi;
-            at.layer0 = 0; at.n_layers = e->d.n_layers;
-            rc = run_attn(b, at, st);
+            if (use_fused(b)) {
+                if (attn_ms) NOVA_CUDA_TRY(cudaEventRecord(b->ev[ev_used++], st));
+                rc = run_attn_fused(b, 0, e->d.n_layers, qi, ki, vi, oi, st);
+            } else {
+                AppendLaunch ap;
+                fill_append(b, ap);
+                ap.q = qi; ap.k = ki; ap.v = vi;
+                ap.layer0 = 0; ap.n_layers = e->d.n_layers;
+                rc = launch_rope_append(ap, st);
+                if (rc != NOVA_OK) return rc;
+                if (attn_ms) NOVA_CUDA_TRY(cudaEventRecord(b->ev[ev_used++], st));
+                AttnLaunch at;
+                fill_attn(b, at);
+                at.q = qi; at.out = oi;
+                at.layer0 = 0; at.n_layers = e->d.n_layers;
+                rc = run_attn(b, at, st);
+            }
             if (rc != NOVA_OK) return rc;
             if (attn_ms) NOVA_CUDA_TRY(cudaEventRecord(b->ev[ev_used++], st));
             rc = nova_batch_advance(b, s);
@@ -772,8 +834,9 @@ int nova_batch_run_steps(nova_batch* b, int n_steps, float* q, float* k, const f
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk, ki, kv_elems * 4, cudaMemcpyDeviceToDevice, st));
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv, vi, kv_elems * 4, cudaMemcpyDeviceToDevice, st));
             NOVA_CUDA_TRY(cudaGraphLaunch(b->graph, st));
-            count_launch(3 * e->d.n_layers + 1);
-            NOVA_CUDA_TRY(cudaMemcpyAsync(qi, b->dq, q_elems * 4, cudaMemcpyDeviceToDevice, st));   // q rotated in place
+            count_launch((use_fused(b) ? 2 : 3) * e->d.n_layers + 1);
+            NOVA_CUDA_TRY(cudaMemcpyAsync(qi, b->dq, q_elems * 4, cudaMemcpyDeviceToDevice, st));   // q, k rotated in place
+            NOVA_CUDA_TRY(cudaMemcpyAsync(ki, b->dk, kv_elems * 4, cudaMemcpyDeviceToDevice, st));
             NOVA_CUDA_TRY(cudaMemcpyAsync(oi, b->dout, q_elems * 4, cudaMemcpyDeviceToDevice, st));
             for (int j = 0; j < b->n; ++j) {
                 SliceState* sl = e->pool.p.find(b->slices[(size_t)j]);

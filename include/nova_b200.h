@@ -257,10 +257,11 @@ int  nova_batch_sync_positions(nova_batch* b, nova_stream_t s);
 /* Select the attention kernel: 0 = SIMT, 1 = tensor-core (mma + bulk-copy pipeline, fp16 KV). */
 int  nova_batch_set_kernel(nova_batch* b, int which);
 int  nova_batch_get_kernel(const nova_batch* b);
-/* Profiling aid (tensor-core kernel): dev_buf = 148*8 uint64 in device memory, or NULL to switch off.
+/* Profiling aid (tensor-core kernel): dev_buf = 148*12 uint64 in device memory, or NULL to switch off.
  * Every CTA of the next attention launches leaves %globaltimer stamps there: [0] start, [1] work split
  * known, [2] first page requested, [3] last page requested, [4] first page landed, [5] last page
- * consumed, [6] results/partials written. */
+ * consumed, [6] results/partials written; after those 148*8 values the first 148 CTAs of the combine
+ * kernel leave four stamps each (start, dependency met, first maximum known, end). */
 int  nova_batch_set_timeline(nova_batch* b, void* dev_buf);
 
 /* For each session s of the batch: session_cow(s, n_past, 1).  One kernel copies
@@ -271,6 +272,22 @@ int  nova_batch_cow(nova_batch* b, nova_stream_t s);
 int  nova_batch_append(nova_batch* b, int layer, float* q, float* k, const float* v, nova_stream_t s);
 /* AttnOp decode branch (dense.h:86-95): n_keys = n_past[s] + 1; out [S][NH][HD]. */
 int  nova_batch_attn(nova_batch* b, int layer, const float* q, float* out, nova_stream_t s);
+/* RopeKvOp + AttnOp of one layer as one call.  With nova_batch_set_fused_append(b, 1) (tensor-core
+ * kernel, NeoX RoPE) both run in ONE launch: the CTA that reads a session's last page rotates k, stores
+ * k/v into it and uses them at once; q is rotated in registers and the buffer is left un-rotated.
+ * Otherwise it is nova_batch_append followed by nova_batch_attn (q rotated in place).  Callers must
+ * not rely on the contents of q afterwards (the reference does not read it after AttnOp either). */
+int  nova_batch_set_fused_append(nova_batch* b, int on);
+/* Programmatic dependent launch for nova_batch_run_steps / nova_batch_decode_step_host with the fused
+ * append: the attention launch of every layer after the first may start while the previous layer's
+ * merge is still running; it prefetches KV pages and waits (griddepcontrol.wait) before touching q, the
+ * new k/v or any output. */
+int  nova_batch_set_pdl(nova_batch* b, int on);
+/* Tuning knob of the attention work split: how many pages' worth of time starting a session inside a
+ * CTA costs (default 2).  A CTA whose page range crosses a session boundary gets that many fewer pages. */
+int  nova_batch_set_row_setup_pages(nova_batch* b, int pages);
+int  nova_batch_append_attn(nova_batch* b, int layer, float* q, float* k, const float* v, float* out,
+                            nova_stream_t s);
 /* n_past[s] += 1 on host and device (the caller's ++A->n_past, cow_e2e_demo.cpp:64). */
 int  nova_batch_advance(nova_batch* b, nova_stream_t s);
 /* All layers at once (inputs of different layers are independent here):

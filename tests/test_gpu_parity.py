@@ -32,10 +32,13 @@ def kernels_for(nv, kv_dtype):
 
 
 def try_set_kernel(nv, batch, which):
-    rc = nv.lib.nova_batch_set_kernel(batch.h, which)
+    """0 = SIMT, 1 = tensor-core, 2 = tensor-core with RoPE+append fused into the attention launch."""
+    rc = nv.lib.nova_batch_set_kernel(batch.h, min(which, 1))
     if rc == nv.ERR_UNSUPPORTED:
         pytest.skip("kernel not built for this dtype")
     assert rc == 0
+    if which == 2:
+        batch.set_fused_append(1)
 
 
 # --------------------------------------------------------------------------------------------
@@ -199,14 +202,14 @@ def build_case(nv, ob, model, kvd, ctx_lens, L=2, seed=21, spare=0):
     return eng, ss, sh, pk, pv, cs, sn, rng
 
 
-@pytest.mark.parametrize("kernel", [0, 1])
+@pytest.mark.parametrize("kernel", [0, 1, 2])
 @pytest.mark.parametrize("model,dtype", [("qwen25_1p5b", "f16"), ("qwen25_7b", "f16"), ("qwen25_14b", "f16"),
                                          ("qwen25_7b", "f32"), ("qwen25_1p5b", "f32")])
 def test_decode_steps_vs_oracle(nv, ob, model, dtype, kernel):
     """Sessions of ragged lengths (a fresh one, page-boundary cases, a long one), three decode steps
     per-layer and all-layers: pages bit-exact, attention within tolerance of the exact softmax."""
     kvd = nv.KV_F16 if dtype == "f16" else nv.KV_F32
-    if kernel == 1 and kvd != nv.KV_F16:
+    if kernel >= 1 and kvd != nv.KV_F16:
         pytest.skip("tensor-core kernel is fp16-KV only")
     ctx_lens = [0, 1, 15, 16, 17, 31, 33, 100, 255, 1024, 1500]
     eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, kvd, ctx_lens)
@@ -227,14 +230,23 @@ def test_decode_steps_vs_oracle(nv, ob, model, dtype, kernel):
         else:
             qs, ks = S * NH * 128 * 4, S * NKV * 128 * 4
             for layer in range(L):
-                batch.append(layer, dq.ptr + layer * qs, dk.ptr + layer * ks, dv.ptr + layer * ks)
-                batch.attn(layer, dq.ptr + layer * qs, out_d.ptr + layer * qs)
+                if kernel == 2:
+                    batch.append_attn(layer, dq.ptr + layer * qs, dk.ptr + layer * ks, dv.ptr + layer * ks,
+                                      out_d.ptr + layer * qs)
+                else:
+                    batch.append(layer, dq.ptr + layer * qs, dk.ptr + layer * ks, dv.ptr + layer * ks)
+                    batch.attn(layer, dq.ptr + layer * qs, out_d.ptr + layer * qs)
         batch.advance()
         nv.check(nv.lib.dev_sync())
         assert batch.device_status() == 0
+        q_in = q.copy()
         want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)
         got = out_d.download(np.float32).reshape(L, S, NH, 128)
-        assert np.array_equal(bits(dq.download(np.float32)), bits(q.ravel())), "q rotated in place"
+        if kernel == 2:     # fused: q is rotated in registers only, the buffer keeps the input
+            assert np.array_equal(bits(dq.download(np.float32)), bits(q_in.ravel())), "q left as it was"
+        else:
+            assert np.array_equal(bits(dq.download(np.float32)), bits(q.ravel())), "q rotated in place"
+        assert np.array_equal(bits(dk.download(np.float32)), bits(k.ravel())), "k rotated in place"
         for i in range(S):
             assert_attn_close(got[:, i], want[:, i], f"step {step} session {i} n_keys {pos[i] + 1}")
         pos = [p + 1 for p in pos]
@@ -347,7 +359,8 @@ def test_partial_and_lse_combine(nv, ob, kernel):
     eng.close()
 
 
-def test_cow_shared_prefix(nv, ob):
+@pytest.mark.parametrize("kernel", [0, 2])
+def test_cow_shared_prefix(nv, ob, kernel):
     """Config-3 in miniature: sessions share a donor's prefix whose tail page is partly filled; the
     first append of each un-shares that page exactly once (tests/cow_e2e_demo.cpp:87-105,
     tests/reuse_demo.cpp:72-81).  Pages and attention against the oracle; the host bookkeeping itself is
@@ -364,6 +377,7 @@ def test_cow_shared_prefix(nv, ob):
     assert eng.pool.refcnt(tail) == n_fork + 1
     donor_tail_before = eng.read_page("k", 1, tail).copy()
     batch = eng.batch(forks)
+    try_set_kernel(nv, batch, kernel)
     NH, NKV, S = eng.NH, eng.NKV, n_fork
     out_d = nv.DevBuf(L * S * NH * 128 * 4)
     pos = [P] * S
@@ -447,11 +461,13 @@ def test_bad_table_entry_is_reported_not_followed(nv):
     eng.close()
 
 
-def test_decode_step_from_host_buffers(nv, ob):
+@pytest.mark.parametrize("kernel", [0, 1, 2])
+def test_decode_step_from_host_buffers(nv, ob, kernel):
     eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, "qwen25_1p5b", nv.KV_F16, [50, 7], L=3, seed=13)
     L, S, NH, NKV = eng.L, 2, eng.NH, eng.NKV
     tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
     batch = eng.batch(ss)
+    try_set_kernel(nv, batch, kernel)
     pos = [50, 7]
     for step, per_layer in enumerate((1, 0, 1)):
         q = rng.standard_normal((L, S, NH, 128)).astype(np.float32)
@@ -464,5 +480,42 @@ def test_decode_step_from_host_buffers(nv, ob):
         pos = [p + 1 for p in pos]
     gk, gv = eng.read_pools()
     assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    batch.close()
+    eng.close()
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("kernel,pdl", [(0, 0), (1, 0), (2, 0), (2, 1)])
+def test_run_steps_native_loop(nv, ob, mode, kernel, pdl):
+    """nova_batch_run_steps (the native multi-step loop the bench times): all-layer launches, per-layer
+    launches and CUDA-graph replay, with and without the fused append and programmatic dependent
+    launch, against the oracle over four steps."""
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, "qwen25_7b", nv.KV_F16, [300, 14, 47, 1000], L=3, seed=17)
+    L, S, NH, NKV = eng.L, len(ss), eng.NH, eng.NKV
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
+    batch = eng.batch(ss)
+    try_set_kernel(nv, batch, kernel)
+    batch.set_pdl(pdl)
+    n_steps = 4
+    q = rng.standard_normal((n_steps, L, S, NH, 128)).astype(np.float32)
+    k = rng.standard_normal((n_steps, L, S, NKV, 128)).astype(np.float32)
+    v = rng.standard_normal((n_steps, L, S, NKV, 128)).astype(np.float32)
+    dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+    dout = nv.DevBuf(q.nbytes)
+    st = nv.Stream()
+    batch.run_steps(n_steps, dq.ptr, dk.ptr, dv.ptr, dout.ptr, q[0].size, k[0].size, mode, st.h)
+    st.sync()
+    assert batch.device_status() == 0
+    got = dout.download(np.float32).reshape(q.shape)
+    pos = [300, 14, 47, 1000]
+    for i in range(n_steps):
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q[i], k[i], v[i], cs, sn, exact=True)
+        assert_attn_close(got[i], want, f"step {i}")
+        pos = [p + 1 for p in pos]
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    assert np.array_equal(bits(dk.download(np.float32)), bits(k.ravel())), "k rotated in place"
+    assert [eng.n_past(s) for s in ss] == pos
+    st.close()
     batch.close()
     eng.close()
