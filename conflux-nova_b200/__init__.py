@@ -14,7 +14,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libnova_b200.so")
+LIB_PATH = os.environ.get("NOVA_B200_LIB") or os.path.join(HERE, "libnova_b200.so")   # override: try another build
 
 OK = 0
 ERR_INVALID, ERR_POOL_FULL, ERR_NO_SLICE, ERR_NO_SESSION, ERR_CUDA = -1, -2, -3, -4, -5

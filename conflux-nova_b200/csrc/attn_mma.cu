@@ -8,7 +8,7 @@
 //     (cp.async.bulk.tensor, no multicast): a page of one pool is [16 slots][NKV][128] fp16 and
 //     is fetched as two boxes [64 dims][16 slots][kv group] with the 128-byte swizzle, so that
 //     each kv head's 16 key rows sit in 16 consecutive 128-byte lines.  A ring of
-//     kStages page sets (K+V, 32 KiB each at 4 kv heads) keeps ~190 KiB per SM in flight.
+//     kStages page sets (K+V, 32 KiB each at 4 kv heads) keeps ~128 KiB per SM in flight.
 //   * One consumer warp per kv head.  The G = NH/NKV query heads of that kv head are the rows
 //     of an m16n8k16 tile: S = Q.K^T and O += P.V run on mma.sync (fp16 inputs, fp32
 //     accumulate) with bank-conflict-free ldmatrix reads; q is split into fp16 hi + lo parts so
@@ -26,7 +26,10 @@
 namespace novab {
 namespace {
 
-constexpr int kStages = 6;
+#ifndef NOVA_ATTN_STAGES
+#define NOVA_ATTN_STAGES 4
+#endif
+constexpr int kStages = NOVA_ATTN_STAGES;   // page sets in flight per CTA; more only adds queueing delay in HBM
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s per barrier wait
 
 __device__ __forceinline__ float ex2(float x) {
@@ -118,6 +121,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     using Cfg = MmaCfg<KVG>;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int s_prefix[kMaxRowsSmem + 1];
+    __shared__ int s_slice[kMaxRowsSmem];
     __shared__ __align__(8) unsigned long long s_full[kStages];
     __shared__ __align__(8) unsigned long long s_empty[kStages];
     __shared__ int s_kcount[kStages];
@@ -143,7 +147,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    plan_build_prefix(a, s_prefix, n_groups);   // ends with __syncthreads()
+    plan_build_prefix(a, s_prefix, n_groups, s_slice);   // ends with __syncthreads()
 
     PlanView pv;
     pv.prefix = s_prefix;
@@ -187,50 +191,112 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
 
     // ------------------------------------------------------------------ producer warp
     if (warp == KVG) {
-        if (lane != 0) return;
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
-        uint32_t it = 0;
-        for (int64_t pos = lo; pos < hi;) {
-            const Segment sg = plan_segment(pv, pos, hi, a.row_setup_pages);
-            pos += sg.span;
-            const int s = sg.session;
-            const int n_keys = plan_session_keys(a, s);
-            int first_page, n_pages_row;
-            plan_session_pages(a, s, first_page, n_pages_row);
-            const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
-            const int layer = a.layer0 + sg.layer_local;
-            for (int pg = 0; pg < sg.page_count; ++pg, ++it) {
-                const int stage = (int)(it % kStages);
-                const uint32_t round = it / kStages;
-                if (round > 0 && !mbar_wait(smem_u32(&s_empty[stage]), (round - 1) & 1, &s_abort)) {
-                    if (a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
-                    return;
-                }
-                const int page = first_page + sg.page_first + pg;
-                int phys = __ldg(table + page);
-                int kcount = n_keys - page * kKvBlock;
-                if (kcount > kKvBlock) kcount = kKvBlock;
-                if (phys < 0 || phys >= a.nb) {      // never follow a bad entry: load page 0, use none of it
-                    if (a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
-                    phys = 0;
-                    kcount = 0;
-                }
-                s_kcount[stage] = kcount;
-                s_phys[stage] = phys;
-                const uint32_t bar = smem_u32(&s_full[stage]);
-                const uint32_t dst = stage0 + (uint32_t)stage * Cfg::kStageBytes;
-                const int c1 = (int)(((int64_t)layer * a.nb + phys) * kKvBlock);
-                const int c2 = sg.group * KVG;
-                mbar_expect_tx(bar, Cfg::kStageBytes);
-                tma_load_3d(dst, &tmk, 0, c1, c2, bar);
-                tma_load_3d(dst + Cfg::kBoxBytes, &tmk, 64, c1, c2, bar);
-                tma_load_3d(dst + 2 * Cfg::kBoxBytes, &tmv, 0, c1, c2, bar);
-                tma_load_3d(dst + 3 * Cfg::kBoxBytes, &tmv, 64, c1, c2, bar);
-                if (tl && it == 0) tl[2] = now_ns();
-            }
+        // The whole warp walks the CTA's page range in batches of up to 32 pages: each lane fetches
+        // one block-table entry of the NEXT batch while lane 0 issues the TMA copies of the current
+        // one, so a table read (a ~1 us round trip when it misses) never stops the copy stream.
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
         }
-        if (tl) tl[3] = now_ns();
+        struct Batch {
+            int count;              // 0: no more work
+            int layer, group, n_keys, page0;
+            const int32_t* table;
+        };
+        int64_t pos = lo;
+        Segment sg;
+        sg.page_count = 0;
+        int seg_done = 0, seg_first_page = 0, seg_keys = 0;
+        const int32_t* seg_table = nullptr;
+        auto next_batch = [&]() -> Batch {
+            Batch b;
+            b.count = 0;
+            while (seg_done >= sg.page_count) {          // open the next segment that has real pages
+                if (pos >= hi) return b;
+                sg = plan_segment(pv, pos, hi, a.row_setup_pages);
+                pos += sg.span;
+                seg_done = 0;
+                const int s = sg.session;
+                seg_keys = plan_session_keys(a, s);
+                int n_pages_row;
+                plan_session_pages(a, s, seg_first_page, n_pages_row);
+                seg_table = a.table_base + (int64_t)s_slice[s] * a.table_stride;
+                // warm L2 with what the consumers will ask for when they reach this segment
+                const float* qrow = a.q + (((int64_t)sg.layer_local * S + s) * NH + (int64_t)sg.group * KVG * G) * kHeadDim;
+                for (int i = lane; i < heads_per_row * 4; i += 32)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(qrow + i * 32));
+                if (a.fuse_append) {
+                    const int64_t tok = (((int64_t)sg.layer_local * S + s) * a.n_kv_heads + (int64_t)sg.group * KVG) * kHeadDim;
+                    for (int i = lane; i < KVG * 4; i += 32) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(a.k_new + tok + i * 32));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(a.v_new + tok + i * 32));
+                    }
+                    const int pn = seg_keys - a.keys_add;      // n_past[s]
+                    if (lane < 4 && pn >= 0 && pn < a.rope_rows)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"((lane < 2 ? a.rope_cs : a.rope_sn) +
+                                                                       (int64_t)pn * (kHeadDim / 2) + (lane & 1) * 32));
+                }
+            }
+            b.count = sg.page_count - seg_done < 32 ? sg.page_count - seg_done : 32;
+            b.layer = a.layer0 + sg.layer_local;
+            b.group = sg.group;
+            b.n_keys = seg_keys;
+            b.page0 = seg_first_page + sg.page_first + seg_done;
+            b.table = seg_table;
+            seg_done += b.count;
+            return b;
+        };
+        uint32_t it = 0;
+        Batch cur = next_batch();
+        int phys_cur = (cur.count > 0 && lane < cur.count) ? __ldg(cur.table + cur.page0 + lane) : 0;
+        while (cur.count > 0) {
+            // Issue the first few pages of the batch before looking ahead, so that opening the next
+            // segment (work split, prefetch hints) never delays copies that could already be in flight.
+            const int head_n = cur.count < kStages ? cur.count : kStages;
+            Batch nxt;
+            int phys_nxt = 0;
+            for (int j = 0; j < cur.count; ++j, ++it) {
+                int phys = __shfl_sync(0xffffffffu, phys_cur, j);
+                int ok = 1;
+                if (lane == 0) {
+                    const int stage = (int)(it % kStages);
+                    const uint32_t round = it / kStages;
+                    if (round > 0 && !mbar_wait(smem_u32(&s_empty[stage]), (round - 1) & 1, &s_abort)) {
+                        if (a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
+                        ok = 0;
+                    } else {
+                        const int page = cur.page0 + j;
+                        int kcount = cur.n_keys - page * kKvBlock;
+                        if (kcount > kKvBlock) kcount = kKvBlock;
+                        if (phys < 0 || phys >= a.nb) {      // never follow a bad entry: load page 0, use none of it
+                            if (a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
+                            phys = 0;
+                            kcount = 0;
+                        }
+                        s_kcount[stage] = kcount;
+                        s_phys[stage] = phys;
+                        const uint32_t bar = smem_u32(&s_full[stage]);
+                        const uint32_t dst = stage0 + (uint32_t)stage * Cfg::kStageBytes;
+                        const int c1 = (int)(((int64_t)cur.layer * a.nb + phys) * kKvBlock);
+                        const int c2 = cur.group * KVG;
+                        mbar_expect_tx(bar, Cfg::kStageBytes);
+                        tma_load_3d(dst, &tmk, 0, c1, c2, bar);
+                        tma_load_3d(dst + Cfg::kBoxBytes, &tmk, 64, c1, c2, bar);
+                        tma_load_3d(dst + 2 * Cfg::kBoxBytes, &tmv, 0, c1, c2, bar);
+                        tma_load_3d(dst + 3 * Cfg::kBoxBytes, &tmv, 64, c1, c2, bar);
+                        if (tl && it == 0) tl[2] = now_ns();
+                    }
+                }
+                if (!__shfl_sync(0xffffffffu, ok, 0)) return;
+                if (j + 1 == head_n) {                      // look ahead: next batch's table entries in flight
+                    nxt = next_batch();
+                    phys_nxt = (nxt.count > 0 && lane < nxt.count) ? __ldg(nxt.table + nxt.page0 + lane) : 0;
+                }
+            }
+            cur = nxt;
+            phys_cur = phys_nxt;
+        }
+        if (tl && lane == 0) tl[3] = now_ns();
         return;
     }
 

@@ -50,8 +50,12 @@ __device__ __forceinline__ void plan_session_pages(const AttnLaunch& a, int s, i
 }
 
 // Fills prefix[0..rows] (shared memory) with a warp scan; call from all threads of the CTA.
-__device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n_groups) {
+// slice_out (optional, shared memory, n_sessions entries) receives each session's slice id, fetched by
+// the second warp at the same time, so that no later table lookup waits for it.
+__device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n_groups, int* slice_out = nullptr) {
     const int rows = a.n_sessions * n_groups;
+    if (slice_out && threadIdx.x >= 32 && threadIdx.x < 64)
+        for (int s = (int)threadIdx.x - 32; s < a.n_sessions; s += 32) slice_out[s] = a.slice_ids ? a.slice_ids[s] : s;
     if (threadIdx.x < 32) {
         const int lane = (int)threadIdx.x;
         int carry = 0;

@@ -133,7 +133,7 @@ struct AttnLaunch {
     unsigned long long* timeline;   // optional [n_ctas][8] globaltimer stamps (profiling aid), or nullptr
 };
 
-constexpr int kMaxRowsSmem = 2048;   // (sessions x kv groups) prefix entries kept in shared memory
+constexpr int kMaxRowsSmem = 1024;   // (sessions x kv groups) prefix entries kept in shared memory
 
 // Launchers (defined in attn_simt.cu / attn_mma.cu).  n_ctas == 0 picks a default.
 int launch_attn_simt(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s);
