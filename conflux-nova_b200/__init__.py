@@ -97,6 +97,8 @@ SIGNATURES = {
     "nova_launch_rope_append_paged": (i32, [C.POINTER(KvShape), vp, vp, vp, i32, i32, i32, i64, vp, vp, vp, vp, vp, vp]),
     "nova_attn_scratch_floats": (sz, [C.POINTER(KvShape)]),
     "nova_launch_attn_decode_paged": (i32, [C.POINTER(KvShape), vp, vp, vp, vp, i32, i32, i32, vp, vp, vp]),
+    "nova_attn_static_scratch_max_heads": (sz, []),
+    "nova_launch_attn_decode_paged_static": (i32, [C.POINTER(KvShape), vp, vp, vp, vp, i32, i32, i32, vp, vp]),
     "nova_synth_key": (u64, [u64, u64, u64, u64]), "nova_synth_normal": (i32, [vp, sz, u64, u64, vp]),
     "nova_batch_create": (i32, [vp, c_i32p, i32, C.POINTER(vp)]), "nova_batch_destroy": (None, [vp]),
     "nova_batch_size": (i32, [vp]), "nova_batch_sync_positions": (i32, [vp, vp]),

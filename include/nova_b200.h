@@ -238,6 +238,25 @@ int nova_launch_attn_decode_paged(const nova_kv_shape* sh, const float* q,
                                   const int32_t* table, int layer, int nb, int n_keys,
                                   float* o, float* scratch, nova_stream_t s);
 
+/* No counterpart in the reference.  The same attention as nova_launch_attn_decode_paged for callers
+ * that cannot provide scratch memory because they may not allocate on the device at all (an engine
+ * whose start-up arena is spoken for and whose operators must not call cudaMalloc, code inside a
+ * stream capture, a plug-in host that forbids allocation).  The split-K scratch is a fixed array
+ * inside the library's device image; this call performs no cudaMalloc/cudaFree and calls nothing
+ * that allocates.
+ *   - Limit: n_heads <= nova_attn_static_scratch_max_heads() (64); more returns NOVA_ERR_TOO_LARGE.
+ *     The array (1.02 MiB) is held on every GPU that loads the library until the process exits.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ *     that first call outside of any stream capture.
+ *   - All calls on a device share the one array: calls whose kernels may overlap on the GPU (other
+ *     streams, concurrent host threads) race on it and must be ordered by the caller.  Nothing in
+ *     it needs clearing between calls; what a previous call left there is never read. */
+size_t nova_attn_static_scratch_max_heads(void);
+int nova_launch_attn_decode_paged_static(const nova_kv_shape* sh, const float* q,
+                                         const void* pool_k, const void* pool_v,
+                                         const int32_t* table, int layer, int nb, int n_keys,
+                                         float* o, nova_stream_t s);
+
 /* Synthetic inputs for tests and benchmarks (no counterpart in the reference, which feeds
  * real activations): dst[i] = value(key, first_index + i), an integer-only Irwin-Hall(12)
  * approximation of N(0,1) built from 64-bit hashes, bit-identical on host and device. */
