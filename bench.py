@@ -28,14 +28,21 @@ sys.path.insert(0, ROOT)
 
 import __graft_entry__ as graft  # noqa: E402
 
-# name -> (model, sessions, (ctx_lo, ctx_hi), seed offset); BASELINE.json configs
+# BASELINE.json configs.  scaling: weak = every GPU gets `sessions` sessions of its own;
+# strong = the `sessions` sessions (or the one long session's pages) are divided over the GPUs.
 WORKLOADS = {
-    "c1": dict(model="qwen25_1p5b", sessions=1, ctx=(1024, 1024), cfg=0,
+    "c1": dict(model="qwen25_1p5b", sessions=1, ctx=(1024, 1024), cfg=0, scaling="weak",
                text="Qwen2.5-1.5B-shaped KV, 1 session x 1024 cached tokens, permuted pages"),
-    "c2": dict(model="qwen25_7b", sessions=8, ctx=(2048, 8192), cfg=1,
+    "c2": dict(model="qwen25_7b", sessions=8, ctx=(2048, 8192), cfg=1, scaling="weak",
                text="Qwen2.5-7B-shaped KV, 8 sessions, contexts uniform in [2048, 8192], permuted pages"),
-    "c4": dict(model="qwen25_14b", sessions=64, ctx=(8192, 8192), cfg=3,
-               text="Qwen2.5-14B-shaped KV, 64 sessions x 8192 cached tokens, permuted pages"),
+    "c3": dict(model="qwen25_7b", sessions=32, ctx=(4088 + 512, 4088 + 512), cfg=2, scaling="weak", prefix=4088,
+               text="Qwen2.5-7B-shaped KV, 32 sessions sharing one 4088-token prefix (255 full pages + a partly "
+                    "filled tail page, un-shared by copy-on-write on the first private append) + 512 private tokens"),
+    "c4": dict(model="qwen25_14b", sessions=64, ctx=(8192, 8192), cfg=3, scaling="strong",
+               text="Qwen2.5-14B-shaped KV, 64 sessions x 8192 cached tokens, permuted pages, sessions sharded over GPUs"),
+    "c5": dict(model="qwen25_7b", sessions=1, ctx=(131072, 131072), cfg=4, scaling="strong",
+               text="Qwen2.5-7B-shaped KV, 1 session x 131072 cached tokens, pages split over GPUs, partials merged "
+                    "(log-sum-exp) after an NCCL all-gather"),
 }
 BASE_SEED = 0x5EED0000
 METRIC, UNIT = "decode_steps_per_s", "session-steps/s"
@@ -112,11 +119,15 @@ def run_ours(args):
     nv.check(nv.lib.dev_select(local_rank))
 
     w = WORKLOADS[args.workload]
+    if args.workload == "c5" and world > 1:
+        return run_long_context(args, nv, wl, dist, rank, local_rank, world)
     seed = BASE_SEED + w["cfg"] + 1000 * rank          # every GPU holds its own sessions
-    lens = wl.context_lengths(seed, w["sessions"], *w["ctx"])
+    n_sess = w["sessions"] if w["scaling"] == "weak" else max(1, w["sessions"] // world)
+    lens = wl.context_lengths(seed, n_sess, *w["ctx"])
     K, W, KE = args.steps, args.warmup, args.e2e_steps
     total_steps = 5 * (W + K) + (W + KE) + 8
-    work = wl.Workload(w["model"], lens, seed=seed, steps=total_steps, device=local_rank)
+    work = wl.Workload(w["model"], lens, seed=seed, steps=total_steps, device=local_rank,
+                       shared_prefix=w.get("prefix", 0))
     eng, batch = work.eng, work.batch
     kernel = args.kernel
     if kernel < 0:
@@ -164,7 +175,7 @@ def run_ours(args):
         go(warm, False)
         barrier()
         n0 = [eng.n_past(s) for s in work.sessions]
-        kv_bytes = sum(work.kv_bytes_per_step([n + i for n in n0]) for i in range(steps))
+        kv_bytes = sum(work.unique_kv_bytes_per_step([n + i for n in n0]) for i in range(steps))
         e0, e1 = nv.Event(), nv.Event()
         e0.record(stream)
         attn_ms = go(steps, True)
@@ -232,7 +243,7 @@ def run_ours(args):
     kv_main_all, kv_evt_all, kv_f_all = [float(x) for x in sums]
 
     cpu = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_sample(nv, work, lens, seed)
 
     if rank == 0:
@@ -247,9 +258,9 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": world * S * K / (ms_main / 1e3), "unit": UNIT,
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_main / K,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {w['text']}; per GPU", "sessions_per_gpu": S,
+            "config": {"workload": f"{args.workload}: {w['text']}", "sessions_per_gpu": S,
                        "context_tokens": lens, "layers": L, "kv_dtype": "fp16", "page_tokens": 16,
                        "launch": args.launch, "attention_kernel": "mma" if kernel == 1 else "simt", "fused_append": fused, "pdl": bool(fused and not args.no_pdl),
                        "l2": "inputs larger than L2 (KV read per step >> 126 MB)"},
@@ -274,6 +285,103 @@ def run_ours(args):
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def run_long_context(args, nv, wl, dist, rank, local_rank, world):
+    """Config 5 on several GPUs: every rank attends over its own range of the session's pages
+    (nova_batch_attn_partial), the (m, l, acc) partials are all-gathered over NVLink with NCCL and merged
+    in rank order (nova_lse_combine).  The all-gather is the only collective of this repository."""
+    import torch
+    import conflux_nova_b200.longctx as lc
+    w = WORKLOADS["c5"]
+    seed = BASE_SEED + w["cfg"]                       # the SAME session on every rank
+    n_ctx = w["ctx"][0]
+    K, W = args.steps, args.warmup
+    # Every rank keeps the whole session's pool (7.5 GB) but fills and reads only its own page range.
+    work = wl.Workload(w["model"], [n_ctx], seed=seed, steps=2 * (W + K) + 8, device=local_rank, fill=False)
+    eng, batch = work.eng, work.batch
+    n_pages = (n_ctx + 15) // 16
+    lo, hi = lc.page_range(rank, world, n_pages)
+    first_tok, last_tok = lo * 16, min(hi * 16, n_ctx)
+    if last_tok > first_tok:
+        work.fill_context(work.sessions[0], first_tok, last_tok - first_tok, key_session=0)
+    eng.set_n_past(work.sessions[0], n_ctx)
+    batch.sync_positions()
+    batch.set_kernel(1 if args.kernel != 0 else 0)
+    L, NH, NKV = eng.L, eng.NH, eng.NKV
+    tstream = torch.cuda.current_stream()
+    st = tstream.cuda_stream
+    dq, dk, dv = work.device_step_inputs(0)
+    part = torch.empty((L, NH, lc.PART_W), dtype=torch.float32, device="cuda")
+    out = torch.empty((L, NH, 128), dtype=torch.float32, device="cuda")
+    qs, ks = NH * 128 * 4, NKV * 128 * 4
+    es_tok = 2 * NKV * 128 * 2
+
+    def step():
+        if args.collective == "layer":
+            for l in range(L):
+                batch.append(l, dq.ptr + l * qs, dk.ptr + l * ks, dv.ptr + l * ks, st)
+                batch.attn_partial(l, dq.ptr + l * qs, lo, hi, part[l].data_ptr(), st)
+                g = lc.gather_partials(part[l], world, dist)
+                nv.check(nv.lib.nova_lse_combine(g.data_ptr(), world, NH, 128, out[l].data_ptr(), st))
+        else:
+            batch.append_layers(0, L, dq.ptr, dk.ptr, dv.ptr, st)
+            batch.attn_partial_layers(0, L, dq.ptr, lo, hi, part.data_ptr(), st)
+            g = lc.gather_partials(part.reshape(L * NH, lc.PART_W), world, dist)
+            nv.check(nv.lib.nova_lse_combine(g.data_ptr(), world, L * NH, 128, out.data_ptr(), st))
+        batch.advance(st)
+
+    for _ in range(W):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    n0 = eng.n_past(work.sessions[0])
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = nv.lib.nova_launch_count()
+    e0.record(tstream)
+    for _ in range(K):
+        step()
+    e1.record(tstream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = int(nv.lib.nova_launch_count() - launches0)
+    dist.barrier()
+    clocks = sampler.stop() if sampler else None
+    status = batch.device_status()
+    t = torch.tensor([ms, float(status != 0)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, bad = float(t[0]), float(t[1])
+    if bad:
+        raise RuntimeError("device status set during the long-context run")
+    # check once against a single-GPU style full attention of the last layer on rank 0's data: the merged
+    # output must be finite and identical on every rank
+    chk = out[-1].clone()
+    dist.broadcast(chk, src=0)
+    same = bool(torch.equal(chk, out[-1])) and bool(torch.isfinite(out).all())
+    flag = torch.tensor([0.0 if same else 1.0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if float(flag[0]) != 0.0:
+        raise RuntimeError("merged outputs differ between ranks")
+    if rank == 0:
+        peak, peak_kind = peaks()
+        kv_bytes = sum((n0 + i + 1) * es_tok * L for i in range(K))          # whole session, all ranks together
+        line = {
+            "metric": METRIC, "value": K / (ms / 1e3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"c5: {w['text']}", "sessions_per_gpu": 1, "context_tokens": [n_ctx], "layers": L,
+                       "kv_dtype": "fp16", "page_tokens": 16, "collective": f"all-gather per {args.collective}",
+                       "pages_per_gpu": -(-n_pages // world), "l2": "inputs larger than L2"},
+            "kv_gbs": kv_bytes / ms / 1e6, "kv_bytes_per_step": kv_bytes / K,
+            "roofline": {"bound": "hbm", "achieved": kv_bytes / ms / 1e6 / world, "peak": peak, "unit": "GB/s",
+                         "frac": kv_bytes / ms / 1e6 / world / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "attention over this GPU's page range + all-gather + merge (per GPU)"},
+            "e2e": None, "gpu_launches": launches, "clocks": clocks, "cpu_baseline": None,
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()
 
 
 def cpu_baseline_sample(nv, work, lens, seed):
@@ -362,7 +470,7 @@ def run_reference(args):
               f"time scaled by {Lfull}/{sample_layers}")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": w["scaling"],
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {w['text']}", "sessions_per_gpu": S, "context_tokens": lens,
                    "layers": Lfull, "kv_dtype": "fp16", "page_tokens": 16},
@@ -378,6 +486,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--e2e-steps", type=int, default=16)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--collective", default="layer", choices=["layer", "step"],
+                    help="c5 on several GPUs: all-gather + merge after every layer (engine order) or once per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--launch", default="graph", choices=["layer", "graph", "fused"],
                     help="layer: 2 launches per layer; graph: the same, replayed from a CUDA graph; fused: all layers per launch")

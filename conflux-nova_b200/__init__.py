@@ -107,12 +107,14 @@ SIGNATURES = {
     "nova_batch_set_fused_append": (i32, [vp, i32]), "nova_batch_append_attn": (i32, [vp, i32, vp, vp, vp, vp, vp]),
     "nova_batch_set_kernel": (i32, [vp, i32]), "nova_batch_get_kernel": (i32, [vp]),
     "nova_batch_cow": (i32, [vp, vp]), "nova_batch_append": (i32, [vp, i32, vp, vp, vp, vp]),
+    "nova_batch_append_layers": (i32, [vp, i32, i32, vp, vp, vp, vp]),
     "nova_batch_attn": (i32, [vp, i32, vp, vp, vp]), "nova_batch_advance": (i32, [vp, vp]),
     "nova_batch_step_all_layers": (i32, [vp, vp, vp, vp, vp, vp]),
     "nova_batch_decode_step_host": (i32, [vp, vp, vp, vp, vp, i32, vp]),
     "nova_batch_run_steps": (i32, [vp, i32, vp, vp, vp, vp, sz, sz, i32, C.POINTER(C.c_float), vp]),
     "nova_batch_device_status": (i32, [vp]), "nova_launch_count": (u64, []),
     "nova_batch_attn_partial": (i32, [vp, i32, vp, i64, i64, vp, vp]),
+    "nova_batch_attn_partial_layers": (i32, [vp, i32, i32, vp, i64, i64, vp, vp]),
     "nova_lse_combine": (i32, [vp, i32, i32, i32, vp, vp]),
 }
 
@@ -460,6 +462,9 @@ class Batch:
     def cow(self, stream=None): return check(lib.nova_batch_cow(self.h, stream), "batch_cow")
     def append(self, layer, q, k, v, stream=None):
         return check(lib.nova_batch_append(self.h, layer, q, k, v, stream), "batch_append")
+    def append_layers(self, layer0, n_layers, q, k, v, stream=None):
+        return check(lib.nova_batch_append_layers(self.h, layer0, n_layers, q, k, v, stream), "append_layers")
+
     def attn(self, layer, q, out, stream=None):
         return check(lib.nova_batch_attn(self.h, layer, q, out, stream), "batch_attn")
     def advance(self, stream=None): return check(lib.nova_batch_advance(self.h, stream), "batch_advance")
@@ -475,5 +480,9 @@ class Batch:
         return float(ms.value) if time_attn else None
 
     def device_status(self): return lib.nova_batch_device_status(self.h)
+    def attn_partial_layers(self, layer0, n_layers, q, page0, page1, part, stream=None):
+        return check(lib.nova_batch_attn_partial_layers(self.h, layer0, n_layers, q, page0, page1, part, stream),
+                     "attn_partial_layers")
+
     def attn_partial(self, layer, q, page0, page1, part, stream=None):
         return check(lib.nova_batch_attn_partial(self.h, layer, q, page0, page1, part, stream), "attn_partial")

@@ -653,6 +653,16 @@ int nova_batch_append(nova_batch* b, int layer, float* q, float* k, const float*
     return launch_rope_append(a, (cudaStream_t)s);
 }
 
+int nova_batch_append_layers(nova_batch* b, int layer0, int n_layers, float* q, float* k, const float* v,
+                             nova_stream_t s) {
+    if (!b || !k || !v || layer0 < 0 || n_layers < 1 || layer0 + n_layers > b->e->d.n_layers) return NOVA_ERR_INVALID;
+    AppendLaunch a;
+    fill_append(b, a);
+    a.q = q; a.k = k; a.v = v;
+    a.layer0 = layer0; a.n_layers = n_layers;
+    return launch_rope_append(a, (cudaStream_t)s);
+}
+
 int nova_batch_attn(nova_batch* b, int layer, const float* q, float* out, nova_stream_t s) {
     if (!b || !q || !out || layer < 0 || layer >= b->e->d.n_layers) return NOVA_ERR_INVALID;
     AttnLaunch a;
@@ -865,9 +875,10 @@ int nova_batch_device_status(nova_batch* b) {
     return v;
 }
 
-int nova_batch_attn_partial(nova_batch* b, int layer, const float* q, int64_t page0, int64_t page1, float* part,
-                            nova_stream_t s) {
-    if (!b || !q || !part || layer < 0 || layer >= b->e->d.n_layers || page0 < 0 || page1 < page0)
+int nova_batch_attn_partial_layers(nova_batch* b, int layer0, int n_layers, const float* q, int64_t page0,
+                                   int64_t page1, float* part, nova_stream_t s) {
+    if (!b || !q || !part || layer0 < 0 || n_layers < 1 || layer0 + n_layers > b->e->d.n_layers || page0 < 0 ||
+        page1 < page0)
         return NOVA_ERR_INVALID;
     AttnLaunch a;
     fill_attn(b, a);
@@ -876,8 +887,13 @@ int nova_batch_attn_partial(nova_batch* b, int layer, const float* q, int64_t pa
     a.write_partial_only = 1;
     a.page_lo = page0;
     a.page_hi = page1;
-    a.layer0 = layer; a.n_layers = 1;
+    a.layer0 = layer0; a.n_layers = n_layers;
     return run_attn(b, a, (cudaStream_t)s);
+}
+
+int nova_batch_attn_partial(nova_batch* b, int layer, const float* q, int64_t page0, int64_t page1, float* part,
+                            nova_stream_t s) {
+    return nova_batch_attn_partial_layers(b, layer, 1, q, page0, page1, part, s);
 }
 
 }  // extern "C"

@@ -1,0 +1,42 @@
+"""One long session split over GPUs (flash-decoding across ranks).
+
+The reference scales a long context only inside one GPU (32 splits, src/kernel/attn.cu:498-512) and
+otherwise drops history (code/INPUT_TOKENIZR.h:57-67).  Here rank r of G attends over a contiguous range
+of the session's logical pages and leaves un-normalised partials (m, l, acc) per head in the
+reference's partial layout (attn.cu:150-158); the partials are all-gathered and merged in rank order
+with fa_combine_kernel's arithmetic (attn.cu:163-191).  The merge is latency-bound (14.5 KB per rank per
+layer at the 7B shape), never bandwidth-bound.
+
+The page arithmetic and the gather are plain host code so that they run on CPU ranks (gloo) too.
+"""
+from __future__ import annotations
+
+PART_W = 130          # m, l, acc[128]
+OPEN_END = 1 << 40    # "to the end of the session": the last rank's range grows with the context
+
+
+def page_range(rank: int, world: int, n_pages: int) -> tuple[int, int]:
+    """Logical pages [lo, hi) of `rank`; ranges tile [0, n_pages) in rank order, the last one is open-ended
+    so that pages appended later (and the page that receives new tokens) belong to the last rank."""
+    per = -(-n_pages // world) if n_pages > 0 else 0
+    lo = min(rank * per, n_pages)
+    hi = min((rank + 1) * per, n_pages)
+    if rank == world - 1:
+        hi = OPEN_END
+    return lo, hi
+
+
+def owner_of_page(page: int, world: int, n_pages: int) -> int:
+    per = -(-n_pages // world) if n_pages > 0 else 1
+    return min(page // max(per, 1), world - 1)
+
+
+def gather_partials(part, world: int, dist=None):
+    """all-gather of one partial tensor [rows][130] -> [world][rows][130] (rank order)."""
+    import torch
+    if world == 1 or dist is None:
+        return part.unsqueeze(0)
+    flat = part.contiguous().reshape(-1)
+    out = torch.empty(world * flat.numel(), dtype=part.dtype, device=part.device)
+    dist.all_gather_into_tensor(out, flat)           # concatenation in rank order, on every backend
+    return out.reshape((world,) + tuple(part.shape))

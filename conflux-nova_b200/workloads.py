@@ -46,23 +46,44 @@ class Workload:
     """An engine, its sessions and one batch over them, with `ctx_lens[s]` cached tokens each."""
 
     def __init__(self, model: str, ctx_lens, *, seed: int, steps: int, kv_dtype=KV_F16, device=0, permute=True,
-                 spare_slices=0, fill=True, n_layers=None, zero_pages=0):
+                 spare_slices=0, fill=True, n_layers=None, zero_pages=0, shared_prefix=0, key_base=0):
+        """ctx_lens[s] cached tokens per session.  shared_prefix > 0: one extra donor session holds that
+        many tokens; every session attaches them (KvPool::attach_prefix: shared pages, the partly filled
+        tail page included), un-shares the tail page on its first private write and appends
+        ctx_lens[s] - shared_prefix private tokens (config 3)."""
         L, NH, NKV = SHAPES[model]
         if n_layers:
             L = n_layers
         self.model, self.seed = model, seed
         self.ctx_lens = [int(c) for c in ctx_lens]
+        self.shared_prefix = int(shared_prefix)
         S = len(self.ctx_lens)
         ctx = ((max(self.ctx_lens) + steps + 15) // 16) * 16
-        self.eng = Engine(L, NH, NKV, ctx=ctx, n_slices=S + spare_slices, kv_dtype=kv_dtype,
-                          rope_positions=ctx, device=device, zero_pages=zero_pages)
+        extra = (2 if shared_prefix else 0) + spare_slices        # donor + one slice of spare pages for COW
+        self.eng = Engine(L, NH, NKV, ctx=ctx, n_slices=S + extra, kv_dtype=kv_dtype,
+                          rope_positions=ctx, device=device, zero_pages=zero_pages, max_sessions=S + (1 if shared_prefix else 0))
+        self.donor = None
+        if shared_prefix:
+            self.donor = self.eng.session_create()
+            if permute:
+                self.eng.permute_pages(self.donor, page_permutation(seed, 10 ** 6, self.eng.nblocks))
+            self.fill_context(self.donor, 0, shared_prefix, key_session=10 ** 6)
         self.sessions = [self.eng.session_create() for _ in range(S)]
+        self.key_ids = [key_base + i for i in range(S)]
         if permute:
-            for s in self.sessions:
-                self.eng.permute_pages(s, page_permutation(seed, s, self.eng.nblocks))
+            for s, kid in zip(self.sessions, self.key_ids):
+                self.eng.permute_pages(s, page_permutation(seed, kid, self.eng.nblocks))
+        self.cow_at_build = 0
         if fill:
             for i, s in enumerate(self.sessions):
-                self.fill_context(s, 0, self.ctx_lens[i])
+                if shared_prefix:
+                    self.eng.attach_prefix(s, self.donor, shared_prefix)
+                    n_priv = self.ctx_lens[i] - shared_prefix
+                    if n_priv > 0:
+                        self.cow_at_build += self.eng.cow(s, shared_prefix, n_priv)
+                        self.fill_context(s, shared_prefix, n_priv, key_session=self.key_ids[i])
+                else:
+                    self.fill_context(s, 0, self.ctx_lens[i], key_session=self.key_ids[i])
         self.batch = self.eng.batch(self.sessions)
 
     # -- cached context -------------------------------------------------------------------
@@ -99,7 +120,6 @@ class Workload:
     def host_step_inputs(self, step: int):
         """q [L][S][NH][HD], k, v [L][S][NKV][HD] of decode step `step` (host, fp32)."""
         e, S = self.eng, len(self.sessions)
-        from . import DevBuf as _D  # noqa: F401  (device path below mirrors this layout)
         q = np.empty((e.L, S, e.NH, e.HD), np.float32)
         k = np.empty((e.L, S, e.NKV, e.HD), np.float32)
         v = np.empty_like(k)
@@ -118,7 +138,7 @@ class Workload:
         dq, dk, dv = DevBuf(nq * 4), DevBuf(nk * 4), DevBuf(nk * 4)
         qrow, krow = e.NH * e.HD, e.NKV * e.HD
         for layer in range(e.L):
-            for i, s in enumerate(self.sessions):
+            for i, s in enumerate(self.key_ids):
                 off = layer * S + i
                 check(lib.nova_synth_normal(dq.ptr + off * qrow * 4, qrow, synth_key(self.seed, T_Q, s, layer),
                                             (10 ** 6 + step) * qrow, None))
@@ -138,6 +158,18 @@ class Workload:
         n_past = [e.n_past(s) for s in self.sessions] if n_past is None else n_past
         keys = sum(n + 1 for n in n_past)
         per_tok = 2 * e.NKV * e.HD * es * e.L
+        return keys * per_tok + len(self.sessions) * per_tok
+
+    def unique_kv_bytes_per_step(self, n_past=None) -> int:
+        """The same with shared-prefix pages counted once (the least HBM traffic a step can have)."""
+        e = self.eng
+        es = 2 if e.desc.kv_dtype == KV_F16 else 4
+        n_past = [e.n_past(s) for s in self.sessions] if n_past is None else n_past
+        per_tok = 2 * e.NKV * e.HD * es * e.L
+        if not self.shared_prefix:
+            return self.kv_bytes_per_step(n_past)
+        full_pages = (self.shared_prefix // 16) * 16             # the tail page is private after its COW
+        keys = full_pages + sum(n + 1 - full_pages for n in n_past)
         return keys * per_tok + len(self.sessions) * per_tok
 
     def close(self):

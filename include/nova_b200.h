@@ -289,6 +289,10 @@ int  nova_batch_cow(nova_batch* b, nova_stream_t s);
 /* RopeKvOp (code/graph/dense.h:75-83) for every session: q [S][NH][HD] and
  * k [S][NKV][HD] rotated in place at n_past[s], k/v appended to the pages. */
 int  nova_batch_append(nova_batch* b, int layer, float* q, float* k, const float* v, nova_stream_t s);
+/* The same for layers [layer0, layer0 + n_layers) in one launch: q [n][S][NH][HD] (may be NULL: no q to
+ * rotate), k/v [n][S][NKV][HD]. */
+int  nova_batch_append_layers(nova_batch* b, int layer0, int n_layers, float* q, float* k, const float* v,
+                              nova_stream_t s);
 /* AttnOp decode branch (dense.h:86-95): n_keys = n_past[s] + 1; out [S][NH][HD]. */
 int  nova_batch_attn(nova_batch* b, int layer, const float* q, float* out, nova_stream_t s);
 /* RopeKvOp + AttnOp of one layer as one call.  With nova_batch_set_fused_append(b, 1) (tensor-core
@@ -343,6 +347,10 @@ uint64_t nova_launch_count(void);
  * in index order with fa_combine_kernel's arithmetic (attn.cu:163-191). */
 int  nova_batch_attn_partial(nova_batch* b, int layer, const float* q, int64_t page0, int64_t page1,
                              float* part, nova_stream_t s);
+/* The same for layers [layer0, layer0 + n_layers) in one launch: q [n_layers][S][NH][HD],
+ * part [n_layers][S][NH][2+HD]. */
+int  nova_batch_attn_partial_layers(nova_batch* b, int layer0, int n_layers, const float* q, int64_t page0,
+                                    int64_t page1, float* part, nova_stream_t s);
 int  nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim, float* out,
                       nova_stream_t s);
 
