@@ -44,6 +44,10 @@ WORKLOADS = {
                text="Qwen2.5-7B-shaped KV, 1 session x 131072 cached tokens, pages split over GPUs, partials merged "
                     "(log-sum-exp) after an NCCL all-gather"),
 }
+# dram__bytes_read + dram__bytes_write per attention launch from the ncu captures summarised in
+# profiles/attn_mma_kernel_c2.md (split + merge kernels; config 2 only)
+NCU_TRAFFIC = {("c2", "layer"): 91.49e6 + 3.46e6 + 2.33e6, ("c2", "graph"): 91.49e6 + 3.46e6 + 2.33e6,
+               ("c2", "fused"): 2.5634e9 + 7.6e6}
 BASE_SEED = 0x5EED0000
 METRIC, UNIT = "decode_steps_per_s", "session-steps/s"
 
@@ -268,7 +272,8 @@ def run_ours(args):
             "kv_gbs": kv_main_all / ms_main / 1e6,
             "kv_bytes_per_step": kv_main / K,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC.get((args.workload, args.launch)),
+                         "peak_kind": peak_kind,
                          "kernel": "attention (%s)" % ("all layers per launch" if mode == 0 else "one layer per launch"),
                          "launch_us": launch_us, "algorithmic_bytes_per_launch": per_launch_bytes,
                          "isolated_launch_us": isolated_us,
