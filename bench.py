@@ -250,6 +250,10 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_sample(nv, work, lens, seed)
 
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.no_ref_gpu and args.workload in ("c1", "c2"):
+        ref_gpu = reference_gpu_sample(nv, work)
+
     if rank == 0:
         peak, peak_kind = peaks()
         n_attn = K * (1 if mode == 0 else L)
@@ -286,6 +290,7 @@ def run_ours(args):
             "gpu_launches": launches,
             "clocks": clocks,
             "cpu_baseline": cpu,
+            "reference_kernels_on_this_gpu": ref_gpu,
         }
         print(json.dumps(line))
     if dist is not None:
@@ -387,6 +392,59 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
         }
         print(json.dumps(line))
     dist.destroy_process_group()
+
+
+def reference_gpu_sample(nv, work):
+    """The reference's own CUDA kernels for this path (src/kernel/rope.cu, elem.cu, attn.cu compiled
+    unmodified for sm_100a, oracle/_ref) on this GPU, on a bounded sample of the same workload: one layer,
+    every session, in the reference's call order (per session: rope_batch, kv_store_paged, attn_decode_paged
+    = split + combine), fp32 pools holding the same values.  Time scaled by the layer count."""
+    from oracle import binding as ob
+    model = {"qwen25_7b": "qwen25_7b", "qwen25_1p5b": "qwen25_1p5b"}.get(work.model)
+    g = ob.ref_gpu(model) if model else None
+    if g is None:
+        return None
+    eng = work.eng
+    S, NH, NKV = len(work.sessions), eng.NH, eng.NKV
+    n = eng.nb * eng.page_bytes // 2
+    pk = nv.to_device(nv.download_ptr(eng.k_base, np.float16, n).astype(np.float32))     # layer 0 only
+    pv = nv.to_device(nv.download_ptr(eng.v_base, np.float16, n).astype(np.float32))
+    rng = np.random.default_rng(2)
+    q = nv.to_device(rng.standard_normal((S, NH, 128)).astype(np.float32))
+    k = nv.to_device(rng.standard_normal((S, NKV, 128)).astype(np.float32))
+    v = nv.to_device(rng.standard_normal((S, NKV, 128)).astype(np.float32))
+    o = nv.DevBuf(S * NH * 128 * 4)
+    scr = nv.DevBuf(NH * 32 * 130 * 4)
+    cs, sn = nv.lib.nova_rope_cos(eng.h), nv.lib.nova_rope_sin(eng.h)      # long enough for every position
+    pos = [eng.n_past(s) for s in work.sessions]
+    tabs = [nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(s)) for s in work.sessions]
+    st = nv.Stream()
+
+    def layer_pass():
+        for i in range(S):
+            qi, ki, vi = q.ptr + i * NH * 512, k.ptr + i * NKV * 512, v.ptr + i * NKV * 512
+            g.ref_gpu_rope_batch(qi, ki, 1, pos[i], cs, sn, st.h)
+            g.ref_gpu_kv_store_paged(pk.ptr, pv.ptr, tabs[i], 0, eng.nb, 1, pos[i], ki, vi, st.h)
+            g.ref_gpu_attn_decode_paged(qi, pk.ptr, pv.ptr, tabs[i], 0, eng.nb, pos[i] + 1, o.ptr + i * NH * 512,
+                                        scr.ptr, st.h)
+    for _ in range(3):
+        layer_pass()
+    st.sync()
+    reps = 10
+    e0, e1 = nv.Event(), nv.Event()
+    e0.record(st)
+    for _ in range(reps):
+        layer_pass()
+    e1.record(st)
+    e1.sync()
+    ms_layer = e0.elapsed_ms(e1) / reps
+    ok = g.ref_gpu_last_error() == 0
+    for b in (pk, pv, q, k, v, o, scr):
+        b.free()
+    ms_step = ms_layer * eng.L
+    return {"value": S / (ms_step / 1e3), "unit": UNIT, "ms_per_step": ms_step, "ok": ok,
+            "sample": f"{reps} x one layer of {eng.L}, all {S} sessions, fp32 pools, the reference's launch order "
+                      f"(4 launches per session per layer); time scaled by {eng.L}"}
 
 
 def cpu_baseline_sample(nv, work, lens, seed):
@@ -502,6 +560,7 @@ def main():
     ap.add_argument("--row-setup", type=int, default=-1, help="work-split weight of a session start, in pages")
     ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own kernels (sm_100a build)")
     ap.add_argument("--quick", action="store_true",
                     help="only the main timed region (for profiler captures): no other modes, e2e or CPU baseline")
     args = ap.parse_args()
