@@ -63,6 +63,8 @@ struct nova_batch {
     int graph_kernel = -1;
     unsigned long long* timeline = nullptr;   // caller-owned profiling buffer, see nova_batch_set_timeline
     std::vector<cudaEvent_t> ev;       // event pool for per-launch timing
+    cudaStream_t s_in = nullptr, s_out = nullptr;      // copy streams of the host-buffer step
+    cudaEvent_t ev_in[4] = {}, ev_cmp[4] = {}, ev_out = nullptr, ev_begin = nullptr;
 };
 
 namespace {
@@ -570,6 +572,14 @@ void nova_batch_destroy(nova_batch* b) {
     cudaFree(b->dout);
     if (b->graph) cudaGraphExecDestroy(b->graph);
     for (cudaEvent_t e : b->ev) cudaEventDestroy(e);
+    for (int i = 0; i < 4; ++i) {
+        if (b->ev_in[i]) cudaEventDestroy(b->ev_in[i]);
+        if (b->ev_cmp[i]) cudaEventDestroy(b->ev_cmp[i]);
+    }
+    if (b->ev_out) cudaEventDestroy(b->ev_out);
+    if (b->ev_begin) cudaEventDestroy(b->ev_begin);
+    if (b->s_in) cudaStreamDestroy(b->s_in);
+    if (b->s_out) cudaStreamDestroy(b->s_out);
     delete b;
 }
 
@@ -704,26 +714,66 @@ int nova_batch_decode_step_host(nova_batch* b, const float* q, const float* k, c
     if (!b || !q || !k || !v || !out) return NOVA_ERR_INVALID;
     nova_engine* e = b->e;
     cudaStream_t st = (cudaStream_t)s;
-    const size_t L = (size_t)e->d.n_layers, S = (size_t)b->n;
-    const size_t q_elems = L * S * e->d.n_heads * kHeadDim, kv_elems = L * S * e->d.n_kv_heads * kHeadDim;
+    const int L = e->d.n_layers;
+    const size_t S = (size_t)b->n;
+    const size_t qs = S * e->d.n_heads * kHeadDim, ks = S * e->d.n_kv_heads * kHeadDim;   // floats per layer
     int rc = ensure_staging(b);
     if (rc != NOVA_OK) return rc;
     rc = nova_batch_cow(b, s);
     if (rc < 0) return rc;
-    NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq, q, q_elems * 4, cudaMemcpyHostToDevice, st));
-    NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk, k, kv_elems * 4, cudaMemcpyHostToDevice, st));
-    NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv, v, kv_elems * 4, cudaMemcpyHostToDevice, st));
-    if (per_layer_launch) {
-        const size_t qs = S * e->d.n_heads * kHeadDim, ks = S * e->d.n_kv_heads * kHeadDim;
-        for (int l = 0; l < e->d.n_layers; ++l) {
-            rc = nova_batch_append_attn(b, l, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, s);
-            if (rc != NOVA_OK) return rc;
-        }
-    } else {
+    if (!per_layer_launch) {
+        NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq, q, L * qs * 4, cudaMemcpyHostToDevice, st));
+        NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk, k, L * ks * 4, cudaMemcpyHostToDevice, st));
+        NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv, v, L * ks * 4, cudaMemcpyHostToDevice, st));
         rc = nova_batch_step_all_layers(b, b->dq, b->dk, b->dv, b->dout, s);
         if (rc != NOVA_OK) return rc;
+        NOVA_CUDA_TRY(cudaMemcpyAsync(out, b->dout, L * qs * 4, cudaMemcpyDeviceToHost, st));
+    } else {
+        // Layers are issued in order; their inputs arrive in up to four growing chunks on a copy stream
+        // and finished outputs leave on another, so that only the first chunk's upload and the last
+        // chunk's download are not hidden behind the attention launches.
+        if (!b->s_in) {
+            NOVA_CUDA_TRY(cudaStreamCreateWithFlags(&b->s_in, cudaStreamNonBlocking));
+            NOVA_CUDA_TRY(cudaStreamCreateWithFlags(&b->s_out, cudaStreamNonBlocking));
+            for (int i = 0; i < 4; ++i) {
+                NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_in[i], cudaEventDisableTiming));
+                NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_cmp[i], cudaEventDisableTiming));
+            }
+            NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_out, cudaEventDisableTiming));
+            NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_begin, cudaEventDisableTiming));
+        }
+        int cut[5] = {0, L < 2 ? L : 2, L < 6 ? L : 6, L < 14 ? L : 14, L};
+        NOVA_CUDA_TRY(cudaEventRecord(b->ev_begin, st));              // the COW copies above precede everything
+        NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_in, b->ev_begin, 0));
+        NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_out, b->ev_begin, 0));
+        for (int c = 0; c < 4; ++c) {
+            const int l0 = cut[c], n = cut[c + 1] - cut[c];
+            if (n <= 0) continue;
+            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq + l0 * qs, q + l0 * qs, n * qs * 4, cudaMemcpyHostToDevice, b->s_in));
+            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk + l0 * ks, k + l0 * ks, n * ks * 4, cudaMemcpyHostToDevice, b->s_in));
+            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv + l0 * ks, v + l0 * ks, n * ks * 4, cudaMemcpyHostToDevice, b->s_in));
+            NOVA_CUDA_TRY(cudaEventRecord(b->ev_in[c], b->s_in));
+        }
+        for (int c = 0; c < 4; ++c) {
+            const int l0 = cut[c], l1 = cut[c + 1];
+            if (l1 <= l0) continue;
+            NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_in[c], 0));
+            for (int l = l0; l < l1; ++l) {
+                if (use_fused(b))   // dependent launch only inside a chunk: an event wait sits between chunks
+                    rc = run_attn_fused(b, l, 1, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, st,
+                                        b->pdl && l > l0);
+                else
+                    rc = nova_batch_append_attn(b, l, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, s);
+                if (rc != NOVA_OK) return rc;
+            }
+            NOVA_CUDA_TRY(cudaEventRecord(b->ev_cmp[c], st));
+            NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_out, b->ev_cmp[c], 0));
+            NOVA_CUDA_TRY(cudaMemcpyAsync(out + l0 * qs, b->dout + l0 * qs, (size_t)(l1 - l0) * qs * 4,
+                                          cudaMemcpyDeviceToHost, b->s_out));
+        }
+        NOVA_CUDA_TRY(cudaEventRecord(b->ev_out, b->s_out));
+        NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_out, 0));
     }
-    NOVA_CUDA_TRY(cudaMemcpyAsync(out, b->dout, q_elems * 4, cudaMemcpyDeviceToHost, st));
     rc = nova_batch_advance(b, s);
     if (rc != NOVA_OK) return rc;
     NOVA_CUDA_TRY(cudaStreamSynchronize(st));
