@@ -131,7 +131,7 @@ def run_ours(args):
     K, W, KE = args.steps, args.warmup, args.e2e_steps
     total_steps = 5 * (W + K) + (W + KE) + 8
     work = wl.Workload(w["model"], lens, seed=seed, steps=total_steps, device=local_rank,
-                       shared_prefix=w.get("prefix", 0))
+                       shared_prefix=w.get("prefix", 0), kv_dtype=nv.KV_F32 if args.kv == "f32" else nv.KV_F16)
     eng, batch = work.eng, work.batch
     kernel = args.kernel
     if kernel < 0:
@@ -196,7 +196,7 @@ def run_ours(args):
     launches = int(nv.lib.nova_launch_count() - launches0) * K // (K + W)
     if args.quick:
         if rank == 0:
-            print(json.dumps({"quick": True, "launch": args.launch, "fused_append": fused, "pdl": bool(fused and not args.no_pdl), "ms_per_step": ms_main / K,
+            print(json.dumps({"quick": True, "launch": args.launch, "fused_append": fused, "pdl": bool(fused and not args.no_pdl), "kv": args.kv, "kernel": kernel, "ms_per_step": ms_main / K,
                               "kv_gbs": kv_main / ms_main / 1e6, "gpu_launches": launches}))
         return
     # the same K steps again with an event pair around every attention launch: the dominant kernel's own time
@@ -267,9 +267,9 @@ def run_ours(args):
             "metric": METRIC, "value": world * S * K / (ms_main / 1e3), "unit": UNIT,
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_main / K,
             "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic",
+            "dtype": args.kv, "data": "synthetic",
             "config": {"workload": f"{args.workload}: {w['text']}", "sessions_per_gpu": S,
-                       "context_tokens": lens, "layers": L, "kv_dtype": "fp16", "page_tokens": 16,
+                       "context_tokens": lens, "layers": L, "kv_dtype": "fp16" if args.kv == "f16" else "fp32", "page_tokens": 16,
                        "launch": args.launch, "attention_kernel": "mma" if kernel == 1 else "simt", "fused_append": fused, "pdl": bool(fused and not args.no_pdl),
                        "l2": "inputs larger than L2 (KV read per step >> 126 MB)"},
             "batch_steps_per_s": K / (ms_main / 1e3),
@@ -559,6 +559,8 @@ def main():
                     help="keep RoPE+append as its own launch instead of doing it inside the attention launch")
     ap.add_argument("--row-setup", type=int, default=-1, help="work-split weight of a session start, in pages")
     ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between layers")
+    ap.add_argument("--kv", default="f16", choices=["f16", "f32"],
+                    help="KV pool element type (f32 = the reference's own format; SIMT kernel)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own kernels (sm_100a build)")
     ap.add_argument("--quick", action="store_true",

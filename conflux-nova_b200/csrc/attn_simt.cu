@@ -7,7 +7,8 @@
 // V row is read from HBM once (the reference reads it G times).  Each lane owns 4 of the 128
 // dims; a key costs G 4-term dot partials, one transposing butterfly (9 shuffles + G
 // broadcasts instead of 5G), an online softmax in the exp2 domain and 4G fp32 FMAs on V.
-// Pages are walked straight from global memory with 8/16-byte loads, two keys in flight.
+// Pages are walked straight from global memory with 8/16-byte loads, two batches of 8 (fp16) or
+// 4 (fp32) keys in flight per warp.
 // Work is cut stream-K style over pages (attn_plan.cuh); rows split over several CTAs leave
 // partials for the combine kernel (attn_combine.cu) — no flags, no spinning anywhere.
 //
@@ -34,6 +35,27 @@ __device__ __forceinline__ void load4(const __half* p, float (&x)[4]) {
     const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
     x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
 }
+
+// Raw (unconverted) 4-element pieces of a K or V row, kept in registers while later loads are in flight.
+template <typename KvT> struct RawRow;
+template <> struct RawRow<float> {
+    using type = float4;
+    static constexpr int kBatch = 4;       // keys per batch: 2 batches x (K + V) x 4 regs = 64 registers
+    __device__ static __forceinline__ type load(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+    __device__ static __forceinline__ type zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ static __forceinline__ void unpack(const type& t, float (&x)[4]) { x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w; }
+};
+template <> struct RawRow<__half> {
+    using type = uint2;
+    static constexpr int kBatch = 8;
+    __device__ static __forceinline__ type load(const __half* p) { return __ldcs(reinterpret_cast<const uint2*>(p)); }
+    __device__ static __forceinline__ type zero() { return make_uint2(0u, 0u); }
+    __device__ static __forceinline__ void unpack(const type& t, float (&x)[4]) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+        x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+    }
+};
 
 // Sum v[g] over the 32 lanes for up to 8 values at once: after three exchange-and-halve
 // steps each lane holds one value's partial for head (lane>>2)&7, two more steps finish it.
@@ -151,27 +173,54 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
         HeadState<G> st;
         st.reset();
 
-        for (int pg = 0; pg < sg.page_count; ++pg) {
-            const int page = first_page + sg.page_first + pg;
-            const int phys = __ldg(table + page);
+        // Keys are taken in batches of B (half or a quarter of a page).  The K and V pieces of batch j+1
+        // are requested before batch j is used, so each warp keeps two batches of loads in flight; with
+        // only the two keys of the inner step in flight the kernel was bound by memory latency.
+        using RR = RawRow<KvT>;
+        constexpr int B = RR::kBatch, BPP = kKvBlock / B;
+        const int n_batches = sg.page_count * BPP;
+        int chunk = -1, phys_lane = 0;
+        typename RR::type rk[2][B], rv[2][B];
+        int kc[2] = {0, 0};
+        auto fetch = [&](int j, typename RR::type (&bk)[B], typename RR::type (&bv)[B], int& cnt) {
+            cnt = 0;
+#pragma unroll
+            for (int i = 0; i < B; ++i) { bk[i] = RR::zero(); bv[i] = RR::zero(); }
+            if (j >= n_batches) return;
+            const int pg = j / BPP, slot0 = (j - pg * BPP) * B;
+            if ((pg >> 5) != chunk) {                 // 32 block-table entries at a time, one per lane
+                chunk = pg >> 5;
+                const int idx = (chunk << 5) + lane;
+                phys_lane = idx < sg.page_count ? __ldg(table + first_page + sg.page_first + idx) : 0;
+            }
+            const int phys = __shfl_sync(0xffffffffu, phys_lane, pg & 31);
             if (phys < 0 || phys >= a.nb) {
                 if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
-                continue;
+                return;
             }
-            int kcount = n_keys - page * kKvBlock;
-            if (kcount > kKvBlock) kcount = kKvBlock;
-            const int64_t base = (((int64_t)layer * a.nb + phys) * kKvBlock) * row_elems + (int64_t)kvh * kHeadDim + 4 * lane;
-            const KvT* kp = pool_k + base;
-            const KvT* vp = pool_v + base;
-            for (int slot = 0; slot < kcount; slot += 2) {
-                const bool two = slot + 1 < kcount;
-                float k0[4], k1[4] = {0.f, 0.f, 0.f, 0.f}, v0[4], v1[4] = {0.f, 0.f, 0.f, 0.f};
-                load4(kp + (int64_t)slot * row_elems, k0);
-                load4(vp + (int64_t)slot * row_elems, v0);
-                if (two) {
-                    load4(kp + (int64_t)(slot + 1) * row_elems, k1);
-                    load4(vp + (int64_t)(slot + 1) * row_elems, v1);
+            const int page = first_page + sg.page_first + pg;
+            int kcount = n_keys - page * kKvBlock - slot0;
+            if (kcount > B) kcount = B;
+            if (kcount <= 0) return;
+            cnt = kcount;
+            const int64_t base = (((int64_t)layer * a.nb + phys) * kKvBlock + slot0) * row_elems + (int64_t)kvh * kHeadDim + 4 * lane;
+#pragma unroll
+            for (int i = 0; i < B; ++i)
+                if (i < kcount) {
+                    bk[i] = RR::load(pool_k + base + (int64_t)i * row_elems);
+                    bv[i] = RR::load(pool_v + base + (int64_t)i * row_elems);
                 }
+        };
+        auto consume = [&](const typename RR::type (&bk)[B], const typename RR::type (&bv)[B], int cnt) {
+#pragma unroll
+            for (int i = 0; i < B; i += 2) {
+                if (i >= cnt) break;
+                const bool two = i + 1 < cnt;
+                float k0[4], k1[4], v0[4], v1[4];
+                RR::unpack(bk[i], k0);
+                RR::unpack(bk[i + 1], k1);
+                RR::unpack(bv[i], v0);
+                RR::unpack(bv[i + 1], v1);
                 float d0[8], d1[8];
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
@@ -200,6 +249,13 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
                     st.m[g] = mn;
                 }
             }
+        };
+        fetch(0, rk[0], rv[0], kc[0]);
+        for (int j = 0; j < n_batches; j += 2) {
+            fetch(j + 1, rk[1], rv[1], kc[1]);
+            consume(rk[0], rv[0], kc[0]);
+            fetch(j + 2, rk[0], rv[0], kc[0]);
+            consume(rk[1], rv[1], kc[1]);
         }
 
         const int n_contrib = sg.c_last - sg.c_first + 1;
