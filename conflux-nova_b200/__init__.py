@@ -109,6 +109,8 @@ SIGNATURES = {
     "nova_batch_cow": (i32, [vp, vp]), "nova_batch_append": (i32, [vp, i32, vp, vp, vp, vp]),
     "nova_batch_append_layers": (i32, [vp, i32, i32, vp, vp, vp, vp]),
     "nova_batch_attn": (i32, [vp, i32, vp, vp, vp]), "nova_batch_advance": (i32, [vp, vp]),
+    "nova_batch_prefill_max_tokens": (i32, [vp]), "nova_batch_advance_by": (i32, [vp, i32, vp]),
+    "nova_batch_prefill": (i32, [vp, i32, i32, vp, vp, vp, vp, vp]),
     "nova_batch_step_all_layers": (i32, [vp, vp, vp, vp, vp, vp]),
     "nova_batch_decode_step_host": (i32, [vp, vp, vp, vp, vp, i32, vp]),
     "nova_batch_run_steps": (i32, [vp, i32, vp, vp, vp, vp, sz, sz, i32, C.POINTER(C.c_float), vp]),
@@ -468,6 +470,10 @@ class Batch:
     def attn(self, layer, q, out, stream=None):
         return check(lib.nova_batch_attn(self.h, layer, q, out, stream), "batch_attn")
     def advance(self, stream=None): return check(lib.nova_batch_advance(self.h, stream), "batch_advance")
+    def advance_by(self, n, stream=None): return check(lib.nova_batch_advance_by(self.h, n, stream), "advance_by")
+    def prefill_max_tokens(self): return lib.nova_batch_prefill_max_tokens(self.h)
+    def prefill(self, layer, n_tokens, q, k, v, out, stream=None):
+        return check(lib.nova_batch_prefill(self.h, layer, n_tokens, q, k, v, out, stream), "batch_prefill")
     def step_all_layers(self, q, k, v, out, stream=None):
         return check(lib.nova_batch_step_all_layers(self.h, q, k, v, out, stream), "step_all_layers")
     def decode_step_host(self, q, k, v, out, per_layer=1, stream=None):

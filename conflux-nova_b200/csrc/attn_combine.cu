@@ -39,7 +39,8 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(AttnLaunch a, int n_c
     if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[1]));
     PlanView pv;
     pv.prefix = s_prefix;
-    pv.rows_per_layer = a.n_sessions * n_groups;
+    const int S = a.n_sessions * plan_nq(a);        // units
+    pv.rows_per_layer = S * n_groups;
     pv.n_groups = n_groups;
     pv.pages_per_layer = s_prefix[pv.rows_per_layer];
     pv.pages_total = pv.pages_per_layer * a.n_layers;
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(AttnLaunch a, int n_c
         const int n = c_last - c_first + 1;
         if (n == 1) continue;                                     // written by the split kernel
         const int s = row / n_groups, grp = row - s * n_groups;
-        const int64_t head = ((int64_t)ll * a.n_sessions + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
+        const int64_t head = ((int64_t)ll * S + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
         const float* base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
 
         // Contributors are taken 32 at a time: lane i holds (m, l) of contributor c0 + i while every
@@ -146,7 +147,8 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restric
 int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
     if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
     const int G = a.n_heads / a.n_kv_heads;
-    const int64_t units = (int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) * a.n_layers * (int64_t)(a.kv_group * G);
+    const int64_t units = (int64_t)a.n_sessions * (a.n_q > 1 ? a.n_q : 1) * (a.n_kv_heads / a.kv_group) * a.n_layers *
+                          (int64_t)(a.kv_group * G);
     int64_t ctas = (units + 3) / 4;
     if (ctas > 148 * 8) ctas = 148 * 8;
     // Always a programmatic dependent of the split kernel launched just before it.

@@ -132,7 +132,8 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const int warp = (int)threadIdx.x >> 5;
     const int G = a.n_heads / a.n_kv_heads;
     const int n_groups = a.n_kv_heads / KVG;
-    const int NH = a.n_heads, S = a.n_sessions;
+    const int NQ = plan_nq(a);
+    const int NH = a.n_heads, S = a.n_sessions * NQ;     // S counts units (session x query token)
     const int heads_per_row = KVG * G;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
@@ -220,7 +221,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                 seg_keys = plan_session_keys(a, s);
                 int n_pages_row;
                 plan_session_pages(a, s, seg_first_page, n_pages_row);
-                seg_table = a.table_base + (int64_t)s_slice[s] * a.table_stride;
+                seg_table = a.table_base + (int64_t)s_slice[s / NQ] * a.table_stride;
                 // warm L2 with what the consumers will ask for when they reach this segment
                 const float* qrow = a.q + (((int64_t)sg.layer_local * S + s) * NH + (int64_t)sg.group * KVG * G) * kHeadDim;
                 for (int i = lane; i < heads_per_row * 4; i += 32)
@@ -595,12 +596,13 @@ int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
 
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
     if (kv_dtype != NOVA_KV_F16 || !a.tmap_k || !a.tmap_v) return NOVA_ERR_UNSUPPORTED;
+    if (a.fuse_append && a.n_q > 1) return NOVA_ERR_UNSUPPORTED;      // the fused append is a decode (one token) path
     if (a.fuse_append && (!a.n_past || !a.k_new || !a.v_new || !a.rope_cs || !a.rope_sn || !a.pool_k_w || !a.pool_v_w))
         return NOVA_ERR_INVALID;
     if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
     if (a.n_heads % a.n_kv_heads || a.n_kv_heads % a.kv_group) return NOVA_ERR_INVALID;
     if (a.n_heads / a.n_kv_heads > 8) return NOVA_ERR_UNSUPPORTED;
-    if ((int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
+    if ((int64_t)a.n_sessions * (a.n_q > 1 ? a.n_q : 1) * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
     switch (a.kv_group) {
         case 4: return launch_kvg<4>(a, attn_split_ctas_mma(a, n_ctas), s);
         case 2: return launch_kvg<2>(a, attn_split_ctas_mma(a, n_ctas), s);

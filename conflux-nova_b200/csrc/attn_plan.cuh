@@ -23,7 +23,7 @@ struct PlanView {
 struct Segment {
     int layer_local;   // 0 .. n_layers-1
     int row;           // row within the layer
-    int session;
+    int session;       // the unit (session * n_q + query token)
     int group;
     int64_t row_id;    // layer_local * rows_per_layer + row
     int page_first;    // first REAL page of this segment, relative to the row's first page
@@ -33,11 +33,16 @@ struct Segment {
     int c_last;
 };
 
-__device__ __forceinline__ int plan_session_keys(const AttnLaunch& a, int s) {
-    return a.n_past ? (a.n_past[s] + a.keys_add) : a.keys_imm;
+__device__ __forceinline__ int plan_nq(const AttnLaunch& a) { return a.n_q > 1 ? a.n_q : 1; }
+
+// Keys seen by unit u = s * n_q + t (query token t of session s).
+__device__ __forceinline__ int plan_session_keys(const AttnLaunch& a, int u) {
+    const int nq = plan_nq(a);
+    const int s = u / nq, t = u - s * nq;
+    return (a.n_past ? (a.n_past[s] + a.keys_add) : a.keys_imm) + t;
 }
 
-// First logical page and page count of session s inside the launch's page window.
+// First logical page and page count of unit s inside the launch's page window.
 __device__ __forceinline__ void plan_session_pages(const AttnLaunch& a, int s, int& first, int& count) {
     const int n_keys = plan_session_keys(a, s);
     int64_t total = n_keys > 0 ? (((int64_t)n_keys + kKvBlock - 1) >> kKvShift) : 0;
@@ -53,7 +58,7 @@ __device__ __forceinline__ void plan_session_pages(const AttnLaunch& a, int s, i
 // slice_out (optional, shared memory, n_sessions entries) receives each session's slice id, fetched by
 // the second warp at the same time, so that no later table lookup waits for it.
 __device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n_groups, int* slice_out = nullptr) {
-    const int rows = a.n_sessions * n_groups;
+    const int rows = a.n_sessions * plan_nq(a) * n_groups;
     if (slice_out && threadIdx.x >= 32 && threadIdx.x < 64)
         for (int s = (int)threadIdx.x - 32; s < a.n_sessions; s += 32) slice_out[s] = a.slice_ids ? a.slice_ids[s] : s;
     if (threadIdx.x < 32) {

@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
     const int warp = (int)threadIdx.x >> 5;
     const int KVG = a.kv_group;
     const int n_groups = a.n_kv_heads / KVG;
-    const int NKV = a.n_kv_heads, NH = a.n_heads, S = a.n_sessions;
+    const int NQ = plan_nq(a);
+    const int NKV = a.n_kv_heads, NH = a.n_heads, S = a.n_sessions * NQ;    // S counts units
     const int heads_per_row = KVG * G;
 
     plan_build_prefix(a, s_prefix, n_groups);
@@ -161,7 +162,8 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
         const int n_keys = plan_session_keys(a, s);
         int first_page, n_pages_row;
         plan_session_pages(a, s, first_page, n_pages_row);
-        const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
+        const int rs = s / NQ;                            // the real session of this unit
+        const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[rs] : rs) * a.table_stride;
         const int64_t head0 = ((int64_t)sg.layer_local * S + s) * NH + (int64_t)kvh * G;
 
         float qr[G][4];
@@ -316,7 +318,7 @@ int launch_attn_simt(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t
     if (a.n_sessions <= 0 || a.n_layers <= 0) return NOVA_OK;
     if (a.n_heads % a.n_kv_heads || a.kv_group < 1 || a.kv_group > 4 || a.n_kv_heads % a.kv_group)
         return NOVA_ERR_INVALID;
-    if ((int64_t)a.n_sessions * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
+    if ((int64_t)a.n_sessions * (a.n_q > 1 ? a.n_q : 1) * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
     n_ctas = attn_split_ctas_simt(a, n_ctas);
     const int G = a.n_heads / a.n_kv_heads;
     int rc;

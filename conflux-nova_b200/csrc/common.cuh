@@ -101,6 +101,9 @@ struct AttnLaunch {
     float* part;                 // partial slots [(C + rows)][heads_per_row][kSlotW]
     int32_t* status;             // device status word (0 ok)
     int32_t n_sessions;
+    int32_t n_q;                 // query tokens per session (0/1 = decode).  Query t of session s sees
+                                 // n_past[s] + keys_add + t keys (causal prefill); q/out are [layers][S][n_q][NH][128].
+                                 // "Unit" below = s * n_q + t, a session as far as the work split is concerned.
     int32_t layer0;              // first layer of the pools this launch reads
     int32_t n_layers;            // layers covered by this launch (1 = per-layer call)
     int32_t nb;                  // physical pages per layer
@@ -166,7 +169,7 @@ int launch_cow_copy(void* pool_k, void* pool_v, int n_layers, int nb, size_t pag
                     const CowEvent* ev, int n_events, cudaStream_t s);
 int launch_zero_pages(void* pool_k, void* pool_v, int n_layers, int nb, size_t page_bytes,
                       const int32_t* table_dev, int n_pages, cudaStream_t s);
-int launch_advance(int32_t* n_past, int n, cudaStream_t s);
+int launch_advance(int32_t* n_past, int n, cudaStream_t s, int delta = 1);
 int launch_synth_normal(float* dst, size_t n, uint64_t key, uint64_t first_index, cudaStream_t s);
 
 }  // namespace novab

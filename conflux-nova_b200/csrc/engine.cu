@@ -537,7 +537,8 @@ int nova_batch_create(nova_engine* e, const int32_t* sessions, int n, nova_batch
     NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
     const int64_t rows = (int64_t)e->d.n_layers * n * (e->d.n_kv_heads / e->kv_group);
     const int heads_per_row = e->kv_group * (e->d.n_heads / e->d.n_kv_heads);
-    const size_t part_floats = (size_t)(rows + kMaxSplitCtas) * heads_per_row * kSlotW;
+    const int64_t rows_alloc = rows > kMaxRowsSmem ? rows : kMaxRowsSmem;   // a prefill launch has up to kMaxRowsSmem rows
+    const size_t part_floats = (size_t)(rows_alloc + kMaxSplitCtas) * heads_per_row * kSlotW;
     cudaError_t ce = cudaSuccess;
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->d_slices, (size_t)n * sizeof(int32_t));
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->d_n_past, (size_t)n * sizeof(int32_t));
@@ -682,13 +683,57 @@ int nova_batch_attn(nova_batch* b, int layer, const float* q, float* out, nova_s
     return run_attn(b, a, (cudaStream_t)s);
 }
 
-int nova_batch_advance(nova_batch* b, nova_stream_t s) {
-    if (!b) return NOVA_ERR_INVALID;
+int nova_batch_advance_by(nova_batch* b, int n_tokens, nova_stream_t s) {
+    if (!b || n_tokens < 0) return NOVA_ERR_INVALID;
     for (int i = 0; i < b->n; ++i) {
         SliceState* st = b->e->pool.p.find(b->slices[(size_t)i]);
-        if (st) st->n_past += 1;
+        if (st) st->n_past += n_tokens;
     }
-    return launch_advance(b->d_n_past, b->n, (cudaStream_t)s);
+    return launch_advance(b->d_n_past, b->n, (cudaStream_t)s, n_tokens);
+}
+
+int nova_batch_advance(nova_batch* b, nova_stream_t s) { return nova_batch_advance_by(b, 1, s); }
+
+int nova_batch_prefill_max_tokens(const nova_batch* b) {
+    if (!b) return 0;
+    const int per = kMaxRowsSmem / (b->n * (b->e->d.n_kv_heads / b->e->kv_group));
+    return per < 1 ? 0 : per;
+}
+
+// RopeKvOp + AttnOp with n > 1 (code/graph/dense.h:75-95): COW guard over [n_past, n_past + n), RoPE + append
+// of n tokens per session, then causal attention of the n queries over the paged keys.
+int nova_batch_prefill(nova_batch* b, int layer, int n_tokens, float* q, float* k, const float* v, float* out,
+                       nova_stream_t s) {
+    if (!b || !q || !k || !v || !out || layer < 0 || layer >= b->e->d.n_layers || n_tokens < 1) return NOVA_ERR_INVALID;
+    if (n_tokens > nova_batch_prefill_max_tokens(b)) return NOVA_ERR_TOO_LARGE;
+    nova_engine* e = b->e;
+    if (layer == 0) {        // un-share every page the new tokens will land in, once per prefill chunk
+        std::vector<CowEvent> ev;
+        int rc = NOVA_OK;
+        for (int i = 0; i < b->n && rc == NOVA_OK; ++i) {
+            const SliceState* st = e->pool.p.find(b->slices[(size_t)i]);
+            rc = collect_cow(e, b->slices[(size_t)i], st->n_past, n_tokens, ev);
+        }
+        if (!ev.empty()) {
+            const int lrc = launch_cow_copy(e->pool_k, e->pool_v, e->d.n_layers, e->nb, e->page_bytes, ev.data(),
+                                            (int)ev.size(), (cudaStream_t)s);
+            if (lrc != NOVA_OK) return lrc;
+        }
+        if (rc != NOVA_OK) return rc;
+    }
+    AppendLaunch ap;
+    fill_append(b, ap);
+    ap.q = q; ap.k = k; ap.v = v;
+    ap.layer0 = layer; ap.n_layers = 1;
+    ap.n_tok = n_tokens;
+    int rc = launch_rope_append(ap, (cudaStream_t)s);
+    if (rc != NOVA_OK) return rc;
+    AttnLaunch at;
+    fill_attn(b, at);
+    at.q = q; at.out = out;
+    at.layer0 = layer; at.n_layers = 1;
+    at.n_q = n_tokens;
+    return run_attn(b, at, (cudaStream_t)s);
 }
 
 int nova_batch_step_all_layers(nova_batch* b, float* q, float* k, const float* v, float* out, nova_stream_t s) {

@@ -132,9 +132,9 @@ __global__ void __launch_bounds__(256) zero_pages_kernel(char* __restrict__ pool
     for (int i = (int)threadIdx.x; i < n16; i += (int)blockDim.x) dst[i] = z;
 }
 
-__global__ void advance_kernel(int32_t* n_past, int n) {
+__global__ void advance_kernel(int32_t* n_past, int n, int delta) {
     const int i = (int)(blockIdx.x * blockDim.x + threadIdx.x);
-    if (i < n) n_past[i] += 1;
+    if (i < n) n_past[i] += delta;
 }
 
 __device__ __forceinline__ uint64_t mix64(uint64_t x) {
@@ -215,9 +215,9 @@ int launch_zero_pages(void* pool_k, void* pool_v, int n_layers, int nb, size_t p
     return NOVA_OK;
 }
 
-int launch_advance(int32_t* n_past, int n, cudaStream_t s) {
+int launch_advance(int32_t* n_past, int n, cudaStream_t s, int delta) {
     if (n <= 0) return NOVA_OK;
-    advance_kernel<<<(n + 127) / 128, 128, 0, s>>>(n_past, n);
+    advance_kernel<<<(n + 127) / 128, 128, 0, s>>>(n_past, n, delta);
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }

@@ -313,6 +313,16 @@ int  nova_batch_append_attn(nova_batch* b, int layer, float* q, float* k, const 
                             nova_stream_t s);
 /* n_past[s] += 1 on host and device (the caller's ++A->n_past, cow_e2e_demo.cpp:64). */
 int  nova_batch_advance(nova_batch* b, nova_stream_t s);
+/* Prefill (RopeKvOp + AttnOp with n > 1, code/graph/dense.h:75-95; launch_attn_prefill_paged,
+ * src/kernel/attn.cu:292-357,514-526): for every session of the batch append n_tokens tokens at
+ * n_past.. (k rotated in place, COW guard of the touched pages when layer == 0) and attend causally:
+ * query t sees n_past + t + 1 keys.  q/out [S][n_tokens][NH][HD], k/v [S][n_tokens][NKV][HD].
+ * n_tokens <= nova_batch_prefill_max_tokens(b) per call; after the last layer call
+ * nova_batch_advance_by(b, n_tokens). */
+int  nova_batch_prefill_max_tokens(const nova_batch* b);
+int  nova_batch_prefill(nova_batch* b, int layer, int n_tokens, float* q, float* k, const float* v, float* out,
+                        nova_stream_t s);
+int  nova_batch_advance_by(nova_batch* b, int n_tokens, nova_stream_t s);
 /* All layers at once (inputs of different layers are independent here):
  * q [L][S][NH][HD], k/v [L][S][NKV][HD], out [L][S][NH][HD]; one append launch and
  * one attention launch.  Does not advance. */

@@ -54,6 +54,8 @@ def oracle() -> C.CDLL:
         o.oracle_attn_decode_paged.argtypes = [P, vp, vp, vp, vp, i32, i32, i32, vp]
         o.oracle_attn_decode_paged_f64.restype = None
         o.oracle_attn_decode_paged_f64.argtypes = [P, vp, vp, vp, vp, i32, i32, i32, vp]
+        o.oracle_attn_prefill_paged.restype = None
+        o.oracle_attn_prefill_paged.argtypes = [P, vp, vp, vp, vp, i32, i32, i32, i32, vp]
         o.oracle_attn_partial_f64.restype = None
         o.oracle_attn_partial_f64.argtypes = [P, vp, vp, vp, vp, i32, i32, i32, i64, i64, vp]
         o.oracle_lse_combine.restype, o.oracle_lse_combine.argtypes = None, [vp, i32, i32, i32, vp]
@@ -128,6 +130,9 @@ def ref_gpu(model: str) -> C.CDLL | None:
         g.ref_gpu_attn_decode_paged.restype = None
         g.ref_gpu_attn_decode_paged.argtypes = [vp, vp, vp, vp, i32, i32, i32, vp, vp, vp]
         g.ref_gpu_attn_decode.restype, g.ref_gpu_attn_decode.argtypes = None, [vp, vp, vp, vp, i32, vp, vp]
+        if hasattr(g, "ref_gpu_attn_prefill_paged"):
+            g.ref_gpu_attn_prefill_paged.restype = None
+            g.ref_gpu_attn_prefill_paged.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
         g.ref_gpu_last_error.restype = i32
         _ref_gpu[model] = g
     return _ref_gpu[model]
@@ -244,6 +249,15 @@ def attn_decode_paged(sh, q, pool_k, pool_v, table, layer, nb, n_keys, exact=Fal
     o = np.empty((sh.n_heads, sh.head_dim), dtype=np.float32)
     fn = oracle().oracle_attn_decode_paged_f64 if exact else oracle().oracle_attn_decode_paged
     fn(C.byref(sh), _p(q), _p(pool_k), _p(pool_v), _p(t), layer, nb, n_keys, _p(o))
+    return o
+
+
+def attn_prefill_paged(sh, q, pool_k, pool_v, table, layer, nb, n_q, n_past) -> np.ndarray:
+    """q [n_q][NH][HD] -> o, in the arithmetic order of the reference's flash_paged_kernel."""
+    t = np.ascontiguousarray(table, dtype=np.int32)
+    qq = np.ascontiguousarray(q, dtype=np.float32)
+    o = np.empty_like(qq)
+    oracle().oracle_attn_prefill_paged(C.byref(sh), _p(qq), _p(pool_k), _p(pool_v), _p(t), layer, nb, n_q, n_past, _p(o))
     return o
 
 

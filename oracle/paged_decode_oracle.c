@@ -301,6 +301,43 @@ void oracle_attn_decode_paged_f64(const oracle_shape* sh, const float* q, const 
     free(acc);
 }
 
+/* ---- prefill attention, order-faithful: flash_paged_kernel<false>, src/kernel/attn.cu:292-357 ----
+ * one warp per (head, query): every lane an fma chain over its 4 dims, the shuffle-tree sum, online
+ * softmax over keys 0..n_past+qi in order, out = acc / l.  q, o: [n_q][NH][HD]. */
+void oracle_attn_prefill_paged(const oracle_shape* sh, const float* q, const void* pool_k, const void* pool_v,
+                               const int32_t* table, int layer, int nb, int n_q, int n_past, float* o) {
+    const int HD = sh->head_dim, NH = sh->n_heads, NKV = sh->n_kv_heads, KB = sh->kv_block, G = NH / NKV;
+    const float scale = HD == 64 ? 0.125f : 0.08838834764831845f;
+    int shift = 0;
+    while ((1 << shift) < KB) ++shift;
+    for (int qi = 0; qi < n_q; ++qi)
+        for (int h = 0; h < NH; ++h) {
+            const int kvh = h / G;
+            const float* qp = q + ((size_t)qi * NH + h) * HD;
+            float m = -INFINITY, l = 0.f, acc[128];
+            for (int d = 0; d < HD; ++d) acc[d] = 0.f;
+            for (int p = 0; p <= n_past + qi; ++p) {
+                const int64_t row = (((int64_t)layer * nb + table[p >> shift]) * KB + (p & (KB - 1))) * (int64_t)NKV * HD + (int64_t)kvh * HD;
+                float lanes[32];
+                for (int lane = 0; lane < 32; ++lane) {
+                    float part = 0.f;
+                    for (int t = 0; t < HD / 32; ++t)
+                        part = fmaf(qp[lane + 32 * t], kv_load(pool_k, sh->kv_dtype, row + lane + 32 * t), part);
+                    lanes[lane] = part;
+                }
+                const float qk = warp_tree_sum(lanes) * scale;
+                const float mn = fmaxf(m, qk);
+                const float e = expf(m - mn);
+                const float pe = expf(qk - mn);
+                l = fmaf(l, e, pe);
+                for (int d = 0; d < HD; ++d) acc[d] = fmaf(acc[d], e, pe * kv_load(pool_v, sh->kv_dtype, row + d));
+                m = mn;
+            }
+            const float inv = 1.f / l;
+            for (int d = 0; d < HD; ++d) o[((size_t)qi * NH + h) * HD + d] = acc[d] * inv;
+        }
+}
+
 /* Un-normalised partial over logical pages [page0, page1) of one head set, in the reference's
  * partial layout [m, l, acc[HD]] (attn.cu:150-158), accumulated in double, for checking the
  * multi-GPU split; and the LSE merge of fa_combine_kernel (attn.cu:169-190) over such partials. */

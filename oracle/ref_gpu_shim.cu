@@ -39,6 +39,10 @@ void ref_gpu_attn_decode_paged(const float* q, const float* pool_k, const float*
     nova::launch_attn_decode_paged(q, pool_k, pool_v, table, layer, nb, n_keys, o, scratch,
                                    (cudaStream_t)stream);
 }
+void ref_gpu_attn_prefill_paged(const float* q, const float* pool_k, const float* pool_v, const int32_t* table,
+                                int layer, int nb, int n_q, int n_past, float* o, void* stream) {
+    nova::launch_attn_prefill_paged(q, pool_k, pool_v, table, layer, nb, n_q, n_past, o, (cudaStream_t)stream);
+}
 void ref_gpu_attn_decode(const float* q, const float* kc, const float* vc, float* o, int n_past,
                          float* scratch, void* stream) {
     nova::launch_attn_decode(q, kc, vc, o, n_past, scratch, (cudaStream_t)stream);

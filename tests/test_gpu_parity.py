@@ -519,3 +519,63 @@ def test_run_steps_native_loop(nv, ob, mode, kernel, pdl):
     st.close()
     batch.close()
     eng.close()
+
+
+@pytest.mark.parametrize("kernel", [0, 1])
+@pytest.mark.parametrize("model", ["qwen25_1p5b", "qwen25_7b"])
+def test_prefill_vs_oracle_and_reference(nv, ob, model, kernel):
+    """Paged prefill (multi-token RoPE+append, then causal attention of the new queries): pages bit-exact,
+    attention against the oracle's restatement of flash_paged_kernel and, where the library is present, the
+    reference's own launch_attn_prefill_paged on an fp32 pool with the same values; a chunked prefill followed by
+    decode steps continues the same cache."""
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, nv.KV_F16, [37, 0], L=2, seed=31)
+    L, S, NH, NKV = eng.L, 2, eng.NH, eng.NKV
+    batch = eng.batch(ss)
+    try_set_kernel(nv, batch, kernel)
+    assert batch.prefill_max_tokens() >= 64
+    pos = [37, 0]
+    g = ob.ref_gpu(model)
+    for n_tok in (21, 5):
+        q = rng.standard_normal((L, S, n_tok, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((L, S, n_tok, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((L, S, n_tok, NKV, 128)).astype(np.float32)
+        out = np.empty_like(q)
+        for layer in range(L):
+            dq, dk, dv = nv.to_device(q[layer]), nv.to_device(k[layer]), nv.to_device(v[layer])
+            do = nv.DevBuf(q[layer].nbytes)
+            batch.prefill(layer, n_tok, dq.ptr, dk.ptr, dv.ptr, do.ptr)
+            nv.check(nv.lib.dev_sync())
+            out[layer] = do.download(np.float32).reshape(out[layer].shape)
+            for i, s in enumerate(ss):
+                table = eng.pool.table(eng.session_slice(s))
+                qi, ki = q[layer, i].copy(), k[layer, i].copy()
+                ob.rope_append_paged(sh, pk, pv, table, layer, eng.nb, n_tok, pos[i], qi, ki, v[layer, i], cs, sn)
+                want = ob.attn_prefill_paged(sh, qi, pk, pv, table, layer, eng.nb, n_tok, pos[i])
+                assert_attn_close(out[layer, i], want, f"prefill n={n_tok} layer {layer} session {i}")
+                assert np.array_equal(bits(dq.download(np.float32).reshape(S, n_tok, NH, 128)[i]), bits(qi))
+                if g is not None and hasattr(g, "ref_gpu_attn_prefill_paged") and layer == 1:
+                    rk, rv = nv.to_device(pk.astype(np.float32)), nv.to_device(pv.astype(np.float32))
+                    rq, ro = nv.to_device(qi), nv.DevBuf(qi.nbytes)
+                    g.ref_gpu_attn_prefill_paged(rq.ptr, rk.ptr, rv.ptr, nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(s)),
+                                                 layer, eng.nb, n_tok, pos[i], ro.ptr, None)
+                    nv.check(nv.lib.dev_sync())
+                    ref = ro.download(np.float32).reshape(qi.shape)
+                    assert rel_l2(want, ref) < 2e-6                      # oracle == the reference's kernel
+                    assert_attn_close(out[layer, i], ref, "vs reference prefill kernel")
+        batch.advance_by(n_tok)
+        pos = [p + n_tok for p in pos]
+    assert batch.device_status() == 0
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    # decode continues on the prefilled cache
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
+    q = rng.standard_normal((L, S, NH, 128)).astype(np.float32)
+    k = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+    v = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+    dq, dk, dv, do = nv.to_device(q), nv.to_device(k), nv.to_device(v), nv.DevBuf(q.nbytes)
+    batch.step_all_layers(dq.ptr, dk.ptr, dv.ptr, do.ptr)
+    nv.check(nv.lib.dev_sync())
+    want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)
+    assert_attn_close(do.download(np.float32).reshape(want.shape), want, "decode after prefill")
+    batch.close()
+    eng.close()

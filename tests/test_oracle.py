@@ -165,3 +165,19 @@ def test_synth_generator(ob):
             h = mix((key + 3 * i + r) & M)
             s += (h & 0xFFFF) + ((h >> 16) & 0xFFFF) + ((h >> 32) & 0xFFFF) + (h >> 48)
         assert a[i] == np.float32((s - 393210) / 65536.0)
+
+
+def test_prefill_oracle_is_causal_decode(ob):
+    """flash_paged_kernel's restatement == one exact decode attention per query with n_keys = n_past + qi + 1."""
+    sh = ob.shape(2, 12, 2, ob.KV_F16)
+    rng = np.random.default_rng(6)
+    nb, n_past, n_q, layer = 7, 19, 9, 1
+    table = rng.permutation(nb).astype(np.int32)
+    pk, pv = ob.new_pools(sh, nb)
+    pk[:] = rng.standard_normal(pk.shape).astype(np.float16)
+    pv[:] = rng.standard_normal(pv.shape).astype(np.float16)
+    q = rng.standard_normal((n_q, 12, 128)).astype(np.float32)
+    got = ob.attn_prefill_paged(sh, q, pk, pv, table, layer, nb, n_q, n_past)
+    for qi in range(n_q):
+        want = ob.attn_decode_paged(sh, q[qi], pk, pv, table, layer, nb, n_past + qi + 1, exact=True)
+        assert rel_l2(got[qi], want) < 1e-6
