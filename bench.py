@@ -129,7 +129,8 @@ def run_ours(args):
     n_sess = w["sessions"] if w["scaling"] == "weak" else max(1, w["sessions"] // world)
     lens = wl.context_lengths(seed, n_sess, *w["ctx"])
     K, W, KE = args.steps, args.warmup, args.e2e_steps
-    total_steps = 5 * (W + K) + (W + KE) + 8
+    PF_REPS = 3
+    total_steps = 5 * (W + K) + (W + KE) + 8 + (PF_REPS + 1) * 128
     work = wl.Workload(w["model"], lens, seed=seed, steps=total_steps, device=local_rank,
                        shared_prefix=w.get("prefix", 0), kv_dtype=nv.KV_F32 if args.kv == "f32" else nv.KV_F16)
     eng, batch = work.eng, work.batch
@@ -250,6 +251,10 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_sample(nv, work, lens, seed)
 
+    prefill = None
+    if world == 1 and not args.quick and args.workload in ("c2", "c4"):
+        prefill = prefill_sample(nv, work, stream, PF_REPS)
+
     ref_gpu = None
     if rank == 0 and world == 1 and not args.no_ref_gpu and args.workload in ("c1", "c2"):
         ref_gpu = reference_gpu_sample(nv, work)
@@ -291,6 +296,7 @@ def run_ours(args):
             "clocks": clocks,
             "cpu_baseline": cpu,
             "reference_kernels_on_this_gpu": ref_gpu,
+            "prefill": prefill,
         }
         print(json.dumps(line))
     if dist is not None:
@@ -392,6 +398,44 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
         }
         print(json.dumps(line))
     dist.destroy_process_group()
+
+
+def prefill_sample(nv, work, stream, reps):
+    """Paged prefill (the step before decode): every session takes a chunk of new tokens through
+    all layers — multi-token RoPE+append, then causal attention of the chunk's queries over the paged keys."""
+    eng, batch = work.eng, work.batch
+    L, S, NH, NKV = eng.L, len(work.sessions), eng.NH, eng.NKV
+    n_tok = min(batch.prefill_max_tokens(), 128)
+    if n_tok < 1:
+        return None
+    nq, nk = S * n_tok * NH * 128, S * n_tok * NKV * 128
+    dq, dk, dv, do = nv.DevBuf(nq * 4), nv.DevBuf(nk * 4), nv.DevBuf(nk * 4), nv.DevBuf(nq * 4)
+    for buf, n, t in ((dq, nq, 3), (dk, nk, 1), (dv, nk, 2)):
+        nv.check(nv.lib.nova_synth_normal(buf.ptr, n, nv.synth_key(work.seed, t, 777, 0), 0, None))
+    nv.check(nv.lib.dev_sync())
+
+    def chunk():
+        for l in range(L):
+            batch.prefill(l, n_tok, dq.ptr, dk.ptr, dv.ptr, do.ptr, stream.h)
+        batch.advance_by(n_tok, stream.h)
+    chunk()
+    stream.sync()
+    n0 = [eng.n_past(s) for s in work.sessions]
+    e0, e1 = nv.Event(), nv.Event()
+    e0.record(stream)
+    for _ in range(reps):
+        chunk()
+    e1.record(stream)
+    e1.sync()
+    ms = e0.elapsed_ms(e1)
+    keys = sum(sum(n + r * n_tok + t + 1 for t in range(n_tok)) for n in n0 for r in range(reps))     # (query, key) pairs per head
+    flops = 4.0 * 128 * NH * keys * L
+    for b in (dq, dk, dv, do):
+        b.free()
+    return {"tokens_per_s": S * n_tok * reps / (ms / 1e3), "chunk_tokens_per_session": n_tok, "ms_per_chunk": ms / reps,
+            "attention_tflops": flops / (ms / 1e3) / 1e12,
+            "note": "every query token is a row of the decode kernel's work split (K/V re-read per query, mostly from L2); "
+                    "a query-tiled tensor-core prefill is the next step"}
 
 
 def reference_gpu_sample(nv, work):
