@@ -596,7 +596,7 @@ def main():
     ap.add_argument("--collective", default="layer", choices=["layer", "step"],
                     help="c5 on several GPUs: all-gather + merge after every layer (engine order) or once per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--launch", default="graph", choices=["layer", "graph", "fused"],
+    ap.add_argument("--launch", default="layer", choices=["layer", "graph", "fused"],
                     help="layer: 2 launches per layer; graph: the same, replayed from a CUDA graph; fused: all layers per launch")
     ap.add_argument("--kernel", type=int, default=-1, help="-1 best available, 0 SIMT, 1 tensor-core")
     ap.add_argument("--no-fused-append", action="store_true",

@@ -310,10 +310,12 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const uint32_t v_row = (uint32_t)(w * 2048 + (((lm & 1) << 3) + lr) * 128);
     constexpr float kQScale = kAttnScale * kLog2e;
     uint32_t it = 0;
-    // Everything the consumers read or write from here on (q, the new k/v, out, partial slots) may
-    // belong to the kernel before this one; the producer warp meanwhile prefetches pages, which it
-    // cannot be writing.
-    pdl_wait();
+    // Programmatic dependent launch: a launch that carries the attribute promises that the kernel
+    // before it in the stream (the previous layer's merge) does not produce anything this kernel READS
+    // (q, the new k/v, pages, tables, n_past).  What the two do share is the partial-slot scratch, which
+    // the merge may still be reading, so each consumer warp waits for the previous kernel right before
+    // its first WRITE (new token into the pool, outputs, partial slots) and computes until then.
+    bool dep_met = false;
 
     for (int64_t pos = lo; pos < hi;) {
         const Segment sg = plan_segment(pv, pos, hi, a.row_setup_pages);
@@ -393,6 +395,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     // This page receives the step's new token: rotate k, store k and v into the pool
                     // (for later steps) and straight into the staged copy (for this one).  The TMA
                     // copy of that slot may be old or new bytes; both are overwritten here.
+                    if (!dep_met) { pdl_wait(); dep_met = true; }
                     patched = true;
                     const int slot = pos_new & (kKvBlock - 1);
                     const int layer = a.layer0 + sg.layer_local;
@@ -493,6 +496,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
 
         // ---- segment done: row sums, then direct output or a partial slot
         if (tl && threadIdx.x == 0) tl[5] = now_ns();
+        if (!dep_met) { pdl_wait(); dep_met = true; }
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int n_contrib = sg.c_last - sg.c_first + 1;

@@ -62,6 +62,7 @@ struct nova_batch {
     cudaGraphExec_t graph = nullptr;   // one per-layer decode step on the staging buffers
     int graph_kernel = -1;
     unsigned long long* timeline = nullptr;   // caller-owned profiling buffer, see nova_batch_set_timeline
+    mutable unsigned tl_seq = 0;              // attention launches since the buffer was set (ring of 4 records)
     std::vector<cudaEvent_t> ev;       // event pool for per-launch timing
     cudaStream_t s_in = nullptr, s_out = nullptr;      // copy streams of the host-buffer step
     cudaEvent_t ev_in[4] = {}, ev_cmp[4] = {}, ev_out = nullptr, ev_begin = nullptr;
@@ -142,7 +143,7 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.row_setup_pages = b->row_setup;
     a.tmap_k = e->tmaps_ok ? e->tmap_k : nullptr;
     a.tmap_v = e->tmaps_ok ? e->tmap_v : nullptr;
-    a.timeline = b->timeline;
+    a.timeline = b->timeline ? b->timeline + (size_t)(b->tl_seq++ % 4u) * (148 * 12) : nullptr;
 }
 
 // Split kernel, then the merge of the rows that more than one CTA worked on.
@@ -608,6 +609,7 @@ int nova_batch_set_kernel(nova_batch* b, int which) {
 int nova_batch_set_timeline(nova_batch* b, void* dev_buf) {
     if (!b) return NOVA_ERR_INVALID;
     b->timeline = static_cast<unsigned long long*>(dev_buf);
+    b->tl_seq = 0;
     return NOVA_OK;
 }
 int nova_batch_set_fused_append(nova_batch* b, int on) {

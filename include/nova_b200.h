@@ -276,7 +276,8 @@ int  nova_batch_sync_positions(nova_batch* b, nova_stream_t s);
 /* Select the attention kernel: 0 = SIMT, 1 = tensor-core (mma + bulk-copy pipeline, fp16 KV). */
 int  nova_batch_set_kernel(nova_batch* b, int which);
 int  nova_batch_get_kernel(const nova_batch* b);
-/* Profiling aid (tensor-core kernel): dev_buf = 148*12 uint64 in device memory, or NULL to switch off.
+/* Profiling aid (tensor-core kernel): dev_buf = 4 records of 148*12 uint64 in device memory (launch i
+ * of the batch writes record i % 4), or NULL to switch off.
  * Every CTA of the next attention launches leaves %globaltimer stamps there: [0] start, [1] work split
  * known, [2] first page requested, [3] last page requested, [4] first page landed, [5] last page
  * consumed, [6] results/partials written; after those 148*8 values the first 148 CTAs of the combine
@@ -303,8 +304,9 @@ int  nova_batch_attn(nova_batch* b, int layer, const float* q, float* out, nova_
 int  nova_batch_set_fused_append(nova_batch* b, int on);
 /* Programmatic dependent launch for nova_batch_run_steps / nova_batch_decode_step_host with the fused
  * append: the attention launch of every layer after the first may start while the previous layer's
- * merge is still running; it prefetches KV pages and waits (griddepcontrol.wait) before touching q, the
- * new k/v or any output. */
+ * merge is still running: it streams and processes its pages and waits (griddepcontrol.wait) only before
+ * its first write (new token, outputs, partial slots).  The caller promises that the launch before such a
+ * layer in the stream does not produce that layer's q, k or v (true inside these two calls). */
 int  nova_batch_set_pdl(nova_batch* b, int on);
 /* Tuning knob of the attention work split: how many pages' worth of time starting a session inside a
  * CTA costs (default 2).  A CTA whose page range crosses a session boundary gets that many fewer pages. */
