@@ -19,9 +19,8 @@
 //     reports NOVA_ERR_TIMEOUT through the status word instead of spinning forever.
 //   * Work split and partial slots are those of attn_plan.cuh; rows shared by several CTAs are
 //     merged by the combine kernel that follows (attn_combine.cu) - no flags between CTAs.
-#include <cuda.h>
-
 #include "attn_plan.cuh"
+#include "mma_common.cuh"
 
 namespace novab {
 namespace {
@@ -30,81 +29,6 @@ namespace {
 #define NOVA_ATTN_STAGES 4
 #endif
 constexpr int kStages = NOVA_ATTN_STAGES;   // page sets in flight per CTA; more only adds queueing delay in HBM
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s per barrier wait
-
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false after kWaitLimitNs (or as soon as another thread of the CTA gave up).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try(bar, parity)) return true;
-    const unsigned long long t0 = now_ns();
-    for (;;) {
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (now_ns() - t0 > kWaitLimitNs) {
-            *abort_flag = 1;
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
-}
-
-// m16n8k16, rows 8..15 of A are zero padding (G <= 8 query heads per kv head): a1 = a3 = 0 and
-// the accumulator rows 8..15 (c2, c3) stay zero and are dropped.
-__device__ __forceinline__ void mma_top(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1,
-                                        float c0, float c1) {
-    float x2, x3;
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-        : "=f"(d0), "=f"(d1), "=f"(x2), "=f"(x3)
-        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(0.f), "f"(0.f));
-    (void)x2;
-    (void)x3;
-}
-
-__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
-    const __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
 
 template <int KVG>
 struct MmaCfg {

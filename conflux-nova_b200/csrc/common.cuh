@@ -114,6 +114,8 @@ struct AttnLaunch {
     float* out_part;             // [layers][S][NH][130]
     const void* tmap_k;          // host pointers to the CUtensorMap of each pool (tensor-core kernel only)
     const void* tmap_v;
+    const void* tmap_k1;         // the same pools with one kv head per box (prefill kernel)
+    const void* tmap_v1;
     // Fused RoPE + append (tensor-core kernel): when fuse_append != 0 the CTA that owns a session's
     // last page rotates k_new at n_past[s], stores k_new/v_new into that page (pool and the staged copy)
     // and every CTA rotates q on the fly; q itself is left as it was.
@@ -145,6 +147,8 @@ int attn_default_ctas_simt(int n_kv_heads);
 int attn_default_ctas_mma();
 bool attn_mma_built();
 int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group);
+int launch_attn_prefill(const AttnLaunch& a, cudaStream_t s);     // query-tiled tensor-core prefill (n_q >= 1, one layer)
+int attn_prefill_tile_tokens(int n_heads, int n_kv_heads);
 int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s);   // after either split kernel
 int attn_split_ctas_simt(const AttnLaunch& a, int n_ctas);
 int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas);

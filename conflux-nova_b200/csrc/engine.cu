@@ -40,6 +40,8 @@ struct nova_engine {
     int kv_group = 0;
     alignas(128) unsigned char tmap_k[128];   // CUtensorMap of each fp16 pool (tensor-core attention)
     alignas(128) unsigned char tmap_v[128];
+    alignas(128) unsigned char tmap_k1[128];  // one kv head per box (prefill)
+    alignas(128) unsigned char tmap_v1[128];
     bool tmaps_ok = false;
     std::vector<SessionRec> sess;
     std::mutex mu;
@@ -143,12 +145,16 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.row_setup_pages = b->row_setup;
     a.tmap_k = e->tmaps_ok ? e->tmap_k : nullptr;
     a.tmap_v = e->tmaps_ok ? e->tmap_v : nullptr;
+    a.tmap_k1 = e->tmaps_ok ? e->tmap_k1 : nullptr;
+    a.tmap_v1 = e->tmaps_ok ? e->tmap_v1 : nullptr;
     a.timeline = b->timeline ? b->timeline + (size_t)(b->tl_seq++ % 4u) * (148 * 12) : nullptr;
 }
 
 // Split kernel, then the merge of the rows that more than one CTA worked on.
 int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
     int rc, ctas;
+    if (b->kernel == 1 && a.n_q > 1 && a.n_layers == 1 && !a.write_partial_only)
+        return launch_attn_prefill(a, s);        // query-tiled prefill: every row complete in one CTA, no merge
     if (b->kernel == 1) {
         ctas = attn_split_ctas_mma(a, 0);
         rc = launch_attn_mma(a, b->e->d.kv_dtype, ctas, s);
@@ -248,7 +254,9 @@ int nova_engine_create(const nova_engine_desc* desc, nova_engine** out) {
     if (d.kv_dtype == NOVA_KV_F16 && attn_mma_built()) {
         const int64_t slot_rows = (int64_t)d.n_layers * e->nb * kKvBlock;
         e->tmaps_ok = attn_make_tmap(e->tmap_k, e->pool_k, slot_rows, d.n_kv_heads, e->kv_group) == NOVA_OK &&
-                      attn_make_tmap(e->tmap_v, e->pool_v, slot_rows, d.n_kv_heads, e->kv_group) == NOVA_OK;
+                      attn_make_tmap(e->tmap_v, e->pool_v, slot_rows, d.n_kv_heads, e->kv_group) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_k1, e->pool_k, slot_rows, d.n_kv_heads, 1) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_v1, e->pool_v, slot_rows, d.n_kv_heads, 1) == NOVA_OK;
     }
     int r = launch_rope_table(e->cs, e->sn, d.rope_positions, d.rope_theta, 0);   // Kernel::rope_table, model.cpp:119
     if (r == NOVA_OK && cudaDeviceSynchronize() != cudaSuccess) r = NOVA_ERR_CUDA;
@@ -698,6 +706,7 @@ int nova_batch_advance(nova_batch* b, nova_stream_t s) { return nova_batch_advan
 
 int nova_batch_prefill_max_tokens(const nova_batch* b) {
     if (!b) return 0;
+    if (b->kernel == 1) return 8192;             // the query-tiled kernel has no row table
     const int per = kMaxRowsSmem / (b->n * (b->e->d.n_kv_heads / b->e->kv_group));
     return per < 1 ? 0 : per;
 }
