@@ -190,6 +190,12 @@ def run_ours(args):
         barrier()
         return ms, attn_ms, kv_bytes
 
+    if args.quick_prefill:
+        pf = prefill_sample(nv, work, stream, 1)
+        if rank == 0:
+            print(json.dumps({"quick_prefill": True, "kernel": kernel, **(pf or {})}))
+        return
+
     launches0 = nv.lib.nova_launch_count()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     mode = {"layer": 1, "graph": 2, "fused": 0}[args.launch]
@@ -607,6 +613,7 @@ def main():
                     help="KV pool element type (f32 = the reference's own format; SIMT kernel)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own kernels (sm_100a build)")
+    ap.add_argument("--quick-prefill", action="store_true", help="only the prefill sample (for profiler captures)")
     ap.add_argument("--quick", action="store_true",
                     help="only the main timed region (for profiler captures): no other modes, e2e or CPU baseline")
     args = ap.parse_args()
