@@ -29,12 +29,34 @@ namespace {
 #define NOVA_ATTN_STAGES 4
 #endif
 constexpr int kStages = NOVA_ATTN_STAGES;   // page sets in flight per CTA; more only adds queueing delay in HBM
+// A launch that is a programmatic dependent of the previous layer's kernels leaves this many SMs
+// without a CTA of its own.  With one CTA for every SM each layer's CTAs all start at the same moment
+// (when the previous layer's exit) and all sit in their ~3 us start-up (work split, first table
+// entries, first pages) together, HBM idle; with a few SMs to spare the next layer's first CTAs start
+// early, the layers drift apart and some CTAs are always streaming while others start.  Measured on
+// 8 sessions x 2-8k tokens (7B shape): 0 spare 0.588 ms per 28-layer step, 4: 0.523, 8: 0.510,
+// 12: 0.507, 16: 0.511, 32: 0.529.
+#ifndef NOVA_ATTN_SPARE_SMS
+#define NOVA_ATTN_SPARE_SMS 12
+#endif
+
+// A CTA whose page range crosses a row boundary finishes a segment early.  Under a programmatic
+// dependent launch its result cannot be written yet (the previous layer's merge may still read the
+// partial slots), and waiting there would stall the rest of the CTA's range, so up to kStashSlots
+// finished segments are parked in shared memory: per thread its 32 accumulator values, m, l and the
+// segment's address words.
+#ifndef NOVA_ATTN_STASH
+#define NOVA_ATTN_STASH 2
+#endif
+constexpr int kStashSlots = NOVA_ATTN_STASH;
+constexpr int kStashWords = 38;
 
 template <int KVG>
 struct MmaCfg {
     static constexpr int kBoxBytes = KVG * 16 * 128;          // one [64 dims][16 slots][KVG] box
     static constexpr int kStageBytes = 4 * kBoxBytes;          // K lo/hi dims + V lo/hi dims
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+    static constexpr int kStashBytes = kStashSlots * KVG * kStashWords * 128;   // finished segments parked until the first write
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStashBytes + 1024;
     static constexpr int kThreads = 32 * (KVG + 1);
     static constexpr int kCtasPerSm = 4 / KVG >= 1 ? 4 / KVG : 1;
 };
@@ -62,8 +84,13 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
     pdl_launch_dependents();      // the combine kernel may be scheduled; it waits for this grid to finish
-    unsigned long long* tl = a.timeline ? a.timeline + (size_t)blockIdx.x * 8 : nullptr;
-    if (tl && threadIdx.x == 0) tl[0] = now_ns();
+    unsigned long long* tl = (a.timeline && blockIdx.x < 148) ? a.timeline + (size_t)blockIdx.x * 8 : nullptr;
+    if (tl && threadIdx.x == 0) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        tl[0] = now_ns();
+        tl[7] = smid;
+    }
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) {
             mbar_init(smem_u32(&s_full[i]), 1);
@@ -234,12 +261,44 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const uint32_t v_row = (uint32_t)(w * 2048 + (((lm & 1) << 3) + lr) * 128);
     constexpr float kQScale = kAttnScale * kLog2e;
     uint32_t it = 0;
-    // Programmatic dependent launch: a launch that carries the attribute promises that the kernel
-    // before it in the stream (the previous layer's merge) does not produce anything this kernel READS
-    // (q, the new k/v, pages, tables, n_past).  What the two do share is the partial-slot scratch, which
-    // the merge may still be reading, so each consumer warp waits for the previous kernel right before
-    // its first WRITE (new token into the pool, outputs, partial slots) and computes until then.
-    bool dep_met = false;
+    // Programmatic dependent launch: a launch that carries the attribute promises that the kernels
+    // before it in the stream (the previous layer's split and merge) neither produce anything this
+    // kernel READS (q, the new k/v, pages, tables, n_past) nor touch what it WRITES for its own layers
+    // (their pages, k rows and outputs).  What they do share is the partial-slot scratch, which the
+    // merge may still be reading, so each consumer warp waits for the previous kernel at the end of
+    // its first segment, right before its first output or partial-slot write, and computes until then
+    // (the new token goes into the pool without waiting).  That wait also keeps completion transitive:
+    // this grid cannot finish before the one it depends on.
+    bool dep_met = a.pdl == 0;      // plain launch: the stream already ordered us after everything before
+    int n_stashed = 0;
+    float* stash = reinterpret_cast<float*>(smem_raw + (stage0 - smem_u32(smem_raw)) + kStages * Cfg::kStageBytes);
+
+    // One finished segment -> memory: the row's output when this CTA covered the whole row, else
+    // (m, l, acc) into this CTA's partial slot for the merge kernel.
+    auto emit = [&](bool whole_row, int64_t h0, int row_id, float m_, float l_, auto&& acc) {
+        if (g >= G) return;
+        if (whole_row) {
+            if (a.write_partial_only) {
+                float* op = a.out_part + (h0 + g) * kPartW;
+                if (t == 0) { op[0] = m_ * (1.f / kLog2e); op[1] = l_; }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(op + 2 + 8 * j + 2 * t) = acc(j);
+            } else {
+                const float inv = l_ > 0.f ? 1.f / l_ : 0.f;
+                float* op = a.out + (h0 + g) * kHeadDim;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float2 v = acc(j);
+                    *reinterpret_cast<float2*>(op + 8 * j + 2 * t) = make_float2(v.x * inv, v.y * inv);
+                }
+            }
+            return;
+        }
+        float* pr = a.part + ((size_t)((int64_t)blockIdx.x + row_id) * heads_per_row + (size_t)(w * G + g)) * kSlotW;
+        if (t == 0) *reinterpret_cast<float2*>(pr) = make_float2(m_ * (1.f / kLog2e), l_);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(pr + 4 + 8 * j + 2 * t) = acc(j);
+    };
 
     for (int64_t pos = lo; pos < hi;) {
         const Segment sg = plan_segment(pv, pos, hi, a.row_setup_pages);
@@ -319,7 +378,6 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     // This page receives the step's new token: rotate k, store k and v into the pool
                     // (for later steps) and straight into the staged copy (for this one).  The TMA
                     // copy of that slot may be old or new bytes; both are overwritten here.
-                    if (!dep_met) { pdl_wait(); dep_met = true; }
                     patched = true;
                     const int slot = pos_new & (kKvBlock - 1);
                     const int layer = a.layer0 + sg.layer_local;
@@ -420,36 +478,38 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
 
         // ---- segment done: row sums, then direct output or a partial slot
         if (tl && threadIdx.x == 0) tl[5] = now_ns();
-        if (!dep_met) { pdl_wait(); dep_met = true; }
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int n_contrib = sg.c_last - sg.c_first + 1;
-        if (n_contrib == 1) {
-            if (g < G) {
-                if (a.write_partial_only) {
-                    float* op = a.out_part + (head0 + g) * kPartW;
-                    if (t == 0) { op[0] = m * (1.f / kLog2e); op[1] = l; }
+        if (!dep_met) {
+            if (pos < hi && n_stashed < kStashSlots) {          // more work ahead: park this result, do not wait here
+                float* st = stash + (size_t)((n_stashed * KVG + w) * kStashWords) * 32 + lane;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        *reinterpret_cast<float2*>(op + 2 + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
-                } else {
-                    const float inv = l > 0.f ? 1.f / l : 0.f;
-                    float* op = a.out + (head0 + g) * kHeadDim;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        *reinterpret_cast<float2*>(op + 8 * j + 2 * t) = make_float2(o[j][0] * inv, o[j][1] * inv);
+                for (int j = 0; j < 16; ++j) {
+                    st[(2 * j) * 32] = o[j][0];
+                    st[(2 * j + 1) * 32] = o[j][1];
                 }
+                st[32 * 32] = m;
+                st[33 * 32] = l;
+                st[34 * 32] = __int_as_float(n_contrib == 1 ? -1 : sg.row_id);
+                st[35 * 32] = __int_as_float((int)(head0 & 0xffffffffLL));
+                st[36 * 32] = __int_as_float((int)(head0 >> 32));
+                ++n_stashed;
+                continue;
             }
-            continue;
+            pdl_wait();
+            dep_met = true;
+            for (int si = 0; si < n_stashed; ++si) {
+                const float* st = stash + (size_t)((si * KVG + w) * kStashWords) * 32 + lane;
+                const int row_id = __float_as_int(st[34 * 32]);
+                const int64_t h0 = (int64_t)(((unsigned long long)(unsigned)__float_as_int(st[36 * 32]) << 32) |
+                                             (unsigned long long)(unsigned)__float_as_int(st[35 * 32]));
+                emit(row_id < 0, h0, row_id, st[32 * 32], st[33 * 32],
+                     [&](int j) { return make_float2(st[(2 * j) * 32], st[(2 * j + 1) * 32]); });
+            }
         }
-        // several CTAs share this row: leave (m, l, acc) in this CTA's slot for the combine kernel
-        if (g < G) {
-            float* pr = a.part + ((size_t)((int64_t)blockIdx.x + sg.row_id) * heads_per_row + (size_t)(w * G + g)) * kSlotW;
-            if (t == 0) *reinterpret_cast<float2*>(pr) = make_float2(m * (1.f / kLog2e), l);
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                *reinterpret_cast<float2*>(pr + 4 + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
-        }
+        emit(n_contrib == 1, head0, sg.row_id, m, l, [&](int j) { return make_float2(o[j][0], o[j][1]); });
+        if (tl && threadIdx.x == 0) tl[6] = now_ns();
         if (tl && threadIdx.x == 0) tl[6] = now_ns();
     }
 }
@@ -519,7 +579,7 @@ int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads,
 int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
     if (n_ctas > 0) return n_ctas;
     const int per_sm = a.kv_group >= 4 ? 1 : 4 / a.kv_group;
-    return 148 * per_sm;
+    return (148 - (a.pdl ? NOVA_ATTN_SPARE_SMS : 0)) * per_sm;
 }
 
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
