@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
     pv.pages_per_layer = s_prefix[pv.rows_per_layer];
     pv.pages_total = pv.pages_per_layer * a.n_layers;
     pv.n_ctas = pv.pages_total < (int64_t)n_ctas_split ? (int)pv.pages_total : n_ctas_split;
+    plan_finish(pv);
     if (pv.pages_total == 0) return;
 
     const int64_t units = (int64_t)pv.rows_per_layer * a.n_layers * heads_per_row;

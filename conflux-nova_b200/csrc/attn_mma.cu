@@ -36,6 +36,9 @@ constexpr int kStages = NOVA_ATTN_STAGES;   // page sets in flight per CTA; more
 // early, the layers drift apart and some CTAs are always streaming while others start.  Measured on
 // 8 sessions x 2-8k tokens (7B shape): 0 spare 0.588 ms per 28-layer step, 4: 0.523, 8: 0.510,
 // 12: 0.507, 16: 0.511, 32: 0.529.
+#ifndef NOVA_ATTN_EVICT_FIRST
+#define NOVA_ATTN_EVICT_FIRST 1
+#endif
 #ifndef NOVA_ATTN_SPARE_SMS
 #define NOVA_ATTN_SPARE_SMS 12
 #endif
@@ -68,6 +71,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     extern __shared__ unsigned char smem_raw[];
     __shared__ int s_prefix[kMaxRowsSmem + 1];
     __shared__ int s_slice[kMaxRowsSmem];
+    __shared__ int s_keys[kMaxRowsSmem];          // keys seen by each unit (n_past + this step's token), fetched once
     __shared__ __align__(8) unsigned long long s_full[kStages];
     __shared__ __align__(8) unsigned long long s_empty[kStages];
     __shared__ int s_kcount[kStages];
@@ -91,7 +95,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         tl[0] = now_ns();
         tl[7] = smid;
     }
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 32 * (MmaCfg<KVG>::kThreads / 32 - 1)) {      // the producer's lane 0; warp 0 is busy with the prefix scan
         for (int i = 0; i < kStages; ++i) {
             mbar_init(smem_u32(&s_full[i]), 1);
             mbar_init(smem_u32(&s_empty[i]), KVG);
@@ -99,7 +103,11 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    plan_build_prefix(a, s_prefix, n_groups, s_slice);   // ends with __syncthreads()
+    if (warp == KVG && lane == 0) {     // the tensor maps are needed right after the first table entry
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
+    }
+    plan_build_prefix(a, s_prefix, n_groups, s_slice, s_keys);   // ends with __syncthreads()
 
     PlanView pv;
     pv.prefix = s_prefix;
@@ -108,6 +116,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     pv.pages_per_layer = s_prefix[pv.rows_per_layer];
     pv.pages_total = pv.pages_per_layer * a.n_layers;
     pv.n_ctas = pv.pages_total < (int64_t)gridDim.x ? (int)pv.pages_total : (int)gridDim.x;
+    plan_finish(pv);
 
     const int g = lane >> 2, t = lane & 3;   // fragment row (query head within the kv head) / quad lane
 
@@ -146,10 +155,9 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         // The whole warp walks the CTA's page range in batches of up to 32 pages: each lane fetches
         // one block-table entry of the NEXT batch while lane 0 issues the TMA copies of the current
         // one, so a table read (a ~1 us round trip when it misses) never stops the copy stream.
-        if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
-        }
+#if NOVA_ATTN_EVICT_FIRST
+        const unsigned long long kv_policy = l2_policy_evict_first();
+#endif
         struct Batch {
             int count;              // 0: no more work
             int layer, group, n_keys, page0;
@@ -160,6 +168,10 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         sg.page_count = 0;
         int seg_done = 0, seg_first_page = 0, seg_keys = 0;
         const int32_t* seg_table = nullptr;
+#ifdef NOVA_TL_DEBUG
+        bool dbg_first = true;
+#endif
+        bool first_segment = true;
         auto next_batch = [&]() -> Batch {
             Batch b;
             b.count = 0;
@@ -169,11 +181,18 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                 pos += sg.span;
                 seg_done = 0;
                 const int s = sg.session;
-                seg_keys = plan_session_keys(a, s);
+                seg_keys = s_keys[s];
                 int n_pages_row;
-                plan_session_pages(a, s, seg_first_page, n_pages_row);
+                plan_pages_of_keys(a, seg_keys, seg_first_page, n_pages_row);
                 seg_table = a.table_base + (int64_t)s_slice[s / NQ] * a.table_stride;
-                // warm L2 with what the consumers will ask for when they reach this segment
+#ifdef NOVA_TL_DEBUG
+                if (tl && lane == 0 && dbg_first) { tl[5] = now_ns(); dbg_first = false; }
+#endif
+                // Warm L2 with what the consumers will ask for when they reach this segment.  Not for the
+                // CTA's first segment: the consumers fetch that themselves at this very moment, and the
+                // hints would only delay the first page copies.
+                if (first_segment) { first_segment = false; continue; }
+                {
                 const float* qrow = a.q + (((int64_t)sg.layer_local * S + s) * NH + (int64_t)sg.group * KVG * G) * kHeadDim;
                 for (int i = lane; i < heads_per_row * 4; i += 32)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(qrow + i * 32));
@@ -188,6 +207,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                         asm volatile("prefetch.global.L2 [%0];" ::"l"((lane < 2 ? a.rope_cs : a.rope_sn) +
                                                                        (int64_t)pn * (kHeadDim / 2) + (lane & 1) * 32));
                 }
+                }
             }
             b.count = sg.page_count - seg_done < 32 ? sg.page_count - seg_done : 32;
             b.layer = a.layer0 + sg.layer_local;
@@ -200,7 +220,13 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         };
         uint32_t it = 0;
         Batch cur = next_batch();
+#ifdef NOVA_TL_DEBUG
+        if (tl && lane == 0) tl[3] = now_ns();
+#endif
         int phys_cur = (cur.count > 0 && lane < cur.count) ? __ldg(cur.table + cur.page0 + lane) : 0;
+#ifdef NOVA_TL_DEBUG
+        if (tl && lane == 0 && phys_cur >= -1) tl[6] = now_ns();
+#endif
         while (cur.count > 0) {
             // Issue the first few pages of the batch before looking ahead, so that opening the next
             // segment (work split, prefetch hints) never delays copies that could already be in flight.
@@ -232,10 +258,17 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                         const int c1 = (int)(((int64_t)cur.layer * a.nb + phys) * kKvBlock);
                         const int c2 = cur.group * KVG;
                         mbar_expect_tx(bar, Cfg::kStageBytes);
+#if NOVA_ATTN_EVICT_FIRST
+                        tma_load_3d_hint(dst, &tmk, 0, c1, c2, bar, kv_policy);
+                        tma_load_3d_hint(dst + Cfg::kBoxBytes, &tmk, 64, c1, c2, bar, kv_policy);
+                        tma_load_3d_hint(dst + 2 * Cfg::kBoxBytes, &tmv, 0, c1, c2, bar, kv_policy);
+                        tma_load_3d_hint(dst + 3 * Cfg::kBoxBytes, &tmv, 64, c1, c2, bar, kv_policy);
+#else
                         tma_load_3d(dst, &tmk, 0, c1, c2, bar);
                         tma_load_3d(dst + Cfg::kBoxBytes, &tmk, 64, c1, c2, bar);
                         tma_load_3d(dst + 2 * Cfg::kBoxBytes, &tmv, 0, c1, c2, bar);
                         tma_load_3d(dst + 3 * Cfg::kBoxBytes, &tmv, 64, c1, c2, bar);
+#endif
                         if (tl && it == 0) tl[2] = now_ns();
                     }
                 }
@@ -248,7 +281,9 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             cur = nxt;
             phys_cur = phys_nxt;
         }
+#ifndef NOVA_TL_DEBUG
         if (tl && lane == 0) tl[3] = now_ns();
+#endif
         return;
     }
 
@@ -307,14 +342,14 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         const int kvh = sg.group * KVG + w;
         const int64_t head0 = ((int64_t)sg.layer_local * S + s) * NH + (int64_t)kvh * G;
         int first_page_c, n_pages_row_c;
-        plan_session_pages(a, s, first_page_c, n_pages_row_c);
+        plan_pages_of_keys(a, s_keys[s], first_page_c, n_pages_row_c);
 
         // q fragments of row g (zero for padding rows): hi + lo fp16 parts of q * scale * log2(e).
         // With the fused append q arrives un-rotated: dims d and d+64 of a NeoX pair sit in the same
         // thread (k-steps ks and ks+4), so the rotation at n_past[s] is done here, in registers, with
         // the same fused form as the append kernel.
         uint32_t qh[8][2], ql[8][2];
-        const int pos_new = a.fuse_append ? a.n_past[s] : -1;
+        const int pos_new = a.fuse_append ? s_keys[s] - a.keys_add : -1;      // n_past[s] (the fused append has n_q == 1)
         {
             const float* qp = a.q + (head0 + (g < G ? g : 0)) * kHeadDim;
             float2 x[8][2];
@@ -477,7 +512,9 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         }
 
         // ---- segment done: row sums, then direct output or a partial slot
+#ifndef NOVA_TL_DEBUG
         if (tl && threadIdx.x == 0) tl[5] = now_ns();
+#endif
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int n_contrib = sg.c_last - sg.c_first + 1;
@@ -509,8 +546,12 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             }
         }
         emit(n_contrib == 1, head0, sg.row_id, m, l, [&](int j) { return make_float2(o[j][0], o[j][1]); });
+#ifndef NOVA_TL_DEBUG
         if (tl && threadIdx.x == 0) tl[6] = now_ns();
+#endif
+#ifndef NOVA_TL_DEBUG
         if (tl && threadIdx.x == 0) tl[6] = now_ns();
+#endif
     }
 }
 

@@ -18,7 +18,12 @@ struct PlanView {
     int64_t pages_per_layer;
     int64_t pages_total;   // n_layers * pages_per_layer
     int n_ctas;
+    bool small;            // (pages_total + 1) * (n_ctas + 1) fits 32 bits: the split arithmetic uses 32-bit divisions
 };
+
+__device__ __forceinline__ void plan_finish(PlanView& p) {
+    p.small = (unsigned long long)(p.pages_total + 1) * (unsigned long long)(p.n_ctas + 1) < 0xffffffffULL;
+}
 
 struct Segment {
     int layer_local;   // 0 .. n_layers-1
@@ -42,9 +47,8 @@ __device__ __forceinline__ int plan_session_keys(const AttnLaunch& a, int u) {
     return (a.n_past ? (a.n_past[s] + a.keys_add) : a.keys_imm) + t;
 }
 
-// First logical page and page count of unit s inside the launch's page window.
-__device__ __forceinline__ void plan_session_pages(const AttnLaunch& a, int s, int& first, int& count) {
-    const int n_keys = plan_session_keys(a, s);
+// First logical page and page count of a unit that sees n_keys keys, inside the launch's page window.
+__device__ __forceinline__ void plan_pages_of_keys(const AttnLaunch& a, int n_keys, int& first, int& count) {
     int64_t total = n_keys > 0 ? (((int64_t)n_keys + kKvBlock - 1) >> kKvShift) : 0;
     if (total > a.table_stride) total = a.table_stride;   // never walk past the table
     int64_t lo = a.page_lo > 0 ? a.page_lo : 0;
@@ -53,11 +57,16 @@ __device__ __forceinline__ void plan_session_pages(const AttnLaunch& a, int s, i
     first = (int)lo;
     count = (int)(hi - lo);
 }
+__device__ __forceinline__ void plan_session_pages(const AttnLaunch& a, int s, int& first, int& count) {
+    plan_pages_of_keys(a, plan_session_keys(a, s), first, count);
+}
 
 // Fills prefix[0..rows] (shared memory) with a warp scan; call from all threads of the CTA.
 // slice_out (optional, shared memory, n_sessions entries) receives each session's slice id, fetched by
 // the second warp at the same time, so that no later table lookup waits for it.
-__device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n_groups, int* slice_out = nullptr) {
+// keys_out (optional, shared memory, one entry per unit) receives plan_session_keys of every unit.
+__device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n_groups, int* slice_out = nullptr,
+                                         int* keys_out = nullptr) {
     const int rows = a.n_sessions * plan_nq(a) * n_groups;
     if (slice_out && threadIdx.x >= 32 && threadIdx.x < 64)
         for (int s = (int)threadIdx.x - 32; s < a.n_sessions; s += 32) slice_out[s] = a.slice_ids ? a.slice_ids[s] : s;
@@ -70,7 +79,10 @@ __device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n
             int v = 0;
             if (r < rows) {
                 int first, count;
-                plan_session_pages(a, r / n_groups, first, count);
+                const int u = r / n_groups;
+                const int n_keys = plan_session_keys(a, u);
+                if (keys_out && r - u * n_groups == 0) keys_out[u] = n_keys;
+                plan_pages_of_keys(a, n_keys, first, count);
                 v = count > 0 ? count + a.row_setup_pages : 0;
             }
 #pragma unroll
@@ -86,17 +98,19 @@ __device__ inline void plan_build_prefix(const AttnLaunch& a, int* prefix, int n
 }
 
 __device__ __forceinline__ int plan_owner(const PlanView& p, int64_t page) {
+    if (p.small) return (int)((((unsigned)page + 1u) * (unsigned)p.n_ctas - 1u) / (unsigned)p.pages_total);
     return (int)((((page + 1) * (int64_t)p.n_ctas) - 1) / p.pages_total);
 }
 
 __device__ __forceinline__ int64_t plan_cta_begin(const PlanView& p, int c) {
+    if (p.small) return (int64_t)(((unsigned)c * (unsigned)p.pages_total) / (unsigned)p.n_ctas);
     return ((int64_t)c * p.pages_total) / p.n_ctas;
 }
 
 // Segment that starts at launch-wide page `pos` and ends at the row's end or at `hi`.
 __device__ inline Segment plan_segment(const PlanView& p, int64_t pos, int64_t hi, int setup) {
     Segment sg;
-    sg.layer_local = (int)(pos / p.pages_per_layer);
+    sg.layer_local = p.small ? (int)((unsigned)pos / (unsigned)p.pages_per_layer) : (int)(pos / p.pages_per_layer);
     const int64_t layer_base = (int64_t)sg.layer_local * p.pages_per_layer;
     const int r = (int)(pos - layer_base);
     int lo = 0, up = p.rows_per_layer;           // find row with prefix[row] <= r < prefix[row+1]

@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
     // participating CTA owns at least one page and a row's contributors are exactly
     // c_first .. c_last.
     pv.n_ctas = pv.pages_total < (int64_t)gridDim.x ? (int)pv.pages_total : (int)gridDim.x;
+    plan_finish(pv);
 
     // Rows without any page in the window get their "nothing attended" result here.
     {
