@@ -798,34 +798,47 @@ int nova_batch_decode_step_host(nova_batch* b, const float* q, const float* k, c
             NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_out, cudaEventDisableTiming));
             NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_begin, cudaEventDisableTiming));
         }
-        int cut[5] = {0, L < 2 ? L : 2, L < 6 ? L : 6, L < 14 ? L : 14, L};
+        // Uploads go in growing chunks (layers [0,2), [2,6), [6,14), [14,L)), downloads in shrinking ones
+        // ([0,L-14), [L-14,L-6), [L-6,L-2), [L-2,L)): what stays exposed is two layers' inputs before the
+        // first launch and two layers' outputs after the last.
+        int cin[5] = {0, L < 2 ? L : 2, L < 6 ? L : 6, L < 14 ? L : 14, L};
+        int cout[5] = {0, L > 14 ? L - 14 : 0, L > 6 ? L - 6 : 0, L > 2 ? L - 2 : 0, L};
         NOVA_CUDA_TRY(cudaEventRecord(b->ev_begin, st));              // the COW copies above precede everything
         NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_in, b->ev_begin, 0));
         NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_out, b->ev_begin, 0));
         for (int c = 0; c < 4; ++c) {
-            const int l0 = cut[c], n = cut[c + 1] - cut[c];
+            const int l0 = cin[c], n = cin[c + 1] - cin[c];
             if (n <= 0) continue;
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq + l0 * qs, q + l0 * qs, n * qs * 4, cudaMemcpyHostToDevice, b->s_in));
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk + l0 * ks, k + l0 * ks, n * ks * 4, cudaMemcpyHostToDevice, b->s_in));
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv + l0 * ks, v + l0 * ks, n * ks * 4, cudaMemcpyHostToDevice, b->s_in));
             NOVA_CUDA_TRY(cudaEventRecord(b->ev_in[c], b->s_in));
         }
-        for (int c = 0; c < 4; ++c) {
-            const int l0 = cut[c], l1 = cut[c + 1];
-            if (l1 <= l0) continue;
-            NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_in[c], 0));
-            for (int l = l0; l < l1; ++l) {
-                if (use_fused(b))   // dependent launch only inside a chunk: an event wait sits between chunks
-                    rc = run_attn_fused(b, l, 1, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, st,
-                                        b->pdl && l > l0);
-                else
-                    rc = nova_batch_append_attn(b, l, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, s);
-                if (rc != NOVA_OK) return rc;
+        int ci = 0, co = 0;
+        for (int l = 0; l < L; ++l) {
+            bool fresh = l == 0;                 // no dependent launch right after an event wait or record
+            while (ci < 4 && cin[ci] <= l) {
+                if (cin[ci + 1] > cin[ci] && cin[ci] == l) {
+                    NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_in[ci], 0));
+                    fresh = true;
+                }
+                ++ci;
             }
-            NOVA_CUDA_TRY(cudaEventRecord(b->ev_cmp[c], st));
-            NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_out, b->ev_cmp[c], 0));
-            NOVA_CUDA_TRY(cudaMemcpyAsync(out + l0 * qs, b->dout + l0 * qs, (size_t)(l1 - l0) * qs * 4,
-                                          cudaMemcpyDeviceToHost, b->s_out));
+            while (co < 4 && cout[co + 1] <= l) ++co;
+            if (l > 0 && cout[co] == l) fresh = true;     // an output event was recorded just before this layer
+            if (use_fused(b))
+                rc = run_attn_fused(b, l, 1, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, st,
+                                    b->pdl && !fresh);
+            else
+                rc = nova_batch_append_attn(b, l, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, s);
+            if (rc != NOVA_OK) return rc;
+            if (cout[co + 1] == l + 1) {                   // the chunk [cout[co], l + 1) is complete
+                const int l0 = cout[co];
+                NOVA_CUDA_TRY(cudaEventRecord(b->ev_cmp[co], st));
+                NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_out, b->ev_cmp[co], 0));
+                NOVA_CUDA_TRY(cudaMemcpyAsync(out + l0 * qs, b->dout + l0 * qs, (size_t)(l + 1 - l0) * qs * 4,
+                                              cudaMemcpyDeviceToHost, b->s_out));
+            }
         }
         NOVA_CUDA_TRY(cudaEventRecord(b->ev_out, b->s_out));
         NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_out, 0));
