@@ -46,7 +46,7 @@ WORKLOADS = {
 }
 # dram__bytes_read + dram__bytes_write per attention launch from the ncu captures summarised in
 # profiles/attn_mma_kernel_c2.md (split + merge kernels; config 2 only)
-NCU_TRAFFIC = {("c2", "layer"): 91.49e6 + 3.46e6 + 2.33e6, ("c2", "graph"): 91.49e6 + 3.46e6 + 2.33e6,
+NCU_TRAFFIC = {("c2", "layer"): 91.36e6 + 3.06e6 + 2.33e6, ("c2", "graph"): 91.36e6 + 3.06e6 + 2.33e6,
                ("c2", "fused"): 2.5634e9 + 7.6e6}
 BASE_SEED = 0x5EED0000
 METRIC, UNIT = "decode_steps_per_s", "session-steps/s"
