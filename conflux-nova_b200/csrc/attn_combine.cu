@@ -173,7 +173,9 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
 #ifndef NOVA_COMBINE_MAX_CTAS
 #define NOVA_COMBINE_MAX_CTAS 76
 #endif
-    if (ctas > NOVA_COMBINE_MAX_CTAS) ctas = NOVA_COMBINE_MAX_CTAS;
+    // (a launch that covers several layers is not part of such a chain and takes up to 8 CTAs per SM)
+    const int64_t cap = a.n_layers == 1 ? NOVA_COMBINE_MAX_CTAS : 148 * 8;
+    if (ctas > cap) ctas = cap;
     // Always a programmatic dependent of the split kernel launched just before it.
     const cudaError_t le = launch_kernel_pdl(attn_combine_kernel, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split);
     if (le != cudaSuccess) {
