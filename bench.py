@@ -320,7 +320,7 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
     n_ctx = w["ctx"][0]
     K, W = args.steps, args.warmup
     # Every rank keeps the whole session's pool (7.5 GB) but fills and reads only its own page range.
-    work = wl.Workload(w["model"], [n_ctx], seed=seed, steps=2 * (W + K) + 8, device=local_rank, fill=False)
+    work = wl.Workload(w["model"], [n_ctx], seed=seed, steps=2 * (W + K) + 16, device=local_rank, fill=False)
     eng, batch = work.eng, work.batch
     n_pages = (n_ctx + 15) // 16
     lo, hi = lc.page_range(rank, world, n_pages)
@@ -339,17 +339,20 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
     qs, ks = NH * 128 * 4, NKV * 128 * 4
     es_tok = 2 * NKV * 128 * 2
 
-    def step():
-        if args.collective == "layer":
+    gath = torch.empty((L, world, NH, lc.PART_W), dtype=torch.float32, device="cuda")
+    per_layer = args.collective == "layer"
+
+    def step(st=st):
+        if per_layer:
             for l in range(L):
                 batch.append(l, dq.ptr + l * qs, dk.ptr + l * ks, dv.ptr + l * ks, st)
                 batch.attn_partial(l, dq.ptr + l * qs, lo, hi, part[l].data_ptr(), st)
-                g = lc.gather_partials(part[l], world, dist)
+                g = lc.gather_partials(part[l], world, dist, out=gath[l])
                 nv.check(nv.lib.nova_lse_combine(g.data_ptr(), world, NH, 128, out[l].data_ptr(), st))
         else:
             batch.append_layers(0, L, dq.ptr, dk.ptr, dv.ptr, st)
             batch.attn_partial_layers(0, L, dq.ptr, lo, hi, part.data_ptr(), st)
-            g = lc.gather_partials(part.reshape(L * NH, lc.PART_W), world, dist)
+            g = lc.gather_partials(part.reshape(L * NH, lc.PART_W), world, dist, out=gath.reshape(world, L * NH, lc.PART_W))
             nv.check(nv.lib.nova_lse_combine(g.data_ptr(), world, L * NH, 128, out.data_ptr(), st))
         batch.advance(st)
 

@@ -31,12 +31,15 @@ def owner_of_page(page: int, world: int, n_pages: int) -> int:
     return min(page // max(per, 1), world - 1)
 
 
-def gather_partials(part, world: int, dist=None):
-    """all-gather of one partial tensor [rows][130] -> [world][rows][130] (rank order)."""
+def gather_partials(part, world: int, dist=None, out=None):
+    """all-gather of one partial tensor [rows][130] -> [world][rows][130] (rank order).  `out`: an optional
+    contiguous tensor of world * part.numel() elements that receives the result (no allocation per call)."""
     import torch
     if world == 1 or dist is None:
         return part.unsqueeze(0)
     flat = part.contiguous().reshape(-1)
-    out = torch.empty(world * flat.numel(), dtype=part.dtype, device=part.device)
-    dist.all_gather_into_tensor(out, flat)           # concatenation in rank order, on every backend
-    return out.reshape((world,) + tuple(part.shape))
+    if out is None:
+        out = torch.empty(world * flat.numel(), dtype=part.dtype, device=part.device)
+    flat_out = out.reshape(-1)
+    dist.all_gather_into_tensor(flat_out, flat)      # concatenation in rank order, on every backend
+    return flat_out.reshape((world,) + tuple(part.shape))
