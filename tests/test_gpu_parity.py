@@ -521,6 +521,46 @@ def test_run_steps_native_loop(nv, ob, mode, kernel, pdl):
     eng.close()
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("model,n_sessions", [("qwen25_7b", 300), ("qwen25_14b", 120), ("qwen25_1p5b", 200)])
+def test_many_short_sessions_chained_launches(nv, ob, model, n_sessions, mode):
+    """Far more rows than CTAs: every CTA's page range crosses several row boundaries, so finished
+    segments are parked in shared memory (and, past two of them, written after an early dependency
+    wait), the merge CTAs loop over many rows, and some sessions are empty.  Per-layer launches chained
+    by programmatic dependent launch, plain and replayed from a graph, three steps against the oracle."""
+    rng0 = np.random.default_rng(5)
+    ctx_lens = [int(x) for x in rng0.integers(0, 90, n_sessions)]
+    ctx_lens[3] = 0
+    ctx_lens[7] = 16
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, nv.KV_F16, ctx_lens, L=3, seed=23)
+    L, S, NH, NKV = eng.L, len(ss), eng.NH, eng.NKV
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
+    batch = eng.batch(ss)
+    try_set_kernel(nv, batch, 2)
+    batch.set_pdl(1)
+    n_steps = 3
+    q = rng.standard_normal((n_steps, L, S, NH, 128)).astype(np.float32)
+    k = rng.standard_normal((n_steps, L, S, NKV, 128)).astype(np.float32)
+    v = rng.standard_normal((n_steps, L, S, NKV, 128)).astype(np.float32)
+    dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+    dout = nv.DevBuf(q.nbytes)
+    st = nv.Stream()
+    batch.run_steps(n_steps, dq.ptr, dk.ptr, dv.ptr, dout.ptr, q[0].size, k[0].size, mode, st.h)
+    st.sync()
+    assert batch.device_status() == 0
+    got = dout.download(np.float32).reshape(q.shape)
+    pos = list(ctx_lens)
+    for i in range(n_steps):
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q[i], k[i], v[i], cs, sn, exact=True)
+        assert_attn_close(got[i], want, f"step {i}")
+        pos = [p + 1 for p in pos]
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    st.close()
+    batch.close()
+    eng.close()
+
+
 @pytest.mark.parametrize("kernel", [0, 1])
 @pytest.mark.parametrize("model", ["qwen25_1p5b", "qwen25_7b"])
 def test_prefill_vs_oracle_and_reference(nv, ob, model, kernel):
