@@ -168,9 +168,6 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         sg.page_count = 0;
         int seg_done = 0, seg_first_page = 0, seg_keys = 0;
         const int32_t* seg_table = nullptr;
-#ifdef NOVA_TL_DEBUG
-        bool dbg_first = true;
-#endif
         bool first_segment = true;
         auto next_batch = [&]() -> Batch {
             Batch b;
@@ -185,9 +182,6 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                 int n_pages_row;
                 plan_pages_of_keys(a, seg_keys, seg_first_page, n_pages_row);
                 seg_table = a.table_base + (int64_t)s_slice[s / NQ] * a.table_stride;
-#ifdef NOVA_TL_DEBUG
-                if (tl && lane == 0 && dbg_first) { tl[5] = now_ns(); dbg_first = false; }
-#endif
                 // Warm L2 with what the consumers will ask for when they reach this segment.  Not for the
                 // CTA's first segment: the consumers fetch that themselves at this very moment, and the
                 // hints would only delay the first page copies.
@@ -220,13 +214,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         };
         uint32_t it = 0;
         Batch cur = next_batch();
-#ifdef NOVA_TL_DEBUG
-        if (tl && lane == 0) tl[3] = now_ns();
-#endif
         int phys_cur = (cur.count > 0 && lane < cur.count) ? __ldg(cur.table + cur.page0 + lane) : 0;
-#ifdef NOVA_TL_DEBUG
-        if (tl && lane == 0 && phys_cur >= -1) tl[6] = now_ns();
-#endif
         while (cur.count > 0) {
             // Issue the first few pages of the batch before looking ahead, so that opening the next
             // segment (work split, prefetch hints) never delays copies that could already be in flight.
@@ -281,9 +269,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             cur = nxt;
             phys_cur = phys_nxt;
         }
-#ifndef NOVA_TL_DEBUG
         if (tl && lane == 0) tl[3] = now_ns();
-#endif
         return;
     }
 
@@ -512,9 +498,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         }
 
         // ---- segment done: row sums, then direct output or a partial slot
-#ifndef NOVA_TL_DEBUG
         if (tl && threadIdx.x == 0) tl[5] = now_ns();
-#endif
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int n_contrib = sg.c_last - sg.c_first + 1;
@@ -546,12 +530,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             }
         }
         emit(n_contrib == 1, head0, sg.row_id, m, l, [&](int j) { return make_float2(o[j][0], o[j][1]); });
-#ifndef NOVA_TL_DEBUG
         if (tl && threadIdx.x == 0) tl[6] = now_ns();
-#endif
-#ifndef NOVA_TL_DEBUG
-        if (tl && threadIdx.x == 0) tl[6] = now_ns();
-#endif
     }
 }
 

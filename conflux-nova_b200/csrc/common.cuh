@@ -127,9 +127,11 @@ struct AttnLaunch {
     const float* rope_cs;        // [rope_rows][64]
     const float* rope_sn;
     int64_t rope_rows;
-    // Programmatic dependent launch: 1 = this launch may start while the kernel before it in the
-    // stream is still running.  The kernels then read only data that the previous kernel cannot be
-    // writing (pages of earlier steps, tables, n_past) before their griddepcontrol.wait.
+    // Programmatic dependent launch: 1 = this launch may start while the kernels before it in the
+    // stream are still running.  The caller promises that those kernels neither write what this launch
+    // reads (pages of earlier steps, tables, n_past, its q/k/v) nor touch what it writes for its own
+    // layers (their pages, k rows, outputs); the shared partial-slot scratch is written only after
+    // griddepcontrol.wait.
     int32_t pdl;
     // Work-split weight of starting a row inside a CTA (q fetch, and with the fused append the new
     // token's k/v fetch at the row end next to it), in pages: every row is treated as that many pages

@@ -280,8 +280,9 @@ int  nova_batch_get_kernel(const nova_batch* b);
  * of the batch writes record i % 4), or NULL to switch off.
  * Every CTA of the next attention launches leaves %globaltimer stamps there: [0] start, [1] work split
  * known, [2] first page requested, [3] last page requested, [4] first page landed, [5] last page
- * consumed, [6] results/partials written; after those 148*8 values the first 148 CTAs of the combine
- * kernel leave four stamps each (start, dependency met, first maximum known, end). */
+ * consumed, [6] results/partials written, [7] the SM it ran on (%smid, not a time); after those 148*8
+ * values the first 148 CTAs of the combine kernel leave four values each (start, dependency met, %smid,
+ * end). */
 int  nova_batch_set_timeline(nova_batch* b, void* dev_buf);
 
 /* For each session s of the batch: session_cow(s, n_past, 1).  One kernel copies
@@ -303,10 +304,11 @@ int  nova_batch_attn(nova_batch* b, int layer, const float* q, float* out, nova_
  * not rely on the contents of q afterwards (the reference does not read it after AttnOp either). */
 int  nova_batch_set_fused_append(nova_batch* b, int on);
 /* Programmatic dependent launch for nova_batch_run_steps / nova_batch_decode_step_host with the fused
- * append: the attention launch of every layer after the first may start while the previous layer's
- * merge is still running: it streams and processes its pages and waits (griddepcontrol.wait) only before
- * its first write (new token, outputs, partial slots).  The caller promises that the launch before such a
- * layer in the stream does not produce that layer's q, k or v (true inside these two calls). */
+ * append: the launches of every layer after the first may start while the previous layer's kernels are
+ * still running (consecutive layers overlap on the GPU).  Such a launch streams and processes its pages,
+ * appends its layer's new token, and waits (griddepcontrol.wait) only before it writes outputs or
+ * partial slots.  Inside these two calls the layer before never produces the next layer's q, k or v and
+ * never touches its pages; that is the promise the attribute needs. */
 int  nova_batch_set_pdl(nova_batch* b, int on);
 /* Tuning knob of the attention work split: how many pages' worth of time starting a session inside a
  * CTA costs (default 2).  A CTA whose page range crosses a session boundary gets that many fewer pages. */
