@@ -342,8 +342,28 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
     gath = torch.empty((L, world, NH, lc.PART_W), dtype=torch.float32, device="cuda")
     per_layer = args.collective == "layer"
 
+    xch = status_word = None
+    epoch = [0]
+    if args.collective in ("p2p", "p2p-step"):
+        # no all-gather: every rank's partial rows stay in its own exchange buffer and each rank's merge
+        # kernel reads all of them over NVLink (nova_lse_merge_peers)
+        xch = lc.PeerExchange(nv, NH if args.collective == "p2p" else L * NH, rank, world, dist, n_slots=2)
+        status_word = nv.DevBuf(4).zero()
+        dist.barrier()
+
     def step(st=st):
-        if per_layer:
+        if xch is not None and args.collective == "p2p":
+            for l in range(L):
+                epoch[0] += 1
+                batch.append(l, dq.ptr + l * qs, dk.ptr + l * ks, dv.ptr + l * ks, st)
+                batch.attn_partial(l, dq.ptr + l * qs, lo, hi, xch.rows_ptr(epoch[0] % 2), st)
+                xch.merge(epoch[0], out[l].data_ptr(), st, status_word.ptr)
+        elif xch is not None:
+            epoch[0] += 1
+            batch.append_layers(0, L, dq.ptr, dk.ptr, dv.ptr, st)
+            batch.attn_partial_layers(0, L, dq.ptr, lo, hi, xch.rows_ptr(epoch[0] % 2), st)
+            xch.merge(epoch[0], out.data_ptr(), st, status_word.ptr)
+        elif per_layer:
             for l in range(L):
                 batch.append(l, dq.ptr + l * qs, dk.ptr + l * ks, dv.ptr + l * ks, st)
                 batch.attn_partial(l, dq.ptr + l * qs, lo, hi, part[l].data_ptr(), st)
@@ -375,6 +395,8 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
     dist.barrier()
     clocks = sampler.stop() if sampler else None
     status = batch.device_status()
+    if status_word is not None and int(status_word.download(np.int32)[0]) != 0:
+        status = int(status_word.download(np.int32)[0])       # a peer's flag never arrived
     t = torch.tensor([ms, float(status != 0)], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, bad = float(t[0]), float(t[1])
@@ -397,7 +419,9 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"c5: {w['text']}", "sessions_per_gpu": 1, "context_tokens": [n_ctx], "layers": L,
-                       "kv_dtype": "fp16", "page_tokens": 16, "collective": f"all-gather per {args.collective}",
+                       "kv_dtype": "fp16", "page_tokens": 16, "collective": {"layer": "all-gather per layer", "step": "all-gather per step",
+                                      "p2p": "peer reads in the merge kernel, per layer",
+                                      "p2p-step": "peer reads in the merge kernel, per step"}[args.collective],
                        "pages_per_gpu": -(-n_pages // world), "l2": "inputs larger than L2"},
             "kv_gbs": kv_bytes / ms / 1e6, "kv_bytes_per_step": kv_bytes / K,
             "roofline": {"bound": "hbm", "achieved": kv_bytes / ms / 1e6 / world, "peak": peak, "unit": "GB/s",
@@ -406,6 +430,10 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
             "e2e": None, "gpu_launches": launches, "clocks": clocks, "cpu_baseline": None,
         }
         print(json.dumps(line))
+    if xch is not None:
+        torch.cuda.synchronize()
+        dist.barrier()                 # nobody closes a buffer a peer may still be reading
+        xch.close()
     dist.destroy_process_group()
 
 
@@ -602,7 +630,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--e2e-steps", type=int, default=16)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--collective", default="layer", choices=["layer", "step"],
+    ap.add_argument("--collective", default="layer", choices=["layer", "step", "p2p", "p2p-step"],
                     help="c5 on several GPUs: all-gather + merge after every layer (engine order) or once per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--launch", default="layer", choices=["layer", "graph", "fused"],

@@ -54,6 +54,7 @@ SIGNATURES = {
     "dev_upload": (i32, [vp, vp, sz]), "dev_download": (i32, [vp, vp, sz]),
     "dev_zero": (i32, [vp, sz]), "dev_sync": (i32, []), "dev_max_alloc": (sz, []),
     "dev_host_alloc": (vp, [sz]), "dev_host_free": (None, [vp]),
+    "dev_ipc_export": (i32, [vp, vp]), "dev_ipc_open": (i32, [vp, C.POINTER(vp)]), "dev_ipc_close": (i32, [vp]),
     "dev_stream_create": (i32, [C.POINTER(vp)]), "dev_stream_destroy": (i32, [vp]),
     "dev_stream_sync": (i32, [vp]),
     "dev_event_create": (i32, [C.POINTER(vp)]), "dev_event_destroy": (i32, [vp]),
@@ -118,6 +119,8 @@ SIGNATURES = {
     "nova_batch_attn_partial": (i32, [vp, i32, vp, i64, i64, vp, vp]),
     "nova_batch_attn_partial_layers": (i32, [vp, i32, i32, vp, i64, i64, vp, vp]),
     "nova_lse_combine": (i32, [vp, i32, i32, i32, vp, vp]),
+    "nova_peer_slot_bytes": (sz, [i32]),
+    "nova_lse_merge_peers": (i32, [C.POINTER(vp), i32, i32, sz, i32, i32, i64, i32, vp, vp, vp]),
 }
 
 

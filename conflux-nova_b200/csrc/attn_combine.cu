@@ -157,6 +157,74 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restric
     out[(size_t)row * kHeadDim + d] = L > 0.f ? A / L : 0.f;
 }
 
+
+// The same merge with the all-gather folded in: rank r's partial rows live in rank r's own memory
+// (an exchange slot: a 128-byte header whose first 8 bytes are the epoch flag, then n_rows x 130
+// floats) and every rank reads all of them over NVLink.  Each CTA first publishes this rank's flag
+// (its rows were written by kernels that precede this one in the stream), then waits - bounded by
+// wall clock - until every peer's flag has reached the epoch, then merges in rank order.  The kernels
+// that wait on one another run on different GPUs, never on one.
+struct PeerSlots {
+    unsigned char* base[kMaxPeerRanks];
+};
+
+__device__ __forceinline__ long long ld_acquire_sys(const long long* p) {
+    long long v;
+    asm volatile("ld.acquire.sys.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(long long* p, long long v) {
+    asm volatile("st.release.sys.global.s64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(128) lse_merge_peers_kernel(PeerSlots ps, int n_ranks, int my_rank, int n_rows,
+                                                              long long epoch, unsigned long long timeout_ns,
+                                                              float* __restrict__ out, int32_t* status) {
+    __shared__ int s_ok;
+    const int row = (int)blockIdx.x;
+    const int d = (int)threadIdx.x;
+    if (d == 0) {
+        s_ok = 1;
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<long long*>(ps.base[my_rank]), epoch);   // the same value from every CTA
+    }
+    __syncthreads();
+    if (d < n_ranks && d != my_rank) {
+        const long long* flag = reinterpret_cast<const long long*>(ps.base[d]);
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        while (ld_acquire_sys(flag) < epoch) {
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > timeout_ns) {            // the peer never got there: report, do not read its rows
+                s_ok = 0;
+                if (status) atomicCAS(status, 0, NOVA_ERR_TIMEOUT);
+                break;
+            }
+            __nanosleep(200);
+        }
+    }
+    __syncthreads();
+    if (!s_ok || row >= n_rows) return;
+    float M = -INFINITY;
+    for (int p = 0; p < n_ranks; ++p) {
+        const float* pr = reinterpret_cast<const float*>(ps.base[p] + kPeerSlotHeader) + (size_t)row * kPartW;
+        if (__ldcv(pr + 1) > 0.f) M = fmaxf(M, __ldcv(pr));
+    }
+    float L = 0.f, A = 0.f;
+#pragma unroll 4
+    for (int p = 0; p < n_ranks; ++p) {
+        const float* pr = reinterpret_cast<const float*>(ps.base[p] + kPeerSlotHeader) + (size_t)row * kPartW;
+        const float lp = __ldcv(pr + 1), mp = __ldcv(pr), ap = __ldcv(pr + 2 + d);
+        if (lp > 0.f) {
+            const float w = __expf(mp - M);
+            L = fmaf(lp, w, L);
+            A = fmaf(ap, w, A);
+        }
+    }
+    out[(size_t)row * kHeadDim + d] = L > 0.f ? A / L : 0.f;
+}
+
 }  // namespace
 
 int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
@@ -189,6 +257,20 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
 int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s) {
     if (n_rows <= 0 || n_parts <= 0) return NOVA_OK;
     lse_combine_kernel<<<(unsigned)n_rows, kHeadDim, 0, s>>>(parts, n_parts, n_rows, out);
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+}  // namespace novab
+
+namespace novab {
+
+int launch_lse_merge_peers(void* const* slot_base, int n_ranks, int my_rank, int n_rows, long long epoch,
+                           unsigned long long timeout_ns, float* out, int32_t* status, cudaStream_t s) {
+    if (n_rows <= 0) return NOVA_OK;
+    PeerSlots ps;
+    for (int i = 0; i < kMaxPeerRanks; ++i) ps.base[i] = i < n_ranks ? static_cast<unsigned char*>(slot_base[i]) : nullptr;
+    lse_merge_peers_kernel<<<(unsigned)n_rows, kHeadDim, 0, s>>>(ps, n_ranks, my_rank, n_rows, epoch, timeout_ns, out, status);
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }

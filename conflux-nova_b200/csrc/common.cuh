@@ -155,6 +155,10 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s); 
 int attn_split_ctas_simt(const AttnLaunch& a, int n_ctas);
 int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas);
 int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s);
+constexpr int kMaxPeerRanks = 8;        // ranks of one NVLink domain that can share a long session
+constexpr int kPeerSlotHeader = 128;    // bytes in front of an exchange slot's rows; the first 8 are the epoch flag
+int launch_lse_merge_peers(void* const* slot_base, int n_ranks, int my_rank, int n_rows, long long epoch,
+                           unsigned long long timeout_ns, float* out, int32_t* status, cudaStream_t s);
 
 // rope / append / page utilities (rope_append.cu)
 int launch_rope_table(float* cs, float* sn, int64_t n_pos, int theta, cudaStream_t s);

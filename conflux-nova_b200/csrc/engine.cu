@@ -508,6 +508,26 @@ int nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim, 
     return launch_lse_combine(parts, n_parts, n_rows, out, (cudaStream_t)s);
 }
 
+size_t nova_peer_slot_bytes(int n_rows) {
+    if (n_rows <= 0) return 0;
+    const size_t raw = (size_t)kPeerSlotHeader + (size_t)n_rows * kPartW * sizeof(float);
+    return (raw + 127) / 128 * 128;
+}
+
+int nova_lse_merge_peers(void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int slot, int n_rows,
+                         int64_t epoch, int timeout_ms, float* out, int32_t* status, nova_stream_t s) {
+    if (!peer_base || !out || n_ranks < 1 || n_ranks > kMaxPeerRanks || my_rank < 0 || my_rank >= n_ranks || slot < 0 ||
+        n_rows < 0 || epoch < 1 || timeout_ms < 1 || slot_bytes < nova_peer_slot_bytes(n_rows) || slot_bytes % 128)
+        return NOVA_ERR_INVALID;
+    void* base[kMaxPeerRanks];
+    for (int i = 0; i < n_ranks; ++i) {
+        if (!peer_base[i]) return NOVA_ERR_INVALID;
+        base[i] = static_cast<unsigned char*>(peer_base[i]) + (size_t)slot * slot_bytes;
+    }
+    return launch_lse_merge_peers(base, n_ranks, my_rank, n_rows, (long long)epoch,
+                                  (unsigned long long)timeout_ms * 1000000ull, out, status, (cudaStream_t)s);
+}
+
 uint64_t nova_synth_key(uint64_t seed, uint64_t tensor, uint64_t session, uint64_t layer) {
     auto mix = [](uint64_t x) {
         x += 0x9E3779B97F4A7C15ull;

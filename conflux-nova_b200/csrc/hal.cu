@@ -144,4 +144,29 @@ int dev_stream_sync(nova_stream_t s) {
     return NOVA_OK;
 }
 
+// Sharing one device allocation between the processes of a node (one process per GPU): the owner
+// exports a 64-byte handle, a peer opens it and gets a pointer it can use in its own kernels (peer
+// access over NVLink is enabled by the open).  Only whole dev_alloc allocations can be exported.
+int dev_ipc_export(void* dev_ptr, void* handle64) {
+    if (!dev_ptr || !handle64) return NOVA_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    NOVA_CUDA_TRY(cudaIpcGetMemHandle(&h, dev_ptr));
+    std::memcpy(handle64, &h, sizeof(h));
+    return NOVA_OK;
+}
+int dev_ipc_open(const void* handle64, void** dev_ptr) {
+    if (!handle64 || !dev_ptr) return NOVA_ERR_INVALID;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof(h));
+    void* p = nullptr;
+    NOVA_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *dev_ptr = p;
+    return NOVA_OK;
+}
+int dev_ipc_close(void* dev_ptr) {
+    if (dev_ptr) NOVA_CUDA_TRY(cudaIpcCloseMemHandle(dev_ptr));
+    return NOVA_OK;
+}
+
 }  // extern "C"

@@ -43,3 +43,52 @@ def gather_partials(part, world: int, dist=None, out=None):
     flat_out = out.reshape(-1)
     dist.all_gather_into_tensor(flat_out, flat)      # concatenation in rank order, on every backend
     return flat_out.reshape((world,) + tuple(part.shape))
+
+
+class PeerExchange:
+    """Exchange buffers of all ranks of a node for nova_lse_merge_peers: every rank owns `n_slots` slots
+    of partial rows in its own device memory, exports it with dev_ipc_export, and opens the others'.
+    `nv` is the loaded package (ctypes face); `dist` a torch.distributed-like module whose
+    all_gather_object carries the 64-byte handles (None or world 1: only the local buffer)."""
+
+    HEADER = 128
+
+    def __init__(self, nv, n_rows: int, rank: int, world: int, dist=None, n_slots: int = 2):
+        import ctypes as C
+        self.nv, self.rank, self.world, self.n_rows, self.n_slots = nv, rank, world, n_rows, n_slots
+        self.slot_bytes = int(nv.lib.nova_peer_slot_bytes(n_rows))
+        self.buf = nv.DevBuf(self.slot_bytes * n_slots).zero()
+        self.opened = []
+        ptrs = [None] * world
+        ptrs[rank] = self.buf.ptr
+        if world > 1:
+            handle = (C.c_ubyte * 64)()
+            nv.check(nv.lib.dev_ipc_export(self.buf.ptr, handle), "dev_ipc_export")
+            nv.check(nv.lib.dev_sync())
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle))
+            for r in range(world):
+                if r == rank:
+                    continue
+                h = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+                p = C.c_void_p()
+                nv.check(nv.lib.dev_ipc_open(h, C.byref(p)), "dev_ipc_open")
+                self.opened.append(p)
+                ptrs[r] = p.value
+        self.base = (C.c_void_p * world)(*ptrs)
+
+    def rows_ptr(self, slot: int) -> int:
+        """Where this rank's partial rows of `slot` go (the `part` argument of nova_batch_attn_partial)."""
+        return self.buf.ptr + slot * self.slot_bytes + self.HEADER
+
+    def merge(self, epoch: int, out_ptr: int, stream=None, status_ptr=None, timeout_ms: int = 1000, n_rows=None):
+        slot = epoch % self.n_slots
+        self.nv.check(self.nv.lib.nova_lse_merge_peers(self.base, self.world, self.rank, self.slot_bytes, slot,
+                                                        self.n_rows if n_rows is None else n_rows, epoch, timeout_ms,
+                                                        out_ptr, status_ptr, stream), "nova_lse_merge_peers")
+
+    def close(self):
+        for p in self.opened:
+            self.nv.lib.dev_ipc_close(p)
+        self.opened = []
+        self.buf.free()

@@ -63,6 +63,12 @@ int    dev_sync(void);
 size_t dev_max_alloc(void);                                 /* free device bytes right now */
 void*  dev_host_alloc(size_t bytes);                        /* pinned host memory (model.cpp staging buffer) */
 void   dev_host_free(void* p);
+/* One dev_alloc allocation shared between the processes of a node (one process per GPU); no counterpart in
+ * the reference, which is single-process.  The owner exports a 64-byte handle, a peer opens it and gets a
+ * pointer valid in its own kernels (peer access over NVLink is switched on by the open). */
+int    dev_ipc_export(void* dev_ptr, void* handle64);
+int    dev_ipc_open(const void* handle64, void** dev_ptr);
+int    dev_ipc_close(void* dev_ptr);
 int    dev_stream_create(nova_stream_t* out);
 int    dev_stream_destroy(nova_stream_t s);
 int    dev_stream_sync(nova_stream_t s);
@@ -367,6 +373,24 @@ int  nova_batch_attn_partial_layers(nova_batch* b, int layer0, int n_layers, con
                                     int64_t page1, float* part, nova_stream_t s);
 int  nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim, float* out,
                       nova_stream_t s);
+
+/* The merge with the exchange folded in (no counterpart in the reference, which scales a long context
+ * only inside one GPU): every rank keeps its partial rows in its OWN exchange buffer, shared with the
+ * other processes of the node through dev_ipc_export / dev_ipc_open, and the merge kernel of every rank
+ * reads all ranks' rows over NVLink itself - no all-gather.
+ *   exchange buffer = n_slots slots of slot_bytes (>= nova_peer_slot_bytes(n_rows), a multiple of 128),
+ *   zero-filled once; slot = 128-byte header (first 8 bytes: epoch flag) + rows [n_rows][2+HD], i.e.
+ *   nova_batch_attn_partial writes to  base + slot * slot_bytes + 128.
+ * nova_lse_merge_peers, called by every rank with the same slot and epoch after its own partial
+ * kernels on stream s: publishes this rank's flag (= epoch), waits until every peer's flag >= epoch
+ * (each wait bounded by timeout_ms; on expiry *status (device, may be NULL) becomes NOVA_ERR_TIMEOUT
+ * and out is left alone), then merges the ranks' rows in rank order into out [n_rows][HD].
+ * Epochs grow by one per call (start at 1); with slot = epoch % n_slots, n_slots >= 2 is enough: a
+ * rank can be at most one epoch ahead of a peer that is still reading.  peer_base: host array of
+ * n_ranks (<= 8) device pointers, entry my_rank being this rank's own buffer. */
+size_t nova_peer_slot_bytes(int n_rows);
+int  nova_lse_merge_peers(void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int slot, int n_rows,
+                          int64_t epoch, int timeout_ms, float* out, int32_t* status, nova_stream_t s);
 
 #ifdef __cplusplus
 }

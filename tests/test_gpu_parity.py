@@ -359,6 +359,56 @@ def test_partial_and_lse_combine(nv, ob, kernel):
     eng.close()
 
 
+def test_peer_merge_on_one_gpu(nv, ob):
+    """nova_lse_merge_peers, the merge that reads every rank's partial rows from that rank's own exchange
+    buffer: here the 'ranks' are four buffers of this one GPU whose flags are set beforehand (kernels that
+    wait on one another never share a GPU), so no wait happens.  Same result as nova_lse_combine on the
+    stacked rows and as the oracle's merge, for every rank's view, over two epochs (both slots).  Then the
+    bounded wait: one flag that nothing sets -> NOVA_ERR_TIMEOUT in the status word, output left alone."""
+    rng = np.random.default_rng(31)
+    n_ranks, n_rows = 4, 56
+    slot_bytes = int(nv.lib.nova_peer_slot_bytes(n_rows))
+    assert slot_bytes % 128 == 0 and slot_bytes >= 128 + n_rows * 130 * 4
+    bufs = [nv.DevBuf(2 * slot_bytes).zero() for _ in range(n_ranks)]
+    base = (C.c_void_p * n_ranks)(*[b.ptr for b in bufs])
+    status = nv.DevBuf(4).zero()
+    out = nv.DevBuf(n_rows * 128 * 4)
+    for epoch in (1, 2):
+        slot = epoch % 2
+        parts = rng.standard_normal((n_ranks, n_rows, 130)).astype(np.float32)
+        parts[:, :, 1] = np.abs(parts[:, :, 1]) + 0.1
+        parts[2, 5, 1] = 0.0                     # a rank whose page range held no key of that row
+        parts[2, 5, 0] = -np.inf
+        parts[:, 9, 1] = 0.0                     # a row nobody attended
+        for r in range(n_ranks):
+            bufs[r].upload(parts[r], offset=slot * slot_bytes + 128)
+            bufs[r].upload(np.array([epoch], np.int64), offset=slot * slot_bytes)
+        stacked = nv.to_device(parts)
+        ref = nv.DevBuf(n_rows * 128 * 4)
+        nv.check(nv.lib.nova_lse_combine(stacked.ptr, n_ranks, n_rows, 128, ref.ptr, None))
+        nv.check(nv.lib.dev_sync())
+        want = ref.download(np.float32)
+        assert rel_l2(ob.lse_combine(parts).ravel(), want) < 1e-5
+        for me in range(n_ranks):
+            out.zero()
+            nv.check(nv.lib.nova_lse_merge_peers(base, n_ranks, me, slot_bytes, slot, n_rows, epoch, 200, out.ptr, status.ptr, None))
+            nv.check(nv.lib.dev_sync())
+            assert np.array_equal(bits(out.download(np.float32)), bits(want)), (epoch, me)
+            assert int(status.download(np.int32)[0]) == 0
+    # epoch 3 uses slot 1 again; rank 3 never publishes it
+    for r in range(3):
+        bufs[r].upload(np.array([3], np.int64), offset=slot_bytes)
+    out.upload(np.full(n_rows * 128, 7.0, np.float32))
+    nv.check(nv.lib.nova_lse_merge_peers(base, n_ranks, 0, slot_bytes, 1, n_rows, 3, 50, out.ptr, status.ptr, None))
+    nv.check(nv.lib.dev_sync())
+    assert int(status.download(np.int32)[0]) == nv.ERR_TIMEOUT
+    assert (out.download(np.float32) == 7.0).all()
+    assert nv.lib.nova_lse_merge_peers(base, 9, 0, slot_bytes, 0, n_rows, 1, 50, out.ptr, None, None) == nv.ERR_INVALID
+    assert nv.lib.nova_lse_merge_peers(base, n_ranks, 0, slot_bytes - 128, 0, n_rows, 1, 50, out.ptr, None, None) == nv.ERR_INVALID
+    for b in bufs + [status, out]:
+        b.free()
+
+
 @pytest.mark.parametrize("kernel", [0, 2])
 def test_cow_shared_prefix(nv, ob, kernel):
     """Config-3 in miniature: sessions share a donor's prefix whose tail page is partly filled; the
