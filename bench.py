@@ -31,16 +31,16 @@ import __graft_entry__ as graft  # noqa: E402
 # BASELINE.json configs.  scaling: weak = every GPU gets `sessions` sessions of its own;
 # strong = the `sessions` sessions (or the one long session's pages) are divided over the GPUs.
 WORKLOADS = {
-    "c1": dict(model="qwen25_1p5b", sessions=1, ctx=(1024, 1024), cfg=0, scaling="weak",
+    "c1": dict(model="qwen25_1p5b", sessions=1, ctx=(1024, 1024), cfg=0, scaling="weak", steps=64,
                text="Qwen2.5-1.5B-shaped KV, 1 session x 1024 cached tokens, permuted pages"),
-    "c2": dict(model="qwen25_7b", sessions=8, ctx=(2048, 8192), cfg=1, scaling="weak",
+    "c2": dict(model="qwen25_7b", sessions=8, ctx=(2048, 8192), cfg=1, scaling="weak", steps=256,
                text="Qwen2.5-7B-shaped KV, 8 sessions, contexts uniform in [2048, 8192], permuted pages"),
-    "c3": dict(model="qwen25_7b", sessions=32, ctx=(4088 + 512, 4088 + 512), cfg=2, scaling="weak", prefix=4088,
+    "c3": dict(model="qwen25_7b", sessions=32, ctx=(4088 + 512, 4088 + 512), cfg=2, scaling="weak", prefix=4088, steps=64,
                text="Qwen2.5-7B-shaped KV, 32 sessions sharing one 4088-token prefix (255 full pages + a partly "
                     "filled tail page, un-shared by copy-on-write on the first private append) + 512 private tokens"),
-    "c4": dict(model="qwen25_14b", sessions=64, ctx=(8192, 8192), cfg=3, scaling="strong",
+    "c4": dict(model="qwen25_14b", sessions=64, ctx=(8192, 8192), cfg=3, scaling="strong", steps=128,
                text="Qwen2.5-14B-shaped KV, 64 sessions x 8192 cached tokens, permuted pages, sessions sharded over GPUs"),
-    "c5": dict(model="qwen25_7b", sessions=1, ctx=(131072, 131072), cfg=4, scaling="strong",
+    "c5": dict(model="qwen25_7b", sessions=1, ctx=(131072, 131072), cfg=4, scaling="strong", steps=64,
                text="Qwen2.5-7B-shaped KV, 1 session x 131072 cached tokens, pages split over GPUs, partials merged "
                     "(log-sum-exp) after an NCCL all-gather"),
 }
@@ -626,7 +626,8 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed decode steps (default: the configuration's own count: 64 / 256 / 64 / 128 / 64)")
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--e2e-steps", type=int, default=16)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
@@ -648,6 +649,8 @@ def main():
     ap.add_argument("--quick", action="store_true",
                     help="only the main timed region (for profiler captures): no other modes, e2e or CPU baseline")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = WORKLOADS[args.workload]["steps"] if args.impl == "ours" and not (args.quick or args.quick_prefill) else 32
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     _, _, world = dist_env()
     if args.gpus != world and world > 1:

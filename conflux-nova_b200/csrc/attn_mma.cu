@@ -19,6 +19,12 @@
 //     reports NOVA_ERR_TIMEOUT through the status word instead of spinning forever.
 //   * Work split and partial slots are those of attn_plan.cuh; rows shared by several CTAs are
 //     merged by the combine kernel that follows (attn_combine.cu) - no flags between CTAs.
+//   * K/V copies carry an L2 evict-first hint: pages are read once per step, everything else
+//     (tables, n_past, q, partial slots) is re-read and should stay in L2.
+//   * Under a programmatic launch chain (one layer per launch, each launch a dependent of the one
+//     before) the kernel computes without waiting, parks finished segments in shared memory and
+//     waits for the previous kernels once, right before its first output write; such a launch
+//     leaves NOVA_ATTN_SPARE_SMS SMs without a CTA so that consecutive layers overlap.
 #include "attn_plan.cuh"
 #include "mma_common.cuh"
 
