@@ -331,6 +331,9 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
     eng.set_n_past(work.sessions[0], n_ctx)
     batch.sync_positions()
     batch.set_kernel(1 if args.kernel != 0 else 0)
+    if args.kernel != 0 and args.collective == "p2p":
+        batch.set_fused_append(1)
+        batch.set_pdl(0 if args.no_pdl else 1)
     L, NH, NKV = eng.L, eng.NH, eng.NKV
     tstream = torch.cuda.current_stream()
     st = tstream.cuda_stream
@@ -354,11 +357,12 @@ def run_long_context(args, nv, wl, dist, rank, local_rank, world):
 
     def step(st=st):
         if xch is not None and args.collective == "p2p":
-            for l in range(L):
-                epoch[0] += 1
-                batch.append(l, dq.ptr + l * qs, dk.ptr + l * ks, dv.ptr + l * ks, st)
-                batch.attn_partial(l, dq.ptr + l * qs, lo, hi, xch.rows_ptr(epoch[0] % 2), st)
-                xch.merge(epoch[0], out[l].data_ptr(), st, status_word.ptr)
+            # the whole step natively: per layer fused append + attention over this rank's pages, merge by peer reads
+            nv.check(nv.lib.nova_batch_step_partial_peers(batch.h, dq.ptr, dk.ptr, dv.ptr, lo, hi, xch.base, world, rank,
+                                                          xch.slot_bytes, 2, epoch[0] + 1, 1000, out.data_ptr(),
+                                                          status_word.ptr, st), "step_partial_peers")
+            epoch[0] += L
+            return
         elif xch is not None:
             epoch[0] += 1
             batch.append_layers(0, L, dq.ptr, dk.ptr, dv.ptr, st)

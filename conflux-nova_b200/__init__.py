@@ -120,6 +120,7 @@ SIGNATURES = {
     "nova_batch_attn_partial_layers": (i32, [vp, i32, i32, vp, i64, i64, vp, vp]),
     "nova_lse_combine": (i32, [vp, i32, i32, i32, vp, vp]),
     "nova_peer_slot_bytes": (sz, [i32]),
+    "nova_batch_step_partial_peers": (i32, [vp, vp, vp, vp, i64, i64, C.POINTER(vp), i32, i32, sz, i32, i64, i32, vp, vp, vp]),
     "nova_lse_merge_peers": (i32, [C.POINTER(vp), i32, i32, sz, i32, i32, i64, i32, vp, vp, vp]),
 }
 

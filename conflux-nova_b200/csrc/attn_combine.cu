@@ -183,6 +183,7 @@ __global__ void __launch_bounds__(128) lse_merge_peers_kernel(PeerSlots ps, int 
     __shared__ int s_ok;
     const int row = (int)blockIdx.x;
     const int d = (int)threadIdx.x;
+    pdl_launch_dependents();      // a next layer's attention launch may start; it writes only after this grid is done
     if (d == 0) {
         s_ok = 1;
         __threadfence_system();

@@ -129,9 +129,11 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     // Rows without any page in the window: "nothing attended".
     if (warp < KVG) {
         const int64_t rows_total = (int64_t)pv.rows_per_layer * a.n_layers;
+        bool waited = a.pdl == 0;
         for (int64_t v = blockIdx.x; v < rows_total; v += gridDim.x) {
             const int row = (int)(v % pv.rows_per_layer);
             if (s_prefix[row + 1] != s_prefix[row]) continue;
+            if (!waited) { pdl_wait(); waited = true; }      // an output write: the chain's one rule applies here too
             const int ll = (int)(v / pv.rows_per_layer);
             const int s = row / n_groups, grp = row - s * n_groups;
             const int kvh = grp * KVG + warp;

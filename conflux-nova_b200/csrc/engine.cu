@@ -171,11 +171,18 @@ bool use_fused(const nova_batch* b) { return b->fused && b->kernel == 1 && b->e-
 // RopeKvOp + AttnOp for layers [layer0, layer0 + n_layers) in one split launch (+ combine):
 // k rotated in place and appended with v, q read un-rotated and left as it is.
 int run_attn_fused(const nova_batch* b, int layer0, int n_layers, const float* q, float* k, const float* v,
-                   float* out, cudaStream_t s, bool pdl = false) {
+                   float* out, cudaStream_t s, bool pdl = false, float* out_part = nullptr, int64_t page_lo = 0,
+                   int64_t page_hi = -1) {
     const nova_engine* e = b->e;
     AttnLaunch a;
     fill_attn(b, a);
     a.q = q; a.out = out;
+    if (out_part) {                       // un-normalised partials over the page window [page_lo, page_hi)
+        a.out_part = out_part;
+        a.write_partial_only = 1;
+        a.page_lo = page_lo;
+        a.page_hi = page_hi;
+    }
     a.layer0 = layer0; a.n_layers = n_layers;
     a.fuse_append = 1;
     a.pool_k_w = e->pool_k; a.pool_v_w = e->pool_v;
@@ -1028,6 +1035,45 @@ int nova_batch_attn_partial_layers(nova_batch* b, int layer0, int n_layers, cons
     a.page_hi = page1;
     a.layer0 = layer0; a.n_layers = n_layers;
     return run_attn(b, a, (cudaStream_t)s);
+}
+
+// One decode step of a session split over the GPUs of a node, in the engine's layer order and without any
+// host-side collective: per layer the fused RoPE+append+attention over this rank's page range leaves the
+// partial rows in this rank's exchange slot, and nova_lse_merge_peers merges all ranks' rows into out.
+int nova_batch_step_partial_peers(nova_batch* b, float* q, float* k, const float* v, int64_t page0, int64_t page1,
+                                  void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int n_slots,
+                                  int64_t epoch0, int timeout_ms, float* out, int32_t* status, nova_stream_t s) {
+    if (!b || !q || !k || !v || !out || !peer_base || n_ranks < 1 || n_ranks > kMaxPeerRanks || my_rank < 0 ||
+        my_rank >= n_ranks || n_slots < 2 || epoch0 < 1 || page0 < 0 || page1 < page0)
+        return NOVA_ERR_INVALID;
+    nova_engine* e = b->e;
+    const int L = e->d.n_layers;
+    const int rows = b->n * e->d.n_heads;
+    if (slot_bytes < nova_peer_slot_bytes(rows) || slot_bytes % 128 || !peer_base[my_rank]) return NOVA_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)s;
+    NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    const size_t qs = (size_t)b->n * e->d.n_heads * kHeadDim, ks = (size_t)b->n * e->d.n_kv_heads * kHeadDim;
+    int rc = nova_batch_cow(b, s);
+    if (rc < 0) return rc;
+    for (int l = 0; l < L; ++l) {
+        const int64_t epoch = epoch0 + l;
+        const int slot = (int)(epoch % n_slots);
+        float* part = reinterpret_cast<float*>(static_cast<unsigned char*>(peer_base[my_rank]) + (size_t)slot * slot_bytes +
+                                               kPeerSlotHeader);
+        if (use_fused(b)) {
+            // layers after the first follow the previous layer's merge kernel, which lets its dependents start early
+            rc = run_attn_fused(b, l, 1, q + l * qs, k + l * ks, v + l * ks, nullptr, st, b->pdl && l > 0, part, page0, page1);
+        } else {
+            rc = nova_batch_append(b, l, q + l * qs, k + l * ks, v + l * ks, s);
+            if (rc != NOVA_OK) return rc;
+            rc = nova_batch_attn_partial(b, l, q + l * qs, page0, page1, part, s);
+        }
+        if (rc != NOVA_OK) return rc;
+        rc = nova_lse_merge_peers(peer_base, n_ranks, my_rank, slot_bytes, slot, rows, epoch, timeout_ms, out + l * qs,
+                                  status, s);
+        if (rc != NOVA_OK) return rc;
+    }
+    return nova_batch_advance(b, s);
 }
 
 int nova_batch_attn_partial(nova_batch* b, int layer, const float* q, int64_t page0, int64_t page1, float* part,

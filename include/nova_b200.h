@@ -389,6 +389,15 @@ int  nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim,
  * rank can be at most one epoch ahead of a peer that is still reading.  peer_base: host array of
  * n_ranks (<= 8) device pointers, entry my_rank being this rank's own buffer. */
 size_t nova_peer_slot_bytes(int n_rows);
+/* One whole decode step of the batch's sessions, their pages split over the ranks of a node, issued
+ * natively in layer order: per layer the (fused) RoPE+append+attention over this rank's logical pages
+ * [page0, page1) writes its partial rows [S*NH][2+HD] into slot (epoch0 + layer) % n_slots of this
+ * rank's exchange buffer, then nova_lse_merge_peers with that epoch merges all ranks' rows into
+ * out + layer * S*NH*HD; n_past advances at the end.  q/k/v/out are [layers][S][...] as in
+ * nova_batch_run_steps.  The caller passes epoch0 = 1, 1 + layers, 1 + 2*layers, ... on every rank. */
+int  nova_batch_step_partial_peers(nova_batch* b, float* q, float* k, const float* v, int64_t page0, int64_t page1,
+                                   void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int n_slots,
+                                   int64_t epoch0, int timeout_ms, float* out, int32_t* status, nova_stream_t s);
 int  nova_lse_merge_peers(void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int slot, int n_rows,
                           int64_t epoch, int timeout_ms, float* out, int32_t* status, nova_stream_t s);
 

@@ -409,6 +409,47 @@ def test_peer_merge_on_one_gpu(nv, ob):
         b.free()
 
 
+@pytest.mark.parametrize("kernel,pdl", [(0, 0), (1, 0), (2, 0), (2, 1)])
+def test_step_partial_peers_single_rank(nv, ob, kernel, pdl):
+    """nova_batch_step_partial_peers with one rank (its own exchange buffer, nobody to wait for) is a plain
+    decode step in layer order: outputs, pages and positions against the oracle over three steps; the page
+    window and the epoch/slot walk are the ones a multi-GPU run uses."""
+    ctx_lens = [700, 33, 0, 1500]
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, "qwen25_7b", nv.KV_F16, ctx_lens, L=3, seed=41)
+    L, S, NH, NKV = eng.L, len(ss), eng.NH, eng.NKV
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
+    batch = eng.batch(ss)
+    try_set_kernel(nv, batch, kernel)
+    batch.set_pdl(pdl)
+    rows = S * NH
+    slot_bytes = int(nv.lib.nova_peer_slot_bytes(rows))
+    xbuf = nv.DevBuf(2 * slot_bytes).zero()
+    base = (C.c_void_p * 1)(xbuf.ptr)
+    status = nv.DevBuf(4).zero()
+    st = nv.Stream()
+    pos = list(ctx_lens)
+    dout = nv.DevBuf(L * rows * 128 * 4)
+    for step in range(3):
+        q = rng.standard_normal((L, S, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+        nv.check(nv.lib.nova_batch_step_partial_peers(batch.h, dq.ptr, dk.ptr, dv.ptr, 0, 1 << 40, base, 1, 0, slot_bytes, 2,
+                                                      1 + step * L, 200, dout.ptr, status.ptr, st.h))
+        st.sync()
+        assert batch.device_status() == 0 and int(status.download(np.int32)[0]) == 0
+        got = dout.download(np.float32).reshape(q.shape)
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)
+        assert_attn_close(got, want, f"step {step}")
+        pos = [p + 1 for p in pos]
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    assert [eng.n_past(s) for s in ss] == pos
+    st.close()
+    batch.close()
+    eng.close()
+
+
 @pytest.mark.parametrize("kernel", [0, 2])
 def test_cow_shared_prefix(nv, ob, kernel):
     """Config-3 in miniature: sessions share a donor's prefix whose tail page is partly filled; the
