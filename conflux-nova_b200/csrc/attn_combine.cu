@@ -168,62 +168,86 @@ struct PeerSlots {
     unsigned char* base[kMaxPeerRanks];
 };
 
-__device__ __forceinline__ long long ld_acquire_sys(const long long* p) {
-    long long v;
-    asm volatile("ld.acquire.sys.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(long long* p, long long v) {
-    asm volatile("st.release.sys.global.s64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(long long* p, long long v) {
+    asm volatile("st.relaxed.sys.global.s64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-__global__ void __launch_bounds__(128) lse_merge_peers_kernel(PeerSlots ps, int n_ranks, int my_rank, int n_rows,
-                                                              long long epoch, unsigned long long timeout_ns,
-                                                              float* __restrict__ out, int32_t* status) {
-    __shared__ int s_ok;
+__device__ __forceinline__ long long ld_relaxed_sys(const long long* p) {
+    long long v;
+    asm volatile("ld.relaxed.sys.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One warp per row (a one-warp CTA finds room on an SM next to a running attention CTA, a four-warp one
+// does not and would keep the next layer's CTAs off the SMs it takes).
+__global__ void __launch_bounds__(32) lse_merge_peers_kernel(PeerSlots ps, int n_ranks, int my_rank, int n_rows,
+                                                             long long epoch, unsigned long long timeout_ns,
+                                                             float* __restrict__ out, int32_t* status) {
     const int row = (int)blockIdx.x;
-    const int d = (int)threadIdx.x;
-    pdl_launch_dependents();      // a next layer's attention launch may start; it writes only after this grid is done
-    if (d == 0) {
-        s_ok = 1;
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<long long*>(ps.base[my_rank]), epoch);   // the same value from every CTA
-    }
-    __syncthreads();
-    if (d < n_ranks && d != my_rank) {
-        const long long* flag = reinterpret_cast<const long long*>(ps.base[d]);
+    const int lane = (int)threadIdx.x;
+    // Launched as a programmatic dependent of whatever precedes it in the stream (the local merge of
+    // this layer): the CTAs may become resident early and let a next layer's attention launch start, and
+    // wait here until the kernels that wrote this rank's rows have finished.
+    pdl_launch_dependents();
+    pdl_wait();
+    // Publish with a plain system-scope store: the rows were written by kernels that had completed before
+    // this one started, so they are in this GPU's L2 (where a peer's loads are served) already; a release
+    // fence here cost ~3 us and ordered nothing more.
+    if (lane == 0) st_relaxed_sys(reinterpret_cast<long long*>(ps.base[my_rank]), epoch);   // the same value from every CTA
+    int ok = 1;
+    if (lane < n_ranks && lane != my_rank) {
+        // poll with plain system-scope loads (an acquire on every poll would pay a fence per round trip)
+        const long long* flag = reinterpret_cast<const long long*>(ps.base[lane]);
         unsigned long long t0;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        while (ld_acquire_sys(flag) < epoch) {
+        while (ld_relaxed_sys(flag) < epoch) {
             unsigned long long t1;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
             if (t1 - t0 > timeout_ns) {            // the peer never got there: report, do not read its rows
-                s_ok = 0;
+                ok = 0;
                 if (status) atomicCAS(status, 0, NOVA_ERR_TIMEOUT);
                 break;
             }
-            __nanosleep(200);
         }
     }
-    __syncthreads();
-    if (!s_ok || row >= n_rows) return;
+    // The row loads below bypass the caches (ld.cv) and are issued only after the flag loads have returned
+    // (the loop exit depends on them), so they see what the peer's earlier kernels wrote; no fence (~3 us).
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok || row >= n_rows) return;
+    // All ranks' values first, as independent loads: a load from a peer is a ~2.5 us NVLink round trip,
+    // and one after the other (as a merge over local memory would do it) they would add up.
+    float2 ml[kMaxPeerRanks], a0[kMaxPeerRanks], a1[kMaxPeerRanks];
+#pragma unroll
+    for (int p = 0; p < kMaxPeerRanks; ++p) {
+        ml[p] = make_float2(-INFINITY, 0.f);
+        a0[p] = a1[p] = make_float2(0.f, 0.f);
+        if (p < n_ranks) {
+            const float* pr = reinterpret_cast<const float*>(ps.base[p] + kPeerSlotHeader) + (size_t)row * kPartW;
+            ml[p] = __ldcv(reinterpret_cast<const float2*>(pr));
+            a0[p] = __ldcv(reinterpret_cast<const float2*>(pr + 2 + 4 * lane));
+            a1[p] = __ldcv(reinterpret_cast<const float2*>(pr + 4 + 4 * lane));
+        }
+    }
     float M = -INFINITY;
-    for (int p = 0; p < n_ranks; ++p) {
-        const float* pr = reinterpret_cast<const float*>(ps.base[p] + kPeerSlotHeader) + (size_t)row * kPartW;
-        if (__ldcv(pr + 1) > 0.f) M = fmaxf(M, __ldcv(pr));
-    }
-    float L = 0.f, A = 0.f;
-#pragma unroll 4
-    for (int p = 0; p < n_ranks; ++p) {
-        const float* pr = reinterpret_cast<const float*>(ps.base[p] + kPeerSlotHeader) + (size_t)row * kPartW;
-        const float lp = __ldcv(pr + 1), mp = __ldcv(pr), ap = __ldcv(pr + 2 + d);
-        if (lp > 0.f) {
-            const float w = __expf(mp - M);
-            L = fmaf(lp, w, L);
-            A = fmaf(ap, w, A);
+#pragma unroll
+    for (int p = 0; p < kMaxPeerRanks; ++p)
+        if (p < n_ranks && ml[p].y > 0.f) M = fmaxf(M, ml[p].x);
+    float L = 0.f;
+    float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < kMaxPeerRanks; ++p) {
+        if (p < n_ranks && ml[p].y > 0.f) {
+            const float w = __expf(ml[p].x - M);
+            L = fmaf(ml[p].y, w, L);
+            A.x = fmaf(a0[p].x, w, A.x);
+            A.y = fmaf(a0[p].y, w, A.y);
+            A.z = fmaf(a1[p].x, w, A.z);
+            A.w = fmaf(a1[p].y, w, A.w);
         }
     }
-    out[(size_t)row * kHeadDim + d] = L > 0.f ? A / L : 0.f;
+    const bool some = L > 0.f;
+    *reinterpret_cast<float4*>(out + (size_t)row * kHeadDim + 4 * lane) =
+        make_float4(some ? A.x / L : 0.f, some ? A.y / L : 0.f, some ? A.z / L : 0.f, some ? A.w / L : 0.f);
 }
 
 }  // namespace
@@ -271,7 +295,12 @@ int launch_lse_merge_peers(void* const* slot_base, int n_ranks, int my_rank, int
     if (n_rows <= 0) return NOVA_OK;
     PeerSlots ps;
     for (int i = 0; i < kMaxPeerRanks; ++i) ps.base[i] = i < n_ranks ? static_cast<unsigned char*>(slot_base[i]) : nullptr;
-    lse_merge_peers_kernel<<<(unsigned)n_rows, kHeadDim, 0, s>>>(ps, n_ranks, my_rank, n_rows, epoch, timeout_ns, out, status);
+    const cudaError_t le = launch_kernel_pdl(lse_merge_peers_kernel, dim3((unsigned)n_rows), dim3(32), 0, s, true, ps, n_ranks,
+                                             my_rank, n_rows, epoch, timeout_ns, out, status);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "peer merge launch");
+        return NOVA_ERR_CUDA;
+    }
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }
