@@ -636,8 +636,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--e2e-steps", type=int, default=64)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--collective", default="layer", choices=["layer", "step", "p2p", "p2p-step"],
-                    help="c5 on several GPUs: all-gather + merge after every layer (engine order) or once per step")
+    ap.add_argument("--collective", default="p2p", choices=["layer", "step", "p2p", "p2p-step"],
+                    help="c5 on several GPUs: p2p = merge kernel reads the peers over NVLink, per layer (engine order); layer / step = NCCL all-gather + merge per layer / once per step; p2p-step = peer reads once per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--launch", default="layer", choices=["layer", "graph", "fused"],
                     help="layer: 2 launches per layer; graph: the same, replayed from a CUDA graph; fused: all layers per launch")
