@@ -1,0 +1,98 @@
+"""Two GPUs of one node (skipped where fewer are visible): one session's pages split over two ranks, each
+rank a process of its own with its own pool; nova_batch_step_partial_peers merges over NVLink by peer
+reads (exchange buffers shared with dev_ipc_export / dev_ipc_open).  Every rank's merged output must equal
+the oracle's single-GPU decode step, and both ranks must hold bit-identical outputs."""
+import ctypes as C
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REL_TOL, ABS_TOL = 2e-3, 1e-2          # the tolerance the north-star states for attention
+
+
+def _gpu_count():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+def _worker(rank, world, port, kernel, pdl, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)       # carries the 64-byte handles only
+    import __graft_entry__ as g
+    nv = g.load_package()
+    nv.check(nv.lib.dev_select(rank))
+    import conflux_nova_b200.longctx as lc
+    from oracle import binding as ob
+    ob.oracle()
+    spec = importlib.util.spec_from_file_location("gpu_parity_helpers", os.path.join(ROOT, "tests", "test_gpu_parity.py"))
+    helpers = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(helpers)
+
+    n_ctx = 2500
+    # the same session (same seed) on both ranks; each rank holds all of it but reads only its own pages
+    eng, ss, sh, pk, pv, cs, sn, rng = helpers.build_case(nv, ob, "qwen25_7b", nv.KV_F16, [n_ctx], L=3, seed=77)
+    L, NH, NKV = eng.L, eng.NH, eng.NKV
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
+    batch = eng.batch(ss)
+    helpers.try_set_kernel(nv, batch, kernel)
+    batch.set_pdl(pdl)
+    n_pages = (n_ctx + 15) // 16
+    lo, hi = lc.page_range(rank, world, n_pages)
+    xch = lc.PeerExchange(nv, NH, rank, world, dist, n_slots=2)
+    status = nv.DevBuf(4).zero()
+    dout = nv.DevBuf(L * NH * 128 * 4)
+    st = nv.Stream()
+    pos = [n_ctx]
+    worst = (0.0, 0.0)
+    same = True
+    for step in range(3):
+        q = rng.standard_normal((L, 1, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((L, 1, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((L, 1, NKV, 128)).astype(np.float32)
+        dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+        dist.barrier()
+        nv.check(nv.lib.nova_batch_step_partial_peers(batch.h, dq.ptr, dk.ptr, dv.ptr, lo, hi, xch.base, world, rank,
+                                                      xch.slot_bytes, 2, 1 + step * L, 2000, dout.ptr, status.ptr, st.h))
+        st.sync()
+        assert batch.device_status() == 0 and int(status.download(np.int32)[0]) == 0
+        got = dout.download(np.float32).reshape(q.shape)
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)
+        rel = float(np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want))
+        worst = (max(worst[0], rel), max(worst[1], float(np.abs(got - want).max())))
+        outs = [None] * world
+        dist.all_gather_object(outs, got.tobytes())
+        same = same and all(o == outs[0] for o in outs)
+        pos = [p + 1 for p in pos]
+    dist.barrier()                      # nobody closes a buffer a peer may still read
+    ret[rank] = (worst, same, eng.n_past(ss[0]))
+    xch.close()
+    st.close()
+    batch.close()
+    eng.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs of one node")
+@pytest.mark.parametrize("kernel,pdl", [(1, 0), (2, 1)])
+def test_long_context_step_over_two_gpus(kernel, pdl):
+    import torch.multiprocessing as mp
+    world = 2
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_worker, args=(world, 29700 + kernel * 4 + pdl, kernel, pdl, ret), nprocs=world, join=True)
+        for rank in range(world):
+            (rel, mab), same, n_past = ret[rank]
+            assert rel <= REL_TOL and mab <= ABS_TOL, (rank, rel, mab)
+            assert same, "ranks disagree on the merged output"
+            assert n_past == 2503
