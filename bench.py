@@ -144,6 +144,9 @@ def run_ours(args):
         batch.set_pdl(0 if args.no_pdl else 1)
     if args.row_setup >= 0:
         batch.set_row_setup_pages(args.row_setup)
+    cascade = bool(kernel == 1 and w.get("prefix", 0) and not args.no_cascade)
+    if cascade:
+        batch.set_cascade(1)          # shared prefix pages attended once for all sessions (per-layer launches)
     stream = nv.Stream()
     nq, nk = work.step_input_sizes()
     S, L = len(work.sessions), eng.L
@@ -203,7 +206,7 @@ def run_ours(args):
     launches = int(nv.lib.nova_launch_count() - launches0) * K // (K + W)
     if args.quick:
         if rank == 0:
-            print(json.dumps({"quick": True, "launch": args.launch, "fused_append": fused, "pdl": bool(fused and not args.no_pdl), "kv": args.kv, "kernel": kernel, "ms_per_step": ms_main / K,
+            print(json.dumps({"quick": True, "launch": args.launch, "fused_append": fused, "pdl": bool(fused and not args.no_pdl), "cascade_pages": batch.shared_prefix_pages() if cascade else 0, "kv": args.kv, "kernel": kernel, "ms_per_step": ms_main / K,
                               "kv_gbs": kv_main / ms_main / 1e6, "gpu_launches": launches}))
         return
     # end to end through the host-buffer call: pinned host q/k/v in, out back, every step
@@ -283,6 +286,7 @@ def run_ours(args):
             "config": {"workload": f"{args.workload}: {w['text']}", "sessions_per_gpu": S,
                        "context_tokens": lens, "layers": L, "kv_dtype": "fp16" if args.kv == "f16" else "fp32", "page_tokens": 16,
                        "launch": args.launch, "attention_kernel": "mma" if kernel == 1 else "simt", "fused_append": fused, "pdl": bool(fused and not args.no_pdl),
+                       "cascade_shared_pages": batch.shared_prefix_pages() if cascade else 0,
                        "l2": "inputs larger than L2 (KV read per step >> 126 MB)"},
             "batch_steps_per_s": K / (ms_main / 1e3),
             "kv_gbs": kv_main_all / ms_main / 1e6,
@@ -645,6 +649,7 @@ def main():
     ap.add_argument("--no-fused-append", action="store_true",
                     help="keep RoPE+append as its own launch instead of doing it inside the attention launch")
     ap.add_argument("--row-setup", type=int, default=-1, help="work-split weight of a session start, in pages")
+    ap.add_argument("--no-cascade", action="store_true", help="config 3: attend the shared prefix per session, as the plain path does")
     ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between layers")
     ap.add_argument("--kv", default="f16", choices=["f16", "f32"],
                     help="KV pool element type (f32 = the reference's own format; SIMT kernel)")

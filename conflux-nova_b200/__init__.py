@@ -120,6 +120,7 @@ SIGNATURES = {
     "nova_batch_attn_partial_layers": (i32, [vp, i32, i32, vp, i64, i64, vp, vp]),
     "nova_lse_combine": (i32, [vp, i32, i32, i32, vp, vp]),
     "nova_peer_slot_bytes": (sz, [i32]),
+    "nova_batch_set_cascade": (i32, [vp, i32]), "nova_batch_shared_prefix_pages": (i32, [vp]),
     "nova_batch_step_partial_peers": (i32, [vp, vp, vp, vp, i64, i64, C.POINTER(vp), i32, i32, sz, i32, i64, i32, vp, vp, vp]),
     "nova_lse_merge_peers": (i32, [C.POINTER(vp), i32, i32, sz, i32, i32, i64, i32, vp, vp, vp]),
 }
@@ -468,6 +469,9 @@ class Batch:
     def cow(self, stream=None): return check(lib.nova_batch_cow(self.h, stream), "batch_cow")
     def append(self, layer, q, k, v, stream=None):
         return check(lib.nova_batch_append(self.h, layer, q, k, v, stream), "batch_append")
+    def set_cascade(self, on): return check(lib.nova_batch_set_cascade(self.h, on), "set_cascade")
+    def shared_prefix_pages(self): return lib.nova_batch_shared_prefix_pages(self.h)
+
     def append_layers(self, layer0, n_layers, q, k, v, stream=None):
         return check(lib.nova_batch_append_layers(self.h, layer0, n_layers, q, k, v, stream), "append_layers")
 

@@ -132,31 +132,65 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
 }
 
 // LSE merge of n_parts stacked caller-visible partial buffers [n_parts][n_rows][130] -> out
-// [n_rows][128], parts taken in index order (the multi-GPU merge after an all-gather).
+// [n_rows][128], parts taken in index order (the multi-GPU merge after an all-gather, and the merge of a
+// cascade's page chunks with the private part).  One warp per row, a lane owns four dims.  The loads
+// are batched so that a row costs a few memory round trips whatever n_parts is: the (m, l) pairs come in
+// 32 at a time (one per lane), the accumulators eight parts at a time; the arithmetic itself runs over
+// the parts in order, one fused multiply-add per part and value, as a scalar loop would.
 __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restrict__ parts, int n_parts, int n_rows,
                                                           float* __restrict__ out) {
-    const int row = (int)blockIdx.x;
-    const int d = (int)threadIdx.x;
+    const int lane = (int)threadIdx.x & 31;
+    const int row = (int)blockIdx.x * 4 + ((int)threadIdx.x >> 5);
+    pdl_launch_dependents();
+    pdl_wait();                    // launched as a programmatic dependent of the kernels that write the parts
     if (row >= n_rows) return;
+    const size_t part_stride = (size_t)n_rows * kPartW;
+    const float* base = parts + (size_t)row * kPartW;
     float M = -INFINITY;
-    for (int p = 0; p < n_parts; ++p) {
-        const float* pr = parts + ((size_t)p * n_rows + row) * kPartW;
-        if (pr[1] > 0.f) M = fmaxf(M, pr[0]);
+    for (int p0 = 0; p0 < n_parts; p0 += 32) {
+        float2 ml = make_float2(-INFINITY, 0.f);
+        if (p0 + lane < n_parts) ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)(p0 + lane) * part_stride));
+        float mc = ml.y > 0.f ? ml.x : -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, o));
+        M = fmaxf(M, mc);
     }
-    float L = 0.f, A = 0.f;
-#pragma unroll 4
-    for (int p = 0; p < n_parts; ++p) {
-        const float* pr = parts + ((size_t)p * n_rows + row) * kPartW;
-        const float lp = pr[1], mp = pr[0], ap = pr[2 + d];
-        if (lp > 0.f) {
-            const float w = __expf(mp - M);
-            L = fmaf(lp, w, L);
-            A = fmaf(ap, w, A);
+    float L = 0.f;
+    float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p0 = 0; p0 < n_parts; p0 += 32) {
+        const int cnt = n_parts - p0 < 32 ? n_parts - p0 : 32;
+        float2 ml = make_float2(-INFINITY, 0.f);
+        if (lane < cnt) ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)(p0 + lane) * part_stride));
+        const float w_mine = ml.y > 0.f ? __expf(ml.x - M) : 0.f;
+        for (int i0 = 0; i0 < cnt; i0 += 8) {
+            float2 x0[8], x1[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x0[i] = x1[i] = make_float2(0.f, 0.f);
+                if (i0 + i < cnt) {
+                    const float* pr = base + (size_t)(p0 + i0 + i) * part_stride + 2 + 4 * lane;
+                    x0[i] = __ldcg(reinterpret_cast<const float2*>(pr));
+                    x1[i] = __ldcg(reinterpret_cast<const float2*>(pr + 2));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float w = __shfl_sync(0xffffffffu, w_mine, (i0 + i) & 31);
+                const float lp = __shfl_sync(0xffffffffu, ml.y, (i0 + i) & 31);
+                if (i0 + i < cnt && lp > 0.f) {
+                    L = fmaf(lp, w, L);
+                    A.x = fmaf(x0[i].x, w, A.x);
+                    A.y = fmaf(x0[i].y, w, A.y);
+                    A.z = fmaf(x1[i].x, w, A.z);
+                    A.w = fmaf(x1[i].y, w, A.w);
+                }
+            }
         }
     }
-    out[(size_t)row * kHeadDim + d] = L > 0.f ? A / L : 0.f;
+    const bool some = L > 0.f;
+    *reinterpret_cast<float4*>(out + (size_t)row * kHeadDim + 4 * lane) =
+        make_float4(some ? A.x / L : 0.f, some ? A.y / L : 0.f, some ? A.z / L : 0.f, some ? A.w / L : 0.f);
 }
-
 
 // The same merge with the all-gather folded in: rank r's partial rows live in rank r's own memory
 // (an exchange slot: a 128-byte header whose first 8 bytes are the epoch flag, then n_rows x 130
@@ -267,7 +301,7 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
 #define NOVA_COMBINE_MAX_CTAS 76
 #endif
     // (a launch that covers several layers is not part of such a chain and takes up to 8 CTAs per SM)
-    const int64_t cap = a.n_layers == 1 ? NOVA_COMBINE_MAX_CTAS : 148 * 8;
+    const int64_t cap = (a.n_layers == 1 && a.pdl && a.pdl_spare) ? NOVA_COMBINE_MAX_CTAS : 148 * 8;
     if (ctas > cap) ctas = cap;
     // Always a programmatic dependent of the split kernel launched just before it.
     const cudaError_t le = launch_kernel_pdl(attn_combine_kernel, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split);
@@ -281,7 +315,14 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
 
 int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s) {
     if (n_rows <= 0 || n_parts <= 0) return NOVA_OK;
-    lse_combine_kernel<<<(unsigned)n_rows, kHeadDim, 0, s>>>(parts, n_parts, n_rows, out);
+    // always a programmatic dependent: the kernel waits for everything before it right at its start, so this is
+    // the plain stream order with the launch latency hidden (and a next layer's kernels may be scheduled early)
+    const cudaError_t le = launch_kernel_pdl(lse_combine_kernel, dim3((unsigned)((n_rows + 3) / 4)), dim3(128), 0, s, true, parts,
+                                             n_parts, n_rows, out);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "merge launch");
+        return NOVA_ERR_CUDA;
+    }
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }

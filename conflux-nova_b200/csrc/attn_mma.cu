@@ -607,7 +607,7 @@ int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads,
 int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
     if (n_ctas > 0) return n_ctas;
     const int per_sm = a.kv_group >= 4 ? 1 : 4 / a.kv_group;
-    return (148 - (a.pdl ? NOVA_ATTN_SPARE_SMS : 0)) * per_sm;
+    return (148 - ((a.pdl && a.pdl_spare) ? NOVA_ATTN_SPARE_SMS : 0)) * per_sm;
 }
 
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {

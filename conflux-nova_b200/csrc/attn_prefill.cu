@@ -24,9 +24,16 @@ constexpr int kPfWarps = 4;                       // consumer warps, 16 tile row
 #ifndef NOVA_PREFILL_CTAS_PER_SM
 #define NOVA_PREFILL_CTAS_PER_SM 2     // 204 registers, no spills; 3 CTAs (128 registers) measured slightly slower
 #endif
+// kPrefix = true is the shared-prefix form used by decode steps of sessions that share their first pages
+// (one refcounted prefix): the "query tokens" are the SESSIONS of the batch (q [S][NH][128], one query
+// each), every row sees all keys of the shared pages [0, prefix_pages) of the first session's table,
+// blockIdx.z-like chunks of those pages go to different CTAs, q is rotated here when the append is
+// fused (position n_past[session]), and the result is an un-normalised partial (m, l, acc) per chunk
+// in the layout of the decode kernels, merged later with the partial over each session's private pages.
+template <bool kPrefix>
 __global__ void __launch_bounds__(32 * (kPfWarps + 1), NOVA_PREFILL_CTAS_PER_SM)
 attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv,
-                    int tq, int n_tiles) {
+                    int tq, int n_tiles, int prefix_pages, int chunk_pages) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long s_full[kPfStages];
     __shared__ __align__(8) unsigned long long s_empty[kPfStages];
@@ -37,19 +44,25 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
     const int G = a.n_heads / a.n_kv_heads;
     const int NH = a.n_heads, NKV = a.n_kv_heads, NQ = a.n_q;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    if (kPrefix) pdl_launch_dependents();      // the split over the private pages shares nothing with this kernel
 
     // blockIdx.x -> (tile, kv head, session); late tiles (most keys) first
     int bid = (int)blockIdx.x;
     const int tile = n_tiles - 1 - bid % n_tiles;
     bid /= n_tiles;
     const int kvh = bid % NKV;
-    const int s = bid / NKV;
+    const int s = kPrefix ? 0 : bid / NKV;                  // prefix form: rows index sessions, the table is the first one's
+    const int chunk = kPrefix ? bid / NKV : 0;
     const int t0 = tile * tq;
     const int t_cnt = NQ - t0 < tq ? NQ - t0 : tq;          // query tokens in this tile
-    const int n_past = a.n_past ? a.n_past[s] : a.keys_imm;
-    const int keys_tile = n_past + a.keys_add + t0 + t_cnt - 1;   // keys seen by the tile's last query
-    const int n_pages = (keys_tile + kKvBlock - 1) >> kKvShift;
-    const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
+    const int n_past = kPrefix ? 0 : (a.n_past ? a.n_past[s] : a.keys_imm);
+    const int keys_tile = kPrefix ? prefix_pages * kKvBlock
+                                  : n_past + a.keys_add + t0 + t_cnt - 1;   // keys seen by the tile's last query
+    const int page_begin = kPrefix ? chunk * chunk_pages : 0;
+    const int page_end_all = (keys_tile + kKvBlock - 1) >> kKvShift;
+    const int page_end = kPrefix && page_begin + chunk_pages < page_end_all ? page_begin + chunk_pages : page_end_all;
+    const int n_pages = page_end - page_begin;
+    const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride + page_begin;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kPfStages; ++i) {
@@ -60,7 +73,7 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (n_pages <= 0 || n_pages > a.table_stride) return;
+    if (n_pages <= 0 || page_end > a.table_stride) return;
 
     // ------------------------------------------------------------------ producer warp
     if (warp == kPfWarps) {
@@ -123,21 +136,56 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
         row_tok[h] = t0 + tk;
         row_head[h] = kvh * G + g;
         // last key this row may see; padding rows see everything (their result is dropped)
-        row_lim[h] = row_ok[h] ? n_past + a.keys_add + row_tok[h] - 1 : 0x7fffffff;
+        row_lim[h] = (row_ok[h] && !kPrefix) ? n_past + a.keys_add + row_tok[h] - 1 : 0x7fffffff;
     }
     uint32_t qa[8][4];
+    if (kPrefix && a.fuse_append) {
+        // q arrives un-rotated: NeoX pairs (d, d + 64) sit in this thread (k-steps ks and ks + 4); rotate at
+        // the session's position with the same fused form as the append kernel, then scale and round.
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
+        for (int h = 0; h < 2; ++h) {
+            const int pos = row_ok[h] ? a.n_past[row_tok[h]] : 0;
+            const bool rot = row_ok[h] && pos >= 0 && pos < a.rope_rows;
+            const float* qp = a.q + ((int64_t)row_tok[h] * NH + row_head[h]) * kHeadDim;
+            const float* cr = a.rope_cs + (int64_t)(rot ? pos : 0) * (kHeadDim / 2);
+            const float* sr = a.rope_sn + (int64_t)(rot ? pos : 0) * (kHeadDim / 2);
 #pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf)
+            for (int ks = 0; ks < 4; ++ks)
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float2 x = make_float2(0.f, 0.f);
-                if (row_ok[h])
-                    x = *reinterpret_cast<const float2*>(a.q + (((int64_t)s * NQ + row_tok[h]) * NH + row_head[h]) * kHeadDim +
-                                                         16 * ks + 8 * hlf + 2 * t);
-                qa[ks][2 * hlf + h] = pack_h2(x.x * kQScale, x.y * kQScale);     // a0,a1 (k lo) / a2,a3 (k hi)
-            }
+                for (int hlf = 0; hlf < 2; ++hlf) {
+                    float2 x0 = make_float2(0.f, 0.f), x1 = make_float2(0.f, 0.f);
+                    if (row_ok[h]) {
+                        x0 = *reinterpret_cast<const float2*>(qp + 16 * ks + 8 * hlf + 2 * t);
+                        x1 = *reinterpret_cast<const float2*>(qp + 64 + 16 * ks + 8 * hlf + 2 * t);
+                    }
+                    if (rot) {
+                        const float2 c = *reinterpret_cast<const float2*>(cr + 16 * ks + 8 * hlf + 2 * t);
+                        const float2 sn = *reinterpret_cast<const float2*>(sr + 16 * ks + 8 * hlf + 2 * t);
+                        const float2 y0 = make_float2(__fmaf_rn(x0.x, c.x, -__fmul_rn(x1.x, sn.x)),
+                                                      __fmaf_rn(x0.y, c.y, -__fmul_rn(x1.y, sn.y)));
+                        const float2 y1 = make_float2(__fmaf_rn(x0.x, sn.x, __fmul_rn(x1.x, c.x)),
+                                                      __fmaf_rn(x0.y, sn.y, __fmul_rn(x1.y, c.y)));
+                        x0 = y0;
+                        x1 = y1;
+                    }
+                    qa[ks][2 * hlf + h] = pack_h2(x0.x * kQScale, x0.y * kQScale);
+                    qa[ks + 4][2 * hlf + h] = pack_h2(x1.x * kQScale, x1.y * kQScale);
+                }
+        }
+    } else {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float2 x = make_float2(0.f, 0.f);
+                    if (row_ok[h])
+                        x = *reinterpret_cast<const float2*>(a.q + (((int64_t)s * NQ + row_tok[h]) * NH + row_head[h]) * kHeadDim +
+                                                             16 * ks + 8 * hlf + 2 * t);
+                    qa[ks][2 * hlf + h] = pack_h2(x.x * kQScale, x.y * kQScale);     // a0,a1 (k lo) / a2,a3 (k hi)
+                }
+    }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[16][4];
 #pragma unroll
@@ -152,7 +200,7 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
         }
         const uint32_t sk = stage0 + (uint32_t)stage * kPfStage;
         const uint32_t sv = sk + 2 * kPfBox;
-        const int key0 = pg * kKvBlock;
+        const int key0 = (page_begin + pg) * kKvBlock;
         const int kcount = keys_tile - key0 < kKvBlock ? keys_tile - key0 : kKvBlock;
         if (kcount < kKvBlock) {
             // rows past the tile's last key hold stale bytes: P is 0 there, but 0 * Inf/NaN would poison O.
@@ -226,7 +274,16 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
         float lh = l[h];
         lh += __shfl_xor_sync(0xffffffffu, lh, 1);
         lh += __shfl_xor_sync(0xffffffffu, lh, 2);
-        if (row_ok[h]) {
+        if (!row_ok[h]) continue;
+        if (kPrefix) {
+            // the chunk partials are re-used by every layer: the previous layer's final merge may still read them
+            if (h == 0 || !row_ok[0]) pdl_wait();
+            float* op = a.out_part + (((int64_t)chunk * NQ + row_tok[h]) * NH + row_head[h]) * kPartW;
+            if (t == 0) { op[0] = m[h] * (1.f / kLog2e); op[1] = lh; }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                *reinterpret_cast<float2*>(op + 2 + 8 * j + 2 * t) = make_float2(o[j][2 * h], o[j][2 * h + 1]);
+        } else {
             const float inv = lh > 0.f ? 1.f / lh : 0.f;
             float* op = a.out + (((int64_t)s * NQ + row_tok[h]) * NH + row_head[h]) * kHeadDim;
 #pragma unroll
@@ -249,7 +306,8 @@ int launch_attn_prefill(const AttnLaunch& a, cudaStream_t s) {
     int dev = 0;
     NOVA_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const int tq = attn_prefill_tile_tokens(a.n_heads, a.n_kv_heads);
@@ -258,7 +316,52 @@ int launch_attn_prefill(const AttnLaunch& a, cudaStream_t s) {
     if (ctas > 0x7fffffffLL) return NOVA_ERR_TOO_LARGE;
     const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k1);
     const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v1);
-    attn_prefill_kernel<<<(unsigned)ctas, 32 * (kPfWarps + 1), kPfSmem, s>>>(a, *tk, *tv, tq, n_tiles);
+    attn_prefill_kernel<false><<<(unsigned)ctas, 32 * (kPfWarps + 1), kPfSmem, s>>>(a, *tk, *tv, tq, n_tiles, 0, 0);
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+// Chunks of the shared prefix for a batch of n_sessions decode queries: enough CTAs for two per SM.
+int attn_prefix_chunks(int n_sessions, int n_heads, int n_kv_heads, int prefix_pages, int* chunk_pages) {
+    const int tq = attn_prefill_tile_tokens(n_heads, n_kv_heads);
+    const int n_tiles = (n_sessions + tq - 1) / tq;
+    int chunks = (2 * 148 + n_tiles * n_kv_heads - 1) / (n_tiles * n_kv_heads);
+    if (chunks > prefix_pages / 4) chunks = prefix_pages / 4;          // at least four pages per CTA
+    if (chunks < 1) chunks = 1;
+    const int per = (prefix_pages + chunks - 1) / chunks;
+    if (chunk_pages) *chunk_pages = per;
+    return (prefix_pages + per - 1) / per;
+}
+
+// Partials of every (session, head) row over the shared pages [0, prefix_pages) of the batch's first session:
+// a.out_part [chunks][n_sessions][NH][130], a.q [n_sessions][NH][128] (un-rotated when a.fuse_append), one layer.
+int launch_attn_prefix(const AttnLaunch& a_in, int prefix_pages, cudaStream_t s) {
+    if (!a_in.tmap_k1 || !a_in.tmap_v1 || a_in.n_layers != 1 || !a_in.out_part || prefix_pages < 1) return NOVA_ERR_UNSUPPORTED;
+    if (a_in.n_heads % a_in.n_kv_heads || a_in.n_heads / a_in.n_kv_heads > 16) return NOVA_ERR_UNSUPPORTED;
+    if (a_in.fuse_append && (!a_in.n_past || !a_in.rope_cs || !a_in.rope_sn)) return NOVA_ERR_INVALID;
+    if (a_in.n_sessions <= 0) return NOVA_OK;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    NOVA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    AttnLaunch a = a_in;
+    a.n_q = a_in.n_sessions;             // the sessions are the query rows of one pseudo-session
+    int chunk_pages = 0;
+    const int chunks = attn_prefix_chunks(a_in.n_sessions, a.n_heads, a.n_kv_heads, prefix_pages, &chunk_pages);
+    const int tq = attn_prefill_tile_tokens(a.n_heads, a.n_kv_heads);
+    const int n_tiles = (a.n_q + tq - 1) / tq;
+    const long long ctas = (long long)n_tiles * a.n_kv_heads * chunks;
+    const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k1);
+    const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v1);
+    const cudaError_t le = launch_kernel_pdl(attn_prefill_kernel<true>, dim3((unsigned)ctas), dim3(32 * (kPfWarps + 1)), (size_t)kPfSmem, s,
+                                             a.pdl != 0, a, *tk, *tv, tq, n_tiles, prefix_pages, chunk_pages);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "prefix attention launch");
+        return NOVA_ERR_CUDA;
+    }
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }

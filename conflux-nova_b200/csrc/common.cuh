@@ -133,6 +133,9 @@ struct AttnLaunch {
     // layers (their pages, k rows, outputs); the shared partial-slot scratch is written only after
     // griddepcontrol.wait.
     int32_t pdl;
+    // With pdl: 1 = shape the launch for a chain of one-layer launches that should overlap (the split leaves
+    // some SMs without a CTA, the merge uses few CTAs); 0 = only the early start and the late wait.
+    int32_t pdl_spare;
     // Work-split weight of starting a row inside a CTA (q fetch, and with the fused append the new
     // token's k/v fetch at the row end next to it), in pages: every row is treated as that many pages
     // longer at its start, so a CTA whose range crosses a row boundary gets fewer real pages.
@@ -151,6 +154,10 @@ bool attn_mma_built();
 int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group);
 int launch_attn_prefill(const AttnLaunch& a, cudaStream_t s);     // query-tiled tensor-core prefill (n_q >= 1, one layer)
 int attn_prefill_tile_tokens(int n_heads, int n_kv_heads);
+// Shared-prefix form of the same kernel: decode queries of n_sessions sessions over the shared pages
+// [0, prefix_pages) of the first session's table, as partials a.out_part [chunks][n_sessions][NH][130].
+int attn_prefix_chunks(int n_sessions, int n_heads, int n_kv_heads, int prefix_pages, int* chunk_pages);
+int launch_attn_prefix(const AttnLaunch& a, int prefix_pages, cudaStream_t s);
 int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s);   // after either split kernel
 int attn_split_ctas_simt(const AttnLaunch& a, int n_ctas);
 int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas);

@@ -59,6 +59,10 @@ struct nova_batch {
     int fused = 0;                   // 1: RoPE+append done inside the tensor-core attention launch
     int pdl = 0;                     // 1: layers after the first of a step launch as programmatic dependents
     int row_setup = 2;               // work-split weight of a row start, in pages (see AttnLaunch)
+    int cascade = 0;                 // 1: the shared leading pages of the batch's sessions are attended once for all
+    int casc_pages = 0;              // shared leading pages found by the last nova_batch_cow (0: none worth it)
+    float* casc_parts = nullptr;     // [chunks + 1][S * NH][130] partials of the cascade
+    size_t casc_floats = 0;
     // staging for the host-buffer step and the graph replay
     float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
     cudaGraphExec_t graph = nullptr;   // one per-layer decode step on the staging buffers
@@ -155,6 +159,31 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
     int rc, ctas;
     if (b->kernel == 1 && a.n_q > 1 && a.n_layers == 1 && !a.write_partial_only)
         return launch_attn_prefill(a, s);        // query-tiled prefill: every row complete in one CTA, no merge
+    if (b->kernel == 1 && b->cascade && b->casc_pages > 0 && a.n_layers == 1 && a.n_q <= 1 && !a.write_partial_only &&
+        a.page_lo == 0 && a.page_hi < 0) {
+        // Cascade over a shared prefix: (1) all sessions' queries against the shared pages, read once, as
+        // partials per page chunk; (2) the usual split over each session's own pages from the first private
+        // page on, also as partials; (3) log-sum-exp merge of the chunks' and the private part's rows.
+        const int P = b->casc_pages;
+        const int rows = b->n * a.n_heads;
+        const int chunks = attn_prefix_chunks(b->n, a.n_heads, a.n_kv_heads, P, nullptr);
+        if ((size_t)(chunks + 1) * rows * kPartW > b->casc_floats) return NOVA_ERR_TOO_LARGE;
+        AttnLaunch pa = a;
+        pa.out_part = b->casc_parts;
+        rc = launch_attn_prefix(pa, P, s);
+        if (rc != NOVA_OK) return rc;
+        AttnLaunch sa = a;
+        sa.pdl_spare = 0;             // the chain here is prefix -> split -> merge -> final merge: early start only
+        sa.page_lo = P;
+        sa.write_partial_only = 1;
+        sa.out_part = b->casc_parts + (size_t)chunks * rows * kPartW;
+        ctas = attn_split_ctas_mma(sa, 0);
+        rc = launch_attn_mma(sa, b->e->d.kv_dtype, ctas, s);
+        if (rc != NOVA_OK) return rc;
+        rc = launch_attn_combine(sa, ctas, s);
+        if (rc != NOVA_OK) return rc;
+        return launch_lse_combine(b->casc_parts, chunks + 1, rows, a.out, s);
+    }
     if (b->kernel == 1) {
         ctas = attn_split_ctas_mma(a, 0);
         rc = launch_attn_mma(a, b->e->d.kv_dtype, ctas, s);
@@ -189,6 +218,7 @@ int run_attn_fused(const nova_batch* b, int layer0, int n_layers, const float* q
     a.k_new = k; a.v_new = v;
     a.rope_cs = e->cs; a.rope_sn = e->sn; a.rope_rows = e->d.rope_positions;
     a.pdl = pdl ? 1 : 0;
+    a.pdl_spare = a.pdl;
     return run_attn(b, a, s);
 }
 
@@ -570,7 +600,14 @@ int nova_batch_create(nova_engine* e, const int32_t* sessions, int n, nova_batch
         b->sessions.push_back(sessions[i]);
         b->slices.push_back(r->slice);
     }
-    NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    {
+        const cudaError_t de = cudaSetDevice(e->d.device);
+        if (de != cudaSuccess) {
+            set_cuda_error(de, "cudaSetDevice");
+            delete b;
+            return NOVA_ERR_CUDA;
+        }
+    }
     const int64_t rows = (int64_t)e->d.n_layers * n * (e->d.n_kv_heads / e->kv_group);
     const int heads_per_row = e->kv_group * (e->d.n_heads / e->d.n_kv_heads);
     const int64_t rows_alloc = rows > kMaxRowsSmem ? rows : kMaxRowsSmem;   // a prefill launch has up to kMaxRowsSmem rows
@@ -603,6 +640,7 @@ void nova_batch_destroy(nova_batch* b) {
     cudaFree(b->d_n_past);
     cudaFreeHost(b->h_n_past);
     cudaFree(b->part);
+    cudaFree(b->casc_parts);
     cudaFree(b->dq);
     cudaFree(b->dk);
     cudaFree(b->dv);
@@ -675,6 +713,47 @@ int nova_batch_append_attn(nova_batch* b, int layer, float* q, float* k, const f
 }
 int nova_batch_get_kernel(const nova_batch* b) { return b ? b->kernel : NOVA_ERR_INVALID; }
 
+// Leading pages that every session of the batch maps to the same physical pages and that are full for all
+// of them (whole pages below the smallest n_past): what the cascade attends once.  Host tables only.
+static int shared_prefix_pages(const nova_batch* b) {
+    const nova_engine* e = b->e;
+    if (b->n < 4) return 0;
+    const SliceState* first = e->pool.p.find(b->slices[0]);
+    if (!first) return 0;
+    int64_t limit = first->n_past >> kKvShift;
+    for (int i = 1; i < b->n; ++i) {
+        const SliceState* st = e->pool.p.find(b->slices[(size_t)i]);
+        if (!st) return 0;
+        if ((st->n_past >> kKvShift) < limit) limit = st->n_past >> kKvShift;
+    }
+    if (limit > (int64_t)first->table.size()) limit = (int64_t)first->table.size();
+    for (int i = 1; i < b->n && limit > 0; ++i) {
+        const SliceState* st = e->pool.p.find(b->slices[(size_t)i]);
+        int64_t p = 0;
+        while (p < limit && st->table[(size_t)p] == first->table[(size_t)p]) ++p;
+        limit = p;
+    }
+    return limit >= 16 ? (int)limit : 0;        // below 256 shared tokens the extra launches cost more than they save
+}
+
+int nova_batch_set_cascade(nova_batch* b, int on) {
+    if (!b) return NOVA_ERR_INVALID;
+    if (on && b->kernel != 1) return NOVA_ERR_UNSUPPORTED;
+    nova_engine* e = b->e;
+    if (on && !b->casc_parts) {
+        NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+        // the chunk count never exceeds what a huge prefix would get (the per-CTA minimum of four pages only lowers it)
+        const int max_chunks = attn_prefix_chunks(b->n, e->d.n_heads, e->d.n_kv_heads, 1 << 24, nullptr);
+        b->casc_floats = (size_t)(max_chunks + 1) * b->n * e->d.n_heads * kPartW;
+        NOVA_CUDA_TRY(cudaMalloc((void**)&b->casc_parts, b->casc_floats * sizeof(float)));
+    }
+    b->cascade = on ? 1 : 0;
+    b->casc_pages = 0;
+    if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+    return NOVA_OK;
+}
+int nova_batch_shared_prefix_pages(const nova_batch* b) { return b ? b->casc_pages : 0; }
+
 int nova_batch_cow(nova_batch* b, nova_stream_t s) {
     if (!b) return NOVA_ERR_INVALID;
     nova_engine* e = b->e;
@@ -683,6 +762,11 @@ int nova_batch_cow(nova_batch* b, nova_stream_t s) {
     for (int i = 0; i < b->n && rc == NOVA_OK; ++i) {
         const SliceState* st = e->pool.p.find(b->slices[(size_t)i]);
         rc = collect_cow(e, b->slices[(size_t)i], st->n_past, 1, ev);
+    }
+    if (b->cascade) {                        // tables may just have changed: look for the shared prefix again
+        const int pages = shared_prefix_pages(b);
+        if (pages != b->casc_pages && b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+        b->casc_pages = pages;
     }
     if (!ev.empty()) {
         const int lrc = launch_cow_copy(e->pool_k, e->pool_v, e->d.n_layers, e->nb, e->page_bytes, ev.data(),

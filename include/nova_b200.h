@@ -309,6 +309,15 @@ int  nova_batch_attn(nova_batch* b, int layer, const float* q, float* out, nova_
  * Otherwise it is nova_batch_append followed by nova_batch_attn (q rotated in place).  Callers must
  * not rely on the contents of q afterwards (the reference does not read it after AttnOp either). */
 int  nova_batch_set_fused_append(nova_batch* b, int on);
+/* Cascade over a shared prefix (kernel 1): when every session of the batch maps its first P logical pages
+ * to the same physical pages (sessions forked from one refcounted prefix, code/session.h:173-180) and those
+ * pages are full for all of them, a decode step attends these pages ONCE for all sessions (the sessions'
+ * queries are the rows of tensor-core tiles), attends each session's own pages as usual, and merges the
+ * two by log-sum-exp.  P is re-read from the host tables by every nova_batch_cow (so after a COW or an
+ * attach the next step sees the new tables); nova_batch_shared_prefix_pages returns the P in use (0: the
+ * plain path).  Results agree with the plain path within the attention tolerance. */
+int  nova_batch_set_cascade(nova_batch* b, int on);
+int  nova_batch_shared_prefix_pages(const nova_batch* b);
 /* Programmatic dependent launch for nova_batch_run_steps / nova_batch_decode_step_host with the fused
  * append: the launches of every layer after the first may start while the previous layer's kernels are
  * still running (consecutive layers overlap on the GPU).  Such a launch streams and processes its pages,

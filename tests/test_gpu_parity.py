@@ -511,6 +511,59 @@ def test_cow_shared_prefix(nv, ob, kernel):
     eng.close()
 
 
+@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("model,n_fork,P", [("qwen25_7b", 12, 700), ("qwen25_14b", 5, 300), ("qwen25_1p5b", 10, 517)])
+def test_cascade_over_shared_prefix(nv, ob, model, n_fork, P, kernel):
+    """Sessions forked from one prefix (partly filled tail page), private suffixes of different lengths, then
+    decode steps with the cascade switched on: the shared full pages are attended once for all sessions, each
+    session's own pages (the un-shared tail page onwards) as usual, merged by log-sum-exp.  Per-layer launches,
+    plain and chained; outputs against the oracle's exact attention, pages bit-exact, the number of shared pages
+    found on the host, and the same steps again without the cascade."""
+    kvd, L = nv.KV_F16, 2
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, kvd, [P], L=L, seed=19, spare=n_fork + 1)
+    donor = ss[0]
+    forks = []
+    for _ in range(n_fork):
+        f = eng.session_create()
+        forks.append(f)
+        eng.attach_prefix(f, donor, P)
+    batch = eng.batch(forks)
+    try_set_kernel(nv, batch, kernel)
+    batch.set_cascade(1)
+    batch.set_pdl(1 if kernel == 2 else 0)
+    NH, NKV, S = eng.NH, eng.NKV, n_fork
+    out_d = nv.DevBuf(L * S * NH * 128 * 4)
+    st = nv.Stream()
+    pos = [P] * S
+    for step in range(20):
+        q = rng.standard_normal((L, S, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        before = {f: eng.pool.table(eng.session_slice(f)).copy() for f in forks}
+        dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+        if step == 4:
+            batch.set_cascade(0)                          # a few plain steps in between: same results
+        if step == 7:
+            batch.set_cascade(1)
+        batch.run_steps(1, dq.ptr, dk.ptr, dv.ptr, out_d.ptr, q.size, k.size, 1, st.h)     # COW guard + per-layer launches
+        st.sync()
+        assert batch.device_status() == 0
+        assert batch.shared_prefix_pages() == (0 if 4 <= step <= 6 else P // 16), step
+        for f in forks:      # oracle: same page copies, in the same order
+            after = eng.pool.table(eng.session_slice(f))
+            for lb in np.nonzero(after != before[f])[0]:
+                ob.cow_copy(sh, pk, pv, eng.nb, int(before[f][lb]), int(after[lb]))
+        tables = np.stack([eng.pool.table(eng.session_slice(f)) for f in forks])
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)
+        assert_attn_close(out_d.download(np.float32).reshape(want.shape), want, f"step {step}")
+        pos = [p + 1 for p in pos]
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    st.close()
+    batch.close()
+    eng.close()
+
+
 def test_sessions_follow_reference_manager(nv):
     """SessionManager semantics (code/session.h:84-142): lowest free slot, slice ids LIFO, errors
     as codes; zeroing of a new session's pages."""
