@@ -32,6 +32,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 #endif
 constexpr int kCombineWarps = NOVA_COMBINE_WARPS;
 
+// kFold = true is the cascade's final merge (extra parts folded in, see AttnLaunch::extra_parts); it is a separate
+// instantiation so that the plain merge keeps its register count (it has to share SMs with the split kernel).
+template <bool kFold>
 __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLaunch a, int n_ctas_split) {
     __shared__ int s_prefix[kMaxRowsSmem + 1];
     const int lane = (int)threadIdx.x & 31;
@@ -69,13 +72,21 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
         const int64_t v = u / heads_per_row;
         const int hr = (int)(u - v * heads_per_row);            // kv head in group * G + query head
         const int row = (int)(v % pv.rows_per_layer);
-        if (s_prefix[row + 1] == s_prefix[row]) continue;        // no pages: written by the split kernel
+        constexpr bool fold = kFold;                             // more parts to fold in: every row is ours to finish
+        const bool no_pages = s_prefix[row + 1] == s_prefix[row];
+        if (no_pages && !fold) continue;                         // no pages: written by the split kernel
         const int ll = (int)(v / pv.rows_per_layer);
         const int64_t row_begin = (int64_t)ll * pv.pages_per_layer + s_prefix[row];
         const int64_t row_end = (int64_t)ll * pv.pages_per_layer + s_prefix[row + 1];
-        const int c_first = plan_owner(pv, row_begin), c_last = plan_owner(pv, row_end - 1);
-        const int n = c_last - c_first + 1;
-        if (n == 1) continue;                                     // written by the split kernel
+        int c_first, n;
+        if constexpr (kFold) {
+            c_first = no_pages ? 0 : plan_owner(pv, row_begin);
+            n = no_pages ? 0 : plan_owner(pv, row_end - 1) - c_first + 1;
+        } else {
+            c_first = plan_owner(pv, row_begin);
+            n = plan_owner(pv, row_end - 1) - c_first + 1;
+            if (n == 1) continue;                                 // written by the split kernel
+        }
         const int s = row / n_groups, grp = row - s * n_groups;
         const int64_t head = ((int64_t)ll * S + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
         const float* base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
@@ -85,7 +96,18 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
         // chunk costs ONE memory round trip (a round trip is ~1 us here; a row usually fits one chunk).
         float M = -INFINITY, L = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c0 = 0; c0 < n; c0 += 32) {
+        if constexpr (kFold) if (n == 1) {            // the split kernel left this row's partial (m, l, acc) in out_part
+            const float* pr = a.out_part + head * kPartW;
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(pr));
+            const float2 y0 = __ldcg(reinterpret_cast<const float2*>(pr + 2 + 4 * lane));
+            const float2 y1 = __ldcg(reinterpret_cast<const float2*>(pr + 4 + 4 * lane));
+            if (ml.y > 0.f) {
+                M = ml.x;
+                L = ml.y;
+                acc = make_float4(y0.x, y0.y, y1.x, y1.y);
+            }
+        }
+        for (int c0 = 0; c0 < ((kFold && n == 1) ? 0 : n); c0 += 32) {
             const int cnt = n - c0 < 32 ? n - c0 : 32;
             const float* src = base + (size_t)c0 * stride_c;
             float2 ml = make_float2(-INFINITY, 0.f);
@@ -115,7 +137,49 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
             }
             M = Mn;
         }
-        if (a.write_partial_only) {
+        if constexpr (kFold) {
+            // the extra parts (a cascade's chunks over the shared pages), 32 (m, l) pairs and 8 accumulators at a time
+            const size_t estride = (size_t)S * a.n_heads * kPartW;
+            const float* eb = a.extra_parts + head * kPartW;
+            for (int e0 = 0; e0 < a.n_extra; e0 += 32) {
+                const int cnt = a.n_extra - e0 < 32 ? a.n_extra - e0 : 32;
+                float2 ml = make_float2(-INFINITY, 0.f);
+                if (lane < cnt) ml = __ldcg(reinterpret_cast<const float2*>(eb + (size_t)(e0 + lane) * estride));
+                const float mc = warp_max(ml.y > 0.f ? ml.x : -INFINITY);
+                const float Mn = fmaxf(M, mc);
+                if (Mn == -INFINITY) continue;
+                const float corr = __expf(M - Mn);
+                const float w = ml.y > 0.f ? __expf(ml.x - Mn) : 0.f;
+                L = fmaf(L, corr, warp_sum(ml.y * w));
+                acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+                for (int i0 = 0; i0 < cnt; i0 += 8) {
+                    float2 x0[8], x1[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        x0[i] = x1[i] = make_float2(0.f, 0.f);
+                        if (i0 + i < cnt) {
+                            const float* pr = eb + (size_t)(e0 + i0 + i) * estride + 2 + 4 * lane;
+                            x0[i] = __ldcg(reinterpret_cast<const float2*>(pr));
+                            x1[i] = __ldcg(reinterpret_cast<const float2*>(pr + 2));
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float wi = __shfl_sync(0xffffffffu, w, (i0 + i) & 31);
+                        if (i0 + i < cnt && wi != 0.f) {
+                            acc.x = fmaf(x0[i].x, wi, acc.x);
+                            acc.y = fmaf(x0[i].y, wi, acc.y);
+                            acc.z = fmaf(x1[i].x, wi, acc.z);
+                            acc.w = fmaf(x1[i].y, wi, acc.w);
+                        }
+                    }
+                }
+                M = Mn;
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =
+                make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        } else if (a.write_partial_only) {
             float* op = a.out_part + head * kPartW;
             if (lane == 0) { op[0] = M; op[1] = L; }
             op[2 + 4 * lane + 0] = acc.x;
@@ -304,7 +368,9 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
     const int64_t cap = (a.n_layers == 1 && a.pdl && a.pdl_spare) ? NOVA_COMBINE_MAX_CTAS : 148 * 8;
     if (ctas > cap) ctas = cap;
     // Always a programmatic dependent of the split kernel launched just before it.
-    const cudaError_t le = launch_kernel_pdl(attn_combine_kernel, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split);
+    const cudaError_t le = a.n_extra > 0
+        ? launch_kernel_pdl(attn_combine_kernel<true>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split)
+        : launch_kernel_pdl(attn_combine_kernel<false>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split);
     if (le != cudaSuccess) {
         set_cuda_error(le, "combine launch");
         return NOVA_ERR_CUDA;

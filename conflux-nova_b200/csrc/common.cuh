@@ -140,6 +140,11 @@ struct AttnLaunch {
     // token's k/v fetch at the row end next to it), in pages: every row is treated as that many pages
     // longer at its start, so a CTA whose range crosses a row boundary gets fewer real pages.
     int32_t row_setup_pages;
+    // Merge kernel only: n_extra more partial rows per (session, head), extra_parts [n_extra][S * NH][130]
+    // (one layer), are folded into every row after the split-K slots, and the normalised result goes to
+    // `out` although the split kernel ran with write_partial_only (the cascade's final merge).
+    const float* extra_parts;
+    int32_t n_extra;
     unsigned long long* timeline;   // optional [n_ctas][8] globaltimer stamps (profiling aid), or nullptr
 };
 

@@ -163,7 +163,7 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
         a.page_lo == 0 && a.page_hi < 0) {
         // Cascade over a shared prefix: (1) all sessions' queries against the shared pages, read once, as
         // partials per page chunk; (2) the usual split over each session's own pages from the first private
-        // page on, also as partials; (3) log-sum-exp merge of the chunks' and the private part's rows.
+        // page on, also as partials; (3) the merge kernel: split-K slots, then the chunks, then the output.
         const int P = b->casc_pages;
         const int rows = b->n * a.n_heads;
         const int chunks = attn_prefix_chunks(b->n, a.n_heads, a.n_kv_heads, P, nullptr);
@@ -177,12 +177,12 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
         sa.page_lo = P;
         sa.write_partial_only = 1;
         sa.out_part = b->casc_parts + (size_t)chunks * rows * kPartW;
+        sa.extra_parts = b->casc_parts;          // the merge kernel folds the chunks in and writes the output
+        sa.n_extra = chunks;
         ctas = attn_split_ctas_mma(sa, 0);
         rc = launch_attn_mma(sa, b->e->d.kv_dtype, ctas, s);
         if (rc != NOVA_OK) return rc;
-        rc = launch_attn_combine(sa, ctas, s);
-        if (rc != NOVA_OK) return rc;
-        return launch_lse_combine(b->casc_parts, chunks + 1, rows, a.out, s);
+        return launch_attn_combine(sa, ctas, s);
     }
     if (b->kernel == 1) {
         ctas = attn_split_ctas_mma(a, 0);
