@@ -33,6 +33,12 @@ class EngineDesc(C.Structure):
                 ("device", C.c_int32), ("zero_pages", C.c_int32)]
 
 
+class Telemetry(C.Structure):
+    _fields_ = [("blocks_total", C.c_int32), ("blocks_free", C.c_int32), ("blocks_shared", C.c_int32),
+                ("cow_count", C.c_int32), ("sessions_live", C.c_int32), ("slices_free", C.c_int32),
+                ("kv_bytes_cap", C.c_uint64), ("kv_bytes_used", C.c_uint64)]
+
+
 class KvShape(C.Structure):
     _fields_ = [("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
                 ("kv_block", C.c_int32), ("kv_dtype", C.c_int32), ("rope_neox", C.c_int32)]
@@ -120,6 +126,8 @@ SIGNATURES = {
     "nova_batch_attn_partial_layers": (i32, [vp, i32, i32, vp, i64, i64, vp, vp]),
     "nova_lse_combine": (i32, [vp, i32, i32, i32, vp, vp]),
     "nova_peer_slot_bytes": (sz, [i32]),
+    "nova_session_fork": (i32, [vp, i32]), "nova_session_attach_block": (i64, [vp, vp, u64, u64, i32]),
+    "nova_engine_telemetry": (i32, [vp, C.POINTER(Telemetry)]),
     "nova_batch_set_cascade": (i32, [vp, i32]), "nova_batch_shared_prefix_pages": (i32, [vp]),
     "nova_batch_step_partial_peers": (i32, [vp, vp, vp, vp, i64, i64, C.POINTER(vp), i32, i32, sz, i32, i64, i32, vp, vp, vp]),
     "nova_lse_merge_peers": (i32, [C.POINTER(vp), i32, i32, sz, i32, i32, i64, i32, vp, vp, vp]),

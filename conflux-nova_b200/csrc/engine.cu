@@ -432,6 +432,55 @@ int nova_session_attach_prefix(nova_engine* e, int dst, int src, int64_t n_token
     return NOVA_OK;
 }
 
+int nova_session_fork(nova_engine* e, int src) {
+    const SessionRec* s = session_of(e, src);
+    if (!s) return NOVA_ERR_INVALID;
+    const SliceState* st = e->pool.p.find(s->slice);
+    if (!st || st->n_past <= 0) return NOVA_ERR_INVALID;
+    const int64_t tokens = st->n_past;
+    const int dst = nova_session_create(e);
+    if (dst < 0) return dst;
+    const int rc = nova_session_attach_prefix(e, dst, src, tokens);
+    if (rc != NOVA_OK) {
+        nova_session_destroy(e, dst);
+        return rc;
+    }
+    return dst;
+}
+
+int64_t nova_session_attach_block(nova_engine* e, const nova_registry* r, uint64_t prefix, uint64_t suffix, int dst) {
+    if (!e || !r || !session_of(e, dst)) return NOVA_ERR_INVALID;
+    nova_kv_block blk;
+    if (!nova_registry_find(r, prefix, suffix, &blk)) return 0;
+    if (blk.session == dst || blk.pos1 <= 0) return 0;
+    const SessionRec* src = session_of(e, blk.session);
+    if (!src) return 0;                                  // the producing session has been closed
+    const SliceState* st = e->pool.p.find(src->slice);
+    if (!st || st->n_past < blk.pos1) return 0;          // ... or re-used for something shorter
+    const int rc = nova_session_attach_prefix(e, dst, blk.session, blk.pos1);
+    return rc == NOVA_OK ? blk.pos1 : (int64_t)rc;
+}
+
+int nova_engine_telemetry(const nova_engine* e, nova_telemetry* out) {
+    if (!e || !out) return NOVA_ERR_INVALID;
+    const PagePool& pp = e->pool.p;
+    std::memset(out, 0, sizeof(*out));
+    out->blocks_total = pp.nb_total();
+    out->blocks_free = pp.free_pages();
+    int shared = 0;
+    for (int r : pp.refs()) shared += r > 1;
+    out->blocks_shared = shared;
+    out->cow_count = pp.cow_count();
+    out->slices_free = pp.free_slices();
+    int live = 0;
+    for (const SessionRec& s : e->sess) live += s.used ? 1 : 0;
+    out->sessions_live = live;
+    const uint64_t per_page = (uint64_t)e->page_bytes * 2ull * (uint64_t)e->d.n_layers;
+    out->kv_bytes_cap = per_page * (uint64_t)pp.nb_total();
+    out->kv_bytes_used = per_page * (uint64_t)(pp.nb_total() - pp.free_pages());
+    return NOVA_OK;
+}
+
 int nova_session_cow_on(nova_engine* e, int session, int64_t pos0, int n, nova_stream_t stream) {
     SessionRec* r = session_of(e, session);
     if (!r || pos0 < 0) return NOVA_ERR_INVALID;

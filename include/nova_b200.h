@@ -201,6 +201,23 @@ int  nova_session_set_n_past(nova_engine* e, int session, int64_t n_past);
  * whole-table upload on dst's stream, stream sync. */
 int  nova_session_attach(nova_engine* e, int dst, int src, int k);
 int  nova_session_attach_prefix(nova_engine* e, int dst, int src, int64_t n_tokens);
+/* EngineHost::fork (client/src/engine_host.cpp:179-192): a new session that shares ALL of src's cached
+ * tokens (session_attach_prefix with n = src's n_past).  Returns the new session id, or an error code
+ * (NOVA_ERR_INVALID when src has no tokens, as the reference returns -1). */
+int  nova_session_fork(nova_engine* e, int src);
+/* Prefix reuse through the block registry (code/graph/kv_registry.h; the reference writes the registry
+ * but never consults it, code/INPUT_START.h:35): looks the block {prefix, suffix} up, and when the session
+ * that produced it is still alive shares that session's first pos1 tokens with dst
+ * (session_attach_prefix).  Returns the number of tokens shared (> 0), 0 when the block is unknown or
+ * its session is gone, or an error code. */
+int64_t nova_session_attach_block(nova_engine* e, const nova_registry* r, uint64_t prefix, uint64_t suffix, int dst);
+/* EngineHost::telemetry (client/src/engine_host.cpp:194-211), the pool part. */
+typedef struct nova_telemetry {
+    int32_t blocks_total, blocks_free, blocks_shared;   /* shared: refcnt > 1 */
+    int32_t cow_count, sessions_live, slices_free;
+    uint64_t kv_bytes_cap, kv_bytes_used;               /* both pools, all layers */
+} nova_telemetry;
+int  nova_engine_telemetry(const nova_engine* e, nova_telemetry* out);
 /* session_cow (session.h:166-171) -> Engine::cow_guard (model.cpp:171-191) for every
  * logical block in [pos0, pos0+n): KvPool::cow_slice, then ONE kernel copies the
  * page in all layers of both pools and rewrites the device table entry.  Returns

@@ -564,6 +564,61 @@ def test_cascade_over_shared_prefix(nv, ob, model, n_fork, P, kernel):
     eng.close()
 
 
+def test_fork_registry_attach_and_telemetry(nv, ob):
+    """EngineHost::fork (client/src/engine_host.cpp:179-192), the telemetry counters (:194-211) and prefix reuse
+    found through the block registry: a fork shares every page of its source (refcounts, no copy), a block id
+    looked up in the registry attaches its producer's first pos1 tokens, and both keep attention on the shared
+    pages identical to the source's."""
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, "qwen25_1p5b", nv.KV_F16, [40], L=2, seed=51, spare=3)
+    a = ss[0]
+    tel = nv.Telemetry()
+    nv.check(nv.lib.nova_engine_telemetry(eng.h, C.byref(tel)))
+    total, free0 = tel.blocks_total, tel.blocks_free
+    assert (tel.blocks_shared, tel.cow_count, tel.sessions_live) == (0, 0, 1) and tel.kv_bytes_cap > tel.kv_bytes_used > 0
+    f = nv.lib.nova_session_fork(eng.h, a)
+    assert f >= 0 and f != a and eng.n_past(f) == 40
+    ta, tf = eng.pool.table(eng.session_slice(a)), eng.pool.table(eng.session_slice(f))
+    assert np.array_equal(ta[:3], tf[:3]) and all(eng.pool.refcnt(int(p)) == 2 for p in ta[:3])
+    nv.check(nv.lib.nova_engine_telemetry(eng.h, C.byref(tel)))
+    assert (tel.blocks_shared, tel.sessions_live, tel.blocks_total) == (3, 2, total)
+    empty = eng.session_create()
+    assert nv.lib.nova_session_fork(eng.h, empty) == nv.ERR_INVALID          # nothing to share (the reference returns -1)
+    # registry-driven reuse: the block {7, 9} was produced by session a and covers its first 32 tokens
+    reg = nv.Registry()
+    reg.put(7, 9, session=a, turn=0, pos0=0, pos1=32)
+    assert nv.lib.nova_session_attach_block(eng.h, reg.h, 7, 10, empty) == 0  # unknown block
+    assert nv.lib.nova_session_attach_block(eng.h, reg.h, 7, 9, empty) == 32
+    assert eng.n_past(empty) == 32
+    te = eng.pool.table(eng.session_slice(empty))
+    assert np.array_equal(te[:2], ta[:2]) and eng.pool.refcnt(int(ta[0])) == 3 and eng.pool.refcnt(int(ta[2])) == 2
+    # one decode step of source, fork and the attached session: the first two see the same 40 keys
+    batch = eng.batch([a, f, empty])
+    try_set_kernel(nv, batch, 2)
+    L, NH, NKV = eng.L, eng.NH, eng.NKV
+    q = np.repeat(rng.standard_normal((L, 1, NH, 128)).astype(np.float32), 3, axis=1)
+    k = np.repeat(rng.standard_normal((L, 1, NKV, 128)).astype(np.float32), 3, axis=1)
+    v = np.repeat(rng.standard_normal((L, 1, NKV, 128)).astype(np.float32), 3, axis=1)
+    out = np.empty_like(q)
+    before = {s: eng.pool.table(eng.session_slice(s)).copy() for s in (a, f, empty)}
+    batch.decode_step_host(q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data, 1)
+    for s in (a, f, empty):
+        after = eng.pool.table(eng.session_slice(s))
+        for lb in np.nonzero(after != before[s])[0]:
+            ob.cow_copy(sh, pk, pv, eng.nb, int(before[s][lb]), int(after[lb]))
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in (a, f, empty)])
+    want = ob.decode_step(sh, pk, pv, tables, eng.nb, [40, 40, 32], q, k, v, cs, sn, exact=True)
+    assert_attn_close(out, want, "shared sessions")
+    assert np.array_equal(bits(out[:, 0]), bits(out[:, 1])), "source and fork attend the same keys"
+    nv.check(nv.lib.nova_engine_telemetry(eng.h, C.byref(tel)))
+    # the partly filled page shared by source and fork is copied once (by whoever appends first); the other then owns it
+    assert tel.cow_count == 1 and tel.blocks_free < free0
+    batch.close()
+    eng.session_destroy(a)
+    other = eng.session_create()
+    assert nv.lib.nova_session_attach_block(eng.h, reg.h, 7, 9, other) in (0, 32)   # producer gone (or its slot re-used)
+    eng.close()
+
+
 def test_sessions_follow_reference_manager(nv):
     """SessionManager semantics (code/session.h:84-142): lowest free slot, slice ids LIFO, errors
     as codes; zeroing of a new session's pages."""
