@@ -1047,6 +1047,25 @@ static int issue_layers(nova_batch* b, float* q, float* k, const float* v, float
     return NOVA_OK;
 }
 
+// The per-layer step on the staging buffers as an executable graph; captured again whenever something baked into
+// it has changed (kernel choice, fused append, number of shared pages of the cascade).
+static int ensure_step_graph(nova_batch* b, cudaStream_t st) {
+    if (b->graph && b->graph_kernel == b->kernel) return NOVA_OK;
+    if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+    cudaGraph_t g = nullptr;
+    NOVA_CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    int rc = issue_layers(b, b->dq, b->dk, b->dv, b->dout, st, nullptr, nullptr);
+    if (rc == NOVA_OK) rc = launch_advance(b->d_n_past, b->n, st);
+    const cudaError_t ce = cudaStreamEndCapture(st, &g);
+    if (rc != NOVA_OK) { if (g) cudaGraphDestroy(g); return rc; }
+    if (ce != cudaSuccess) { set_cuda_error(ce, "cudaStreamEndCapture"); return NOVA_ERR_CUDA; }
+    const cudaError_t ie = cudaGraphInstantiate(&b->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (ie != cudaSuccess) { set_cuda_error(ie, "cudaGraphInstantiate"); return NOVA_ERR_CUDA; }
+    b->graph_kernel = b->kernel;
+    return NOVA_OK;
+}
+
 int nova_batch_run_steps(nova_batch* b, int n_steps, float* q, float* k, const float* v, float* out,
                          size_t q_stride, size_t kv_stride, int mode, float* attn_ms, nova_stream_t s) {
     if (!b || n_steps < 0 || !q || !k || !v || !out || mode < 0 || mode > 2) return NOVA_ERR_INVALID;
@@ -1066,23 +1085,9 @@ int nova_batch_run_steps(nova_batch* b, int n_steps, float* q, float* k, const f
         }
     }
     if (mode == 2) {
-        int rc = ensure_staging(b);
+        const int rc = ensure_staging(b);
         if (rc != NOVA_OK) return rc;
         if (!st) return NOVA_ERR_INVALID;   // stream capture needs a real stream
-        if (!b->graph || b->graph_kernel != b->kernel) {
-            if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
-            cudaGraph_t g = nullptr;
-            NOVA_CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-            rc = issue_layers(b, b->dq, b->dk, b->dv, b->dout, st, nullptr, nullptr);
-            if (rc == NOVA_OK) rc = launch_advance(b->d_n_past, b->n, st);
-            const cudaError_t ce = cudaStreamEndCapture(st, &g);
-            if (rc != NOVA_OK) { if (g) cudaGraphDestroy(g); return rc; }
-            if (ce != cudaSuccess) { set_cuda_error(ce, "cudaStreamEndCapture"); return NOVA_ERR_CUDA; }
-            const cudaError_t ie = cudaGraphInstantiate(&b->graph, g, 0);
-            cudaGraphDestroy(g);
-            if (ie != cudaSuccess) { set_cuda_error(ie, "cudaGraphInstantiate"); return NOVA_ERR_CUDA; }
-            b->graph_kernel = b->kernel;
-        }
     }
     for (int i = 0; i < n_steps; ++i) {
         float* qi = q + (size_t)i * q_stride;
@@ -1119,6 +1124,8 @@ int nova_batch_run_steps(nova_batch* b, int n_steps, float* q, float* k, const f
             rc = nova_batch_advance(b, s);
             if (rc != NOVA_OK) return rc;
         } else {
+            rc = ensure_step_graph(b, st);          // after the COW guard: it may have changed what the graph bakes in
+            if (rc != NOVA_OK) return rc;
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq, qi, q_elems * 4, cudaMemcpyDeviceToDevice, st));
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk, ki, kv_elems * 4, cudaMemcpyDeviceToDevice, st));
             NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv, vi, kv_elems * 4, cudaMemcpyDeviceToDevice, st));

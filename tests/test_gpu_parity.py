@@ -511,13 +511,13 @@ def test_cow_shared_prefix(nv, ob, kernel):
     eng.close()
 
 
-@pytest.mark.parametrize("kernel", [1, 2])
+@pytest.mark.parametrize("kernel,mode", [(1, 1), (2, 1), (2, 2)])
 @pytest.mark.parametrize("model,n_fork,P", [("qwen25_7b", 12, 700), ("qwen25_14b", 5, 300), ("qwen25_1p5b", 10, 517)])
-def test_cascade_over_shared_prefix(nv, ob, model, n_fork, P, kernel):
+def test_cascade_over_shared_prefix(nv, ob, model, n_fork, P, kernel, mode):
     """Sessions forked from one prefix (partly filled tail page), private suffixes of different lengths, then
     decode steps with the cascade switched on: the shared full pages are attended once for all sessions, each
     session's own pages (the un-shared tail page onwards) as usual, merged by log-sum-exp.  Per-layer launches,
-    plain and chained; outputs against the oracle's exact attention, pages bit-exact, the number of shared pages
+    plain, chained and replayed from a graph; outputs against the oracle's exact attention, pages bit-exact, the number of shared pages
     found on the host, and the same steps again without the cascade."""
     kvd, L = nv.KV_F16, 2
     eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, kvd, [P], L=L, seed=19, spare=n_fork + 1)
@@ -545,7 +545,9 @@ def test_cascade_over_shared_prefix(nv, ob, model, n_fork, P, kernel):
             batch.set_cascade(0)                          # a few plain steps in between: same results
         if step == 7:
             batch.set_cascade(1)
-        batch.run_steps(1, dq.ptr, dk.ptr, dv.ptr, out_d.ptr, q.size, k.size, 1, st.h)     # COW guard + per-layer launches
+        # COW guard + per-layer launches, issued directly (mode 1) or replayed from a CUDA graph (mode 2: re-captured
+        # whenever the number of shared pages changes)
+        batch.run_steps(1, dq.ptr, dk.ptr, dv.ptr, out_d.ptr, q.size, k.size, mode, st.h)
         st.sync()
         assert batch.device_status() == 0
         assert batch.shared_prefix_pages() == (0 if 4 <= step <= 6 else P // 16), step
