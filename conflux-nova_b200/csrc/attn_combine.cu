@@ -34,9 +34,14 @@ constexpr int kCombineWarps = NOVA_COMBINE_WARPS;
 
 // kFold = true is the cascade's final merge (extra parts folded in, see AttnLaunch::extra_parts); it is a separate
 // instantiation so that the plain merge keeps its register count (it has to share SMs with the split kernel).
-template <bool kFold>
+// kCoop = true (launches with few (row, head) units, e.g. one long session): a unit belongs to a whole CTA and its
+// contributors are dealt out to the warps 32 at a time, so a row that 136 CTAs worked on costs two memory round
+// trips instead of five; the warps' results meet in shared memory.
+template <bool kFold, bool kCoop = false>
 __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLaunch a, int n_ctas_split) {
     __shared__ int s_prefix[kMaxRowsSmem + 1];
+    __shared__ float s_ml[kCoop ? 2 * kCombineWarps : 1];
+    __shared__ float4 s_acc[kCoop ? kCombineWarps * 32 : 1];
     const int lane = (int)threadIdx.x & 31;
     const int warp = (int)threadIdx.x >> 5;
     // profiling aid: stamps of the first 148 CTAs go after the split kernel's 148 x 8 block
@@ -68,7 +73,8 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
 
     const int64_t units = (int64_t)pv.rows_per_layer * a.n_layers * heads_per_row;
     const size_t stride_c = (size_t)heads_per_row * kSlotW;
-    for (int64_t u = (int64_t)blockIdx.x * kCombineWarps + warp; u < units; u += (int64_t)gridDim.x * kCombineWarps) {
+    for (int64_t u = kCoop ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kCombineWarps + warp; u < units;
+         u += kCoop ? (int64_t)gridDim.x : (int64_t)gridDim.x * kCombineWarps) {
         const int64_t v = u / heads_per_row;
         const int hr = (int)(u - v * heads_per_row);            // kv head in group * G + query head
         const int row = (int)(v % pv.rows_per_layer);
@@ -107,7 +113,7 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
                 acc = make_float4(y0.x, y0.y, y1.x, y1.y);
             }
         }
-        for (int c0 = 0; c0 < ((kFold && n == 1) ? 0 : n); c0 += 32) {
+        for (int c0 = kCoop ? 32 * warp : 0; c0 < ((kFold && n == 1) ? 0 : n); c0 += kCoop ? 32 * kCombineWarps : 32) {
             const int cnt = n - c0 < 32 ? n - c0 : 32;
             const float* src = base + (size_t)c0 * stride_c;
             float2 ml = make_float2(-INFINITY, 0.f);
@@ -136,6 +142,35 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
                 }
             }
             M = Mn;
+        }
+        if constexpr (kCoop) {       // the warps' shares of the row meet here; warp 0 finishes the row
+            if (lane == 0) { s_ml[2 * warp] = M; s_ml[2 * warp + 1] = L; }
+            s_acc[warp * 32 + lane] = acc;
+            __syncthreads();
+            if (warp == 0) {
+                float Mx = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kCombineWarps; ++w)
+                    if (s_ml[2 * w + 1] > 0.f) Mx = fmaxf(Mx, s_ml[2 * w]);
+                L = 0.f;
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < kCombineWarps; ++w) {
+                    const float lw = s_ml[2 * w + 1];
+                    if (lw > 0.f) {
+                        const float cw = __expf(s_ml[2 * w] - Mx);
+                        const float4 x = s_acc[w * 32 + lane];
+                        L = fmaf(lw, cw, L);
+                        acc.x = fmaf(x.x, cw, acc.x);
+                        acc.y = fmaf(x.y, cw, acc.y);
+                        acc.z = fmaf(x.z, cw, acc.z);
+                        acc.w = fmaf(x.w, cw, acc.w);
+                    }
+                }
+                M = Mx;
+            }
+            __syncthreads();
+            if (warp != 0) continue;
         }
         if constexpr (kFold) {
             // the extra parts (a cascade's chunks over the shared pages), 32 (m, l) pairs and 8 accumulators at a time
@@ -368,9 +403,12 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
     const int64_t cap = (a.n_layers == 1 && a.pdl && a.pdl_spare) ? NOVA_COMBINE_MAX_CTAS : 148 * 8;
     if (ctas > cap) ctas = cap;
     // Always a programmatic dependent of the split kernel launched just before it.
+    const bool coop = a.n_extra == 0 && units <= NOVA_COMBINE_MAX_CTAS;      // few units: one CTA per unit
+    if (coop) ctas = units;
     const cudaError_t le = a.n_extra > 0
         ? launch_kernel_pdl(attn_combine_kernel<true>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split)
-        : launch_kernel_pdl(attn_combine_kernel<false>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split);
+        : coop ? launch_kernel_pdl(attn_combine_kernel<false, true>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split)
+               : launch_kernel_pdl(attn_combine_kernel<false>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split);
     if (le != cudaSuccess) {
         set_cuda_error(le, "combine launch");
         return NOVA_ERR_CUDA;
