@@ -18,7 +18,7 @@ LIB_PATH = os.environ.get("NOVA_B200_LIB") or os.path.join(HERE, "libnova_b200.s
 
 OK = 0
 ERR_INVALID, ERR_POOL_FULL, ERR_NO_SLICE, ERR_NO_SESSION, ERR_CUDA = -1, -2, -3, -4, -5
-ERR_BAD_TABLE, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_TOO_LARGE = -6, -7, -8, -9
+ERR_BAD_TABLE, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_TOO_LARGE, ERR_BUSY = -6, -7, -8, -9, -10
 KV_F32, KV_F16 = 0, 1
 
 c_i32p = C.POINTER(C.c_int32)
@@ -81,6 +81,7 @@ SIGNATURES = {
     "nova_pool_attach_prefix": (i32, [vp, i32, i32, i64]), "nova_pool_cow_slice": (i32, [vp, i32, i64]),
     "nova_pool_need_copy": (i32, [vp, i32, C.POINTER(i32), C.POINTER(i32)]),
     "nova_pool_clear_need_copy": (i32, [vp, i32]),
+    "nova_pool_next_slice": (i32, [vp]), "nova_pool_foreign_mappings": (i32, [vp, i32]),
     "nova_pool_nb_total": (i32, [vp]), "nova_pool_nblocks": (i32, [vp]), "nova_pool_cow_count": (i32, [vp]),
     "nova_pool_free_blocks": (i32, [vp]), "nova_pool_free_slices": (i32, [vp]), "nova_pool_used": (i32, [vp]),
     "nova_pool_n_past": (i64, [vp, i32]), "nova_pool_set_n_past": (i32, [vp, i32, i64]),
@@ -245,6 +246,8 @@ class PoolView:
     def free_blocks(self): return lib.nova_pool_free_blocks(self.h)
     def free_slices(self): return lib.nova_pool_free_slices(self.h)
     def used(self): return lib.nova_pool_used(self.h)
+    def next_slice(self): return lib.nova_pool_next_slice(self.h)
+    def foreign_mappings(self, s): return lib.nova_pool_foreign_mappings(self.h, s)
     def n_past(self, s): return int(lib.nova_pool_n_past(self.h, s))
     def set_n_past(self, s, n): return lib.nova_pool_set_n_past(self.h, s, n)
 

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnova_b200.so")
-SOURCES = ["hal.cu", "rope_append.cu", "attn_simt.cu", "attn_mma.cu", "attn_combine.cu", "attn_prefill.cu", "attn_static.cu", "engine.cu", "host_capi.cpp"]
+SOURCES = ["hal.cu", "rope_append.cu", "attn_simt.cu", "attn_mma.cu", "attn_combine.cu", "attn_prefill.cu", "attn_static.cu", "synth.cu", "engine.cu", "host_capi.cpp"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 
@@ -17,7 +17,8 @@ NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a",
 def _deps() -> list[str]:
     out = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
     out += [os.path.join(HERE, "host", f) for f in os.listdir(os.path.join(HERE, "host"))]
-    out.append(os.path.join(os.path.dirname(HERE), "include", "nova_b200.h"))
+    inc = os.path.join(os.path.dirname(HERE), "include")
+    out += [os.path.join(inc, f) for f in ("nova_b200.h", "nova_b200_testing.h")]
     return out
 
 

@@ -44,8 +44,11 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
     __shared__ float4 s_acc[kCoop ? kCombineWarps * 32 : 1];
     const int lane = (int)threadIdx.x & 31;
     const int warp = (int)threadIdx.x >> 5;
-    // profiling aid: stamps of the first 148 CTAs go after the split kernel's 148 x 8 block
-    unsigned long long* tl = (a.timeline && blockIdx.x < 148) ? a.timeline + 148 * 8 + (size_t)blockIdx.x * 4 : nullptr;
+#ifdef NOVA_TIMELINE      // profiling build only: stamps of the first CTAs go after the split kernel's block of stamps
+    unsigned long long* tl = (a.timeline && blockIdx.x < kTimelineCtas) ? a.timeline + kTimelineCtas * 8 + (size_t)blockIdx.x * 4 : nullptr;
+#else
+    constexpr unsigned long long* tl = nullptr;
+#endif
     if (tl && threadIdx.x == 0) {
         unsigned smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -400,7 +403,7 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
 #define NOVA_COMBINE_MAX_CTAS 76
 #endif
     // (a launch that covers several layers is not part of such a chain and takes up to 8 CTAs per SM)
-    const int64_t cap = (a.n_layers == 1 && a.pdl && a.pdl_spare) ? NOVA_COMBINE_MAX_CTAS : 148 * 8;
+    const int64_t cap = (a.n_layers == 1 && a.pdl && a.pdl_spare) ? NOVA_COMBINE_MAX_CTAS : sm_count() * 8;
     if (ctas > cap) ctas = cap;
     // Always a programmatic dependent of the split kernel launched just before it.
     const bool coop = a.n_extra == 0 && units <= NOVA_COMBINE_MAX_CTAS;      // few units: one CTA per unit

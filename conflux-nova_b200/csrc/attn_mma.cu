@@ -94,7 +94,11 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
     pdl_launch_dependents();      // the combine kernel may be scheduled; it waits for this grid to finish
-    unsigned long long* tl = (a.timeline && blockIdx.x < 148) ? a.timeline + (size_t)blockIdx.x * 8 : nullptr;
+#ifdef NOVA_TIMELINE      // profiling build only: per-CTA %globaltimer stamps
+    unsigned long long* tl = (a.timeline && blockIdx.x < kTimelineCtas) ? a.timeline + (size_t)blockIdx.x * 8 : nullptr;
+#else
+    constexpr unsigned long long* tl = nullptr;
+#endif
     if (tl && threadIdx.x == 0) {
         unsigned smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -299,6 +303,14 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     // (the new token goes into the pool without waiting).  That wait also keeps completion transitive:
     // this grid cannot finish before the one it depends on.
     bool dep_met = a.pdl == 0;      // plain launch: the stream already ordered us after everything before
+    if (a.pdl == 2) {
+        // The caller cannot make the promise above for q and the new k / v (in an engine they come out of
+        // the kernels that consume the previous layer's output): wait here, before the first of those reads.
+        // The producer warp does not wait - pages of earlier steps, tables and positions do not depend on
+        // the previous layer - so the ring of page copies fills while the consumers sit here.
+        pdl_wait();
+        dep_met = true;
+    }
     int n_stashed = 0;
     float* stash = reinterpret_cast<float*>(smem_raw + (stage0 - smem_u32(smem_raw)) + kStages * Cfg::kStageBytes);
 
@@ -572,7 +584,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 }  // namespace
 
 bool attn_mma_built() { return true; }
-int attn_default_ctas_mma() { return 148; }
+int attn_default_ctas_mma() { return sm_count(); }
 size_t attn_tmap_bytes() { return sizeof(CUtensorMap); }
 
 // Tensor map over one fp16 pool [rows = L*NB*16][NKV][128]: dim0 = 128 dims, dim1 = slot rows
@@ -607,7 +619,7 @@ int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads,
 int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
     if (n_ctas > 0) return n_ctas;
     const int per_sm = a.kv_group >= 4 ? 1 : 4 / a.kv_group;
-    return (148 - ((a.pdl && a.pdl_spare) ? NOVA_ATTN_SPARE_SMS : 0)) * per_sm;
+    return (sm_count() - ((a.pdl && a.pdl_spare) ? NOVA_ATTN_SPARE_SMS : 0)) * per_sm;
 }
 
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {

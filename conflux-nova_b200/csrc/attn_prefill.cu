@@ -325,7 +325,7 @@ int launch_attn_prefill(const AttnLaunch& a, cudaStream_t s) {
 int attn_prefix_chunks(int n_sessions, int n_heads, int n_kv_heads, int prefix_pages, int* chunk_pages) {
     const int tq = attn_prefill_tile_tokens(n_heads, n_kv_heads);
     const int n_tiles = (n_sessions + tq - 1) / tq;
-    int chunks = (2 * 148 + n_tiles * n_kv_heads - 1) / (n_tiles * n_kv_heads);
+    int chunks = (2 * sm_count() + n_tiles * n_kv_heads - 1) / (n_tiles * n_kv_heads);
     if (chunks > prefix_pages / 4) chunks = prefix_pages / 4;          // at least four pages per CTA
     if (chunks < 1) chunks = 1;
     const int per = (prefix_pages + chunks - 1) / chunks;

@@ -308,7 +308,7 @@ int launch_simt_g(const AttnLaunch& a, int G, int n_ctas, cudaStream_t s) {
 int attn_default_ctas_simt(int n_kv_heads) {
     // 128-thread (or smaller) CTAs, 16 warps per SM resident: enough loads in flight without smem.
     const int kvg = n_kv_heads < 4 ? n_kv_heads : 4;
-    return 148 * (16 / kvg);
+    return sm_count() * (16 / kvg);
 }
 
 int attn_split_ctas_simt(const AttnLaunch& a, int n_ctas) {

@@ -26,19 +26,23 @@ static __device__ __align__(256) float g_attn_scratch[kStaticScratchFloats];
 
 // In host code `g_attn_scratch` is only a handle for the symbol, not an address a kernel can use; the
 // device address has to be asked for, once per device, with that device current.
-float* g_scratch_addr[64] = {};
+// Host threads that make their first call on a device at the same moment may both look the address up;
+// they store the same value, and the atomic keeps that well defined.
+std::atomic<float*> g_scratch_addr[64];
 
 int static_scratch_for_current_device(float** out) {
     int dev = -1;
     NOVA_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return NOVA_ERR_UNSUPPORTED;
-    if (!g_scratch_addr[dev]) {
+    float* addr = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!addr) {
         void* p = nullptr;
         NOVA_CUDA_TRY(cudaGetSymbolAddress(&p, g_attn_scratch));
         if (!p) return NOVA_ERR_CUDA;
-        g_scratch_addr[dev] = static_cast<float*>(p);
+        addr = static_cast<float*>(p);
+        g_scratch_addr[dev].store(addr, std::memory_order_release);
     }
-    *out = g_scratch_addr[dev];
+    *out = addr;
     return NOVA_OK;
 }
 

@@ -22,6 +22,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 // ---- error plumbing -------------------------------------------------------------------
 void set_cuda_error(cudaError_t e, const char* what);
 void count_launch(int n = 1);
+int sm_count();                  // multiprocessors of the current device
+constexpr int kMaxSms = 256;     // upper bound used to size per-SM scratch (partial slots)
+constexpr int kTimelineCtas = 148;   // CTAs per record of the profiling build's time stamps (NOVA_TIMELINE)
 
 // Launch with or without the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>
@@ -131,7 +134,8 @@ struct AttnLaunch {
     // stream are still running.  The caller promises that those kernels neither write what this launch
     // reads (pages of earlier steps, tables, n_past, its q/k/v) nor touch what it writes for its own
     // layers (their pages, k rows, outputs); the shared partial-slot scratch is written only after
-    // griddepcontrol.wait.
+    // griddepcontrol.wait.  2 = the same early start, but without the promise for q, k_new and v_new: the
+    // kernel reads those only after griddepcontrol.wait (tables, positions and page copies still start early).
     int32_t pdl;
     // With pdl: 1 = shape the launch for a chain of one-layer launches that should overlap (the split leaves
     // some SMs without a CTA, the merge uses few CTAs); 0 = only the early start and the late wait.

@@ -22,7 +22,7 @@ struct SessionRec {
     int slice = -1;
     cudaStream_t stream = nullptr;
 };
-constexpr int kMaxSplitCtas = 148 * 8;   // upper bound of CTAs of any attention launch (partial slots)
+constexpr int kMaxSplitCtas = kMaxSms * 8;   // upper bound of CTAs of any attention launch (partial slots)
 }  // namespace
 
 struct nova_engine {
@@ -57,7 +57,8 @@ struct nova_batch {
     float* part = nullptr;
     int kernel = 0;                  // 0 SIMT, 1 tensor-core
     int fused = 0;                   // 1: RoPE+append done inside the tensor-core attention launch
-    int pdl = 0;                     // 1: layers after the first of a step launch as programmatic dependents
+    int pdl = 0;                     // 1: layers after the first of a step launch as programmatic dependents; 2: the same, but
+                                     // they read their q / new k / new v only once the launches before them have finished
     int row_setup = 2;               // work-split weight of a row start, in pages (see AttnLaunch)
     int cascade = 0;                 // 1: the shared leading pages of the batch's sessions are attended once for all
     int casc_pages = 0;              // shared leading pages found by the last nova_batch_cow (0: none worth it)
@@ -151,7 +152,7 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.tmap_v = e->tmaps_ok ? e->tmap_v : nullptr;
     a.tmap_k1 = e->tmaps_ok ? e->tmap_k1 : nullptr;
     a.tmap_v1 = e->tmaps_ok ? e->tmap_v1 : nullptr;
-    a.timeline = b->timeline ? b->timeline + (size_t)(b->tl_seq++ % 4u) * (148 * 12) : nullptr;
+    a.timeline = b->timeline ? b->timeline + (size_t)(b->tl_seq++ % 4u) * (kTimelineCtas * 12) : nullptr;
 }
 
 // Split kernel, then the merge of the rows that more than one CTA worked on.
@@ -217,8 +218,8 @@ int run_attn_fused(const nova_batch* b, int layer0, int n_layers, const float* q
     a.pool_k_w = e->pool_k; a.pool_v_w = e->pool_v;
     a.k_new = k; a.v_new = v;
     a.rope_cs = e->cs; a.rope_sn = e->sn; a.rope_rows = e->d.rope_positions;
-    a.pdl = pdl ? 1 : 0;
-    a.pdl_spare = a.pdl;
+    a.pdl = pdl ? (b->pdl == 2 ? 2 : 1) : 0;
+    a.pdl_spare = a.pdl != 0;
     return run_attn(b, a, s);
 }
 
@@ -347,6 +348,12 @@ int nova_session_create(nova_engine* e) {
         if (!e->sess[i].used) { slot = (int)i; break; }
     if (slot < 0) return NOVA_ERR_NO_SESSION;
     NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    // KvPool::acquire resets the count of every identity page of the slice it hands out.  While another live
+    // session still maps one of them (a fork whose parent was destroyed, a copy-on-write page taken from this
+    // slice while it was free) the two would write the same pages unnoticed: refuse instead.
+    const int next = e->pool.p.next_slice();
+    if (next < 0) return NOVA_ERR_NO_SLICE;
+    if (e->pool.p.foreign_mappings(next) > 0) return NOVA_ERR_BUSY;
     const int slice = e->pool.p.acquire();
     if (slice < 0) return NOVA_ERR_NO_SLICE;
     cudaStream_t st = nullptr;
@@ -356,16 +363,26 @@ int nova_session_create(nova_engine* e) {
         e->pool.p.release(slice);
         return NOVA_ERR_CUDA;
     }
-    SessionRec& r = e->sess[(size_t)slot];
-    r.used = true;
-    r.slice = slice;
-    r.stream = st;
     int rc = upload_table(e, slice, st);
     if (rc == NOVA_OK && e->d.zero_pages)
         rc = launch_zero_pages(e->pool_k, e->pool_v, e->d.n_layers, e->nb, e->page_bytes,
                                e->tables + (size_t)slice * e->nblocks, e->nblocks, st);
-    if (rc == NOVA_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = NOVA_ERR_CUDA;
-    if (rc != NOVA_OK) return rc;
+    if (rc == NOVA_OK) {
+        ce = cudaStreamSynchronize(st);
+        if (ce != cudaSuccess) {
+            set_cuda_error(ce, "cudaStreamSynchronize");
+            rc = NOVA_ERR_CUDA;
+        }
+    }
+    if (rc != NOVA_OK) {               // leave nothing behind: the slice, the stream and the slot stay free
+        cudaStreamDestroy(st);
+        e->pool.p.release(slice);
+        return rc;
+    }
+    SessionRec& r = e->sess[(size_t)slot];
+    r.used = true;
+    r.slice = slice;
+    r.stream = st;
     return slot;
 }
 
@@ -614,25 +631,6 @@ int nova_lse_merge_peers(void* const* peer_base, int n_ranks, int my_rank, size_
                                   (unsigned long long)timeout_ms * 1000000ull, out, status, (cudaStream_t)s);
 }
 
-uint64_t nova_synth_key(uint64_t seed, uint64_t tensor, uint64_t session, uint64_t layer) {
-    auto mix = [](uint64_t x) {
-        x += 0x9E3779B97F4A7C15ull;
-        x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
-        x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
-        return x ^ (x >> 31);
-    };
-    uint64_t k = mix(seed);
-    k = mix(k ^ (tensor * 0xD6E8FEB86659FD93ull));
-    k = mix(k ^ (session * 0xA0761D6478BD642Full));
-    k = mix(k ^ (layer * 0xE7037ED1A0B428DBull));
-    return k;
-}
-
-int nova_synth_normal(float* dst_dev, size_t n, uint64_t key, uint64_t first_index, nova_stream_t s) {
-    if (!dst_dev && n) return NOVA_ERR_INVALID;
-    return launch_synth_normal(dst_dev, n, key, first_index, (cudaStream_t)s);
-}
-
 /* ------------------------------------------------------------------- batches */
 
 int nova_batch_create(nova_engine* e, const int32_t* sessions, int n, nova_batch** out) {
@@ -730,9 +728,14 @@ int nova_batch_set_kernel(nova_batch* b, int which) {
 }
 int nova_batch_set_timeline(nova_batch* b, void* dev_buf) {
     if (!b) return NOVA_ERR_INVALID;
+#ifdef NOVA_TIMELINE
     b->timeline = static_cast<unsigned long long*>(dev_buf);
     b->tl_seq = 0;
     return NOVA_OK;
+#else
+    (void)dev_buf;
+    return NOVA_ERR_UNSUPPORTED;      // the kernels carry the time stamps only in a -DNOVA_TIMELINE build
+#endif
 }
 int nova_batch_set_fused_append(nova_batch* b, int on) {
     if (!b) return NOVA_ERR_INVALID;
@@ -748,8 +751,8 @@ int nova_batch_set_row_setup_pages(nova_batch* b, int pages) {
     return NOVA_OK;
 }
 int nova_batch_set_pdl(nova_batch* b, int on) {
-    if (!b) return NOVA_ERR_INVALID;
-    b->pdl = on ? 1 : 0;
+    if (!b || on < 0 || on > 2) return NOVA_ERR_INVALID;
+    b->pdl = on;
     if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
     return NOVA_OK;
 }
@@ -808,6 +811,8 @@ int nova_batch_cow(nova_batch* b, nova_stream_t s) {
     nova_engine* e = b->e;
     std::vector<CowEvent> ev;
     int rc = NOVA_OK;
+    for (int i = 0; i < b->n; ++i)        // a session of the batch was destroyed behind its back
+        if (!e->pool.p.find(b->slices[(size_t)i])) return NOVA_ERR_INVALID;
     for (int i = 0; i < b->n && rc == NOVA_OK; ++i) {
         const SliceState* st = e->pool.p.find(b->slices[(size_t)i]);
         rc = collect_cow(e, b->slices[(size_t)i], st->n_past, 1, ev);
@@ -878,6 +883,8 @@ int nova_batch_prefill(nova_batch* b, int layer, int n_tokens, float* q, float* 
     if (!b || !q || !k || !v || !out || layer < 0 || layer >= b->e->d.n_layers || n_tokens < 1) return NOVA_ERR_INVALID;
     if (n_tokens > nova_batch_prefill_max_tokens(b)) return NOVA_ERR_TOO_LARGE;
     nova_engine* e = b->e;
+    for (int i = 0; i < b->n; ++i)
+        if (!e->pool.p.find(b->slices[(size_t)i])) return NOVA_ERR_INVALID;
     if (layer == 0) {        // un-share every page the new tokens will land in, once per prefill chunk
         std::vector<CowEvent> ev;
         int rc = NOVA_OK;

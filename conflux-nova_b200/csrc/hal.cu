@@ -17,6 +17,20 @@ void set_cuda_error(cudaError_t e, const char* what) {
     g_last_cuda = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
 }
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// Multiprocessors of the calling thread's current device (cudaDevAttrMultiProcessorCount), looked up once
+// per device.  Concurrent first calls may both query and store the same value.  148 (a B200) when the
+// query fails, so that grid sizing never sees zero.
+int sm_count() {
+    static std::atomic<int> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
+    return n;
+}
 }  // namespace novab
 
 using namespace novab;
@@ -35,6 +49,7 @@ const char* nova_status_string(int status) {
         case NOVA_ERR_TIMEOUT: return "device-side wait timed out";
         case NOVA_ERR_UNSUPPORTED: return "unsupported shape or dtype";
         case NOVA_ERR_TOO_LARGE: return "size beyond the fixed maximum";
+        case NOVA_ERR_BUSY: return "pages of the slice are still mapped by another session";
         default: return "unknown status";
     }
 }

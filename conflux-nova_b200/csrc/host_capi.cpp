@@ -114,6 +114,11 @@ int nova_pool_clear_need_copy(nova_pool* p, int slice) {
     s->copy_from = -1;   // the reference's cow_guard clears only the source (src/model.cpp:175-176)
     return NOVA_OK;
 }
+int nova_pool_next_slice(const nova_pool* p) { return p ? p->p.next_slice() : NOVA_ERR_INVALID; }
+int nova_pool_foreign_mappings(const nova_pool* p, int slice) {
+    if (!p || slice < 0 || (int64_t)(slice + 1) * p->p.nblocks() > p->p.nb_total()) return NOVA_ERR_INVALID;
+    return p->p.foreign_mappings(slice);
+}
 int nova_pool_nb_total(const nova_pool* p) { return p ? p->p.nb_total() : 0; }
 int nova_pool_nblocks(const nova_pool* p) { return p ? p->p.nblocks() : 0; }
 int nova_pool_cow_count(const nova_pool* p) { return p ? p->p.cow_count() : 0; }

@@ -137,29 +137,6 @@ __global__ void advance_kernel(int32_t* n_past, int n, int delta) {
     if (i < n) n_past[i] += delta;
 }
 
-__device__ __forceinline__ uint64_t mix64(uint64_t x) {
-    x += 0x9E3779B97F4A7C15ull;
-    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
-    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
-    return x ^ (x >> 31);
-}
-
-// Integer-only Irwin-Hall(12) "normal": the sum of twelve 16-bit hash fields, centred and
-// scaled by 2^-16.  Every step is exact in fp32, so host and device agree bit for bit.
-__global__ void synth_normal_kernel(float* __restrict__ dst, size_t n, uint64_t key, uint64_t first) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        uint32_t sum = 0;
-#pragma unroll
-        for (int r = 0; r < 3; ++r) {
-            const uint64_t h = mix64(key + 3ull * (first + i) + (uint64_t)r);
-            sum += (uint32_t)(h & 0xFFFF) + (uint32_t)((h >> 16) & 0xFFFF) + (uint32_t)((h >> 32) & 0xFFFF) +
-                   (uint32_t)(h >> 48);
-        }
-        dst[i] = (float)((int32_t)sum - 393210) * (1.0f / 65536.0f);
-    }
-}
-
 }  // namespace
 
 int launch_rope_table(float* cs, float* sn, int64_t n_pos, int theta, cudaStream_t s) {
@@ -218,15 +195,6 @@ int launch_zero_pages(void* pool_k, void* pool_v, int n_layers, int nb, size_t p
 int launch_advance(int32_t* n_past, int n, cudaStream_t s, int delta) {
     if (n <= 0) return NOVA_OK;
     advance_kernel<<<(n + 127) / 128, 128, 0, s>>>(n_past, n, delta);
-    NOVA_LAUNCH_CHECK();
-    return NOVA_OK;
-}
-
-int launch_synth_normal(float* dst, size_t n, uint64_t key, uint64_t first_index, cudaStream_t s) {
-    if (n == 0) return NOVA_OK;
-    size_t blocks = (n + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    synth_normal_kernel<<<(unsigned)blocks, 256, 0, s>>>(dst, n, key, first_index);
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }

@@ -182,6 +182,23 @@ public:
         return nullptr;
     }
 
+    // The slice id the next acquire() hands out (-1: none left).  Does not change anything.
+    int next_slice() const { return slice_stack_.empty() ? -1 : slice_stack_.back(); }
+
+    // Entries of OTHER live tables that map one of `slice`'s identity pages (slice*nblocks + b): pages a
+    // fork still reads after its parent was released, or pages handed out by cow() while the slice was free.
+    // acquire() sets the count of every identity page to 1 whatever it was (kv_pool.h:100-112), so acquiring a
+    // slice for which this is non-zero would let two sessions write the same pages; callers check first.
+    int foreign_mappings(int slice) const {
+        const int first = slice * nblocks_, last = first + nblocks_;
+        int n = 0;
+        for (const auto& s : live_) {
+            if (s.id == slice) continue;
+            for (int32_t pg : s.table) n += (pg >= first && pg < last) ? 1 : 0;
+        }
+        return n;
+    }
+
     int nblocks() const { return nblocks_; }
     int nb_total() const { return nb_total_; }
     int64_t ctx() const { return ctx_; }

@@ -33,6 +33,7 @@ extern "C" {
 #define NOVA_ERR_TIMEOUT     (-7)  /* a bounded device-side wait ran out        */
 #define NOVA_ERR_UNSUPPORTED (-8)  /* shape / dtype not built into the library  */
 #define NOVA_ERR_TOO_LARGE   (-9)  /* size beyond a documented fixed maximum    */
+#define NOVA_ERR_BUSY        (-10) /* pages of the slice are still mapped by another session */
 
 const char* nova_status_string(int status);
 /* Text of the last CUDA error seen by this thread's calls (empty if none). */
@@ -128,6 +129,14 @@ int  nova_pool_attach_prefix(nova_pool* p, int dst, int src, int64_t n_tokens); 
 int  nova_pool_cow_slice(nova_pool* p, int slice, int64_t pos);     /* :153-166; new page, -1 none, -2 full */
 int  nova_pool_need_copy(const nova_pool* p, int slice, int* from, int* blk);   /* KvSlice::need_copy_* :57-58 */
 int  nova_pool_clear_need_copy(nova_pool* p, int slice);            /* what cow_guard does, model.cpp:176 */
+/* No counterpart in the reference.  KvPool::acquire sets the count of every identity page of the slice it
+ * hands out to 1 whatever it was (kv_pool.h:100-112).  If a fork still maps pages of a released parent, or
+ * cow_slice handed such a page out while the slice was free, the new owner and the old reader would share
+ * them unnoticed.  nova_pool_next_slice names the slice the next acquire returns (-1: none);
+ * nova_pool_foreign_mappings counts the entries of other live tables that map its identity pages.
+ * nova_session_create refuses (NOVA_ERR_BUSY) while that count is not zero. */
+int  nova_pool_next_slice(const nova_pool* p);
+int  nova_pool_foreign_mappings(const nova_pool* p, int slice);
 int  nova_pool_nb_total(const nova_pool* p);
 int  nova_pool_nblocks(const nova_pool* p);
 int  nova_pool_cow_count(const nova_pool* p);
@@ -189,7 +198,13 @@ nova_pool*  nova_engine_pool(nova_engine* e);             /* the engine's KvPool
 
 /* SessionManager::create (code/session.h:84-123): lowest free slot, own stream,
  * KvPool::acquire, table upload, page zeroing, stream sync.  Returns the session
- * id (slot) or NOVA_ERR_NO_SESSION / NOVA_ERR_NO_SLICE (the reference exits). */
+ * id (slot) or NOVA_ERR_NO_SESSION / NOVA_ERR_NO_SLICE (the reference exits), or NOVA_ERR_BUSY while
+ * the slice that acquire would hand out has pages that another live session still maps (a fork of a
+ * destroyed parent, a copy-on-write page): destroy or re-home that session first.  On failure nothing is
+ * left allocated.
+ * Threading: create and destroy take the engine's lock; every other call that changes the pool (attach,
+ * cow, fork, permute, the batch calls) must come from one thread at a time, as in the reference
+ * (KvPool is an unsynchronised singleton, kv_pool.h:199). */
 int  nova_session_create(nova_engine* e);
 int  nova_session_destroy(nova_engine* e, int session);             /* session.h:131-142 */
 int  nova_session_live_count(nova_engine* e);                       /* :144 */
@@ -280,12 +295,6 @@ int nova_launch_attn_decode_paged_static(const nova_kv_shape* sh, const float* q
                                          const int32_t* table, int layer, int nb, int n_keys,
                                          float* o, nova_stream_t s);
 
-/* Synthetic inputs for tests and benchmarks (no counterpart in the reference, which feeds
- * real activations): dst[i] = value(key, first_index + i), an integer-only Irwin-Hall(12)
- * approximation of N(0,1) built from 64-bit hashes, bit-identical on host and device. */
-uint64_t nova_synth_key(uint64_t seed, uint64_t tensor, uint64_t session, uint64_t layer);
-int nova_synth_normal(float* dst_dev, size_t n, uint64_t key, uint64_t first_index, nova_stream_t s);
-
 /* ------------------------------------------- batched decode over sessions */
 /* Engine::decode_batch's hot-path calls (model.cpp:281-289) for any number of
  * sessions in one launch per op.  A batch owns device copies of the sessions'
@@ -299,15 +308,6 @@ int  nova_batch_sync_positions(nova_batch* b, nova_stream_t s);
 /* Select the attention kernel: 0 = SIMT, 1 = tensor-core (mma + bulk-copy pipeline, fp16 KV). */
 int  nova_batch_set_kernel(nova_batch* b, int which);
 int  nova_batch_get_kernel(const nova_batch* b);
-/* Profiling aid (tensor-core kernel): dev_buf = 4 records of 148*12 uint64 in device memory (launch i
- * of the batch writes record i % 4), or NULL to switch off.
- * Every CTA of the next attention launches leaves %globaltimer stamps there: [0] start, [1] work split
- * known, [2] first page requested, [3] last page requested, [4] first page landed, [5] last page
- * consumed, [6] results/partials written, [7] the SM it ran on (%smid, not a time); after those 148*8
- * values the first 148 CTAs of the combine kernel leave four values each (start, dependency met, %smid,
- * end). */
-int  nova_batch_set_timeline(nova_batch* b, void* dev_buf);
-
 /* For each session s of the batch: session_cow(s, n_past, 1).  One kernel copies
  * all pages that had to be un-shared.  Returns the number of COW copies. */
 int  nova_batch_cow(nova_batch* b, nova_stream_t s);
@@ -340,7 +340,10 @@ int  nova_batch_shared_prefix_pages(const nova_batch* b);
  * still running (consecutive layers overlap on the GPU).  Such a launch streams and processes its pages,
  * appends its layer's new token, and waits (griddepcontrol.wait) only before it writes outputs or
  * partial slots.  Inside these two calls the layer before never produces the next layer's q, k or v and
- * never touches its pages; that is the promise the attribute needs. */
+ * never touches its pages; that is the promise the attribute needs.
+ * on = 2: for callers that cannot promise that for q, k and v (an engine computes a layer's q/k/v from the
+ * previous layer's attention output): the launches still start early and bring in tables, positions and the
+ * first pages, but read q and the new k/v only after the launches before them have finished. */
 int  nova_batch_set_pdl(nova_batch* b, int on);
 /* Tuning knob of the attention work split: how many pages' worth of time starting a session inside a
  * CTA costs (default 2).  A CTA whose page range crosses a session boundary gets that many fewer pages. */

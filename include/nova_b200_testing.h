@@ -1,0 +1,32 @@
+/* nova_b200_testing.h — aids for tests, benchmarks and profiling builds of libnova_b200.so.
+ *
+ * Nothing here is on the decode path and nothing here has a counterpart in the reference, which feeds real
+ * activations and profiles with its own CUDA-event scopes (code/scope_cuda.h).  The functions are exported
+ * by the same shared library as include/nova_b200.h.
+ */
+#ifndef NOVA_B200_TESTING_H_
+#define NOVA_B200_TESTING_H_
+
+#include "nova_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Synthetic inputs: dst[i] = value(key, first_index + i), an integer-only Irwin-Hall(12) approximation of
+ * N(0,1) built from 64-bit hashes, bit-identical on host and device (every step is exact in fp32). */
+uint64_t nova_synth_key(uint64_t seed, uint64_t tensor, uint64_t session, uint64_t layer);
+int nova_synth_normal(float* dst_dev, size_t n, uint64_t key, uint64_t first_index, nova_stream_t s);
+
+/* In-kernel time stamps of the tensor-core attention launches.  Only a library built with -DNOVA_TIMELINE
+ * carries them; any other build returns NOVA_ERR_UNSUPPORTED.  dev_buf = 4 records of 148*12 uint64 in device
+ * memory (launch i of the batch writes record i % 4), or NULL to switch off.  Every CTA leaves %globaltimer
+ * stamps: [0] start, [1] work split known, [2] first page requested, [3] last page requested, [4] first page
+ * landed, [5] last page consumed, [6] results written, [7] the SM it ran on (%smid); after those 148*8 values
+ * the first 148 CTAs of the merge kernel leave four values each (start, dependency met, %smid, end). */
+int nova_batch_set_timeline(nova_batch* b, void* dev_buf);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NOVA_B200_TESTING_H_ */

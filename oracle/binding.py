@@ -62,6 +62,7 @@ def oracle() -> C.CDLL:
         o.oracle_decode_step.restype = None
         o.oracle_decode_step.argtypes = [P, vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32]
         o.oracle_num_threads.restype, o.oracle_num_threads.argtypes = i32, []
+        o.oracle_set_num_threads.restype, o.oracle_set_num_threads.argtypes = None, [i32]
         _oracle = o
     return _oracle
 
@@ -291,3 +292,14 @@ def decode_step(sh, pool_k, pool_v, tables, nb, pos, q, k, v, cs, sn, fma_mode=1
 
 def num_threads() -> int:
     return int(oracle().oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Let the checker's parallel loops use every core this process may run on (sched_getaffinity), whatever
+    OMP_NUM_THREADS says: launchers such as torchrun export OMP_NUM_THREADS=1 to their children.  Returns the count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    oracle().oracle_set_num_threads(n)
+    return num_threads()

@@ -23,7 +23,18 @@ REF_OUT = os.path.join(HERE, "_ref")
 
 ORACLE_SO = os.path.join(BUILD, "libpaged_decode_oracle.so")
 REF_HOST_SO = os.path.join(REF_OUT, "libnova_ref_host.so")
-REF_GPU_MODELS = {"qwen25_7b": "NOVA_MODEL_QWEN25_7B", "qwen25_1p5b": "NOVA_MODEL_QWEN25_1P5B"}
+# name -> the reference's compile-time switches: the model (include/nova/model/select.h) and, for the
+# page-size variants, NOVA_KV_BLOCK (code/graph/kv_pool_cfg.h:12-26)
+REF_GPU_MODELS = {
+    "qwen25_7b": ["NOVA_MODEL_QWEN25_7B"],
+    "qwen25_1p5b": ["NOVA_MODEL_QWEN25_1P5B"],
+    "r1_llama8b": ["NOVA_MODEL_R1_LLAMA8B"],              # RopeLayout::Norm, theta 500000, 32 q / 8 kv heads
+    "r1_qwen1p5b_abl": ["NOVA_MODEL_R1_QWEN1P5B_ABL"],    # theta 10000
+    "qwen25_7b_kb8": ["NOVA_MODEL_QWEN25_7B", "NOVA_KV_BLOCK=8"],
+    "qwen25_7b_kb32": ["NOVA_MODEL_QWEN25_7B", "NOVA_KV_BLOCK=32"],
+    "qwen25_7b_kb64": ["NOVA_MODEL_QWEN25_7B", "NOVA_KV_BLOCK=64"],
+    "qwen25_1p5b_kb32": ["NOVA_MODEL_QWEN25_1P5B", "NOVA_KV_BLOCK=32"],
+}
 
 
 def ref_gpu_so(model: str) -> str:
@@ -75,7 +86,8 @@ def build_ref_gpu(force: bool = False) -> dict[str, str]:
     ref = reference_dir()
     out: dict[str, str] = {}
     shim = os.path.join(HERE, "ref_gpu_shim.cu")
-    for model, macro in REF_GPU_MODELS.items():
+    procs = []
+    for model, macros in REF_GPU_MODELS.items():
         so = ref_gpu_so(model)
         if ref is None or shutil.which("nvcc") is None:
             if os.path.exists(so):
@@ -83,11 +95,17 @@ def build_ref_gpu(force: bool = False) -> dict[str, str]:
             continue
         if force or not _newer(so, [shim]):
             os.makedirs(REF_OUT, exist_ok=True)
-            _run(["nvcc", "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-                  f"-D{macro}", f"-I{ref}/include", f"-I{ref}/code", "-Xcompiler", "-fPIC", "-shared", "-w",
-                  shim, f"{ref}/src/kernel/rope.cu", f"{ref}/src/kernel/elem.cu", f"{ref}/src/kernel/attn.cu",
-                  "-o", so])
+            cmd = ["nvcc", "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+                   *[f"-D{m}" for m in macros], f"-I{ref}/include", f"-I{ref}/code", "-Xcompiler", "-fPIC", "-shared", "-w",
+                   shim, f"{ref}/src/kernel/rope.cu", f"{ref}/src/kernel/elem.cu", f"{ref}/src/kernel/attn.cu",
+                   "-o", so]
+            procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         out[model] = so
+    for cmd, p in procs:                  # the variants compile side by side
+        text, _ = p.communicate()
+        if p.returncode != 0:
+            sys.stderr.write(" ".join(cmd) + "\n" + (text or ""))
+            raise RuntimeError("build failed: nvcc (reference kernels)")
     return out
 
 

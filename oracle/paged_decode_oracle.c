@@ -269,36 +269,42 @@ void oracle_attn_decode_paged(const oracle_shape* sh, const float* q, const void
 
 /* ---- decode attention, exact: double-precision softmax as in the reference's own numeric
  * check (tests/sycl_bench.cpp:915-938) ---- */
-void oracle_attn_decode_paged_f64(const oracle_shape* sh, const float* q, const void* pool_k, const void* pool_v,
-                                  const int32_t* table, int layer, int nb, int n_keys, float* o) {
-    const int HD = sh->head_dim, NH = sh->n_heads, NKV = sh->n_kv_heads, KB = sh->kv_block, G = NH / NKV;
+static void attn_head_f64(const oracle_shape* sh, const float* qh, const void* pool_k, const void* pool_v,
+                          const int32_t* table, int layer, int nb, int n_keys, int kvh, float* out) {
+    const int HD = sh->head_dim, NKV = sh->n_kv_heads, KB = sh->kv_block;
     const float scale = HD == 64 ? 0.125f : 0.08838834764831845f;
     int shift = 0;
     while ((1 << shift) < KB) ++shift;
     double* sc = (double*)malloc(sizeof(double) * (size_t)(n_keys > 0 ? n_keys : 1));
     double* acc = (double*)malloc(sizeof(double) * (size_t)HD);
-    for (int h = 0; h < NH; ++h) {
-        const int kvh = h / G;
-        double mx = -1e300;
-        for (int p = 0; p < n_keys; ++p) {
-            const int64_t row = (((int64_t)layer * nb + table[p >> shift]) * KB + (p & (KB - 1))) * (int64_t)NKV * HD + (int64_t)kvh * HD;
-            double a = 0.0;
-            for (int d = 0; d < HD; ++d) a += (double)q[(size_t)h * HD + d] * (double)kv_load(pool_k, sh->kv_dtype, row + d);
-            sc[p] = a * (double)scale;
-            if (sc[p] > mx) mx = sc[p];
-        }
-        double sum = 0.0;
-        for (int d = 0; d < HD; ++d) acc[d] = 0.0;
-        for (int p = 0; p < n_keys; ++p) {
-            const int64_t row = (((int64_t)layer * nb + table[p >> shift]) * KB + (p & (KB - 1))) * (int64_t)NKV * HD + (int64_t)kvh * HD;
-            const double w = exp(sc[p] - mx);
-            sum += w;
-            for (int d = 0; d < HD; ++d) acc[d] += w * (double)kv_load(pool_v, sh->kv_dtype, row + d);
-        }
-        for (int d = 0; d < HD; ++d) o[(size_t)h * HD + d] = n_keys > 0 ? (float)(acc[d] / sum) : 0.f;
+    double mx = -1e300;
+    for (int p = 0; p < n_keys; ++p) {
+        const int64_t row = (((int64_t)layer * nb + table[p >> shift]) * KB + (p & (KB - 1))) * (int64_t)NKV * HD + (int64_t)kvh * HD;
+        double a = 0.0;
+        for (int d = 0; d < HD; ++d) a += (double)qh[d] * (double)kv_load(pool_k, sh->kv_dtype, row + d);
+        sc[p] = a * (double)scale;
+        if (sc[p] > mx) mx = sc[p];
     }
+    double sum = 0.0;
+    for (int d = 0; d < HD; ++d) acc[d] = 0.0;
+    for (int p = 0; p < n_keys; ++p) {
+        const int64_t row = (((int64_t)layer * nb + table[p >> shift]) * KB + (p & (KB - 1))) * (int64_t)NKV * HD + (int64_t)kvh * HD;
+        const double w = exp(sc[p] - mx);
+        sum += w;
+        for (int d = 0; d < HD; ++d) acc[d] += w * (double)kv_load(pool_v, sh->kv_dtype, row + d);
+    }
+    for (int d = 0; d < HD; ++d) out[d] = n_keys > 0 ? (float)(acc[d] / sum) : 0.f;
     free(sc);
     free(acc);
+}
+
+void oracle_attn_decode_paged_f64(const oracle_shape* sh, const float* q, const void* pool_k, const void* pool_v,
+                                  const int32_t* table, int layer, int nb, int n_keys, float* o) {
+    const int HD = sh->head_dim, NH = sh->n_heads, G = NH / sh->n_kv_heads;
+    /* heads are independent: one thread each (long contexts would otherwise take minutes) */
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int h = 0; h < NH; ++h)
+        attn_head_f64(sh, q + (size_t)h * HD, pool_k, pool_v, table, layer, nb, n_keys, h / G, o + (size_t)h * HD);
 }
 
 /* ---- prefill attention, order-faithful: flash_paged_kernel<false>, src/kernel/attn.cu:292-357 ----
@@ -310,6 +316,8 @@ void oracle_attn_prefill_paged(const oracle_shape* sh, const float* q, const voi
     const float scale = HD == 64 ? 0.125f : 0.08838834764831845f;
     int shift = 0;
     while ((1 << shift) < KB) ++shift;
+    /* every (query, head) pair is one warp of the kernel and independent of the others */
+#pragma omp parallel for collapse(2) schedule(dynamic, 4)
     for (int qi = 0; qi < n_q; ++qi)
         for (int h = 0; h < NH; ++h) {
             const int kvh = h / G;
@@ -412,20 +420,43 @@ void oracle_decode_step(const oracle_shape* sh, void* pool_k, void* pool_v, cons
                         int layer0, int layer1) {
     const int NH = sh->n_heads, NKV = sh->n_kv_heads, HD = sh->head_dim;
     const int64_t S = n_sessions;
+    const int G = NH / NKV;
+    /* phase 1: rope + store of every (layer, session); phase 2: attention per (layer, session, head) - the heads
+     * of the reference's kernel are independent CTAs, so the order inside each head is untouched */
 #pragma omp parallel for collapse(2) schedule(dynamic, 1)
     for (int l = layer0; l < layer1; ++l)
         for (int s = 0; s < n_sessions; ++s) {
             float* ql = q + ((int64_t)l * S + s) * NH * HD;
             float* kl = k + ((int64_t)l * S + s) * NKV * HD;
             const float* vl = v + ((int64_t)l * S + s) * NKV * HD;
-            float* ol = out + ((int64_t)l * S + s) * NH * HD;
             const int32_t* tb = tables + (int64_t)s * table_stride;
             oracle_rope_append_paged(sh, pool_k, pool_v, tb, l, nb, 1, pos[s], ql, kl, vl, cs, sn, fma_mode);
-            if (exact)
-                oracle_attn_decode_paged_f64(sh, ql, pool_k, pool_v, tb, l, nb, (int)pos[s] + 1, ol);
-            else
-                oracle_attn_decode_paged(sh, ql, pool_k, pool_v, tb, l, nb, (int)pos[s] + 1, ol);
         }
+#pragma omp parallel for collapse(3) schedule(dynamic, 1)
+    for (int l = layer0; l < layer1; ++l)
+        for (int s = 0; s < n_sessions; ++s)
+            for (int h = 0; h < NH; ++h) {
+                const float* qh = q + (((int64_t)l * S + s) * NH + h) * HD;
+                float* oh = out + (((int64_t)l * S + s) * NH + h) * HD;
+                const int32_t* tb = tables + (int64_t)s * table_stride;
+                if (exact) {
+                    attn_head_f64(sh, qh, pool_k, pool_v, tb, l, nb, (int)pos[s] + 1, h / G, oh);
+                } else {
+                    float part[32 * (128 + 2)];
+                    attn_head_ref_order(sh, qh, pool_k, pool_v, tb, l, nb, (int)pos[s] + 1, h / G, oh, part);
+                }
+            }
+}
+
+/* Thread count of the parallel loops above; oracle_set_num_threads overrides what the environment
+ * (OMP_NUM_THREADS) asked for. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
 }
 
 int oracle_num_threads(void) {

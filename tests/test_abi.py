@@ -1,5 +1,5 @@
 """The drop-in boundary: libnova_b200.so loads without a GPU and exports every function that
-include/nova_b200.h declares; the Python binding declares the same set.  No compute is called."""
+include/nova_b200.h and include/nova_b200_testing.h declare; the Python binding declares the same set.  No compute is called."""
 import ctypes
 import os
 import re
@@ -8,7 +8,7 @@ from conftest import ROOT
 
 
 def declared_functions():
-    text = open(os.path.join(ROOT, "include", "nova_b200.h")).read()
+    text = "".join(open(os.path.join(ROOT, "include", f)).read() for f in ("nova_b200.h", "nova_b200_testing.h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     text = re.sub(r"typedef struct \{.*?\} \w+;", "", text, flags=re.S)
     names = re.findall(r"\b((?:nova|dev)_\w+)\s*\(", text)

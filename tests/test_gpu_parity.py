@@ -10,7 +10,11 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 REL_TOL, ABS_TOL = 2e-3, 1e-2
-SHAPES = {"qwen25_1p5b": (12, 2), "qwen25_7b": (28, 4), "qwen25_14b": (40, 8)}
+SHAPES = {"qwen25_1p5b": (12, 2), "qwen25_7b": (28, 4), "qwen25_14b": (40, 8),
+          "r1_llama8b": (32, 8), "r1_qwen1p5b_abl": (12, 2)}
+# RoPE of the reference's other models (include/nova/model/matrix.h:52-53, include/nova/arch/traits.h:25):
+# (theta, NeoX pairing)
+ROPE = {"r1_llama8b": (500000, 0), "r1_qwen1p5b_abl": (10000, 1)}
 
 
 def rel_l2(a, b):
@@ -170,13 +174,122 @@ def test_append_vs_reference_kernels(nv, ob, model):
     assert np.array_equal(bits(v16.ravel()), bits(ref[1].astype(np.float16)))
 
 
+@pytest.mark.parametrize("model", ["r1_llama8b", "r1_qwen1p5b_abl"])
+def test_other_rope_layouts_vs_reference_kernels(nv, ob, model):
+    """The reference's other RoPE variants - adjacent pairs (2i, 2i+1) with theta 500000 (R1-Llama-8B,
+    include/nova/arch/traits.h:25, model/matrix.h:53) and NeoX pairs with theta 10000 (the abliterated 1.5B,
+    matrix.h:52) - against the reference's own kernels compiled for those models: cos/sin tables, rotated q/k and
+    appended fp32 pages bit-identical; fp16 pages == round-to-nearest-even of the reference's; decode attention
+    (batched calls, every kernel that the layout allows) within tolerance of the reference's kernel."""
+    g = ob.ref_gpu(model)
+    if g is None:
+        pytest.skip("reference CUDA library not built")
+    NH, NKV = SHAPES[model]
+    theta, neox = ROPE[model]
+    shape6 = (C.c_int32 * 6)()
+    g.ref_gpu_shape(shape6)
+    assert (shape6[1], shape6[2], shape6[5]) == (NH, NKV, theta)
+    L, ctx, n, pos0, layer = 2, 4096, 200, 3000, 1
+    rng = np.random.default_rng(11)
+    q = rng.standard_normal((n, NH, 128)).astype(np.float32)
+    k = rng.standard_normal((n, NKV, 128)).astype(np.float32)
+    v = rng.standard_normal((n, NKV, 128)).astype(np.float32)
+    rcs, rsn = nv.DevBuf(4096 * 64 * 4), nv.DevBuf(4096 * 64 * 4)
+    g.ref_gpu_rope_table(rcs.ptr, rsn.ptr, None)
+    nv.check(nv.lib.dev_sync())
+    ref_cs, ref_sn = rcs.download(np.float32).reshape(4096, 64), rsn.download(np.float32).reshape(4096, 64)
+    ocs, osn = ob.rope_table(4096, 128, theta)          # the host libm is not the GPU's: close, not identical
+    assert np.abs(ocs - ref_cs).max() < 2e-3 and np.abs(osn - ref_sn).max() < 2e-3
+    assert ref_cs[0, 0] == 1.0 and ref_sn[0, 0] == 0.0
+    res = {}
+    for kvd in (nv.KV_F32, nv.KV_F16):
+        eng = nv.Engine(L, NH, NKV, ctx=ctx, n_slices=1, kv_dtype=kvd, rope_positions=4096, rope_theta=theta,
+                        rope_neox=neox)
+        cs, sn = eng.rope_tables()
+        assert np.array_equal(bits(cs), bits(ref_cs)) and np.array_equal(bits(sn), bits(ref_sn))
+        s = eng.session_create()
+        eng.permute_pages(s, np.random.default_rng(6).permutation(eng.nblocks))
+        tab = nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(s))
+        dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+        shp = eng.shape()
+        nv.check(nv.lib.nova_launch_rope_append_paged(C.byref(shp), eng.k_base, eng.v_base, tab, layer, eng.nb, n, pos0,
+                                                      dq.ptr, dk.ptr, dv.ptr, nv.lib.nova_rope_cos(eng.h),
+                                                      nv.lib.nova_rope_sin(eng.h), None))
+        nv.check(nv.lib.dev_sync())
+        res[kvd] = (eng.read_pools(), dq.download(np.float32), dk.download(np.float32))
+        if kvd == nv.KV_F32:
+            rpk = nv.DevBuf(L * eng.nb * eng.page_bytes).zero()
+            rpv = nv.DevBuf(L * eng.nb * eng.page_bytes).zero()
+            rq, rk, rv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+            g.ref_gpu_rope_batch(rq.ptr, rk.ptr, n, pos0, rcs.ptr, rsn.ptr, None)
+            g.ref_gpu_kv_store_paged(rpk.ptr, rpv.ptr, tab, layer, eng.nb, n, pos0, rk.ptr, rv.ptr, None)
+            nv.check(nv.lib.dev_sync())
+            assert g.ref_gpu_last_error() == 0
+            ref = (rpk.download(np.float32), rpv.download(np.float32), rq.download(np.float32), rk.download(np.float32))
+            # the oracle's rotation of the same rows (its non-NeoX branch) is the reference's too
+            sh = ob.shape(L, NH, NKV, ob.KV_F32, rope_neox=neox)
+            opk, opv = ob.new_pools(sh, eng.nb)
+            oq, ok_ = q.copy(), k.copy()
+            ob.rope_append_paged(sh, opk, opv, eng.pool.table(eng.session_slice(s)), layer, eng.nb, n, pos0, oq, ok_, v,
+                                 cs, sn)
+            assert np.array_equal(bits(oq.ravel()), bits(ref[2])) and np.array_equal(bits(ok_.ravel()), bits(ref[3]))
+            assert np.array_equal(bits(opk.ravel()), bits(ref[0]))
+        eng.close()
+    (k32, v32), q32, kk32 = res[nv.KV_F32]
+    assert np.array_equal(bits(q32), bits(ref[2])) and np.array_equal(bits(kk32), bits(ref[3]))
+    assert np.array_equal(bits(k32.ravel()), bits(ref[0])) and np.array_equal(bits(v32.ravel()), bits(ref[1]))
+    (k16, v16), _, _ = res[nv.KV_F16]
+    assert np.array_equal(bits(k16.ravel()), bits(ref[0].astype(np.float16)))
+    assert np.array_equal(bits(v16.ravel()), bits(ref[1].astype(np.float16)))
+    # decode steps through the batched calls with this layout: append kernel + attention, and where the layout
+    # allows it the fused launch; attention against the reference's own kernel on an fp32 copy of the pages
+    for kernel in (0, 1, 2):
+        if kernel == 2 and not neox:
+            continue                                      # the fused append is a NeoX-pairs path
+        eng, ss, sh, pk, pv, cs, sn, rng2 = build_case(nv, ob, model, nv.KV_F16, [333, 16], L=2, seed=77)
+        S = len(ss)
+        batch = eng.batch(ss)
+        try_set_kernel(nv, batch, kernel)
+        tables = np.stack([eng.pool.table(eng.session_slice(x)) for x in ss])
+        pos = [333, 16]
+        out_d = nv.DevBuf(2 * S * NH * 128 * 4)
+        for step in range(2):
+            qq = rng2.standard_normal((2, S, NH, 128)).astype(np.float32)
+            kk = rng2.standard_normal((2, S, NKV, 128)).astype(np.float32)
+            vv = rng2.standard_normal((2, S, NKV, 128)).astype(np.float32)
+            dq, dk, dv = nv.to_device(qq), nv.to_device(kk), nv.to_device(vv)
+            batch.step_all_layers(dq.ptr, dk.ptr, dv.ptr, out_d.ptr)
+            batch.advance()
+            nv.check(nv.lib.dev_sync())
+            assert batch.device_status() == 0
+            want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, qq, kk, vv, cs, sn, exact=True)   # rotates qq, kk
+            got = out_d.download(np.float32).reshape(2, S, NH, 128)
+            assert_attn_close(got, want, f"{model} kernel {kernel} step {step}")
+            assert np.array_equal(bits(dk.download(np.float32)), bits(kk.ravel())), "k rotated in place"
+            # the reference's attention on the same pages (fp32 copies of the fp16 values), layer 1, session 0
+            rk, rv = nv.to_device(pk.astype(np.float32)), nv.to_device(pv.astype(np.float32))
+            rq = nv.to_device(qq[1, 0])
+            ro, scr = nv.DevBuf(NH * 128 * 4), nv.DevBuf(NH * 32 * 130 * 4)
+            g.ref_gpu_attn_decode_paged(rq.ptr, rk.ptr, rv.ptr, nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(ss[0])),
+                                        1, eng.nb, pos[0] + 1, ro.ptr, scr.ptr, None)
+            nv.check(nv.lib.dev_sync())
+            assert g.ref_gpu_last_error() == 0
+            assert_attn_close(got[1, 0], ro.download(np.float32).reshape(NH, 128), "vs reference attention kernel")
+            pos = [p + 1 for p in pos]
+        gk, gv = eng.read_pools()
+        assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+        batch.close()
+        eng.close()
+
+
 def build_case(nv, ob, model, kvd, ctx_lens, L=2, seed=21, spare=0):
     """Engine + sessions with permuted tables and random cached context, mirrored in numpy pools."""
     NH, NKV = SHAPES[model]
+    theta, neox = ROPE.get(model, (1000000, 1))
     ctx = ((max(ctx_lens) + 40 + 15) // 16) * 16
-    eng = nv.Engine(L, NH, NKV, ctx=ctx, n_slices=len(ctx_lens) + spare, kv_dtype=kvd)
+    eng = nv.Engine(L, NH, NKV, ctx=ctx, n_slices=len(ctx_lens) + spare, kv_dtype=kvd, rope_theta=theta, rope_neox=neox)
     rng = np.random.default_rng(seed)
-    sh = ob.shape(L, NH, NKV, kvd)
+    sh = ob.shape(L, NH, NKV, kvd, rope_neox=neox)
     pk, pv = ob.new_pools(sh, eng.nb)
     cs, sn = eng.rope_tables()
     shp = eng.shape()
@@ -639,6 +752,31 @@ def test_sessions_follow_reference_manager(nv):
     k, v = eng.read_pools()
     assert not k.any() and not v.any()
     assert nv.lib.nova_session_destroy(eng.h, 7) == nv.ERR_INVALID
+    eng.close()
+
+
+def test_session_errors_are_codes(nv):
+    """Host error paths of the session layer: a slice whose pages a fork still maps is not handed out again
+    (NOVA_ERR_BUSY until the fork is gone), and a batch that names a destroyed session reports NOVA_ERR_INVALID
+    instead of following a dangling slice."""
+    eng = nv.Engine(1, 12, 2, ctx=64, n_slices=3, kv_dtype=nv.KV_F16)
+    parent = eng.session_create()
+    eng.set_n_past(parent, 40)
+    fork = nv.lib.nova_session_fork(eng.h, parent)
+    assert fork >= 0
+    eng.session_destroy(parent)
+    assert nv.lib.nova_session_create(eng.h) == nv.ERR_BUSY          # the parent's slice is next, its pages still read
+    assert nv.lib.nova_session_live_count(eng.h) == 1 and eng.pool.used() == 1     # and nothing was left half made
+    eng.session_destroy(fork)
+    again = eng.session_create()
+    assert again >= 0
+    other = eng.session_create()
+    batch = eng.batch([again, other])
+    eng.session_destroy(other)
+    assert nv.lib.nova_batch_cow(batch.h, None) == nv.ERR_INVALID
+    d = nv.DevBuf(2 * 4 * 12 * 128 * 4)
+    assert nv.lib.nova_batch_prefill(batch.h, 0, 4, d.ptr, d.ptr, d.ptr, d.ptr, None) == nv.ERR_INVALID
+    batch.close()
     eng.close()
 
 

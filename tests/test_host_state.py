@@ -122,3 +122,34 @@ def test_pool_vs_reference_live(nv, ob, seed):
         if op[0] == "release":
             live.remove(op[1])
         assert mine.state() == ref.state(), op
+
+
+def test_slice_reuse_guard(nv):
+    """KvPool::acquire resets the count of every identity page of the slice it hands out (kv_pool.h:100-112).  A
+    fork that still maps pages of a released parent, or a copy-on-write page taken from a free slice, would then be
+    shared with the next owner of that slice unnoticed.  The pool itself stays state-identical to the reference;
+    nova_pool_next_slice / nova_pool_foreign_mappings let the session layer see the hazard and refuse."""
+    p = nv.PoolView()
+    p.init(3, 64)                       # 3 slices x 4 pages
+    parent, fork = p.acquire(), p.acquire()
+    assert (parent, fork) == (0, 1) and p.next_slice() == 2
+    assert p.attach_prefix(fork, parent, 40) == 0          # 3 pages of the parent, the last one half full
+    assert p.foreign_mappings(parent) == 3 and p.foreign_mappings(fork) == 0
+    p.release(parent)
+    assert p.next_slice() == parent                        # LIFO: the parent's slice would be handed out next ...
+    assert p.foreign_mappings(parent) == 3                 # ... while the fork still reads three of its pages
+    assert [p.refcnt(b) for b in range(4)] == [1, 1, 1, 0]
+    # what the guard prevents: acquire would set those counts to 1 with two tables mapping the pages
+    fresh = p.cow_slice(fork, 40)                          # the fork un-shares nothing (count is 1): no copy ...
+    assert fresh == -1
+    p.release(fork)
+    assert p.foreign_mappings(parent) == 0                 # ... and once it is gone the slice is safe again
+    # a copy-on-write page taken from a free slice is a foreign mapping of that slice too
+    a, b = p.acquire(), p.acquire()
+    p.set_n_past(a, 20)
+    assert p.attach_prefix(b, a, 20) == 0
+    spare = p.next_slice()
+    page = p.cow_slice(b, 16)
+    assert page >= 0 and page // p.nblocks() == spare
+    assert p.foreign_mappings(spare) == 1
+    assert p.foreign_mappings(99) == nv.ERR_INVALID

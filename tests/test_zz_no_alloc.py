@@ -5,7 +5,8 @@ engine that lives inside one start-up arena, code between cudaStreamBeginCapture
 plug-in sandbox — and therefore cannot pass a scratch buffer.  Its scratch is a fixed array inside the
 library, shared by all calls on a GPU, so this file checks, through the C ABI, that two calls in a row
 (the second with other inputs and a different split, so that anything left over from the first would
-show) give what the caller-scratch entry point gives, and that a shape beyond the fixed size is refused.
+show) give what the caller-scratch entry point gives and what the CPU oracle's exact softmax gives on the
+downloaded pages, and that a shape beyond the fixed size is refused.
 
 Collected last on purpose: a failure here must not hide the results of any other test.
 """
@@ -19,7 +20,7 @@ pytestmark = pytest.mark.gpu
 REL_TOL, ABS_TOL = 2e-3, 1e-2     # the tolerance of the other attention tests
 
 
-def test_static_scratch_matches_caller_scratch(nv):
+def test_static_scratch_matches_caller_scratch(nv, ob):
     NH, NKV, L, layer = 28, 4, 2, 1
     eng = nv.Engine(L, NH, NKV, ctx=2048, n_slices=1, kv_dtype=nv.KV_F16)
     s = eng.session_create()
@@ -37,10 +38,14 @@ def test_static_scratch_matches_caller_scratch(nv):
     nv.check(nv.lib.dev_sync())
     scratch = nv.DevBuf(int(nv.lib.nova_attn_scratch_floats(C.byref(shp))) * 4)
     want_d, got_d = nv.DevBuf(NH * 128 * 4), nv.DevBuf(NH * 128 * 4)
-    qs = [nv.to_device(rng.standard_normal((NH, 128)).astype(np.float32)) for _ in range(2)]
+    q_host = [rng.standard_normal((NH, 128)).astype(np.float32) for _ in range(2)]
+    qs = [nv.to_device(q) for q in q_host]
     nv.check(nv.lib.dev_sync())
+    host_k, host_v = eng.read_pools()                                   # for the oracle
+    host_table = eng.pool.table(eng.session_slice(s))
+    osh = ob.shape(L, NH, NKV, ob.KV_F16)
     free_before = nv.lib.dev_max_alloc()
-    for q, n_keys in zip(qs, (1500, 37)):          # two calls in a row on the shared array
+    for q, qh, n_keys in zip(qs, q_host, (1500, 37)):          # two calls in a row on the shared array
         nv.check(nv.lib.nova_launch_attn_decode_paged(C.byref(shp), q.ptr, eng.k_base, eng.v_base, tab, layer, eng.nb,
                                                       n_keys, want_d.ptr, scratch.ptr, None))
         got_d.zero()
@@ -51,6 +56,9 @@ def test_static_scratch_matches_caller_scratch(nv):
         assert np.isfinite(got).all() and np.abs(want).max() > 0
         rel = np.linalg.norm(got - want) / np.linalg.norm(want)
         assert rel <= REL_TOL and np.abs(got - want).max() <= ABS_TOL, (n_keys, rel)
+        exact = ob.attn_decode_paged(osh, qh, host_k, host_v, host_table, layer, eng.nb, n_keys, exact=True).ravel()
+        rel = np.linalg.norm(got - exact) / np.linalg.norm(exact)
+        assert rel <= REL_TOL and np.abs(got - exact).max() <= ABS_TOL, ("oracle", n_keys, rel)
     assert nv.lib.dev_max_alloc() == free_before                   # nothing was allocated on the device
     # a shape the fixed array cannot hold is refused with a clear code, not truncated
     big = nv.KvShape(int(nv.lib.nova_attn_static_scratch_max_heads()) + 8, 8, 128, 16, nv.KV_F16, 1)
