@@ -729,6 +729,10 @@ def test_fork_registry_attach_and_telemetry(nv, ob):
     assert tel.cow_count == 1 and tel.blocks_free < free0
     batch.close()
     eng.session_destroy(a)
+    # the fork and the attached session still read pages of a's slice, which would be handed out next: refused
+    assert nv.lib.nova_session_create(eng.h) == nv.ERR_BUSY
+    eng.session_destroy(f)
+    eng.session_destroy(empty)
     other = eng.session_create()
     assert nv.lib.nova_session_attach_block(eng.h, reg.h, 7, 9, other) in (0, 32)   # producer gone (or its slot re-used)
     eng.close()
