@@ -131,7 +131,7 @@ SIGNATURES = {
     "nova_engine_telemetry": (i32, [vp, C.POINTER(Telemetry)]),
     "nova_batch_set_cascade": (i32, [vp, i32]), "nova_batch_shared_prefix_pages": (i32, [vp]),
     "nova_batch_step_partial_peers": (i32, [vp, vp, vp, vp, i64, i64, C.POINTER(vp), i32, i32, sz, i32, i64, i32, vp, vp, vp]),
-    "nova_lse_merge_peers": (i32, [C.POINTER(vp), i32, i32, sz, i32, i32, i64, i32, vp, vp, vp]),
+    "nova_lse_merge_peers": (i32, [vp, C.POINTER(vp), i32, i32, sz, i32, i32, i64, i32, vp, vp, vp]),
 }
 
 

@@ -294,96 +294,295 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restric
         make_float4(some ? A.x / L : 0.f, some ? A.y / L : 0.f, some ? A.z / L : 0.f, some ? A.w / L : 0.f);
 }
 
-// The same merge with the all-gather folded in: rank r's partial rows live in rank r's own memory
-// (an exchange slot: a 128-byte header whose first 8 bytes are the epoch flag, then n_rows x 130
-// floats) and every rank reads all of them over NVLink.  Each CTA first publishes this rank's flag
-// (its rows were written by kernels that precede this one in the stream), then waits - bounded by
-// wall clock - until every peer's flag has reached the epoch, then merges in rank order.  The kernels
-// that wait on one another run on different GPUs, never on one.
+// ---- exchange of partial rows between the GPUs of a node (one long session split over ranks) ---------------
+//
+// Every rank ends a layer with one un-normalised partial row (m, l, acc[128]) per (session, head) over its own
+// pages.  The rows cross NVLink ONCE, one way: the warp that holds a finished row stores it straight into the
+// exchange buffer of every peer (plain stores to the peer's memory, mapped through dev_ipc_open; no multicast,
+// no tensor map over peer memory), then waits - bounded by wall clock - until the peers' rows have arrived in
+// ITS OWN buffer, and merges all ranks' rows in rank order from local memory.
+//
+// There is no separate flag and no fence: a row travels as 16-byte words {value, epoch, value, epoch}; an
+// aligned 8-byte half of such a word is written and read as one piece, so a reader that finds the expected
+// epoch in both halves has the two values that were written with it (the protocol NCCL calls LL).  The epoch
+// grows by one per exchange and a buffer has two slots (epoch parity), so what an earlier exchange left in a
+// slot can never be mistaken for the current one.  A rank can be at most one epoch ahead of a peer that is
+// still reading: its next exchange needs that peer's next row, which the peer sends only after the kernel of
+// its previous exchange has finished (every kernel between two exchanges waits for its predecessor).
+//
+// Slot layout: [source rank 0..7][row][65 words of 16 B]; word 0 = (m, l), word 1 + 2i and 2 + 2i = the four
+// accumulator values of lane i.
 struct PeerSlots {
-    unsigned char* base[kMaxPeerRanks];
+    unsigned char* base[kMaxPeerRanks];      // this epoch's slot in every rank's buffer
 };
 
-__device__ __forceinline__ void st_relaxed_sys(long long* p, long long v) {
-    asm volatile("st.relaxed.sys.global.s64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+__device__ __forceinline__ void ll_store(void* p, float d0, float d1, uint32_t flag) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(__float_as_uint(d0)), "r"(flag),
+                 "r"(__float_as_uint(d1)), "r"(flag)
+                 : "memory");
 }
-
-__device__ __forceinline__ long long ld_relaxed_sys(const long long* p) {
-    long long v;
-    asm volatile("ld.relaxed.sys.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ll_load(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 
-// One warp per row (a one-warp CTA finds room on an SM next to a running attention CTA, a four-warp one
-// does not and would keep the next layer's CTAs off the SMs it takes).
-__global__ void __launch_bounds__(32) lse_merge_peers_kernel(PeerSlots ps, int n_ranks, int my_rank, int n_rows,
-                                                             long long epoch, unsigned long long timeout_ns,
-                                                             float* __restrict__ out, int32_t* status) {
-    const int row = (int)blockIdx.x;
-    const int lane = (int)threadIdx.x;
-    // Launched as a programmatic dependent of whatever precedes it in the stream (the local merge of
-    // this layer): the CTAs may become resident early and let a next layer's attention launch start, and
-    // wait here until the kernels that wrote this rank's rows have finished.
-    pdl_launch_dependents();
-    pdl_wait();
-    // Publish with a plain system-scope store: the rows were written by kernels that had completed before
-    // this one started, so they are in this GPU's L2 (where a peer's loads are served) already; a release
-    // fence here cost ~3 us and ordered nothing more.
-    if (lane == 0) st_relaxed_sys(reinterpret_cast<long long*>(ps.base[my_rank]), epoch);   // the same value from every CTA
-    int ok = 1;
-    if (lane < n_ranks && lane != my_rank) {
-        // poll with plain system-scope loads (an acquire on every poll would pay a fence per round trip)
-        const long long* flag = reinterpret_cast<const long long*>(ps.base[lane]);
-        unsigned long long t0;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        while (ld_relaxed_sys(flag) < epoch) {
-            unsigned long long t1;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-            if (t1 - t0 > timeout_ns) {            // the peer never got there: report, do not read its rows
-                ok = 0;
-                if (status) atomicCAS(status, 0, NOVA_ERR_TIMEOUT);
-                break;
-            }
-        }
-    }
-    // The row loads below bypass the caches (ld.cv) and are issued only after the flag loads have returned
-    // (the loop exit depends on them), so they see what the peer's earlier kernels wrote; no fence (~3 us).
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok || row >= n_rows) return;
-    // All ranks' values first, as independent loads: a load from a peer is a ~2.5 us NVLink round trip,
-    // and one after the other (as a merge over local memory would do it) they would add up.
-    float2 ml[kMaxPeerRanks], a0[kMaxPeerRanks], a1[kMaxPeerRanks];
+// One warp: sends its row (M, L, acc: lane i holds dims 4i..4i+3) to every peer, receives the peers' rows and
+// merges all of them in rank order.  Returns false (and sets *status) when a peer's row did not arrive in time;
+// then `acc` is left alone.  All 32 lanes must call it.
+__device__ inline bool exchange_and_merge(const PeerSlots& ps, size_t region_bytes, int n_ranks, int my_rank, int row,
+                                          uint32_t epoch, unsigned long long timeout_ns, int32_t* status, float& M, float& L,
+                                          float4& acc) {
+    const int lane = (int)threadIdx.x & 31;
+    const size_t row_off = (size_t)row * kLLRowBytes;
+    // send: all stores of all peers are independent of one another
 #pragma unroll
     for (int p = 0; p < kMaxPeerRanks; ++p) {
-        ml[p] = make_float2(-INFINITY, 0.f);
-        a0[p] = a1[p] = make_float2(0.f, 0.f);
-        if (p < n_ranks) {
-            const float* pr = reinterpret_cast<const float*>(ps.base[p] + kPeerSlotHeader) + (size_t)row * kPartW;
-            ml[p] = __ldcv(reinterpret_cast<const float2*>(pr));
-            a0[p] = __ldcv(reinterpret_cast<const float2*>(pr + 2 + 4 * lane));
-            a1[p] = __ldcv(reinterpret_cast<const float2*>(pr + 4 + 4 * lane));
+        if (p < n_ranks && p != my_rank) {
+            unsigned char* dst = ps.base[p] + (size_t)my_rank * region_bytes + row_off;
+            if (lane == 0) ll_store(dst, M, L, epoch);
+            ll_store(dst + 16 * (1 + 2 * lane), acc.x, acc.y, epoch);
+            ll_store(dst + 16 * (2 + 2 * lane), acc.z, acc.w, epoch);
         }
     }
-    float M = -INFINITY;
+    // receive: poll this rank's own memory until every peer's words carry this epoch
+    float pm[kMaxPeerRanks], pl[kMaxPeerRanks];
+    float4 pa[kMaxPeerRanks];
+    unsigned pending = 0;
+#pragma unroll
+    for (int p = 0; p < kMaxPeerRanks; ++p) {
+        pm[p] = -INFINITY;
+        pl[p] = 0.f;
+        pa[p] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p < n_ranks && p != my_rank) pending |= 1u << p;
+    }
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    const unsigned char* mine = ps.base[my_rank];
+    bool failed = false;
+    while (__any_sync(0xffffffffu, pending != 0)) {
+        uint4 w0[kMaxPeerRanks], w1[kMaxPeerRanks], w2[kMaxPeerRanks];
+#pragma unroll
+        for (int p = 0; p < kMaxPeerRanks; ++p) {          // all loads first, then the checks
+            if (pending & (1u << p)) {
+                const unsigned char* src = mine + (size_t)p * region_bytes + row_off;
+                w0[p] = ll_load(src);                       // every lane needs (m, l)
+                w1[p] = ll_load(src + 16 * (1 + 2 * lane));
+                w2[p] = ll_load(src + 16 * (2 + 2 * lane));
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < kMaxPeerRanks; ++p) {
+            if (pending & (1u << p)) {
+                const bool ok = w0[p].y == epoch && w0[p].w == epoch && w1[p].y == epoch && w1[p].w == epoch &&
+                                w2[p].y == epoch && w2[p].w == epoch;
+                if (ok) {
+                    pm[p] = __uint_as_float(w0[p].x);
+                    pl[p] = __uint_as_float(w0[p].z);
+                    pa[p] = make_float4(__uint_as_float(w1[p].x), __uint_as_float(w1[p].z), __uint_as_float(w2[p].x),
+                                        __uint_as_float(w2[p].z));
+                    pending &= ~(1u << p);
+                }
+            }
+        }
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (__any_sync(0xffffffffu, t1 - t0 > timeout_ns)) {     // a peer never got there: report, merge nothing
+            failed = pending != 0;
+            break;
+        }
+    }
+    failed = __any_sync(0xffffffffu, failed);
+    if (failed) {
+        if (lane == 0 && status) atomicCAS(status, 0, NOVA_ERR_TIMEOUT);
+        return false;
+    }
+#pragma unroll
+    for (int p = 0; p < kMaxPeerRanks; ++p) {             // this rank's own row sits at its place in the order
+        if (p == my_rank) {
+            pm[p] = M;
+            pl[p] = L;
+            pa[p] = acc;
+        }
+    }
+    float Mx = -INFINITY;
 #pragma unroll
     for (int p = 0; p < kMaxPeerRanks; ++p)
-        if (p < n_ranks && ml[p].y > 0.f) M = fmaxf(M, ml[p].x);
-    float L = 0.f;
+        if (p < n_ranks && pl[p] > 0.f) Mx = fmaxf(Mx, pm[p]);
+    float Ls = 0.f;
     float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int p = 0; p < kMaxPeerRanks; ++p) {
-        if (p < n_ranks && ml[p].y > 0.f) {
-            const float w = __expf(ml[p].x - M);
-            L = fmaf(ml[p].y, w, L);
-            A.x = fmaf(a0[p].x, w, A.x);
-            A.y = fmaf(a0[p].y, w, A.y);
-            A.z = fmaf(a1[p].x, w, A.z);
-            A.w = fmaf(a1[p].y, w, A.w);
+        if (p < n_ranks && pl[p] > 0.f) {
+            const float w = __expf(pm[p] - Mx);
+            Ls = fmaf(pl[p], w, Ls);
+            A.x = fmaf(pa[p].x, w, A.x);
+            A.y = fmaf(pa[p].y, w, A.y);
+            A.z = fmaf(pa[p].z, w, A.z);
+            A.w = fmaf(pa[p].w, w, A.w);
         }
     }
-    const bool some = L > 0.f;
+    M = Mx;
+    L = Ls;
+    acc = A;
+    return true;
+}
+
+// The exchange on its own, for partial rows that are already in memory (part [n_rows][130], written by the
+// kernels before this one in the stream): one warp per row.  A one-warp CTA finds room on an SM next to a
+// running attention CTA; a larger one would keep a next layer's CTAs off the SMs it takes.
+__global__ void __launch_bounds__(32) lse_exchange_kernel(const float* __restrict__ part, PeerSlots ps, size_t region_bytes,
+                                                          int n_ranks, int my_rank, int n_rows, uint32_t epoch,
+                                                          unsigned long long timeout_ns, float* __restrict__ out,
+                                                          int32_t* status) {
+    const int row = (int)blockIdx.x;
+    const int lane = (int)threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();                                  // the rows come from the kernels before this one
+    if (row >= n_rows) return;
+    const float* pr = part + (size_t)row * kPartW;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(pr));
+    const float2 a0 = __ldcg(reinterpret_cast<const float2*>(pr + 2 + 4 * lane));
+    const float2 a1 = __ldcg(reinterpret_cast<const float2*>(pr + 4 + 4 * lane));
+    float M = ml.x, L = ml.y;
+    float4 acc = make_float4(a0.x, a0.y, a1.x, a1.y);
+    if (!(L > 0.f)) {                            // nothing attended on this rank: send a clean empty row
+        M = -INFINITY;
+        L = 0.f;
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (!exchange_and_merge(ps, region_bytes, n_ranks, my_rank, row, epoch, timeout_ns, status, M, L, acc)) return;
+    const float inv = L > 0.f ? 1.f / L : 0.f;
     *reinterpret_cast<float4*>(out + (size_t)row * kHeadDim + 4 * lane) =
-        make_float4(some ? A.x / L : 0.f, some ? A.y / L : 0.f, some ? A.z / L : 0.f, some ? A.w / L : 0.f);
+        make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+}
+
+// The merge that follows a split kernel with the exchange folded in: one CTA per (row, head) unit, the
+// contributors of the split dealt out to its warps (as attn_combine_kernel<false, true>), then warp 0 sends the
+// finished row to the peers, receives theirs and writes the output.  The split kernel ran with
+// write_partial_only: rows that a single CTA covered (or that have no page on this rank) are in a.out_part.
+__global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_exchange_kernel(AttnLaunch a, int n_ctas_split, PeerSlots ps,
+                                                                                   size_t region_bytes, int n_ranks, int my_rank,
+                                                                                   uint32_t epoch, unsigned long long timeout_ns,
+                                                                                   int32_t* xstatus) {
+    __shared__ int s_prefix[kMaxRowsSmem + 1];
+    __shared__ float s_ml[2 * kCombineWarps];
+    __shared__ float4 s_acc[kCombineWarps * 32];
+    const int lane = (int)threadIdx.x & 31;
+    const int warp = (int)threadIdx.x >> 5;
+    pdl_launch_dependents();
+    const int KVG = a.kv_group;
+    const int G = a.n_heads / a.n_kv_heads;
+    const int n_groups = a.n_kv_heads / KVG;
+    const int heads_per_row = KVG * G;
+    plan_build_prefix(a, s_prefix, n_groups);     // n_past: not written by the split kernel before us
+    PlanView pv;
+    pv.prefix = s_prefix;
+    const int S = a.n_sessions * plan_nq(a);
+    pv.rows_per_layer = S * n_groups;
+    pv.n_groups = n_groups;
+    pv.pages_per_layer = s_prefix[pv.rows_per_layer];
+    pv.pages_total = pv.pages_per_layer * a.n_layers;
+    pv.n_ctas = pv.pages_total < (int64_t)n_ctas_split ? (int)pv.pages_total : n_ctas_split;
+    plan_finish(pv);
+    pdl_wait();                                   // the split kernel's partials are complete from here on
+
+    const int64_t units = (int64_t)pv.rows_per_layer * a.n_layers * heads_per_row;
+    const size_t stride_c = (size_t)heads_per_row * kSlotW;
+    for (int64_t u = blockIdx.x; u < units; u += gridDim.x) {
+        const int64_t v = u / heads_per_row;
+        const int hr = (int)(u - v * heads_per_row);
+        const int row = (int)(v % pv.rows_per_layer);
+        const int ll = (int)(v / pv.rows_per_layer);
+        const bool no_pages = pv.pages_total == 0 || s_prefix[row + 1] == s_prefix[row];
+        int c_first = 0, n = 0;
+        if (!no_pages) {
+            const int64_t row_begin = (int64_t)ll * pv.pages_per_layer + s_prefix[row];
+            const int64_t row_end = (int64_t)ll * pv.pages_per_layer + s_prefix[row + 1];
+            c_first = plan_owner(pv, row_begin);
+            n = plan_owner(pv, row_end - 1) - c_first + 1;
+        }
+        const int s = row / n_groups, grp = row - s * n_groups;
+        const int64_t head = ((int64_t)ll * S + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
+        float M = -INFINITY, L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (n <= 1) {                 // the split kernel left this row's partial (or an empty row) in out_part
+            if (warp == 0) {
+                const float* pr = a.out_part + head * kPartW;
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(pr));
+                const float2 y0 = __ldcg(reinterpret_cast<const float2*>(pr + 2 + 4 * lane));
+                const float2 y1 = __ldcg(reinterpret_cast<const float2*>(pr + 4 + 4 * lane));
+                if (ml.y > 0.f) {
+                    M = ml.x;
+                    L = ml.y;
+                    acc = make_float4(y0.x, y0.y, y1.x, y1.y);
+                }
+            }
+        } else {
+            const float* base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
+            for (int c0 = 32 * warp; c0 < n; c0 += 32 * kCombineWarps) {
+                const int cnt = n - c0 < 32 ? n - c0 : 32;
+                const float* src = base + (size_t)c0 * stride_c;
+                float2 ml = make_float2(-INFINITY, 0.f);
+                if (lane < cnt) ml = __ldcg(reinterpret_cast<const float2*>(src + (size_t)lane * stride_c));
+                float4 x[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (i < cnt) x[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * stride_c + 4 + 4 * lane));
+                }
+                const float mc = warp_max(ml.y > 0.f ? ml.x : -INFINITY);
+                const float Mn = fmaxf(M, mc);
+                if (Mn == -INFINITY) continue;
+                const float corr = __expf(M - Mn);
+                const float w = ml.y > 0.f ? __expf(ml.x - Mn) : 0.f;
+                L = fmaf(L, corr, warp_sum(ml.y * w));
+                acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float wi = __shfl_sync(0xffffffffu, w, i);
+                    if (wi != 0.f) {
+                        acc.x = fmaf(x[i].x, wi, acc.x);
+                        acc.y = fmaf(x[i].y, wi, acc.y);
+                        acc.z = fmaf(x[i].z, wi, acc.z);
+                        acc.w = fmaf(x[i].w, wi, acc.w);
+                    }
+                }
+                M = Mn;
+            }
+            if (lane == 0) { s_ml[2 * warp] = M; s_ml[2 * warp + 1] = L; }
+            s_acc[warp * 32 + lane] = acc;
+            __syncthreads();
+            if (warp == 0) {
+                float Mx = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kCombineWarps; ++w)
+                    if (s_ml[2 * w + 1] > 0.f) Mx = fmaxf(Mx, s_ml[2 * w]);
+                L = 0.f;
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < kCombineWarps; ++w) {
+                    const float lw = s_ml[2 * w + 1];
+                    if (lw > 0.f) {
+                        const float cw = __expf(s_ml[2 * w] - Mx);
+                        const float4 x = s_acc[w * 32 + lane];
+                        L = fmaf(lw, cw, L);
+                        acc.x = fmaf(x.x, cw, acc.x);
+                        acc.y = fmaf(x.y, cw, acc.y);
+                        acc.z = fmaf(x.z, cw, acc.z);
+                        acc.w = fmaf(x.w, cw, acc.w);
+                    }
+                }
+                M = L > 0.f ? Mx : -INFINITY;
+            }
+            __syncthreads();
+        }
+        if (warp != 0) continue;
+        if (!exchange_and_merge(ps, region_bytes, n_ranks, my_rank, (int)head, epoch, timeout_ns, xstatus, M, L, acc)) continue;
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =
+            make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    }
 }
 
 }  // namespace
@@ -438,15 +637,45 @@ int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, 
 
 namespace novab {
 
-int launch_lse_merge_peers(void* const* slot_base, int n_ranks, int my_rank, int n_rows, long long epoch,
-                           unsigned long long timeout_ns, float* out, int32_t* status, cudaStream_t s) {
+size_t peer_region_bytes(int n_rows) { return ((size_t)n_rows * kLLRowBytes + 127) / 128 * 128; }
+
+static void fill_slots(PeerSlots& ps, void* const* slot_base, int n_ranks) {
+    for (int i = 0; i < kMaxPeerRanks; ++i) ps.base[i] = i < n_ranks ? static_cast<unsigned char*>(slot_base[i]) : nullptr;
+}
+
+int launch_lse_exchange(const float* part, void* const* slot_base, int n_ranks, int my_rank, int n_rows, long long epoch,
+                        unsigned long long timeout_ns, float* out, int32_t* status, cudaStream_t s) {
     if (n_rows <= 0) return NOVA_OK;
     PeerSlots ps;
-    for (int i = 0; i < kMaxPeerRanks; ++i) ps.base[i] = i < n_ranks ? static_cast<unsigned char*>(slot_base[i]) : nullptr;
-    const cudaError_t le = launch_kernel_pdl(lse_merge_peers_kernel, dim3((unsigned)n_rows), dim3(32), 0, s, true, ps, n_ranks,
-                                             my_rank, n_rows, epoch, timeout_ns, out, status);
+    fill_slots(ps, slot_base, n_ranks);
+    const cudaError_t le = launch_kernel_pdl(lse_exchange_kernel, dim3((unsigned)n_rows), dim3(32), 0, s, true, part, ps,
+                                             peer_region_bytes(n_rows), n_ranks, my_rank, n_rows, (uint32_t)epoch, timeout_ns, out,
+                                             status);
     if (le != cudaSuccess) {
-        set_cuda_error(le, "peer merge launch");
+        set_cuda_error(le, "exchange launch");
+        return NOVA_ERR_CUDA;
+    }
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+// After a split kernel that ran with write_partial_only (one layer): merge + exchange + output in one launch.
+int launch_attn_combine_exchange(const AttnLaunch& a, int n_ctas_split, void* const* slot_base, int n_ranks, int my_rank,
+                                 long long epoch, unsigned long long timeout_ns, int32_t* status, cudaStream_t s) {
+    if (a.n_sessions <= 0 || a.n_layers != 1 || !a.out_part || !a.out) return NOVA_ERR_INVALID;
+    const int n_rows = a.n_sessions * a.n_heads;
+    PeerSlots ps;
+    fill_slots(ps, slot_base, n_ranks);
+    // one CTA per (row, head); more units than that loop (the CTAs wait for the peers, so they are kept few enough
+    // to be resident together next to the attention CTAs)
+    int ctas = n_rows;
+    const int cap = 2 * sm_count();
+    if (ctas > cap) ctas = cap;
+    const cudaError_t le = launch_kernel_pdl(attn_combine_exchange_kernel, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true,
+                                             a, n_ctas_split, ps, peer_region_bytes(n_rows), n_ranks, my_rank, (uint32_t)epoch,
+                                             timeout_ns, status);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "merge + exchange launch");
         return NOVA_ERR_CUDA;
     }
     NOVA_LAUNCH_CHECK();

@@ -172,9 +172,12 @@ int attn_split_ctas_simt(const AttnLaunch& a, int n_ctas);
 int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas);
 int launch_lse_combine(const float* parts, int n_parts, int n_rows, float* out, cudaStream_t s);
 constexpr int kMaxPeerRanks = 8;        // ranks of one NVLink domain that can share a long session
-constexpr int kPeerSlotHeader = 128;    // bytes in front of an exchange slot's rows; the first 8 are the epoch flag
-int launch_lse_merge_peers(void* const* slot_base, int n_ranks, int my_rank, int n_rows, long long epoch,
-                           unsigned long long timeout_ns, float* out, int32_t* status, cudaStream_t s);
+constexpr int kLLRowBytes = 16 * (1 + kHeadDim / 2);   // a partial row as 16-byte {value, epoch, value, epoch} words: (m, l) + 128 values
+size_t peer_region_bytes(int n_rows);   // bytes one source rank's rows take in an exchange slot
+int launch_lse_exchange(const float* part, void* const* slot_base, int n_ranks, int my_rank, int n_rows, long long epoch,
+                        unsigned long long timeout_ns, float* out, int32_t* status, cudaStream_t s);
+int launch_attn_combine_exchange(const AttnLaunch& a, int n_ctas_split, void* const* slot_base, int n_ranks, int my_rank,
+                                 long long epoch, unsigned long long timeout_ns, int32_t* status, cudaStream_t s);
 
 // rope / append / page utilities (rope_append.cu)
 int launch_rope_table(float* cs, float* sn, int64_t n_pos, int theta, cudaStream_t s);

@@ -62,6 +62,7 @@ struct nova_batch {
     int row_setup = 2;               // work-split weight of a row start, in pages (see AttnLaunch)
     int cascade = 0;                 // 1: the shared leading pages of the batch's sessions are attended once for all
     int casc_pages = 0;              // shared leading pages found by the last nova_batch_cow (0: none worth it)
+    float* xparts = nullptr;         // [S * NH][130] this rank's partial rows of one layer before they are exchanged
     float* casc_parts = nullptr;     // [chunks + 1][S * NH][130] partials of the cascade
     size_t casc_floats = 0;
     // staging for the host-buffer step and the graph replay
@@ -613,22 +614,22 @@ int nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim, 
 
 size_t nova_peer_slot_bytes(int n_rows) {
     if (n_rows <= 0) return 0;
-    const size_t raw = (size_t)kPeerSlotHeader + (size_t)n_rows * kPartW * sizeof(float);
-    return (raw + 127) / 128 * 128;
+    return (size_t)kMaxPeerRanks * peer_region_bytes(n_rows);
 }
 
-int nova_lse_merge_peers(void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int slot, int n_rows,
-                         int64_t epoch, int timeout_ms, float* out, int32_t* status, nova_stream_t s) {
-    if (!peer_base || !out || n_ranks < 1 || n_ranks > kMaxPeerRanks || my_rank < 0 || my_rank >= n_ranks || slot < 0 ||
-        n_rows < 0 || epoch < 1 || timeout_ms < 1 || slot_bytes < nova_peer_slot_bytes(n_rows) || slot_bytes % 128)
+int nova_lse_merge_peers(const float* part, void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int slot,
+                         int n_rows, int64_t epoch, int timeout_ms, float* out, int32_t* status, nova_stream_t s) {
+    if (!part || !peer_base || !out || n_ranks < 1 || n_ranks > kMaxPeerRanks || my_rank < 0 || my_rank >= n_ranks || slot < 0 ||
+        n_rows < 0 || epoch < 1 || epoch > 0x7fffffffLL || timeout_ms < 1 || slot_bytes < nova_peer_slot_bytes(n_rows) ||
+        slot_bytes % 128)
         return NOVA_ERR_INVALID;
     void* base[kMaxPeerRanks];
     for (int i = 0; i < n_ranks; ++i) {
         if (!peer_base[i]) return NOVA_ERR_INVALID;
         base[i] = static_cast<unsigned char*>(peer_base[i]) + (size_t)slot * slot_bytes;
     }
-    return launch_lse_merge_peers(base, n_ranks, my_rank, n_rows, (long long)epoch,
-                                  (unsigned long long)timeout_ms * 1000000ull, out, status, (cudaStream_t)s);
+    return launch_lse_exchange(part, base, n_ranks, my_rank, n_rows, (long long)epoch,
+                               (unsigned long long)timeout_ms * 1000000ull, out, status, (cudaStream_t)s);
 }
 
 /* ------------------------------------------------------------------- batches */
@@ -688,6 +689,7 @@ void nova_batch_destroy(nova_batch* b) {
     cudaFreeHost(b->h_n_past);
     cudaFree(b->part);
     cudaFree(b->casc_parts);
+    cudaFree(b->xparts);
     cudaFree(b->dq);
     cudaFree(b->dk);
     cudaFree(b->dv);
@@ -1185,39 +1187,66 @@ int nova_batch_attn_partial_layers(nova_batch* b, int layer0, int n_layers, cons
 }
 
 // One decode step of a session split over the GPUs of a node, in the engine's layer order and without any
-// host-side collective: per layer the fused RoPE+append+attention over this rank's page range leaves the
-// partial rows in this rank's exchange slot, and nova_lse_merge_peers merges all ranks' rows into out.
+// host-side collective: per layer the fused RoPE+append+attention over this rank's page range, then ONE launch
+// that merges this rank's split-K partials, sends the finished rows to every peer, receives theirs and writes
+// the merged output.
 int nova_batch_step_partial_peers(nova_batch* b, float* q, float* k, const float* v, int64_t page0, int64_t page1,
                                   void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int n_slots,
                                   int64_t epoch0, int timeout_ms, float* out, int32_t* status, nova_stream_t s) {
     if (!b || !q || !k || !v || !out || !peer_base || n_ranks < 1 || n_ranks > kMaxPeerRanks || my_rank < 0 ||
-        my_rank >= n_ranks || n_slots < 2 || epoch0 < 1 || page0 < 0 || page1 < page0)
+        my_rank >= n_ranks || n_slots < 2 || epoch0 < 1 || page0 < 0 || page1 < page0 || timeout_ms < 1)
         return NOVA_ERR_INVALID;
     nova_engine* e = b->e;
     const int L = e->d.n_layers;
     const int rows = b->n * e->d.n_heads;
-    if (slot_bytes < nova_peer_slot_bytes(rows) || slot_bytes % 128 || !peer_base[my_rank]) return NOVA_ERR_INVALID;
+    if (epoch0 + L > 0x7fffffffLL) return NOVA_ERR_INVALID;
+    if (slot_bytes < nova_peer_slot_bytes(rows) || slot_bytes % 128) return NOVA_ERR_INVALID;
+    for (int i = 0; i < n_ranks; ++i)
+        if (!peer_base[i]) return NOVA_ERR_INVALID;
     cudaStream_t st = (cudaStream_t)s;
     NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
+    if (!b->xparts) NOVA_CUDA_TRY(cudaMalloc((void**)&b->xparts, (size_t)rows * kPartW * sizeof(float)));
     const size_t qs = (size_t)b->n * e->d.n_heads * kHeadDim, ks = (size_t)b->n * e->d.n_kv_heads * kHeadDim;
+    const unsigned long long timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
     int rc = nova_batch_cow(b, s);
     if (rc < 0) return rc;
     for (int l = 0; l < L; ++l) {
         const int64_t epoch = epoch0 + l;
-        const int slot = (int)(epoch % n_slots);
-        float* part = reinterpret_cast<float*>(static_cast<unsigned char*>(peer_base[my_rank]) + (size_t)slot * slot_bytes +
-                                               kPeerSlotHeader);
+        void* base[kMaxPeerRanks];
+        for (int i = 0; i < n_ranks; ++i)
+            base[i] = static_cast<unsigned char*>(peer_base[i]) + (size_t)(epoch % n_slots) * slot_bytes;
+        AttnLaunch a;
+        fill_attn(b, a);
+        a.q = q + l * qs;
+        a.out = out + l * qs;
+        a.out_part = b->xparts;
+        a.write_partial_only = 1;
+        a.page_lo = page0;
+        a.page_hi = page1;
+        a.layer0 = l;
+        a.n_layers = 1;
         if (use_fused(b)) {
-            // layers after the first follow the previous layer's merge kernel, which lets its dependents start early
-            rc = run_attn_fused(b, l, 1, q + l * qs, k + l * ks, v + l * ks, nullptr, st, b->pdl && l > 0, part, page0, page1);
+            a.fuse_append = 1;
+            a.pool_k_w = e->pool_k; a.pool_v_w = e->pool_v;
+            a.k_new = k + l * ks; a.v_new = v + l * ks;
+            a.rope_cs = e->cs; a.rope_sn = e->sn; a.rope_rows = e->d.rope_positions;
+            // layers after the first follow the previous layer's merge + exchange launch, which lets its dependents start early
+            a.pdl = (b->pdl && l > 0) ? (b->pdl == 2 ? 2 : 1) : 0;
+            a.pdl_spare = a.pdl != 0;
         } else {
             rc = nova_batch_append(b, l, q + l * qs, k + l * ks, v + l * ks, s);
             if (rc != NOVA_OK) return rc;
-            rc = nova_batch_attn_partial(b, l, q + l * qs, page0, page1, part, s);
+        }
+        int ctas;
+        if (b->kernel == 1) {
+            ctas = attn_split_ctas_mma(a, 0);
+            rc = launch_attn_mma(a, e->d.kv_dtype, ctas, st);
+        } else {
+            ctas = attn_split_ctas_simt(a, 0);
+            rc = launch_attn_simt(a, e->d.kv_dtype, ctas, st);
         }
         if (rc != NOVA_OK) return rc;
-        rc = nova_lse_merge_peers(peer_base, n_ranks, my_rank, slot_bytes, slot, rows, epoch, timeout_ms, out + l * qs,
-                                  status, s);
+        rc = launch_attn_combine_exchange(a, ctas, base, n_ranks, my_rank, (long long)epoch, timeout_ns, status, st);
         if (rc != NOVA_OK) return rc;
     }
     return nova_batch_advance(b, s);

@@ -46,18 +46,18 @@ def gather_partials(part, world: int, dist=None, out=None):
 
 
 class PeerExchange:
-    """Exchange buffers of all ranks of a node for nova_lse_merge_peers: every rank owns `n_slots` slots
-    of partial rows in its own device memory, exports it with dev_ipc_export, and opens the others'.
-    `nv` is the loaded package (ctypes face); `dist` a torch.distributed-like module whose
-    all_gather_object carries the 64-byte handles (None or world 1: only the local buffer)."""
-
-    HEADER = 128
+    """Exchange buffers of all ranks of a node for nova_lse_merge_peers / nova_batch_step_partial_peers: every rank
+    owns `n_slots` slots in its own device memory that the peers WRITE their partial rows into, exports the buffer
+    with dev_ipc_export and opens the others'.  `nv` is the loaded package (ctypes face); `dist` a
+    torch.distributed-like module whose all_gather_object carries the 64-byte handles (None or world 1: only the
+    local buffer)."""
 
     def __init__(self, nv, n_rows: int, rank: int, world: int, dist=None, n_slots: int = 2):
         import ctypes as C
         self.nv, self.rank, self.world, self.n_rows, self.n_slots = nv, rank, world, n_rows, n_slots
         self.slot_bytes = int(nv.lib.nova_peer_slot_bytes(n_rows))
         self.buf = nv.DevBuf(self.slot_bytes * n_slots).zero()
+        self.part = nv.DevBuf(n_rows * PART_W * 4).zero()       # this rank's rows before they are sent
         self.opened = []
         ptrs = [None] * world
         ptrs[rank] = self.buf.ptr
@@ -77,13 +77,13 @@ class PeerExchange:
                 ptrs[r] = p.value
         self.base = (C.c_void_p * world)(*ptrs)
 
-    def rows_ptr(self, slot: int) -> int:
-        """Where this rank's partial rows of `slot` go (the `part` argument of nova_batch_attn_partial)."""
-        return self.buf.ptr + slot * self.slot_bytes + self.HEADER
+    def rows_ptr(self, slot: int = 0) -> int:
+        """Where this rank's partial rows go before the exchange (the `part` argument of nova_batch_attn_partial)."""
+        return self.part.ptr
 
     def merge(self, epoch: int, out_ptr: int, stream=None, status_ptr=None, timeout_ms: int = 1000, n_rows=None):
         slot = epoch % self.n_slots
-        self.nv.check(self.nv.lib.nova_lse_merge_peers(self.base, self.world, self.rank, self.slot_bytes, slot,
+        self.nv.check(self.nv.lib.nova_lse_merge_peers(self.part.ptr, self.base, self.world, self.rank, self.slot_bytes, slot,
                                                         self.n_rows if n_rows is None else n_rows, epoch, timeout_ms,
                                                         out_ptr, status_ptr, stream), "nova_lse_merge_peers")
 
@@ -92,3 +92,4 @@ class PeerExchange:
             self.nv.lib.dev_ipc_close(p)
         self.opened = []
         self.buf.free()
+        self.part.free()

@@ -403,32 +403,33 @@ int  nova_batch_attn_partial_layers(nova_batch* b, int layer0, int n_layers, con
 int  nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim, float* out,
                       nova_stream_t s);
 
-/* The merge with the exchange folded in (no counterpart in the reference, which scales a long context
- * only inside one GPU): every rank keeps its partial rows in its OWN exchange buffer, shared with the
- * other processes of the node through dev_ipc_export / dev_ipc_open, and the merge kernel of every rank
- * reads all ranks' rows over NVLink itself - no all-gather.
- *   exchange buffer = n_slots slots of slot_bytes (>= nova_peer_slot_bytes(n_rows), a multiple of 128),
- *   zero-filled once; slot = 128-byte header (first 8 bytes: epoch flag) + rows [n_rows][2+HD], i.e.
- *   nova_batch_attn_partial writes to  base + slot * slot_bytes + 128.
- * nova_lse_merge_peers, called by every rank with the same slot and epoch after its own partial
- * kernels on stream s: publishes this rank's flag (= epoch), waits until every peer's flag >= epoch
- * (each wait bounded by timeout_ms; on expiry *status (device, may be NULL) becomes NOVA_ERR_TIMEOUT
- * and out is left alone), then merges the ranks' rows in rank order into out [n_rows][HD].
- * Epochs grow by one per call (start at 1); with slot = epoch % n_slots, n_slots >= 2 is enough: a
- * rank can be at most one epoch ahead of a peer that is still reading.  peer_base: host array of
- * n_ranks (<= 8) device pointers, entry my_rank being this rank's own buffer. */
+/* The merge with the exchange folded in (no counterpart in the reference, which scales a long context only
+ * inside one GPU).  Every rank owns an exchange buffer of n_slots slots of slot_bytes
+ * (>= nova_peer_slot_bytes(n_rows), a multiple of 128), zero-filled once and shared with the other processes of
+ * the node through dev_ipc_export / dev_ipc_open.  A rank SENDS its partial rows: the warp that holds a finished
+ * row stores it into every peer's buffer (plain stores over NVLink, one way; no multicast), waits - each wait
+ * bounded by timeout_ms; on expiry *status (device, may be NULL) becomes NOVA_ERR_TIMEOUT and the row's output is
+ * left alone - until the peers' rows have arrived in its own buffer, and merges all ranks' rows in rank order from
+ * local memory.  Rows travel as 16-byte words {value, epoch, value, epoch}: a word whose two epoch fields match
+ * is complete, so there is no separate flag and no fence.
+ * Epochs grow by one per exchange, start at 1 and stay below 2^31; slot = epoch % n_slots and n_slots >= 2 is
+ * enough: a rank can be at most one epoch ahead of a peer that is still reading.  peer_base: host array of
+ * n_ranks (<= 8) device pointers, entry my_rank being this rank's own buffer.
+ *
+ * nova_lse_merge_peers: the exchange on its own, called by every rank with the same slot and epoch after the
+ * kernels that wrote part [n_rows][2+HD] on stream s; out [n_rows][HD]. */
 size_t nova_peer_slot_bytes(int n_rows);
-/* One whole decode step of the batch's sessions, their pages split over the ranks of a node, issued
- * natively in layer order: per layer the (fused) RoPE+append+attention over this rank's logical pages
- * [page0, page1) writes its partial rows [S*NH][2+HD] into slot (epoch0 + layer) % n_slots of this
- * rank's exchange buffer, then nova_lse_merge_peers with that epoch merges all ranks' rows into
- * out + layer * S*NH*HD; n_past advances at the end.  q/k/v/out are [layers][S][...] as in
- * nova_batch_run_steps.  The caller passes epoch0 = 1, 1 + layers, 1 + 2*layers, ... on every rank. */
+int  nova_lse_merge_peers(const float* part, void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int slot,
+                          int n_rows, int64_t epoch, int timeout_ms, float* out, int32_t* status, nova_stream_t s);
+/* One whole decode step of the batch's sessions, their pages split over the ranks of a node, issued natively in
+ * layer order: per layer the (fused) RoPE+append+attention over this rank's logical pages [page0, page1), then ONE
+ * launch that merges the split-K partials of this rank, exchanges the finished rows [S*NH] with the peers in slot
+ * (epoch0 + layer) % n_slots and writes out + layer * S*NH*HD; n_past advances at the end.  q/k/v/out are
+ * [layers][S][...] as in nova_batch_run_steps.  The caller passes epoch0 = 1, 1 + layers, 1 + 2*layers, ... on every
+ * rank.  With the fused append, k is rotated in place only on the rank whose page range holds the new token. */
 int  nova_batch_step_partial_peers(nova_batch* b, float* q, float* k, const float* v, int64_t page0, int64_t page1,
                                    void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int n_slots,
                                    int64_t epoch0, int timeout_ms, float* out, int32_t* status, nova_stream_t s);
-int  nova_lse_merge_peers(void* const* peer_base, int n_ranks, int my_rank, size_t slot_bytes, int slot, int n_rows,
-                          int64_t epoch, int timeout_ms, float* out, int32_t* status, nova_stream_t s);
 
 #ifdef __cplusplus
 }

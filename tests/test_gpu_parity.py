@@ -472,16 +472,36 @@ def test_partial_and_lse_combine(nv, ob, kernel):
     eng.close()
 
 
-def test_peer_merge_on_one_gpu(nv, ob):
-    """nova_lse_merge_peers, the merge that reads every rank's partial rows from that rank's own exchange
-    buffer: here the 'ranks' are four buffers of this one GPU whose flags are set beforehand (kernels that
-    wait on one another never share a GPU), so no wait happens.  Same result as nova_lse_combine on the
-    stacked rows and as the oracle's merge, for every rank's view, over two epochs (both slots).  Then the
-    bounded wait: one flag that nothing sets -> NOVA_ERR_TIMEOUT in the status word, output left alone."""
+def ll_encode(rows, epoch):
+    """Partial rows [n][130] as they travel between ranks: 65 words of 16 bytes {value, epoch, value, epoch} per row;
+    word 0 = (m, l), word j = accumulator values 2(j-1), 2(j-1)+1.  Rows with l <= 0 travel as clean empty rows."""
+    rows = np.ascontiguousarray(rows, np.float32).copy()
+    empty = ~(rows[:, 1] > 0)
+    rows[empty] = 0.0
+    rows[empty, 0] = -np.inf
+    u = rows.view(np.uint32)
+    w = np.zeros((rows.shape[0], 65, 4), np.uint32)
+    w[:, :, 1] = epoch
+    w[:, :, 3] = epoch
+    w[:, 0, 0], w[:, 0, 2] = u[:, 0], u[:, 1]
+    acc = u[:, 2:].reshape(rows.shape[0], 64, 2)
+    w[:, 1:, 0], w[:, 1:, 2] = acc[:, :, 0], acc[:, :, 1]
+    return w
+
+
+def test_peer_exchange_on_one_gpu(nv, ob):
+    """nova_lse_merge_peers: every rank stores its partial rows into the peers' exchange buffers, waits until the
+    peers' rows have arrived in its own, and merges in rank order.  Here the 'ranks' are four buffers of this one GPU
+    and run one after the other (kernels that wait on one another never share a GPU): rank r finds the rows of the
+    ranks before it where THEIR kernels stored them, and the rows of the ranks after it where the test put them
+    beforehand.  Same result as nova_lse_combine on the stacked rows and as the oracle's merge for every rank, over
+    two epochs (both slots); what each rank stored is checked word for word.  Then the bounded wait: rows that never
+    arrive -> NOVA_ERR_TIMEOUT in the status word, output left alone."""
     rng = np.random.default_rng(31)
     n_ranks, n_rows = 4, 56
     slot_bytes = int(nv.lib.nova_peer_slot_bytes(n_rows))
-    assert slot_bytes % 128 == 0 and slot_bytes >= 128 + n_rows * 130 * 4
+    region = slot_bytes // 8
+    assert slot_bytes % 128 == 0 and region >= n_rows * 65 * 16
     bufs = [nv.DevBuf(2 * slot_bytes).zero() for _ in range(n_ranks)]
     base = (C.c_void_p * n_ranks)(*[b.ptr for b in bufs])
     status = nv.DevBuf(4).zero()
@@ -493,9 +513,6 @@ def test_peer_merge_on_one_gpu(nv, ob):
         parts[2, 5, 1] = 0.0                     # a rank whose page range held no key of that row
         parts[2, 5, 0] = -np.inf
         parts[:, 9, 1] = 0.0                     # a row nobody attended
-        for r in range(n_ranks):
-            bufs[r].upload(parts[r], offset=slot * slot_bytes + 128)
-            bufs[r].upload(np.array([epoch], np.int64), offset=slot * slot_bytes)
         stacked = nv.to_device(parts)
         ref = nv.DevBuf(n_rows * 128 * 4)
         nv.check(nv.lib.nova_lse_combine(stacked.ptr, n_ranks, n_rows, 128, ref.ptr, None))
@@ -503,23 +520,104 @@ def test_peer_merge_on_one_gpu(nv, ob):
         want = ref.download(np.float32)
         assert rel_l2(ob.lse_combine(parts).ravel(), want) < 1e-5
         for me in range(n_ranks):
+            for later in range(me + 1, n_ranks):          # ranks that have not run yet: their rows, as they would arrive
+                bufs[me].upload(ll_encode(parts[later], epoch), offset=slot * slot_bytes + later * region)
+            mine = nv.to_device(parts[me])
             out.zero()
-            nv.check(nv.lib.nova_lse_merge_peers(base, n_ranks, me, slot_bytes, slot, n_rows, epoch, 200, out.ptr, status.ptr, None))
+            nv.check(nv.lib.nova_lse_merge_peers(mine.ptr, base, n_ranks, me, slot_bytes, slot, n_rows, epoch, 200, out.ptr,
+                                                 status.ptr, None))
             nv.check(nv.lib.dev_sync())
-            assert np.array_equal(bits(out.download(np.float32)), bits(want)), (epoch, me)
             assert int(status.download(np.int32)[0]) == 0
-    # epoch 3 uses slot 1 again; rank 3 never publishes it
-    for r in range(3):
-        bufs[r].upload(np.array([3], np.int64), offset=slot_bytes)
+            got = out.download(np.float32)
+            assert rel_l2(got, want) < 1e-6 and np.abs(got - want).max() < 1e-6, (epoch, me)
+            assert not got.reshape(n_rows, 128)[9].any()
+            sent = ll_encode(parts[me], epoch)
+            for peer in range(n_ranks):
+                if peer != me:
+                    landed = bufs[peer].download(np.uint32, sent.size, slot * slot_bytes + me * region).reshape(sent.shape)
+                    assert np.array_equal(landed, sent), (epoch, me, peer)
+    # rows that never arrive: epoch 3 goes to slot 1, which still holds epoch 1
     out.upload(np.full(n_rows * 128, 7.0, np.float32))
-    nv.check(nv.lib.nova_lse_merge_peers(base, n_ranks, 0, slot_bytes, 1, n_rows, 3, 50, out.ptr, status.ptr, None))
+    mine = nv.to_device(parts[0])
+    nv.check(nv.lib.nova_lse_merge_peers(mine.ptr, base, n_ranks, 0, slot_bytes, 1, n_rows, 3, 50, out.ptr, status.ptr, None))
     nv.check(nv.lib.dev_sync())
     assert int(status.download(np.int32)[0]) == nv.ERR_TIMEOUT
     assert (out.download(np.float32) == 7.0).all()
-    assert nv.lib.nova_lse_merge_peers(base, 9, 0, slot_bytes, 0, n_rows, 1, 50, out.ptr, None, None) == nv.ERR_INVALID
-    assert nv.lib.nova_lse_merge_peers(base, n_ranks, 0, slot_bytes - 128, 0, n_rows, 1, 50, out.ptr, None, None) == nv.ERR_INVALID
+    assert nv.lib.nova_lse_merge_peers(mine.ptr, base, 9, 0, slot_bytes, 0, n_rows, 1, 50, out.ptr, None, None) == nv.ERR_INVALID
+    assert nv.lib.nova_lse_merge_peers(mine.ptr, base, n_ranks, 0, slot_bytes - 128, 0, n_rows, 1, 50, out.ptr, None, None) == nv.ERR_INVALID
     for b in bufs + [status, out]:
         b.free()
+
+
+@pytest.mark.parametrize("me", [1, 0])
+@pytest.mark.parametrize("kernel,pdl", [(1, 0), (2, 1), (0, 0)])
+def test_step_partial_peers_two_ranks_on_one_gpu(nv, ob, kernel, pdl, me):
+    """nova_batch_step_partial_peers as one of two ranks, the other one played by the oracle: its partial rows of
+    every layer (over its own page range) are placed in this rank's exchange buffer as they would arrive over
+    NVLink.  me = 1: this rank owns the pages from `cut` on (the page that receives the new token included);
+    me = 0: it owns pages [0, cut), one session lies wholly inside (no page on the other rank), the new tokens of
+    the longer sessions belong to the other rank and are not written here.  The merged outputs must be the oracle's
+    whole decode step; what this rank stored into the peer's buffer must be its own partial rows."""
+    ctx_lens = [1200, 90, 40]
+    cut = 2 if me == 1 else 3                     # 41 keys = pages 0..2
+    lo, hi = (cut, 1 << 40) if me == 1 else (0, cut)
+    olo, ohi = (0, cut) if me == 1 else (cut, 1 << 40)
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, "qwen25_7b", nv.KV_F16, ctx_lens, L=3, seed=43)
+    L, S, NH, NKV = eng.L, len(ss), eng.NH, eng.NKV
+    tables = np.stack([eng.pool.table(eng.session_slice(s)) for s in ss])
+    batch = eng.batch(ss)
+    try_set_kernel(nv, batch, kernel)
+    batch.set_pdl(pdl)
+    rows = S * NH
+    slot_bytes = int(nv.lib.nova_peer_slot_bytes(rows))
+    region = slot_bytes // 8
+    n_slots = 4                                   # one slot per layer of a step, so that all can be filled beforehand
+    mine, peer = nv.DevBuf(n_slots * slot_bytes).zero(), nv.DevBuf(n_slots * slot_bytes).zero()
+    base = (C.c_void_p * 2)(*([peer.ptr, mine.ptr] if me == 1 else [mine.ptr, peer.ptr]))
+    status = nv.DevBuf(4).zero()
+    st = nv.Stream()
+    pos = list(ctx_lens)
+    dout = nv.DevBuf(L * rows * 128 * 4)
+    epoch0 = 1
+    for step in range(2):
+        q = rng.standard_normal((L, S, NH, 128)).astype(np.float32)
+        k = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        v = rng.standard_normal((L, S, NKV, 128)).astype(np.float32)
+        dq, dk, dv = nv.to_device(q), nv.to_device(k), nv.to_device(v)
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)       # rotates q, k; appends
+        for layer in range(L):                    # the other rank's rows of this step, layer by layer
+            other = np.stack([ob.attn_partial(sh, q[layer, i], pk, pv, tables[i], layer, eng.nb, pos[i] + 1, olo, ohi)
+                              for i in range(S)]).reshape(rows, 130)
+            epoch = epoch0 + layer
+            mine.upload(ll_encode(other, epoch), offset=(epoch % n_slots) * slot_bytes + (1 - me) * region)
+        nv.check(nv.lib.nova_batch_step_partial_peers(batch.h, dq.ptr, dk.ptr, dv.ptr, lo, hi, base, 2, me, slot_bytes,
+                                                      n_slots, epoch0, 500, dout.ptr, status.ptr, st.h))
+        st.sync()
+        assert batch.device_status() == 0 and int(status.download(np.int32)[0]) == 0
+        got = dout.download(np.float32).reshape(want.shape)
+        assert_attn_close(got, want, f"step {step}")
+        for layer in range(L):                    # what crossed to the peer: this rank's partial rows over its own pages
+            epoch = epoch0 + layer
+            landed = peer.download(np.uint32, rows * 65 * 4, (epoch % n_slots) * slot_bytes + me * region).reshape(rows, 65, 4)
+            assert (landed[:, :, 1] == epoch).all() and (landed[:, :, 3] == epoch).all()
+            sent = np.empty((rows, 130), np.float32)
+            sent[:, 0], sent[:, 1] = landed[:, 0, 0].view(np.float32), landed[:, 0, 2].view(np.float32)
+            sent[:, 2:] = np.stack([landed[:, 1:, 0], landed[:, 1:, 2]], axis=-1).reshape(rows, 128).view(np.float32)
+            for i in range(S):
+                wp = ob.attn_partial(sh, q[layer, i], pk, pv, tables[i], layer, eng.nb, pos[i] + 1, lo, hi)
+                sp = sent.reshape(S, NH, 130)[i]
+                if wp[0, 1] == 0:
+                    assert not (sp[:, 1] > 0).any()
+                else:
+                    assert_attn_close(sp[:, 2:] / sp[:, 1:2], wp[:, 2:] / wp[:, 1:2], f"sent rows layer {layer} session {i}")
+        pos = [p + 1 for p in pos]
+        epoch0 += L
+    if me == 1:                                   # the last rank wrote every new token
+        gk, gv = eng.read_pools()
+        assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    st.close()
+    batch.close()
+    eng.close()
 
 
 @pytest.mark.parametrize("kernel,pdl", [(0, 0), (1, 0), (2, 0), (2, 1)])
