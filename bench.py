@@ -264,34 +264,6 @@ def run_ours(args):
                               "cascade_pages": batch.shared_prefix_pages() if cascade else 0, "kv": args.kv, "kernel": kernel,
                               "ms_per_step": ms_main / K, "kv_gbs": kv_main / ms_main / 1e6, "gpu_launches": launches}))
         return
-    # end to end through the host-buffer call: pinned host q/k/v in, out back, every step
-    hq, hk, hv = nv.lib.dev_host_alloc(nq * 4), nv.lib.dev_host_alloc(nk * 4), nv.lib.dev_host_alloc(nk * 4)
-    ho = nv.lib.dev_host_alloc(nq * 4)
-    nv.check(nv.lib.dev_download(hq, inp.dq.ptr, nq * 4))
-    nv.check(nv.lib.dev_download(hk, inp.dk.ptr, nk * 4))
-    nv.check(nv.lib.dev_download(hv, inp.dv.ptr, nk * 4))
-    for _ in range(W):
-        batch.decode_step_host(hq, hk, hv, ho, 1 if mode else 0, stream.h)
-    cx.barrier()
-    e0, e1 = nv.Event(), nv.Event()
-    e0.record(stream)
-    t0 = time.perf_counter()
-    for _ in range(KE):
-        batch.decode_step_host(hq, hk, hv, ho, 1 if mode else 0, stream.h)
-    e1.record(stream)
-    e1.sync()
-    ms_e2e = max(e0.elapsed_ms(e1), (time.perf_counter() - t0) * 1e3)
-    cx.barrier()
-    # the same K steps again with an event pair around every attention launch: the dominant kernel's own time
-    ms_evt, attn_ms, kv_evt = timed_steps(cx, work, inp, stream, 1 if mode == 2 else mode, K, W, time_attn=True)
-    # the other launch modes
-    other = {}
-    for name, m in (("fused", 0), ("layer", 1), ("graph", 2)):
-        if m != mode:
-            ms_o, _, kv_o = timed_steps(cx, work, inp, stream, m, K, W)
-            other[name] = dict(ms_per_step=ms_o / K, kv_gbs=kv_o / ms_o / 1e6)
-    # all layers in one launch (the isolated path; legal because layer inputs are independent here)
-    ms_f, attn_f, kv_f = timed_steps(cx, work, inp, stream, 0, K, W, time_attn=True)
     # per-layer launches whose q / new k / new v are read only after the previous layer's kernels have finished
     # (what an engine needs: layer l+1's inputs come out of the matrix products that consume layer l's output);
     # tables, positions and the first ring of page copies still start early
@@ -306,14 +278,49 @@ def run_ours(args):
         ms_strict, _, kv_strict = timed_steps(cx, work, inp, stream, 1, K, W)
         batch.set_pdl(2 if late_main else 1)
 
+    # end to end through the host-buffer call: pinned host q/k/v in, out back, every step.  Steps are queued (the call
+    # does not synchronise per step; two host output buffers are used in turn) and the clock stops when the last
+    # step's output has arrived.
+    hq, hk, hv = nv.lib.dev_host_alloc(nq * 4), nv.lib.dev_host_alloc(nk * 4), nv.lib.dev_host_alloc(nk * 4)
+    ho, ho2 = nv.lib.dev_host_alloc(nq * 4), nv.lib.dev_host_alloc(nq * 4)
+    nv.check(nv.lib.dev_download(hq, inp.dq.ptr, nq * 4))
+    nv.check(nv.lib.dev_download(hk, inp.dk.ptr, nk * 4))
+    nv.check(nv.lib.dev_download(hv, inp.dv.ptr, nk * 4))
+
+    def e2e_steps(n, no_sync):
+        for i in range(n):
+            batch.decode_step_host(hq, hk, hv, ho if i % 2 == 0 else ho2, 1 if mode else 0, stream.h, no_sync=no_sync)
+        batch.host_wait(stream.h)
+    e2e_steps(W, True)
+    cx.barrier()
+    t0 = time.perf_counter()
+    e2e_steps(KE, True)
+    ms_e2e = (time.perf_counter() - t0) * 1e3
+    cx.barrier()
+    # the same with a synchronisation after every step (the caller reads each result before it issues the next step)
+    e2e_steps(W, False)
+    t0 = time.perf_counter()
+    e2e_steps(KE, False)
+    ms_e2e_sync = (time.perf_counter() - t0) * 1e3
+    cx.barrier()
+    # the same K steps again with an event pair around every attention launch: the dominant kernel's own time
+    ms_evt, attn_ms, kv_evt = timed_steps(cx, work, inp, stream, 1 if mode == 2 else mode, K, W, time_attn=True)
+    # the other launch modes
+    other = {}
+    for name, m in (("fused", 0), ("layer", 1), ("graph", 2)):
+        if m != mode:
+            ms_o, _, kv_o = timed_steps(cx, work, inp, stream, m, K, W)
+            other[name] = dict(ms_per_step=ms_o / K, kv_gbs=kv_o / ms_o / 1e6)
+    # all layers in one launch (the isolated path; legal because layer inputs are independent here)
+    ms_f, attn_f, kv_f = timed_steps(cx, work, inp, stream, 0, K, W, time_attn=True)
     cx.barrier()
     clocks = sampler.stop() if sampler else None
     status = batch.device_status()
     if status != 0:
         raise RuntimeError(f"device status {status} after the timed regions")
 
-    ms_main, ms_e2e, ms_evt, attn_ms, ms_f, attn_f, ms_late_r, ms_strict_r = cx.reduce(
-        [ms_main, ms_e2e, ms_evt, attn_ms, ms_f, attn_f, ms_late or 0.0, ms_strict or 0.0], "max")
+    ms_main, ms_e2e, ms_evt, attn_ms, ms_f, attn_f, ms_late_r, ms_strict_r, ms_e2e_sync = cx.reduce(
+        [ms_main, ms_e2e, ms_evt, attn_ms, ms_f, attn_f, ms_late or 0.0, ms_strict or 0.0, ms_e2e_sync], "max")
     kv_main_all, kv_evt_all, kv_f_all = cx.reduce([kv_main, kv_evt, kv_f], "sum")
 
     cpu = None
@@ -373,7 +380,9 @@ def run_ours(args):
                                                    "launch_us": attn_f / K * 1e3}},
             "other_launch_modes": other,
             "e2e": {"value": world * S * KE / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": (nq + 2 * nk) * 4,
-                    "d2h_bytes_per_step": nq * 4, "ms_per_step": ms_e2e / KE, "steps": KE},
+                    "d2h_bytes_per_step": nq * 4, "ms_per_step": ms_e2e / KE, "steps": KE,
+                    "timing": "host wall clock from the first call to the arrival of the last step's output; steps queued",
+                    "synchronised_every_step": {"value": world * S * KE / (ms_e2e_sync / 1e3), "ms_per_step": ms_e2e_sync / KE}},
             "gpu_launches": launches,
             "clocks": clocks,
             "cpu_baseline": cpu,
@@ -384,7 +393,7 @@ def run_ours(args):
 
     # configurations 4 and 5 in the same process group, after the headline's pools are gone
     inp.free()
-    for p in (hq, hk, hv, ho):
+    for p in (hq, hk, hv, ho, ho2):
         nv.lib.dev_host_free(p)
     work.close()
     if args.workload == "c2" and not args.no_scaling_workloads:

@@ -112,6 +112,7 @@ SIGNATURES = {
     "nova_batch_size": (i32, [vp]), "nova_batch_sync_positions": (i32, [vp, vp]),
     "nova_batch_set_timeline": (i32, [vp, vp]),
     "nova_batch_set_pdl": (i32, [vp, i32]), "nova_batch_set_row_setup_pages": (i32, [vp, i32]),
+    "nova_batch_set_split_ctas": (i32, [vp, i32]),
     "nova_batch_set_fused_append": (i32, [vp, i32]), "nova_batch_append_attn": (i32, [vp, i32, vp, vp, vp, vp, vp]),
     "nova_batch_set_kernel": (i32, [vp, i32]), "nova_batch_get_kernel": (i32, [vp]),
     "nova_batch_cow": (i32, [vp, vp]), "nova_batch_append": (i32, [vp, i32, vp, vp, vp, vp]),
@@ -120,7 +121,7 @@ SIGNATURES = {
     "nova_batch_prefill_max_tokens": (i32, [vp]), "nova_batch_advance_by": (i32, [vp, i32, vp]),
     "nova_batch_prefill": (i32, [vp, i32, i32, vp, vp, vp, vp, vp]),
     "nova_batch_step_all_layers": (i32, [vp, vp, vp, vp, vp, vp]),
-    "nova_batch_decode_step_host": (i32, [vp, vp, vp, vp, vp, i32, vp]),
+    "nova_batch_decode_step_host": (i32, [vp, vp, vp, vp, vp, i32, vp]), "nova_batch_host_wait": (i32, [vp, vp]),
     "nova_batch_run_steps": (i32, [vp, i32, vp, vp, vp, vp, sz, sz, i32, C.POINTER(C.c_float), vp]),
     "nova_batch_device_status": (i32, [vp]), "nova_launch_count": (u64, []),
     "nova_batch_attn_partial": (i32, [vp, i32, vp, i64, i64, vp, vp]),
@@ -473,6 +474,7 @@ class Batch:
     def set_kernel(self, which): return check(lib.nova_batch_set_kernel(self.h, which), "set_kernel")
     def set_fused_append(self, on): return check(lib.nova_batch_set_fused_append(self.h, int(on)), "set_fused_append")
     def set_pdl(self, on): return check(lib.nova_batch_set_pdl(self.h, int(on)), "set_pdl")
+    def set_split_ctas(self, n): return check(lib.nova_batch_set_split_ctas(self.h, int(n)), "set_split_ctas")
     def set_row_setup_pages(self, n): return check(lib.nova_batch_set_row_setup_pages(self.h, int(n)), "set_row_setup")
     def append_attn(self, layer, q, k, v, out, stream=None):
         return check(lib.nova_batch_append_attn(self.h, layer, q, k, v, out, stream), "append_attn")
@@ -495,8 +497,10 @@ class Batch:
         return check(lib.nova_batch_prefill(self.h, layer, n_tokens, q, k, v, out, stream), "batch_prefill")
     def step_all_layers(self, q, k, v, out, stream=None):
         return check(lib.nova_batch_step_all_layers(self.h, q, k, v, out, stream), "step_all_layers")
-    def decode_step_host(self, q, k, v, out, per_layer=1, stream=None):
-        return check(lib.nova_batch_decode_step_host(self.h, q, k, v, out, per_layer, stream), "decode_step_host")
+    def decode_step_host(self, q, k, v, out, per_layer=1, stream=None, no_sync=False):
+        return check(lib.nova_batch_decode_step_host(self.h, q, k, v, out, (1 if per_layer else 0) | (2 if no_sync else 0), stream),
+                     "decode_step_host")
+    def host_wait(self, stream=None): return check(lib.nova_batch_host_wait(self.h, stream), "host_wait")
     def run_steps(self, n_steps, q, k, v, out, q_stride, kv_stride, mode, stream=None, time_attn=False):
         """Returns the summed attention-kernel time in ms when time_attn, else None."""
         ms = C.c_float(0.0)

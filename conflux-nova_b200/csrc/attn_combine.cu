@@ -22,6 +22,73 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+__device__ __forceinline__ float2 ld_cg_f2(const float* p) {
+    float2 v;
+    asm volatile("ld.global.cg.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_cg_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Folds up to 32 contributors' partial rows (slot layout: m, l, 2 pad, acc[128]; `stride` floats apart) into the
+// running (M, L, acc) of a warp; lane i owns dims 4i..4i+3.  ONE memory round trip (about a microsecond here while
+// a next layer streams): the (m, l) pair of contributor `lane` and the accumulators of all contributors are loaded
+// before anything is used.  The loads are volatile asm so that they stay together in program order; kBlock of them
+// are in flight per lane (16: 64 registers; a second block follows only when there are more contributors).
+__device__ __forceinline__ void fold_contributors(const float* __restrict__ src, size_t stride, int cnt, int lane, float& M,
+                                                  float& L, float4& acc) {
+    constexpr int kBlock = 16;
+    float2 ml = make_float2(-INFINITY, 0.f);
+    if (lane < cnt) ml = ld_cg_f2(src + (size_t)lane * stride);
+    float4 x[kBlock], y[kBlock];
+#pragma unroll
+    for (int i = 0; i < kBlock; ++i) {
+        x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < cnt) x[i] = ld_cg_f4(src + (size_t)i * stride + 4 + 4 * lane);
+    }
+    const bool more = cnt > kBlock;           // warp-uniform
+    if (more) {
+#pragma unroll
+        for (int i = 0; i < kBlock; ++i) {
+            y[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (kBlock + i < cnt) y[i] = ld_cg_f4(src + (size_t)(kBlock + i) * stride + 4 + 4 * lane);
+        }
+    }
+    const float mc = warp_max(ml.y > 0.f ? ml.x : -INFINITY);
+    const float Mn = fmaxf(M, mc);
+    if (Mn == -INFINITY) return;                       // nothing attended in this chunk or before
+    const float corr = __expf(M - Mn);                 // 0 on the first chunk (M = -inf)
+    const float w = ml.y > 0.f ? __expf(ml.x - Mn) : 0.f;
+    L = fmaf(L, corr, warp_sum(ml.y * w));
+    acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+#pragma unroll
+    for (int i = 0; i < kBlock; ++i) {
+        const float wi = __shfl_sync(0xffffffffu, w, i);
+        if (wi != 0.f) {                               // a slot with l == 0 carries no accumulator (and may hold anything)
+            acc.x = fmaf(x[i].x, wi, acc.x);
+            acc.y = fmaf(x[i].y, wi, acc.y);
+            acc.z = fmaf(x[i].z, wi, acc.z);
+            acc.w = fmaf(x[i].w, wi, acc.w);
+        }
+    }
+    if (more) {
+#pragma unroll
+        for (int i = 0; i < kBlock; ++i) {
+            const float wi = __shfl_sync(0xffffffffu, w, kBlock + i);
+            if (wi != 0.f) {
+                acc.x = fmaf(y[i].x, wi, acc.x);
+                acc.y = fmaf(y[i].y, wi, acc.y);
+                acc.z = fmaf(y[i].z, wi, acc.z);
+                acc.w = fmaf(y[i].w, wi, acc.w);
+            }
+        }
+    }
+    M = Mn;
+}
+
 // Three warps per CTA, not four: the split kernel's CTAs have five warps of ~250 registers, so one of
 // the SM's four register-file partitions holds two of them and has no room for a merge warp.  A
 // three-warp CTA fits into the other three partitions and can sit on an SM next to a running split
@@ -116,36 +183,8 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
                 acc = make_float4(y0.x, y0.y, y1.x, y1.y);
             }
         }
-        for (int c0 = kCoop ? 32 * warp : 0; c0 < ((kFold && n == 1) ? 0 : n); c0 += kCoop ? 32 * kCombineWarps : 32) {
-            const int cnt = n - c0 < 32 ? n - c0 : 32;
-            const float* src = base + (size_t)c0 * stride_c;
-            float2 ml = make_float2(-INFINITY, 0.f);
-            if (lane < cnt) ml = __ldcg(reinterpret_cast<const float2*>(src + (size_t)lane * stride_c));
-            float4 x[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i < cnt) x[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * stride_c + 4 + 4 * lane));
-            }
-            const float mc = warp_max(ml.y > 0.f ? ml.x : -INFINITY);
-            const float Mn = fmaxf(M, mc);
-            if (Mn == -INFINITY) continue;                       // nothing attended in this chunk or before
-            const float corr = __expf(M - Mn);                   // 0 on the first chunk (M = -inf)
-            const float w = ml.y > 0.f ? __expf(ml.x - Mn) : 0.f;
-            L = fmaf(L, corr, warp_sum(ml.y * w));
-            acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float wi = __shfl_sync(0xffffffffu, w, i);
-                if (wi != 0.f) {     // a slot with l == 0 carries no accumulator (and may hold anything)
-                    acc.x = fmaf(x[i].x, wi, acc.x);
-                    acc.y = fmaf(x[i].y, wi, acc.y);
-                    acc.z = fmaf(x[i].z, wi, acc.z);
-                    acc.w = fmaf(x[i].w, wi, acc.w);
-                }
-            }
-            M = Mn;
-        }
+        for (int c0 = kCoop ? 32 * warp : 0; c0 < ((kFold && n == 1) ? 0 : n); c0 += kCoop ? 32 * kCombineWarps : 32)
+            fold_contributors(base + (size_t)c0 * stride_c, stride_c, n - c0 < 32 ? n - c0 : 32, lane, M, L, acc);
         if constexpr (kCoop) {       // the warps' shares of the row meet here; warp 0 finishes the row
             if (lane == 0) { s_ml[2 * warp] = M; s_ml[2 * warp + 1] = L; }
             s_acc[warp * 32 + lane] = acc;
@@ -330,7 +369,7 @@ __device__ __forceinline__ uint4 ll_load(const void* p) {
 // One warp: sends its row (M, L, acc: lane i holds dims 4i..4i+3) to every peer, receives the peers' rows and
 // merges all of them in rank order.  Returns false (and sets *status) when a peer's row did not arrive in time;
 // then `acc` is left alone.  All 32 lanes must call it.
-__device__ inline bool exchange_and_merge(const PeerSlots& ps, size_t region_bytes, int n_ranks, int my_rank, int row,
+__device__ __forceinline__ bool exchange_and_merge(const PeerSlots& ps, const unsigned char* mine, size_t region_bytes, int n_ranks, int my_rank, int row,
                                           uint32_t epoch, unsigned long long timeout_ns, int32_t* status, float& M, float& L,
                                           float4& acc) {
     const int lane = (int)threadIdx.x & 31;
@@ -358,30 +397,34 @@ __device__ inline bool exchange_and_merge(const PeerSlots& ps, size_t region_byt
     }
     unsigned long long t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-    const unsigned char* mine = ps.base[my_rank];
     bool failed = false;
     while (__any_sync(0xffffffffu, pending != 0)) {
-        uint4 w0[kMaxPeerRanks], w1[kMaxPeerRanks], w2[kMaxPeerRanks];
 #pragma unroll
-        for (int p = 0; p < kMaxPeerRanks; ++p) {          // all loads first, then the checks
-            if (pending & (1u << p)) {
-                const unsigned char* src = mine + (size_t)p * region_bytes + row_off;
-                w0[p] = ll_load(src);                       // every lane needs (m, l)
-                w1[p] = ll_load(src + 16 * (1 + 2 * lane));
-                w2[p] = ll_load(src + 16 * (2 + 2 * lane));
+        for (int half = 0; half < kMaxPeerRanks; half += 4) {      // four peers at a time: all their loads first, then the checks
+            uint4 w0[4], w1[4], w2[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int p = half + j;
+                if (pending & (1u << p)) {
+                    const unsigned char* src = mine + (size_t)p * region_bytes + row_off;
+                    w0[j] = ll_load(src);                       // every lane needs (m, l)
+                    w1[j] = ll_load(src + 16 * (1 + 2 * lane));
+                    w2[j] = ll_load(src + 16 * (2 + 2 * lane));
+                }
             }
-        }
 #pragma unroll
-        for (int p = 0; p < kMaxPeerRanks; ++p) {
-            if (pending & (1u << p)) {
-                const bool ok = w0[p].y == epoch && w0[p].w == epoch && w1[p].y == epoch && w1[p].w == epoch &&
-                                w2[p].y == epoch && w2[p].w == epoch;
-                if (ok) {
-                    pm[p] = __uint_as_float(w0[p].x);
-                    pl[p] = __uint_as_float(w0[p].z);
-                    pa[p] = make_float4(__uint_as_float(w1[p].x), __uint_as_float(w1[p].z), __uint_as_float(w2[p].x),
-                                        __uint_as_float(w2[p].z));
-                    pending &= ~(1u << p);
+            for (int j = 0; j < 4; ++j) {
+                const int p = half + j;
+                if (pending & (1u << p)) {
+                    const bool ok = w0[j].y == epoch && w0[j].w == epoch && w1[j].y == epoch && w1[j].w == epoch &&
+                                    w2[j].y == epoch && w2[j].w == epoch;
+                    if (ok) {
+                        pm[p] = __uint_as_float(w0[j].x);
+                        pl[p] = __uint_as_float(w0[j].z);
+                        pa[p] = make_float4(__uint_as_float(w1[j].x), __uint_as_float(w1[j].z), __uint_as_float(w2[j].x),
+                                            __uint_as_float(w2[j].z));
+                        pending &= ~(1u << p);
+                    }
                 }
             }
         }
@@ -431,7 +474,7 @@ __device__ inline bool exchange_and_merge(const PeerSlots& ps, size_t region_byt
 // The exchange on its own, for partial rows that are already in memory (part [n_rows][130], written by the
 // kernels before this one in the stream): one warp per row.  A one-warp CTA finds room on an SM next to a
 // running attention CTA; a larger one would keep a next layer's CTAs off the SMs it takes.
-__global__ void __launch_bounds__(32) lse_exchange_kernel(const float* __restrict__ part, PeerSlots ps, size_t region_bytes,
+__global__ void __launch_bounds__(32) lse_exchange_kernel(const float* __restrict__ part, PeerSlots ps, const unsigned char* mine, size_t region_bytes,
                                                           int n_ranks, int my_rank, int n_rows, uint32_t epoch,
                                                           unsigned long long timeout_ns, float* __restrict__ out,
                                                           int32_t* status) {
@@ -451,7 +494,7 @@ __global__ void __launch_bounds__(32) lse_exchange_kernel(const float* __restric
         L = 0.f;
         acc = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    if (!exchange_and_merge(ps, region_bytes, n_ranks, my_rank, row, epoch, timeout_ns, status, M, L, acc)) return;
+    if (!exchange_and_merge(ps, mine, region_bytes, n_ranks, my_rank, row, epoch, timeout_ns, status, M, L, acc)) return;
     const float inv = L > 0.f ? 1.f / L : 0.f;
     *reinterpret_cast<float4*>(out + (size_t)row * kHeadDim + 4 * lane) =
         make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
@@ -462,7 +505,7 @@ __global__ void __launch_bounds__(32) lse_exchange_kernel(const float* __restric
 // finished row to the peers, receives theirs and writes the output.  The split kernel ran with
 // write_partial_only: rows that a single CTA covered (or that have no page on this rank) are in a.out_part.
 __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_exchange_kernel(AttnLaunch a, int n_ctas_split, PeerSlots ps,
-                                                                                   size_t region_bytes, int n_ranks, int my_rank,
+                                                                                   const unsigned char* mine, size_t region_bytes, int n_ranks, int my_rank,
                                                                                    uint32_t epoch, unsigned long long timeout_ns,
                                                                                    int32_t* xstatus) {
     __shared__ int s_prefix[kMaxRowsSmem + 1];
@@ -470,6 +513,17 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_exchange_kern
     __shared__ float4 s_acc[kCombineWarps * 32];
     const int lane = (int)threadIdx.x & 31;
     const int warp = (int)threadIdx.x >> 5;
+#ifdef NOVA_TIMELINE
+    unsigned long long* tl = (a.timeline && blockIdx.x < kTimelineCtas) ? a.timeline + kTimelineCtas * 8 + (size_t)blockIdx.x * 4 : nullptr;
+#else
+    constexpr unsigned long long* tl = nullptr;
+#endif
+    if (tl && threadIdx.x == 0) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[0]));
+        tl[2] = smid;
+    }
     pdl_launch_dependents();
     const int KVG = a.kv_group;
     const int G = a.n_heads / a.n_kv_heads;
@@ -486,6 +540,7 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_exchange_kern
     pv.n_ctas = pv.pages_total < (int64_t)n_ctas_split ? (int)pv.pages_total : n_ctas_split;
     plan_finish(pv);
     pdl_wait();                                   // the split kernel's partials are complete from here on
+    if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[1]));
 
     const int64_t units = (int64_t)pv.rows_per_layer * a.n_layers * heads_per_row;
     const size_t stride_c = (size_t)heads_per_row * kSlotW;
@@ -520,36 +575,8 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_exchange_kern
             }
         } else {
             const float* base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
-            for (int c0 = 32 * warp; c0 < n; c0 += 32 * kCombineWarps) {
-                const int cnt = n - c0 < 32 ? n - c0 : 32;
-                const float* src = base + (size_t)c0 * stride_c;
-                float2 ml = make_float2(-INFINITY, 0.f);
-                if (lane < cnt) ml = __ldcg(reinterpret_cast<const float2*>(src + (size_t)lane * stride_c));
-                float4 x[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (i < cnt) x[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * stride_c + 4 + 4 * lane));
-                }
-                const float mc = warp_max(ml.y > 0.f ? ml.x : -INFINITY);
-                const float Mn = fmaxf(M, mc);
-                if (Mn == -INFINITY) continue;
-                const float corr = __expf(M - Mn);
-                const float w = ml.y > 0.f ? __expf(ml.x - Mn) : 0.f;
-                L = fmaf(L, corr, warp_sum(ml.y * w));
-                acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float wi = __shfl_sync(0xffffffffu, w, i);
-                    if (wi != 0.f) {
-                        acc.x = fmaf(x[i].x, wi, acc.x);
-                        acc.y = fmaf(x[i].y, wi, acc.y);
-                        acc.z = fmaf(x[i].z, wi, acc.z);
-                        acc.w = fmaf(x[i].w, wi, acc.w);
-                    }
-                }
-                M = Mn;
-            }
+            for (int c0 = 32 * warp; c0 < n; c0 += 32 * kCombineWarps)
+                fold_contributors(base + (size_t)c0 * stride_c, stride_c, n - c0 < 32 ? n - c0 : 32, lane, M, L, acc);
             if (lane == 0) { s_ml[2 * warp] = M; s_ml[2 * warp + 1] = L; }
             s_acc[warp * 32 + lane] = acc;
             __syncthreads();
@@ -578,10 +605,11 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_exchange_kern
             __syncthreads();
         }
         if (warp != 0) continue;
-        if (!exchange_and_merge(ps, region_bytes, n_ranks, my_rank, (int)head, epoch, timeout_ns, xstatus, M, L, acc)) continue;
+        if (!exchange_and_merge(ps, mine, region_bytes, n_ranks, my_rank, (int)head, epoch, timeout_ns, xstatus, M, L, acc)) continue;
         const float inv = L > 0.f ? 1.f / L : 0.f;
         *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =
             make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[3]));
     }
 }
 
@@ -649,7 +677,7 @@ int launch_lse_exchange(const float* part, void* const* slot_base, int n_ranks, 
     PeerSlots ps;
     fill_slots(ps, slot_base, n_ranks);
     const cudaError_t le = launch_kernel_pdl(lse_exchange_kernel, dim3((unsigned)n_rows), dim3(32), 0, s, true, part, ps,
-                                             peer_region_bytes(n_rows), n_ranks, my_rank, n_rows, (uint32_t)epoch, timeout_ns, out,
+                                             static_cast<const unsigned char*>(slot_base[my_rank]), peer_region_bytes(n_rows), n_ranks, my_rank, n_rows, (uint32_t)epoch, timeout_ns, out,
                                              status);
     if (le != cudaSuccess) {
         set_cuda_error(le, "exchange launch");
@@ -672,7 +700,8 @@ int launch_attn_combine_exchange(const AttnLaunch& a, int n_ctas_split, void* co
     const int cap = 2 * sm_count();
     if (ctas > cap) ctas = cap;
     const cudaError_t le = launch_kernel_pdl(attn_combine_exchange_kernel, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true,
-                                             a, n_ctas_split, ps, peer_region_bytes(n_rows), n_ranks, my_rank, (uint32_t)epoch,
+                                             a, n_ctas_split, ps, static_cast<const unsigned char*>(slot_base[my_rank]),
+                                             peer_region_bytes(n_rows), n_ranks, my_rank, (uint32_t)epoch,
                                              timeout_ns, status);
     if (le != cudaSuccess) {
         set_cuda_error(le, "merge + exchange launch");

@@ -60,6 +60,7 @@ struct nova_batch {
     int pdl = 0;                     // 1: layers after the first of a step launch as programmatic dependents; 2: the same, but
                                      // they read their q / new k / new v only once the launches before them have finished
     int row_setup = 2;               // work-split weight of a row start, in pages (see AttnLaunch)
+    int split_ctas = 0;              // CTAs of a chained one-layer attention launch; 0: chosen from the work (pick_split_ctas)
     int cascade = 0;                 // 1: the shared leading pages of the batch's sessions are attended once for all
     int casc_pages = 0;              // shared leading pages found by the last nova_batch_cow (0: none worth it)
     float* xparts = nullptr;         // [S * NH][130] this rank's partial rows of one layer before they are exchanged
@@ -67,13 +68,16 @@ struct nova_batch {
     size_t casc_floats = 0;
     // staging for the host-buffer step and the graph replay
     float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
+    float *dq2 = nullptr, *dk2 = nullptr, *dv2 = nullptr, *dout2 = nullptr;   // second set: host-buffer steps alternate
+    unsigned host_seq = 0;             // host-buffer steps issued so far (set = host_seq & 1)
     cudaGraphExec_t graph = nullptr;   // one per-layer decode step on the staging buffers
     int graph_kernel = -1;
     unsigned long long* timeline = nullptr;   // caller-owned profiling buffer, see nova_batch_set_timeline
     mutable unsigned tl_seq = 0;              // attention launches since the buffer was set (ring of 4 records)
     std::vector<cudaEvent_t> ev;       // event pool for per-launch timing
     cudaStream_t s_in = nullptr, s_out = nullptr;      // copy streams of the host-buffer step
-    cudaEvent_t ev_in[4] = {}, ev_cmp[4] = {}, ev_out = nullptr, ev_begin = nullptr;
+    cudaEvent_t ev_in[4] = {}, ev_cmp[4] = {}, ev_out = nullptr;
+    cudaEvent_t ev_free[2] = {}, ev_dl[2] = {};      // per staging set: its inputs consumed / its outputs downloaded
 };
 
 namespace {
@@ -156,6 +160,8 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.timeline = b->timeline ? b->timeline + (size_t)(b->tl_seq++ % 4u) * (kTimelineCtas * 12) : nullptr;
 }
 
+int pick_split_ctas(const nova_batch* b, const AttnLaunch& a);
+
 // Split kernel, then the merge of the rows that more than one CTA worked on.
 int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
     int rc, ctas;
@@ -181,13 +187,13 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
         sa.out_part = b->casc_parts + (size_t)chunks * rows * kPartW;
         sa.extra_parts = b->casc_parts;          // the merge kernel folds the chunks in and writes the output
         sa.n_extra = chunks;
-        ctas = attn_split_ctas_mma(sa, 0);
+        ctas = pick_split_ctas(b, sa);
         rc = launch_attn_mma(sa, b->e->d.kv_dtype, ctas, s);
         if (rc != NOVA_OK) return rc;
         return launch_attn_combine(sa, ctas, s);
     }
     if (b->kernel == 1) {
-        ctas = attn_split_ctas_mma(a, 0);
+        ctas = pick_split_ctas(b, a);
         rc = launch_attn_mma(a, b->e->d.kv_dtype, ctas, s);
     } else {
         ctas = attn_split_ctas_simt(a, 0);
@@ -198,6 +204,33 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
 }
 
 bool use_fused(const nova_batch* b) { return b->fused && b->kernel == 1 && b->e->d.rope_neox; }
+
+// CTAs of one tensor-core attention launch.  A launch of a programmatic chain (one layer per launch) that has
+// little to stream - fewer than 16 pages per CTA, so that a CTA's start-up outweighs its streaming - takes only
+// half (or a third) of the SMs: consecutive layers then run side by side on different SMs, one starting up (positions, work
+// split, first table entries, first pages) while the other streams or waits for the launch before it.
+int pick_split_ctas(const nova_batch* b, const AttnLaunch& a) {
+    const int all = attn_split_ctas_mma(a, 0);
+    if (b->split_ctas > 0) return b->split_ctas < all ? b->split_ctas : all;
+    if (!(a.pdl && a.pdl_spare && a.n_layers == 1 && a.n_q <= 1)) return all;
+    const PagePool& pp = b->e->pool.p;
+    int64_t pages = 0;
+    for (int slice : b->slices) {
+        const SliceState* st = pp.find(slice);
+        if (!st) continue;
+        int64_t total = (st->n_past + 1 + kKvBlock - 1) >> kKvShift;
+        const int64_t lo = a.page_lo > 0 ? a.page_lo : 0;
+        const int64_t hi = (a.page_hi >= 0 && a.page_hi < total) ? a.page_hi : total;
+        if (hi > lo) pages += hi - lo;
+    }
+    pages *= a.n_kv_heads / a.kv_group;
+    const int per_sm = a.kv_group >= 4 ? 1 : 4 / a.kv_group;
+    const int half = (sm_count() / 2) * per_sm, third = (sm_count() / 3) * per_sm;
+    // measured on one 7B-shaped session (per layer): 1024 pages 8.7-9.4 us with 37-56 CTAs, 9.5 with 74, 11.8 with 136;
+    // 2048 pages 14.3 with 74 or 136; 4096 pages 24.5 with 74, 23.0 with 136
+    if (pages < (int64_t)all * 8) return third < all ? third : all;
+    return pages < (int64_t)all * 16 ? (half < all ? half : all) : all;
+}
 
 // RopeKvOp + AttnOp for layers [layer0, layer0 + n_layers) in one split launch (+ combine):
 // k rotated in place and appended with v, q read un-rotated and left as it is.
@@ -694,6 +727,10 @@ void nova_batch_destroy(nova_batch* b) {
     cudaFree(b->dk);
     cudaFree(b->dv);
     cudaFree(b->dout);
+    cudaFree(b->dq2);
+    cudaFree(b->dk2);
+    cudaFree(b->dv2);
+    cudaFree(b->dout2);
     if (b->graph) cudaGraphExecDestroy(b->graph);
     for (cudaEvent_t e : b->ev) cudaEventDestroy(e);
     for (int i = 0; i < 4; ++i) {
@@ -701,7 +738,10 @@ void nova_batch_destroy(nova_batch* b) {
         if (b->ev_cmp[i]) cudaEventDestroy(b->ev_cmp[i]);
     }
     if (b->ev_out) cudaEventDestroy(b->ev_out);
-    if (b->ev_begin) cudaEventDestroy(b->ev_begin);
+    for (int i = 0; i < 2; ++i) {
+        if (b->ev_free[i]) cudaEventDestroy(b->ev_free[i]);
+        if (b->ev_dl[i]) cudaEventDestroy(b->ev_dl[i]);
+    }
     if (b->s_in) cudaStreamDestroy(b->s_in);
     if (b->s_out) cudaStreamDestroy(b->s_out);
     delete b;
@@ -749,6 +789,12 @@ int nova_batch_set_fused_append(nova_batch* b, int on) {
 int nova_batch_set_row_setup_pages(nova_batch* b, int pages) {
     if (!b || pages < 0 || pages > 64) return NOVA_ERR_INVALID;
     b->row_setup = pages;
+    if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+    return NOVA_OK;
+}
+int nova_batch_set_split_ctas(nova_batch* b, int n_ctas) {
+    if (!b || n_ctas < 0 || n_ctas > kMaxSplitCtas) return NOVA_ERR_INVALID;
+    b->split_ctas = n_ctas;
     if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
     return NOVA_OK;
 }
@@ -935,8 +981,9 @@ int nova_batch_step_all_layers(nova_batch* b, float* q, float* k, const float* v
 static int ensure_staging(nova_batch* b);
 
 int nova_batch_decode_step_host(nova_batch* b, const float* q, const float* k, const float* v, float* out,
-                                int per_layer_launch, nova_stream_t s) {
-    if (!b || !q || !k || !v || !out) return NOVA_ERR_INVALID;
+                                int flags, nova_stream_t s) {
+    if (!b || !q || !k || !v || !out || flags < 0 || flags > 3) return NOVA_ERR_INVALID;
+    const bool per_layer_launch = (flags & 1) != 0, no_sync = (flags & 2) != 0;
     nova_engine* e = b->e;
     cudaStream_t st = (cudaStream_t)s;
     const int L = e->d.n_layers;
@@ -944,43 +991,62 @@ int nova_batch_decode_step_host(nova_batch* b, const float* q, const float* k, c
     const size_t qs = S * e->d.n_heads * kHeadDim, ks = S * e->d.n_kv_heads * kHeadDim;   // floats per layer
     int rc = ensure_staging(b);
     if (rc != NOVA_OK) return rc;
+    if (!b->s_in) {
+        NOVA_CUDA_TRY(cudaStreamCreateWithFlags(&b->s_in, cudaStreamNonBlocking));
+        NOVA_CUDA_TRY(cudaStreamCreateWithFlags(&b->s_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 4; ++i) {
+            NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_in[i], cudaEventDisableTiming));
+            NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_cmp[i], cudaEventDisableTiming));
+        }
+        for (int i = 0; i < 2; ++i) {
+            NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_free[i], cudaEventDisableTiming));
+            NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_dl[i], cudaEventDisableTiming));
+        }
+        NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_out, cudaEventDisableTiming));
+    }
+    // Two sets of staging buffers, used in turn: while the kernels of one step run on its set, the inputs of the
+    // next step are already arriving in the other one and the outputs of the step before are still leaving.
+    const int set = (int)(b->host_seq++ & 1u);
+    float* dq = set ? b->dq2 : b->dq;
+    float* dk = set ? b->dk2 : b->dk;
+    float* dv = set ? b->dv2 : b->dv;
+    float* dout = set ? b->dout2 : b->dout;
     rc = nova_batch_cow(b, s);
     if (rc < 0) return rc;
+    // the set's previous user (two steps ago) must have consumed its inputs before they are overwritten, and its
+    // outputs must have left before this step's kernels write new ones (both events are complete when never recorded)
+    NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_in, b->ev_free[set], 0));
+    NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_dl[set], 0));
     if (!per_layer_launch) {
-        NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq, q, L * qs * 4, cudaMemcpyHostToDevice, st));
-        NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk, k, L * ks * 4, cudaMemcpyHostToDevice, st));
-        NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv, v, L * ks * 4, cudaMemcpyHostToDevice, st));
-        rc = nova_batch_step_all_layers(b, b->dq, b->dk, b->dv, b->dout, s);
+        NOVA_CUDA_TRY(cudaMemcpyAsync(dq, q, L * qs * 4, cudaMemcpyHostToDevice, b->s_in));
+        NOVA_CUDA_TRY(cudaMemcpyAsync(dk, k, L * ks * 4, cudaMemcpyHostToDevice, b->s_in));
+        NOVA_CUDA_TRY(cudaMemcpyAsync(dv, v, L * ks * 4, cudaMemcpyHostToDevice, b->s_in));
+        NOVA_CUDA_TRY(cudaEventRecord(b->ev_in[0], b->s_in));
+        NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_in[0], 0));
+        rc = nova_batch_step_all_layers(b, dq, dk, dv, dout, s);
         if (rc != NOVA_OK) return rc;
-        NOVA_CUDA_TRY(cudaMemcpyAsync(out, b->dout, L * qs * 4, cudaMemcpyDeviceToHost, st));
+        NOVA_CUDA_TRY(cudaEventRecord(b->ev_cmp[0], st));
+        NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_out, b->ev_cmp[0], 0));
+        NOVA_CUDA_TRY(cudaMemcpyAsync(out, dout, L * qs * 4, cudaMemcpyDeviceToHost, b->s_out));
     } else {
         // Layers are issued in order; their inputs arrive in up to four growing chunks on a copy stream
         // and finished outputs leave on another, so that only the first chunk's upload and the last
         // chunk's download are not hidden behind the attention launches.
-        if (!b->s_in) {
-            NOVA_CUDA_TRY(cudaStreamCreateWithFlags(&b->s_in, cudaStreamNonBlocking));
-            NOVA_CUDA_TRY(cudaStreamCreateWithFlags(&b->s_out, cudaStreamNonBlocking));
-            for (int i = 0; i < 4; ++i) {
-                NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_in[i], cudaEventDisableTiming));
-                NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_cmp[i], cudaEventDisableTiming));
-            }
-            NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_out, cudaEventDisableTiming));
-            NOVA_CUDA_TRY(cudaEventCreateWithFlags(&b->ev_begin, cudaEventDisableTiming));
-        }
         // Uploads go in growing chunks (layers [0,2), [2,6), [6,14), [14,L)), downloads in shrinking ones
         // ([0,L-14), [L-14,L-6), [L-6,L-2), [L-2,L)): what stays exposed is two layers' inputs before the
         // first launch and two layers' outputs after the last.
         int cin[5] = {0, L < 2 ? L : 2, L < 6 ? L : 6, L < 14 ? L : 14, L};
         int cout[5] = {0, L > 14 ? L - 14 : 0, L > 6 ? L - 6 : 0, L > 2 ? L - 2 : 0, L};
-        NOVA_CUDA_TRY(cudaEventRecord(b->ev_begin, st));              // the COW copies above precede everything
-        NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_in, b->ev_begin, 0));
-        NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_out, b->ev_begin, 0));
+        if (no_sync) {       // queued steps hide each other's copies: one chunk each way, fewer calls on the host
+            cin[1] = cin[2] = cin[3] = L;
+            cout[1] = cout[2] = cout[3] = 0;
+        }
         for (int c = 0; c < 4; ++c) {
             const int l0 = cin[c], n = cin[c + 1] - cin[c];
             if (n <= 0) continue;
-            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dq + l0 * qs, q + l0 * qs, n * qs * 4, cudaMemcpyHostToDevice, b->s_in));
-            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dk + l0 * ks, k + l0 * ks, n * ks * 4, cudaMemcpyHostToDevice, b->s_in));
-            NOVA_CUDA_TRY(cudaMemcpyAsync(b->dv + l0 * ks, v + l0 * ks, n * ks * 4, cudaMemcpyHostToDevice, b->s_in));
+            NOVA_CUDA_TRY(cudaMemcpyAsync(dq + l0 * qs, q + l0 * qs, n * qs * 4, cudaMemcpyHostToDevice, b->s_in));
+            NOVA_CUDA_TRY(cudaMemcpyAsync(dk + l0 * ks, k + l0 * ks, n * ks * 4, cudaMemcpyHostToDevice, b->s_in));
+            NOVA_CUDA_TRY(cudaMemcpyAsync(dv + l0 * ks, v + l0 * ks, n * ks * 4, cudaMemcpyHostToDevice, b->s_in));
             NOVA_CUDA_TRY(cudaEventRecord(b->ev_in[c], b->s_in));
         }
         int ci = 0, co = 0;
@@ -996,25 +1062,34 @@ int nova_batch_decode_step_host(nova_batch* b, const float* q, const float* k, c
             while (co < 4 && cout[co + 1] <= l) ++co;
             if (l > 0 && cout[co] == l) fresh = true;     // an output event was recorded just before this layer
             if (use_fused(b))
-                rc = run_attn_fused(b, l, 1, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, st,
-                                    b->pdl && !fresh);
+                rc = run_attn_fused(b, l, 1, dq + l * qs, dk + l * ks, dv + l * ks, dout + l * qs, st, b->pdl && !fresh);
             else
-                rc = nova_batch_append_attn(b, l, b->dq + l * qs, b->dk + l * ks, b->dv + l * ks, b->dout + l * qs, s);
+                rc = nova_batch_append_attn(b, l, dq + l * qs, dk + l * ks, dv + l * ks, dout + l * qs, s);
             if (rc != NOVA_OK) return rc;
             if (cout[co + 1] == l + 1) {                   // the chunk [cout[co], l + 1) is complete
                 const int l0 = cout[co];
                 NOVA_CUDA_TRY(cudaEventRecord(b->ev_cmp[co], st));
                 NOVA_CUDA_TRY(cudaStreamWaitEvent(b->s_out, b->ev_cmp[co], 0));
-                NOVA_CUDA_TRY(cudaMemcpyAsync(out + l0 * qs, b->dout + l0 * qs, (size_t)(l + 1 - l0) * qs * 4,
+                NOVA_CUDA_TRY(cudaMemcpyAsync(out + l0 * qs, dout + l0 * qs, (size_t)(l + 1 - l0) * qs * 4,
                                               cudaMemcpyDeviceToHost, b->s_out));
             }
         }
-        NOVA_CUDA_TRY(cudaEventRecord(b->ev_out, b->s_out));
-        NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_out, 0));
     }
+    NOVA_CUDA_TRY(cudaEventRecord(b->ev_free[set], st));        // this set's inputs have been consumed
+    NOVA_CUDA_TRY(cudaEventRecord(b->ev_dl[set], b->s_out));    // ... and its outputs are on their way out
     rc = nova_batch_advance(b, s);
     if (rc != NOVA_OK) return rc;
+    if (no_sync) return NOVA_OK;
+    NOVA_CUDA_TRY(cudaEventRecord(b->ev_out, b->s_out));
+    NOVA_CUDA_TRY(cudaStreamWaitEvent(st, b->ev_out, 0));
     NOVA_CUDA_TRY(cudaStreamSynchronize(st));
+    return NOVA_OK;
+}
+
+int nova_batch_host_wait(nova_batch* b, nova_stream_t s) {
+    if (!b) return NOVA_ERR_INVALID;
+    NOVA_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)s));
+    if (b->s_out) NOVA_CUDA_TRY(cudaStreamSynchronize(b->s_out));
     return NOVA_OK;
 }
 
@@ -1027,6 +1102,10 @@ static int ensure_staging(nova_batch* b) {
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dk, kv_elems * 4);
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dv, kv_elems * 4);
     if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dout, q_elems * 4);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dq2, q_elems * 4);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dk2, kv_elems * 4);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dv2, kv_elems * 4);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&b->dout2, q_elems * 4);
     if (ce != cudaSuccess) { set_cuda_error(ce, "step staging"); return NOVA_ERR_CUDA; }
     return NOVA_OK;
 }
@@ -1239,7 +1318,7 @@ int nova_batch_step_partial_peers(nova_batch* b, float* q, float* k, const float
         }
         int ctas;
         if (b->kernel == 1) {
-            ctas = attn_split_ctas_mma(a, 0);
+            ctas = pick_split_ctas(b, a);
             rc = launch_attn_mma(a, e->d.kv_dtype, ctas, st);
         } else {
             ctas = attn_split_ctas_simt(a, 0);

@@ -348,6 +348,9 @@ int  nova_batch_set_pdl(nova_batch* b, int on);
 /* Tuning knob of the attention work split: how many pages' worth of time starting a session inside a
  * CTA costs (default 2).  A CTA whose page range crosses a session boundary gets that many fewer pages. */
 int  nova_batch_set_row_setup_pages(nova_batch* b, int pages);
+/* Tuning knob: CTAs of a tensor-core attention launch (0 = chosen by the library: one per SM, a few fewer in a
+ * programmatic chain, half of the SMs when a chained launch has little to stream). */
+int  nova_batch_set_split_ctas(nova_batch* b, int n_ctas);
 int  nova_batch_append_attn(nova_batch* b, int layer, float* q, float* k, const float* v, float* out,
                             nova_stream_t s);
 /* n_past[s] += 1 on host and device (the caller's ++A->n_past, cow_e2e_demo.cpp:64). */
@@ -367,11 +370,17 @@ int  nova_batch_advance_by(nova_batch* b, int n_tokens, nova_stream_t s);
  * one attention launch.  Does not advance. */
 int  nova_batch_step_all_layers(nova_batch* b, float* q, float* k, const float* v, float* out,
                                 nova_stream_t s);
-/* Whole decode step from HOST buffers (layouts as above, pinned or pageable):
- * COW guard, H2D of q/k/v, L x (append, attention), D2H of out, advance, stream sync.
- * per_layer_launch: 1 = two launches per layer (engine order), 0 = all layers per launch. */
+/* Whole decode step from HOST buffers (layouts as above, pinned or pageable): COW guard, H2D of q/k/v,
+ * L x (append, attention), D2H of out, advance.
+ * flags bit 0: 1 = one attention launch per layer (engine order), 0 = all layers per launch.
+ * flags bit 1: 0 = the call returns when `out` is complete (stream sync); 1 = the call only queues the step and
+ *   returns: uploads, kernels and downloads of consecutive steps then overlap (two sets of staging buffers are
+ *   used in turn).  The caller keeps q/k/v valid and leaves `out` alone until nova_batch_host_wait() has returned,
+ *   and gives every step that is in flight its own `out`. */
 int  nova_batch_decode_step_host(nova_batch* b, const float* q, const float* k, const float* v,
-                                 float* out, int per_layer_launch, nova_stream_t s);
+                                 float* out, int flags, nova_stream_t s);
+/* Blocks until every queued host-buffer step on stream s has delivered its `out`. */
+int  nova_batch_host_wait(nova_batch* b, nova_stream_t s);
 /* n_steps whole decode steps from DEVICE buffers, issued from native code (no per-launch
  * interpreter cost): per step the COW guard, L x (append, attention) and the advance.
  * Step i reads q + i*q_stride floats (layout [L][S][NH][HD]), k/v + i*kv_stride ([L][S][NKV][HD])

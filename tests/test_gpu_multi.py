@@ -1,7 +1,10 @@
 """Two GPUs of one node (skipped where fewer are visible): one session's pages split over two ranks, each
-rank a process of its own with its own pool; nova_batch_step_partial_peers merges over NVLink by peer
-reads (exchange buffers shared with dev_ipc_export / dev_ipc_open).  Every rank's merged output must equal
-the oracle's single-GPU decode step, and both ranks must hold bit-identical outputs."""
+rank a process of its own with its own pool; nova_batch_step_partial_peers exchanges the partial rows over
+NVLink (every rank stores its rows into the peers' exchange buffers, shared with dev_ipc_export /
+dev_ipc_open).  Every rank's merged output must equal the oracle's single-GPU decode step, and both ranks must
+hold bit-identical outputs.  A soak of several hundred steps checks that the exchange never loses or mixes up
+a row: outputs bit-identical across the ranks at every step, and within float noise of the path that gathers
+the partial rows on the host and merges them with nova_lse_combine."""
 import ctypes as C
 import importlib.util
 import os
@@ -96,3 +99,93 @@ def test_long_context_step_over_two_gpus(kernel, pdl):
             assert rel <= REL_TOL and mab <= ABS_TOL, (rank, rel, mab)
             assert same, "ranks disagree on the merged output"
             assert n_past == 2503
+
+
+def _soak_worker(rank, world, port, n_steps, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import __graft_entry__ as g
+    nv = g.load_package()
+    nv.check(nv.lib.dev_select(rank))
+    import conflux_nova_b200.longctx as lc
+    import conflux_nova_b200.workloads as wl
+    from oracle import binding as ob
+    n_ctx, L = 3000, 2
+    work = wl.Workload("qwen25_7b", [n_ctx], seed=0x5EED0044, steps=n_steps + 16, device=rank, n_layers=L)   # same session on both
+    eng, batch = work.eng, work.batch
+    NH, NKV = eng.NH, eng.NKV
+    batch.set_kernel(1)
+    batch.set_fused_append(1)
+    batch.set_pdl(1)
+    cs, sn = eng.rope_tables()
+    sh1 = ob.shape(1, NH, NKV, ob.KV_F16)
+    n_pages = (n_ctx + 15) // 16
+    lo, hi = lc.page_range(rank, world, n_pages)
+    xch = lc.PeerExchange(nv, NH, rank, world, dist, n_slots=2)
+    status = nv.DevBuf(4).zero()
+    dout = nv.DevBuf(L * NH * 128 * 4)
+    part = nv.DevBuf(NH * 130 * 4)
+    merged = nv.DevBuf(NH * 128 * 4)
+    st = nv.Stream()
+    same, worst, checked = True, 0.0, 0
+    dist.barrier()
+    for step in range(n_steps):
+        dq, dk, dv = work.device_step_inputs(step)
+        hq = dq.download(np.float32).reshape(L, NH, 128) if step % 50 == 49 else None
+        pos = eng.n_past(work.sessions[0])
+        nv.check(nv.lib.nova_batch_step_partial_peers(batch.h, dq.ptr, dk.ptr, dv.ptr, lo, hi, xch.base, world, rank,
+                                                      xch.slot_bytes, 2, 1 + step * L, 2000, dout.ptr, status.ptr, st.h))
+        st.sync()
+        assert batch.device_status() == 0 and int(status.download(np.int32)[0]) == 0, step
+        got = dout.download(np.float32).reshape(L, NH, 128)
+        outs = [None] * world
+        dist.all_gather_object(outs, got.tobytes())
+        same = same and all(o == outs[0] for o in outs)
+        if hq is not None:
+            # the other path: partial rows of the last layer over the same keys, gathered on the host, merged on the device
+            layer = L - 1
+            q_rot = hq[layer].copy().reshape(1, NH, 128)
+            kd = np.zeros((1, NKV, 128), np.float32)
+            ob.oracle().oracle_rope_batch(C.byref(sh1), q_rot.ctypes.data, kd.ctypes.data, 1, pos, cs.ctypes.data, sn.ctypes.data, 1)
+            eng.set_n_past(work.sessions[0], pos)            # n_keys = pos + 1, as during the step
+            batch.sync_positions()
+            batch.set_fused_append(0)
+            dqr = nv.to_device(q_rot)
+            batch.attn_partial(layer, dqr.ptr, lo, hi, part.ptr)
+            nv.check(nv.lib.dev_sync())
+            parts = [None] * world
+            dist.all_gather_object(parts, part.download(np.float32).tobytes())
+            stacked = nv.to_device(np.stack([np.frombuffer(p, np.float32).reshape(NH, 130) for p in parts]))
+            nv.check(nv.lib.nova_lse_combine(stacked.ptr, world, NH, 128, merged.ptr, None))
+            nv.check(nv.lib.dev_sync())
+            ref = merged.download(np.float32).reshape(NH, 128)
+            worst = max(worst, float(np.linalg.norm(got[layer].astype(np.float64) - ref) / np.linalg.norm(ref)))
+            checked += 1
+            eng.set_n_past(work.sessions[0], pos + 1)
+            batch.sync_positions()
+            batch.set_fused_append(1)
+            batch.set_pdl(1)
+        for b in (dq, dk, dv):
+            b.free()
+    dist.barrier()
+    ret[rank] = (same, worst, checked, eng.n_past(work.sessions[0]))
+    xch.close()
+    st.close()
+    work.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs of one node")
+def test_long_context_exchange_soak():
+    import torch.multiprocessing as mp
+    world, n_steps = 2, 500
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_soak_worker, args=(world, 29750, n_steps, ret), nprocs=world, join=True)
+        for rank in range(world):
+            same, worst, checked, n_past = ret[rank]
+            assert same, "ranks disagree on a merged output"
+            assert checked == n_steps // 50 and worst < 1e-3, (rank, worst)      # same arithmetic; another work split, another transport
+            assert n_past == 3000 + n_steps

@@ -919,8 +919,35 @@ def test_decode_step_from_host_buffers(nv, ob, kernel):
         want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q.copy(), k.copy(), v, cs, sn, exact=True)
         assert_attn_close(out, want, f"step {step}")
         pos = [p + 1 for p in pos]
+    # queued steps (no synchronisation per step): uploads, kernels and downloads of consecutive steps overlap on two
+    # sets of staging buffers; every step in flight has its own pinned host buffers, checked after one wait
+    if kernel == 2:
+        batch.set_pdl(1)
+    st = nv.Stream()
+    n_q, n_k = L * S * NH * 128, L * S * NKV * 128
+    steps = []
+    for step in range(7):
+        bufs = [nv.lib.dev_host_alloc(n * 4) for n in (n_q, n_k, n_k, n_q)]
+        views = [np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,)) for p, n in zip(bufs, (n_q, n_k, n_k, n_q))]
+        for v_, n in zip(views[:3], (n_q, n_k, n_k)):
+            v_[:] = rng.standard_normal(n).astype(np.float32)
+        views[3][:] = np.nan
+        batch.decode_step_host(bufs[0], bufs[1], bufs[2], bufs[3], step % 3 != 1, st.h, no_sync=True)
+        steps.append((bufs, views))
+    batch.host_wait(st.h)
+    assert batch.device_status() == 0
+    for step, (bufs, views) in enumerate(steps):
+        q = views[0].reshape(L, S, NH, 128).copy()
+        k = views[1].reshape(L, S, NKV, 128).copy()
+        v = views[2].reshape(L, S, NKV, 128).copy()
+        want = ob.decode_step(sh, pk, pv, tables, eng.nb, pos, q, k, v, cs, sn, exact=True)
+        assert_attn_close(views[3].reshape(want.shape), want, f"queued step {step}")
+        pos = [p + 1 for p in pos]
+        for p_ in bufs:
+            nv.lib.dev_host_free(p_)
     gk, gv = eng.read_pools()
     assert np.array_equal(bits(gk), bits(pk)) and np.array_equal(bits(gv), bits(pv))
+    st.close()
     batch.close()
     eng.close()
 
