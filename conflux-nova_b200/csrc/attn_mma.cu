@@ -92,6 +92,8 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     const int NH = a.n_heads, S = a.n_sessions * NQ;     // S counts units (session x query token)
     const int heads_per_row = KVG * G;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const PageGeom geo = page_geom(a.kv_shift);
+    const int tpp_mask = (1 << geo.tpp_shift) - 1;
 
     pdl_launch_dependents();      // the combine kernel may be scheduled; it waits for this grid to finish
 #ifdef NOVA_TIMELINE      // profiling build only: per-CTA %globaltimer stamps
@@ -116,6 +118,14 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     if (warp == KVG && lane == 0) {     // the tensor maps are needed right after the first table entry
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
+    }
+    if (geo.tile_keys < kTileKeysMax) {
+        // 8-token pages fill only the first 8 of a stage's 16 key rows per kv head.  The other rows take part in the
+        // tile arithmetic with weight zero, so they must hold finite values: clear the ring once; the page copies
+        // never touch those rows afterwards.
+        for (uint32_t off = threadIdx.x * 16u; off < (uint32_t)(kStages * Cfg::kStageBytes); off += blockDim.x * 16u)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(stage0 + off), "r"(0u) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     plan_build_prefix(a, s_prefix, n_groups, s_slice, s_keys);   // ends with __syncthreads()
 
@@ -226,7 +236,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         };
         uint32_t it = 0;
         Batch cur = next_batch();
-        int phys_cur = (cur.count > 0 && lane < cur.count) ? __ldg(cur.table + cur.page0 + lane) : 0;
+        int phys_cur = (cur.count > 0 && lane < cur.count) ? __ldg(cur.table + ((cur.page0 + lane) >> geo.tpp_shift)) : 0;
         while (cur.count > 0) {
             // Issue the first few pages of the batch before looking ahead, so that opening the next
             // segment (work split, prefetch hints) never delays copies that could already be in flight.
@@ -243,9 +253,9 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                         if (a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
                         ok = 0;
                     } else {
-                        const int page = cur.page0 + j;
-                        int kcount = cur.n_keys - page * kKvBlock;
-                        if (kcount > kKvBlock) kcount = kKvBlock;
+                        const int page = cur.page0 + j;                  // tile index within the session
+                        int kcount = cur.n_keys - (page << geo.tile_shift);
+                        if (kcount > geo.tile_keys) kcount = geo.tile_keys;
                         if (phys < 0 || phys >= a.nb) {      // never follow a bad entry: load page 0, use none of it
                             if (a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
                             phys = 0;
@@ -255,8 +265,21 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                         s_phys[stage] = phys;
                         const uint32_t bar = smem_u32(&s_full[stage]);
                         const uint32_t dst = stage0 + (uint32_t)stage * Cfg::kStageBytes;
-                        const int c1 = (int)(((int64_t)cur.layer * a.nb + phys) * kKvBlock);
+                        const int c1 = (int)((((int64_t)cur.layer * a.nb + phys) << geo.kv_shift) + ((page & tpp_mask) << 4));
                         const int c2 = cur.group * KVG;
+                        if (geo.tile_keys < kTileKeysMax) {
+                            // 8-token pages: the maps' boxes are [64 dims][8 slots][1 kv head]; each kv head's box goes
+                            // to the first half of that head's 16 rows
+                            mbar_expect_tx(bar, Cfg::kStageBytes / 2);
+                            for (int h = 0; h < KVG; ++h) {
+                                const uint32_t d = dst + (uint32_t)h * 2048u;
+                                tma_load_3d(d, &tmk, 0, c1, c2 + h, bar);
+                                tma_load_3d(d + Cfg::kBoxBytes, &tmk, 64, c1, c2 + h, bar);
+                                tma_load_3d(d + 2 * Cfg::kBoxBytes, &tmv, 0, c1, c2 + h, bar);
+                                tma_load_3d(d + 3 * Cfg::kBoxBytes, &tmv, 64, c1, c2 + h, bar);
+                            }
+                            if (tl && it == 0) tl[2] = now_ns();
+                        } else {
                         mbar_expect_tx(bar, Cfg::kStageBytes);
 #if NOVA_ATTN_EVICT_FIRST
                         tma_load_3d_hint(dst, &tmk, 0, c1, c2, bar, kv_policy);
@@ -270,12 +293,13 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                         tma_load_3d(dst + 3 * Cfg::kBoxBytes, &tmv, 64, c1, c2, bar);
 #endif
                         if (tl && it == 0) tl[2] = now_ns();
+                        }
                     }
                 }
                 if (!__shfl_sync(0xffffffffu, ok, 0)) return;
                 if (j + 1 == head_n) {                      // look ahead: next batch's table entries in flight
                     nxt = next_batch();
-                    phys_nxt = (nxt.count > 0 && lane < nxt.count) ? __ldg(nxt.table + nxt.page0 + lane) : 0;
+                    phys_nxt = (nxt.count > 0 && lane < nxt.count) ? __ldg(nxt.table + ((nxt.page0 + lane) >> geo.tpp_shift)) : 0;
                 }
             }
             cur = nxt;
@@ -384,6 +408,9 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             } else if (a.fuse_append && lane == 0 && a.status) {
                 atomicCAS(a.status, 0, NOVA_ERR_INVALID);      // position beyond the RoPE table
             }
+            // the step's token has no block-table entry (the session is at its context limit): it cannot be stored
+            if (a.fuse_append && lane == 0 && a.status && pos_new >= 0 && ((int64_t)pos_new >> geo.kv_shift) >= a.table_stride)
+                atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
 #pragma unroll
@@ -415,20 +442,20 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
             if (kcount > 0) {
                 bool patched = false;
                 if (a.fuse_append && pos_new >= 0 && pos_new < a.rope_rows &&
-                    (pos_new >> kKvShift) == first_page_c + sg.page_first + pg) {
+                    (pos_new >> geo.tile_shift) == first_page_c + sg.page_first + pg) {
                     // This page receives the step's new token: rotate k, store k and v into the pool
                     // (for later steps) and straight into the staged copy (for this one).  The TMA
                     // copy of that slot may be old or new bytes; both are overwritten here.
                     patched = true;
-                    const int slot = pos_new & (kKvBlock - 1);
+                    const int slot = pos_new & (geo.tile_keys - 1);          // key row inside the staged tile
                     const int layer = a.layer0 + sg.layer_local;
                     const int64_t tok = ((int64_t)sg.layer_local * S + s) * a.n_kv_heads + kvh;
                     float* kn = a.k_new + tok * kHeadDim;
                     const float* vn = a.v_new + tok * kHeadDim;
                     const float* cr = a.rope_cs + (int64_t)pos_new * (kHeadDim / 2);
                     const float* sr = a.rope_sn + (int64_t)pos_new * (kHeadDim / 2);
-                    const int64_t grow = (((int64_t)layer * a.nb + s_phys[stage]) * kKvBlock + slot) * (int64_t)a.n_kv_heads * kHeadDim +
-                                         (int64_t)kvh * kHeadDim;
+                    const int64_t grow = ((((int64_t)layer * a.nb + s_phys[stage]) << geo.kv_shift) + (pos_new & ((1 << geo.kv_shift) - 1))) *
+                                             (int64_t)a.n_kv_heads * kHeadDim + (int64_t)kvh * kHeadDim;
                     __half* gk = static_cast<__half*>(a.pool_k_w) + grow;
                     __half* gv = static_cast<__half*>(a.pool_v_w) + grow;
                     const uint32_t srow = (uint32_t)(w * 2048 + slot * 128);
@@ -453,10 +480,10 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     }
                     __syncwarp();
                 }
-                if (kcount < kKvBlock) {
+                if (kcount < geo.tile_keys) {
                     // Rows past the last key hold whatever the page held before: P is 0 there, but
                     // 0 * (Inf/NaN bit patterns) would poison O, so clear those V rows first.
-                    for (int i = lane; i < (kKvBlock - kcount) * 16; i += 32) {
+                    for (int i = lane; i < (geo.tile_keys - kcount) * 16; i += 32) {
                         const int row = kcount + (i >> 4), c = i & 15;
                         const uint32_t addr = sv + (uint32_t)((c >> 3) * Cfg::kBoxBytes + w * 2048 + row * 128 + ((c & 7) << 4));
                         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
@@ -476,7 +503,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     mma_top(sl[1][0], sl[1][1], ql[ks][0], ql[ks][1], b[2], b[3], sl[1][0], sl[1][1]);
                 }
                 float sc[4] = {sh[0][0] + sl[0][0], sh[0][1] + sl[0][1], sh[1][0] + sl[1][0], sh[1][1] + sl[1][1]};
-                if (kcount < kKvBlock) {   // keys 2t, 2t+1, 8+2t, 9+2t of the page
+                if (kcount < kTileKeysMax) {   // keys 2t, 2t+1, 8+2t, 9+2t of the tile
                     if (2 * t >= kcount) sc[0] = -INFINITY;
                     if (2 * t + 1 >= kcount) sc[1] = -INFINITY;
                     if (8 + 2 * t >= kcount) sc[2] = -INFINITY;
@@ -511,7 +538,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     mma_top(o[2 * jp][0], o[2 * jp][1], p0, p1, b[0], b[1], o[2 * jp][0], o[2 * jp][1]);
                     mma_top(o[2 * jp + 1][0], o[2 * jp + 1][1], p0, p1, b[2], b[3], o[2 * jp + 1][0], o[2 * jp + 1][1]);
                 }
-                if (kcount < kKvBlock || patched) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (kcount < geo.tile_keys || patched) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
@@ -565,8 +592,10 @@ int launch_kvg(const AttnLaunch& a, int n_ctas, cudaStream_t s) {
                                            Cfg::kSmemBytes));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k);
-    const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v);
+    // 8-token pages are fetched one kv head at a time (maps with [64][8][1] boxes)
+    const bool per_head = (a.kv_shift ? a.kv_shift : kKvShift) < 4;
+    const CUtensorMap* tk = static_cast<const CUtensorMap*>(per_head ? a.tmap_k1 : a.tmap_k);
+    const CUtensorMap* tv = static_cast<const CUtensorMap*>(per_head ? a.tmap_v1 : a.tmap_v);
     const cudaError_t le = launch_kernel_pdl(attn_mma_kernel<KVG>, dim3((unsigned)n_ctas), dim3(Cfg::kThreads),
                                              (size_t)Cfg::kSmemBytes, s, a.pdl != 0, a, *tk, *tv);
     if (le != cudaSuccess) {
@@ -587,9 +616,9 @@ bool attn_mma_built() { return true; }
 int attn_default_ctas_mma() { return sm_count(); }
 size_t attn_tmap_bytes() { return sizeof(CUtensorMap); }
 
-// Tensor map over one fp16 pool [rows = L*NB*16][NKV][128]: dim0 = 128 dims, dim1 = slot rows
-// (stride NKV*256 B), dim2 = kv head (stride 256 B); box = [64][16][kv_group], 128-byte swizzle.
-int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group) {
+// Tensor map over one fp16 pool [rows = L*NB*page tokens][NKV][128]: dim0 = 128 dims, dim1 = slot rows
+// (stride NKV*256 B), dim2 = kv head (stride 256 B); box = [64][box_rows = 16 or 8][kv_group], 128-byte swizzle.
+int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group, int box_rows) {
     static EncodeTiledFn encode = nullptr;
     if (!encode) {
         cudaDriverEntryPointQueryResult q;
@@ -602,9 +631,10 @@ int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads,
         encode = (EncodeTiledFn)fn;
     }
     if (slot_rows <= 0 || slot_rows > 0x7fffffffLL) return NOVA_ERR_TOO_LARGE;
+    if (box_rows != 8 && box_rows != 16) return NOVA_ERR_INVALID;
     const cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)slot_rows, (cuuint64_t)n_kv_heads};
     const cuuint64_t strides[2] = {(cuuint64_t)n_kv_heads * kHeadDim * 2, (cuuint64_t)kHeadDim * 2};
-    const cuuint32_t box[3] = {64, (cuuint32_t)kKvBlock, (cuuint32_t)kv_group};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)kv_group};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = encode(static_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pool, dims, strides,
                               box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -624,6 +654,7 @@ int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
 
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
     if (kv_dtype != NOVA_KV_F16 || !a.tmap_k || !a.tmap_v) return NOVA_ERR_UNSUPPORTED;
+    if ((a.kv_shift ? a.kv_shift : kKvShift) < 4 && (!a.tmap_k1 || !a.tmap_v1)) return NOVA_ERR_UNSUPPORTED;
     if (a.fuse_append && a.n_q > 1) return NOVA_ERR_UNSUPPORTED;      // the fused append is a decode (one token) path
     if (a.fuse_append && (!a.n_past || !a.k_new || !a.v_new || !a.rope_cs || !a.rope_sn || !a.pool_k_w || !a.pool_v_w))
         return NOVA_ERR_INVALID;

@@ -40,6 +40,21 @@ struct Segment {
 
 __device__ __forceinline__ int plan_nq(const AttnLaunch& a) { return a.n_q > 1 ? a.n_q : 1; }
 
+// Page geometry of a launch.  Everything in this file that is called a "page" is a TILE: the unit the kernels
+// stream, min(16, tokens per page) keys.  tpp_shift = log2(tiles per page): 0 for 8- and 16-token pages, 1 and 2
+// for 32 and 64; tile i of a unit lives in block-table entry i >> tpp_shift at slot rows (i & (tpp - 1)) * 16.
+struct PageGeom {
+    int kv_shift, tile_shift, tpp_shift, tile_keys;
+};
+__device__ __forceinline__ PageGeom page_geom(int kv_shift_field) {
+    PageGeom g;
+    g.kv_shift = kv_shift_field ? kv_shift_field : kKvShift;
+    g.tile_shift = g.kv_shift < 4 ? g.kv_shift : 4;
+    g.tpp_shift = g.kv_shift - g.tile_shift;
+    g.tile_keys = 1 << g.tile_shift;
+    return g;
+}
+
 // Keys seen by unit u = s * n_q + t (query token t of session s).
 __device__ __forceinline__ int plan_session_keys(const AttnLaunch& a, int u) {
     const int nq = plan_nq(a);
@@ -49,10 +64,13 @@ __device__ __forceinline__ int plan_session_keys(const AttnLaunch& a, int u) {
 
 // First logical page and page count of a unit that sees n_keys keys, inside the launch's page window.
 __device__ __forceinline__ void plan_pages_of_keys(const AttnLaunch& a, int n_keys, int& first, int& count) {
-    int64_t total = n_keys > 0 ? (((int64_t)n_keys + kKvBlock - 1) >> kKvShift) : 0;
-    if (total > a.table_stride) total = a.table_stride;   // never walk past the table
-    int64_t lo = a.page_lo > 0 ? a.page_lo : 0;
-    int64_t hi = (a.page_hi >= 0 && a.page_hi < total) ? a.page_hi : total;
+    const PageGeom pg = page_geom(a.kv_shift);
+    int64_t total = n_keys > 0 ? (((int64_t)n_keys + pg.tile_keys - 1) >> pg.tile_shift) : 0;
+    if (total > (a.table_stride << pg.tpp_shift)) total = a.table_stride << pg.tpp_shift;   // never walk past the table
+    // the launch's window is given in pages of the pool
+    int64_t lo = a.page_lo > 0 ? (a.page_lo << pg.tpp_shift) : 0;
+    const int64_t hi_win = a.page_hi >= 0 ? (a.page_hi << pg.tpp_shift) : total;      // callers keep page_hi <= 2^40
+    int64_t hi = hi_win < total ? hi_win : total;
     if (lo > hi) lo = hi;
     first = (int)lo;
     count = (int)(hi - lo);

@@ -7,8 +7,12 @@
 // kv head's pages come in once per TILE through the same TMA ring as the decode kernel (box
 // [64 dims][16 slots][1 head], 128-byte swizzle) and all four warps read them from shared memory:
 // K/V traffic drops by TQ (9 at G = 7) against a per-query stream and every row of the
-// m16n8k16 tiles is a real query.  Causal: the row of query t sees keys 0 .. n_past + t.
+// m16n8k16 tiles is a real query.  Causal: the row of query t sees keys 0 .. n_past + t; with a sliding
+// window W (flash_paged_kernel<true>, attn.cu:317) only the last W of them, and the tile starts at the first
+// page that any of its queries can see.
 // fp16 operands, fp32 accumulation and softmax (exp2 domain), P rounded to fp16 for P.V.
+// "Page" below is a tile of min(16, tokens per page) keys (attn_plan.cuh): pages of 32 / 64 tokens are 2 / 4
+// tiles behind one block-table entry, pages of 8 tokens fill half a stage.
 #include "attn_plan.cuh"
 #include "mma_common.cuh"
 
@@ -33,7 +37,7 @@ constexpr int kPfWarps = 4;                       // consumer warps, 16 tile row
 template <bool kPrefix>
 __global__ void __launch_bounds__(32 * (kPfWarps + 1), NOVA_PREFILL_CTAS_PER_SM)
 attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv,
-                    int tq, int n_tiles, int prefix_pages, int chunk_pages) {
+                    int tq, int n_tiles, int prefix_pages, int chunk_pages) {      // both counts in tiles
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long s_full[kPfStages];
     __shared__ __align__(8) unsigned long long s_empty[kPfStages];
@@ -44,6 +48,8 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
     const int G = a.n_heads / a.n_kv_heads;
     const int NH = a.n_heads, NKV = a.n_kv_heads, NQ = a.n_q;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const PageGeom geo = page_geom(a.kv_shift);
+    const int tpp_mask = (1 << geo.tpp_shift) - 1;
     if (kPrefix) pdl_launch_dependents();      // the split over the private pages shares nothing with this kernel
 
     // blockIdx.x -> (tile, kv head, session); late tiles (most keys) first
@@ -56,13 +62,15 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
     const int t0 = tile * tq;
     const int t_cnt = NQ - t0 < tq ? NQ - t0 : tq;          // query tokens in this tile
     const int n_past = kPrefix ? 0 : (a.n_past ? a.n_past[s] : a.keys_imm);
-    const int keys_tile = kPrefix ? prefix_pages * kKvBlock
+    const int keys_tile = kPrefix ? prefix_pages << geo.tile_shift
                                   : n_past + a.keys_add + t0 + t_cnt - 1;   // keys seen by the tile's last query
-    const int page_begin = kPrefix ? chunk * chunk_pages : 0;
-    const int page_end_all = (keys_tile + kKvBlock - 1) >> kKvShift;
+    // sliding window: the tile's first query sees keys from first_key on, nothing before it matters to any row
+    const int first_key = (!kPrefix && a.window > 0) ? n_past + a.keys_add + t0 - a.window : 0;
+    const int page_begin = kPrefix ? chunk * chunk_pages : (first_key > 0 ? first_key >> geo.tile_shift : 0);
+    const int page_end_all = (keys_tile + geo.tile_keys - 1) >> geo.tile_shift;
     const int page_end = kPrefix && page_begin + chunk_pages < page_end_all ? page_begin + chunk_pages : page_end_all;
     const int n_pages = page_end - page_begin;
-    const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride + page_begin;
+    const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kPfStages; ++i) {
@@ -72,8 +80,13 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (geo.tile_keys < kTileKeysMax) {      // 8-token pages fill rows 0-7 of a stage only: the other rows must be finite
+        for (uint32_t off = threadIdx.x * 16u; off < (uint32_t)(kPfStages * kPfStage); off += blockDim.x * 16u)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(stage0 + off), "r"(0u) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
-    if (n_pages <= 0 || page_end > a.table_stride) return;
+    if (n_pages <= 0 || ((page_end + tpp_mask) >> geo.tpp_shift) > a.table_stride) return;
 
     // ------------------------------------------------------------------ producer warp
     if (warp == kPfWarps) {
@@ -81,10 +94,10 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
         }
-        int phys_cur = lane < n_pages ? __ldg(table + lane) : 0;
+        int phys_cur = lane < n_pages ? __ldg(table + ((page_begin + lane) >> geo.tpp_shift)) : 0;
         for (int base = 0; base < n_pages; base += 32) {
             const int nxt = base + 32 + lane;
-            const int phys_nxt = nxt < n_pages ? __ldg(table + nxt) : 0;
+            const int phys_nxt = nxt < n_pages ? __ldg(table + ((page_begin + nxt) >> geo.tpp_shift)) : 0;
             const int cnt = n_pages - base < 32 ? n_pages - base : 32;
             for (int j = 0; j < cnt; ++j) {
                 int phys = __shfl_sync(0xffffffffu, phys_cur, j);
@@ -103,8 +116,8 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
                         }
                         const uint32_t bar = smem_u32(&s_full[stage]);
                         const uint32_t dst = stage0 + (uint32_t)stage * kPfStage;
-                        const int c1 = (int)(((int64_t)a.layer0 * a.nb + phys) * kKvBlock);
-                        mbar_expect_tx(bar, kPfStage);
+                        const int c1 = (int)((((int64_t)a.layer0 * a.nb + phys) << geo.kv_shift) + (((page_begin + (int)it) & tpp_mask) << 4));
+                        mbar_expect_tx(bar, geo.tile_keys < kTileKeysMax ? kPfStage / 2 : kPfStage);    // 8-row boxes are half the bytes
                         tma_load_3d(dst, &tmk, 0, c1, kvh, bar);
                         tma_load_3d(dst + kPfBox, &tmk, 64, c1, kvh, bar);
                         tma_load_3d(dst + 2 * kPfBox, &tmv, 0, c1, kvh, bar);
@@ -126,7 +139,7 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
     constexpr float kQScale = kAttnScale * kLog2e;
 
     // this thread's two tile rows: r0 = 16*warp + gq, r1 = r0 + 8; row -> (query token, head)
-    int row_tok[2], row_head[2], row_lim[2];
+    int row_tok[2], row_head[2], row_lim[2], row_lo[2];
     bool row_ok[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -137,6 +150,8 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
         row_head[h] = kvh * G + g;
         // last key this row may see; padding rows see everything (their result is dropped)
         row_lim[h] = (row_ok[h] && !kPrefix) ? n_past + a.keys_add + row_tok[h] - 1 : 0x7fffffff;
+        // first key of the row's sliding window (keys row_lo .. row_lim are visible)
+        row_lo[h] = (row_ok[h] && !kPrefix && a.window > 0) ? row_lim[h] - a.window + 1 : 0;
     }
     uint32_t qa[8][4];
     if (kPrefix && a.fuse_append) {
@@ -200,12 +215,12 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
         }
         const uint32_t sk = stage0 + (uint32_t)stage * kPfStage;
         const uint32_t sv = sk + 2 * kPfBox;
-        const int key0 = (page_begin + pg) * kKvBlock;
-        const int kcount = keys_tile - key0 < kKvBlock ? keys_tile - key0 : kKvBlock;
-        if (kcount < kKvBlock) {
+        const int key0 = (page_begin + pg) << geo.tile_shift;
+        const int kcount = keys_tile - key0 < geo.tile_keys ? keys_tile - key0 : geo.tile_keys;
+        if (kcount < geo.tile_keys) {
             // rows past the tile's last key hold stale bytes: P is 0 there, but 0 * Inf/NaN would poison O.
             // Every warp clears them itself (same zeros) before it reads them.
-            for (int i = lane; i < (kKvBlock - kcount) * 16; i += 32) {
+            for (int i = lane; i < (geo.tile_keys - kcount) * 16; i += 32) {
                 const int row = kcount + (i >> 4), c = i & 15;
                 const uint32_t addr = sv + (uint32_t)((c >> 3) * kPfBox + row * 128 + ((c & 7) << 4));
                 asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(addr), "r"(0u) : "memory");
@@ -229,10 +244,12 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
         for (int h = 0; h < 2; ++h) {
             float v[4] = {sc[0][2 * h], sc[0][2 * h + 1], sc[1][2 * h], sc[1][2 * h + 1]};
             const int kbase = key0 + 2 * t;
-            if (kbase > row_lim[h]) v[0] = -INFINITY;
-            if (kbase + 1 > row_lim[h]) v[1] = -INFINITY;
-            if (kbase + 8 > row_lim[h]) v[2] = -INFINITY;
-            if (kbase + 9 > row_lim[h]) v[3] = -INFINITY;
+            // visible: inside the row's causal range (and window) and a real key of this tile
+            const int hi_k = row_lim[h] < key0 + kcount - 1 ? row_lim[h] : key0 + kcount - 1;
+            if (kbase > hi_k || kbase < row_lo[h]) v[0] = -INFINITY;
+            if (kbase + 1 > hi_k || kbase + 1 < row_lo[h]) v[1] = -INFINITY;
+            if (kbase + 8 > hi_k || kbase + 8 < row_lo[h]) v[2] = -INFINITY;
+            if (kbase + 9 > hi_k || kbase + 9 < row_lo[h]) v[3] = -INFINITY;
             float mx = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -264,7 +281,7 @@ attn_prefill_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const
             mma_full(o[2 * jp], pa[0], pa[1], pa[2], pa[3], b[0], b[1]);
             mma_full(o[2 * jp + 1], pa[0], pa[1], pa[2], pa[3], b[2], b[3]);
         }
-        if (kcount < kKvBlock) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (kcount < geo.tile_keys) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
     }

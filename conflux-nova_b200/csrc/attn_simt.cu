@@ -180,7 +180,9 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
         // are requested before batch j is used, so each warp keeps two batches of loads in flight; with
         // only the two keys of the inner step in flight the kernel was bound by memory latency.
         using RR = RawRow<KvT>;
-        constexpr int B = RR::kBatch, BPP = kKvBlock / B;
+        constexpr int B = RR::kBatch;
+        const PageGeom geo = page_geom(a.kv_shift);
+        const int BPP = geo.tile_keys / B;                 // batches per tile (a tile is 16 keys, 8 with 8-token pages)
         const int n_batches = sg.page_count * BPP;
         int chunk = -1, phys_lane = 0;
         typename RR::type rk[2][B], rv[2][B];
@@ -194,19 +196,20 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnLaunch a) {
             if ((pg >> 5) != chunk) {                 // 32 block-table entries at a time, one per lane
                 chunk = pg >> 5;
                 const int idx = (chunk << 5) + lane;
-                phys_lane = idx < sg.page_count ? __ldg(table + first_page + sg.page_first + idx) : 0;
+                phys_lane = idx < sg.page_count ? __ldg(table + ((first_page + sg.page_first + idx) >> geo.tpp_shift)) : 0;
             }
             const int phys = __shfl_sync(0xffffffffu, phys_lane, pg & 31);
             if (phys < 0 || phys >= a.nb) {
                 if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
                 return;
             }
-            const int page = first_page + sg.page_first + pg;
-            int kcount = n_keys - page * kKvBlock - slot0;
+            const int page = first_page + sg.page_first + pg;        // tile index within the session
+            int kcount = n_keys - (page << geo.tile_shift) - slot0;
             if (kcount > B) kcount = B;
             if (kcount <= 0) return;
             cnt = kcount;
-            const int64_t base = (((int64_t)layer * a.nb + phys) * kKvBlock + slot0) * row_elems + (int64_t)kvh * kHeadDim + 4 * lane;
+            const int sub = (page & ((1 << geo.tpp_shift) - 1)) << 4;    // first slot row of the tile inside its page
+            const int64_t base = ((((int64_t)layer * a.nb + phys) << geo.kv_shift) + sub + slot0) * row_elems + (int64_t)kvh * kHeadDim + 4 * lane;
 #pragma unroll
             for (int i = 0; i < B; ++i)
                 if (i < kcount) {

@@ -59,7 +59,7 @@ int nova_launch_attn_decode_paged_static(const nova_kv_shape* sh, const float* q
                                          const void* pool_v, const int32_t* table, int layer, int nb, int n_keys,
                                          float* o, nova_stream_t s) {
     if (!sh || !q || !pool_k || !pool_v || !table || !o || layer < 0 || nb <= 0) return NOVA_ERR_INVALID;
-    if (sh->head_dim != kHeadDim || sh->kv_block != kKvBlock) return NOVA_ERR_UNSUPPORTED;
+    if (sh->head_dim != kHeadDim || kv_shift_of_block(sh->kv_block) < 0) return NOVA_ERR_UNSUPPORTED;
     if (sh->n_kv_heads <= 0 || sh->n_heads % sh->n_kv_heads) return NOVA_ERR_INVALID;
     // The one size the fixed array cannot follow: more query heads than it has rows for.
     if ((size_t)sh->n_heads > kStaticMaxHeads) return NOVA_ERR_TOO_LARGE;
@@ -71,6 +71,7 @@ int nova_launch_attn_decode_paged_static(const nova_kv_shape* sh, const float* q
     std::memset(&a, 0, sizeof(a));
     a.pool_k = pool_k;
     a.pool_v = pool_v;
+    a.kv_shift = kv_shift_of_block(sh->kv_block);
     a.table_base = table;
     a.table_stride = std::numeric_limits<int32_t>::max();
     a.keys_imm = n_keys;

@@ -11,8 +11,13 @@
 namespace novab {
 
 constexpr int kHeadDim = 128;   // the only head_dim built (every model of the reference uses 128)
-constexpr int kKvBlock = 16;    // tokens per page (the reference's default NOVA_KV_BLOCK)
+constexpr int kKvBlock = 16;    // tokens per page by default (the reference's default NOVA_KV_BLOCK)
 constexpr int kKvShift = 4;
+// Pages of 8, 16, 32 or 64 tokens (NOVA_KV_BLOCK, code/graph/kv_pool_cfg.h:12-26) are a runtime property of a
+// launch: kv_shift = log2(tokens per page).  The kernels stream TILES of kTileKeys = min(16, page) keys: a page of
+// 32 or 64 tokens is 2 or 4 tiles that share one block-table entry, a page of 8 tokens is one half-filled tile.
+constexpr int kTileKeysMax = 16;
+inline int kv_shift_of_block(int kv_block) { return kv_block == 8 ? 3 : kv_block == 16 ? 4 : kv_block == 32 ? 5 : kv_block == 64 ? 6 : -1; }
 constexpr int kPartW = kHeadDim + 2;   // partial row handed to callers: m, l, acc[128]  (src/kernel/attn.cu:150-158)
 constexpr int kSlotW = kHeadDim + 4;   // the same row inside the split-K scratch: m, l, 2 pad, acc[128] (acc 16-byte aligned)
 // 1/sqrt(128), the literal the reference uses (src/kernel/attn.cu:21)
@@ -91,8 +96,10 @@ template <> struct KvTraits<__half> {
 // others are merged, in CTA order, by the combine kernel that follows the split kernel
 // (the reference's split + combine pair, src/kernel/attn.cu:498-512).
 struct AttnLaunch {
-    const void* pool_k;          // [L][NB][16][NKV][128]
+    const void* pool_k;          // [L][NB][page tokens][NKV][128]
     const void* pool_v;
+    int32_t kv_shift;            // log2(tokens per page): 3..6; 0 is read as 4 (16-token pages)
+    int32_t window;              // prefill only: > 0 = sliding window, query at position p sees keys (p - window, p]
     const int32_t* table_base;   // device block tables, one per slice
     int64_t table_stride;        // entries per slice table (nblocks)
     const int32_t* slice_ids;    // [S] slice of each batch entry; nullptr: entry s uses table_base + s*stride
@@ -160,7 +167,7 @@ int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t 
 int attn_default_ctas_simt(int n_kv_heads);
 int attn_default_ctas_mma();
 bool attn_mma_built();
-int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group);
+int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group, int box_rows);
 int launch_attn_prefill(const AttnLaunch& a, cudaStream_t s);     // query-tiled tensor-core prefill (n_q >= 1, one layer)
 int attn_prefill_tile_tokens(int n_heads, int n_kv_heads);
 // Shared-prefix form of the same kernel: decode queries of n_sessions sessions over the shared pages
@@ -183,6 +190,7 @@ int launch_attn_combine_exchange(const AttnLaunch& a, int n_ctas_split, void* co
 int launch_rope_table(float* cs, float* sn, int64_t n_pos, int theta, cudaStream_t s);
 struct AppendLaunch {
     void* pool_k; void* pool_v;
+    int32_t kv_shift;             // log2(tokens per page); 0 is read as 4
     const int32_t* table_base; int64_t table_stride;
     const int32_t* slice_ids;     // [S] or nullptr (see AttnLaunch)
     const int32_t* n_past;        // [S] device write positions, or nullptr: pos_imm

@@ -38,6 +38,7 @@ struct nova_engine {
     size_t elem_bytes = 0;
     int nb = 0, nblocks = 0;
     int kv_group = 0;
+    int kv_shift = kKvShift;         // log2(tokens per page)
     alignas(128) unsigned char tmap_k[128];   // CUtensorMap of each fp16 pool (tensor-core attention)
     alignas(128) unsigned char tmap_v[128];
     alignas(128) unsigned char tmap_k1[128];  // one kv head per box (prefill)
@@ -60,6 +61,7 @@ struct nova_batch {
     int pdl = 0;                     // 1: layers after the first of a step launch as programmatic dependents; 2: the same, but
                                      // they read their q / new k / new v only once the launches before them have finished
     int row_setup = 2;               // work-split weight of a row start, in pages (see AttnLaunch)
+    int window = 0;                  // prefill: sliding window in tokens (0: plain causal)
     int split_ctas = 0;              // CTAs of a chained one-layer attention launch; 0: chosen from the work (pick_split_ctas)
     int cascade = 0;                 // 1: the shared leading pages of the batch's sessions are attended once for all
     int casc_pages = 0;              // shared leading pages found by the last nova_batch_cow (0: none worth it)
@@ -85,7 +87,7 @@ namespace {
 int check_desc(const nova_engine_desc& d) {
     if (d.n_layers <= 0 || d.n_heads <= 0 || d.n_kv_heads <= 0 || d.n_slices <= 0 || d.ctx <= 0) return NOVA_ERR_INVALID;
     if (d.n_heads % d.n_kv_heads) return NOVA_ERR_INVALID;
-    if (d.head_dim != kHeadDim || d.kv_block != kKvBlock) return NOVA_ERR_UNSUPPORTED;
+    if (d.head_dim != kHeadDim || kv_shift_of_block(d.kv_block) < 0) return NOVA_ERR_UNSUPPORTED;
     if (d.kv_dtype != NOVA_KV_F32 && d.kv_dtype != NOVA_KV_F16) return NOVA_ERR_UNSUPPORTED;
     const int g = d.n_heads / d.n_kv_heads;
     if (!(g == 1 || g == 2 || (g >= 4 && g <= 8))) return NOVA_ERR_UNSUPPORTED;
@@ -150,6 +152,7 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.n_heads = e->d.n_heads;
     a.n_kv_heads = e->d.n_kv_heads;
     a.kv_group = e->kv_group;
+    a.kv_shift = e->kv_shift;
     a.page_lo = 0;
     a.page_hi = -1;
     a.row_setup_pages = b->row_setup;
@@ -172,7 +175,7 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
         // Cascade over a shared prefix: (1) all sessions' queries against the shared pages, read once, as
         // partials per page chunk; (2) the usual split over each session's own pages from the first private
         // page on, also as partials; (3) the merge kernel: split-K slots, then the chunks, then the output.
-        const int P = b->casc_pages;
+        const int P = b->casc_pages << (b->e->kv_shift > 4 ? b->e->kv_shift - 4 : 0);      // the shared pages as 16-key tiles
         const int rows = b->n * a.n_heads;
         const int chunks = attn_prefix_chunks(b->n, a.n_heads, a.n_kv_heads, P, nullptr);
         if ((size_t)(chunks + 1) * rows * kPartW > b->casc_floats) return NOVA_ERR_TOO_LARGE;
@@ -182,7 +185,7 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
         if (rc != NOVA_OK) return rc;
         AttnLaunch sa = a;
         sa.pdl_spare = 0;             // the chain here is prefix -> split -> merge -> final merge: early start only
-        sa.page_lo = P;
+        sa.page_lo = b->casc_pages;
         sa.write_partial_only = 1;
         sa.out_part = b->casc_parts + (size_t)chunks * rows * kPartW;
         sa.extra_parts = b->casc_parts;          // the merge kernel folds the chunks in and writes the output
@@ -218,9 +221,11 @@ int pick_split_ctas(const nova_batch* b, const AttnLaunch& a) {
     for (int slice : b->slices) {
         const SliceState* st = pp.find(slice);
         if (!st) continue;
-        int64_t total = (st->n_past + 1 + kKvBlock - 1) >> kKvShift;
-        const int64_t lo = a.page_lo > 0 ? a.page_lo : 0;
-        const int64_t hi = (a.page_hi >= 0 && a.page_hi < total) ? a.page_hi : total;
+        // in tiles of min(16, page) keys, as the kernels count them
+        const int ts = b->e->kv_shift < 4 ? b->e->kv_shift : 4, tpp = b->e->kv_shift - ts;
+        int64_t total = (st->n_past + 1 + (1 << ts) - 1) >> ts;
+        const int64_t lo = a.page_lo > 0 ? (a.page_lo << tpp) : 0;
+        const int64_t hi = (a.page_hi >= 0 && (a.page_hi << tpp) < total) ? (a.page_hi << tpp) : total;
         if (hi > lo) pages += hi - lo;
     }
     pages *= a.n_kv_heads / a.kv_group;
@@ -264,6 +269,7 @@ void fill_append(const nova_batch* b, AppendLaunch& a) {
     a.pool_v = e->pool_v;
     a.table_base = e->tables;
     a.table_stride = e->nblocks;
+    a.kv_shift = e->kv_shift;
     a.slice_ids = b->d_slices;
     a.n_past = b->d_n_past;
     a.cs = e->cs;
@@ -305,6 +311,7 @@ int nova_engine_create(const nova_engine_desc* desc, nova_engine** out) {
     e->elem_bytes = d.kv_dtype == NOVA_KV_F16 ? 2 : 4;
     e->page_bytes = (size_t)d.kv_block * d.n_kv_heads * d.head_dim * e->elem_bytes;
     e->kv_group = kv_group_of(d.n_kv_heads);
+    e->kv_shift = kv_shift_of_block(d.kv_block);
     e->sess.resize((size_t)d.max_sessions);
 
     const size_t pool_bytes = (size_t)d.n_layers * (size_t)e->nb * e->page_bytes;
@@ -324,11 +331,12 @@ int nova_engine_create(const nova_engine_desc* desc, nova_engine** out) {
         return NOVA_ERR_CUDA;
     }
     if (d.kv_dtype == NOVA_KV_F16 && attn_mma_built()) {
-        const int64_t slot_rows = (int64_t)d.n_layers * e->nb * kKvBlock;
-        e->tmaps_ok = attn_make_tmap(e->tmap_k, e->pool_k, slot_rows, d.n_kv_heads, e->kv_group) == NOVA_OK &&
-                      attn_make_tmap(e->tmap_v, e->pool_v, slot_rows, d.n_kv_heads, e->kv_group) == NOVA_OK &&
-                      attn_make_tmap(e->tmap_k1, e->pool_k, slot_rows, d.n_kv_heads, 1) == NOVA_OK &&
-                      attn_make_tmap(e->tmap_v1, e->pool_v, slot_rows, d.n_kv_heads, 1) == NOVA_OK;
+        const int64_t slot_rows = (int64_t)d.n_layers * e->nb * d.kv_block;
+        const int box_rows = d.kv_block < kTileKeysMax ? d.kv_block : kTileKeysMax;      // a tile of the page
+        e->tmaps_ok = attn_make_tmap(e->tmap_k, e->pool_k, slot_rows, d.n_kv_heads, e->kv_group, box_rows) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_v, e->pool_v, slot_rows, d.n_kv_heads, e->kv_group, box_rows) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_k1, e->pool_k, slot_rows, d.n_kv_heads, 1, box_rows) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_v1, e->pool_v, slot_rows, d.n_kv_heads, 1, box_rows) == NOVA_OK;
     }
     int r = launch_rope_table(e->cs, e->sn, d.rope_positions, d.rope_theta, 0);   // Kernel::rope_table, model.cpp:119
     if (r == NOVA_OK && cudaDeviceSynchronize() != cudaSuccess) r = NOVA_ERR_CUDA;
@@ -593,10 +601,11 @@ int nova_launch_rope_append_paged(const nova_kv_shape* sh, void* pool_k, void* p
                                   const float* cs, const float* sn, nova_stream_t s) {
     if (!sh || !pool_k || !pool_v || !table || !k || !v || !cs || !sn || layer < 0 || nb <= 0 || pos0 < 0)
         return NOVA_ERR_INVALID;
-    if (sh->head_dim != kHeadDim || sh->kv_block != kKvBlock) return NOVA_ERR_UNSUPPORTED;
+    if (sh->head_dim != kHeadDim || kv_shift_of_block(sh->kv_block) < 0) return NOVA_ERR_UNSUPPORTED;
     AppendLaunch a;
     std::memset(&a, 0, sizeof(a));
     a.pool_k = pool_k; a.pool_v = pool_v;
+    a.kv_shift = kv_shift_of_block(sh->kv_block);
     a.table_base = table;
     a.table_stride = std::numeric_limits<int32_t>::max();   // the caller vouches for the table length, as in the reference
     a.pos_imm = pos0;
@@ -615,11 +624,12 @@ int nova_launch_attn_decode_paged(const nova_kv_shape* sh, const float* q, const
                                   const int32_t* table, int layer, int nb, int n_keys, float* o, float* scratch,
                                   nova_stream_t s) {
     if (!sh || !q || !pool_k || !pool_v || !table || !o || !scratch || layer < 0 || nb <= 0) return NOVA_ERR_INVALID;
-    if (sh->head_dim != kHeadDim || sh->kv_block != kKvBlock) return NOVA_ERR_UNSUPPORTED;
+    if (sh->head_dim != kHeadDim || kv_shift_of_block(sh->kv_block) < 0) return NOVA_ERR_UNSUPPORTED;
     if (sh->n_kv_heads <= 0 || sh->n_heads % sh->n_kv_heads) return NOVA_ERR_INVALID;
     AttnLaunch a;
     std::memset(&a, 0, sizeof(a));
     a.pool_k = pool_k; a.pool_v = pool_v;
+    a.kv_shift = kv_shift_of_block(sh->kv_block);
     a.table_base = table;
     a.table_stride = std::numeric_limits<int32_t>::max();
     a.keys_imm = n_keys;
@@ -792,6 +802,11 @@ int nova_batch_set_row_setup_pages(nova_batch* b, int pages) {
     if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
     return NOVA_OK;
 }
+int nova_batch_set_window(nova_batch* b, int window_tokens) {
+    if (!b || window_tokens < 0) return NOVA_ERR_INVALID;
+    b->window = window_tokens;
+    return NOVA_OK;
+}
 int nova_batch_set_split_ctas(nova_batch* b, int n_ctas) {
     if (!b || n_ctas < 0 || n_ctas > kMaxSplitCtas) return NOVA_ERR_INVALID;
     b->split_ctas = n_ctas;
@@ -820,11 +835,11 @@ static int shared_prefix_pages(const nova_batch* b) {
     if (b->n < 4) return 0;
     const SliceState* first = e->pool.p.find(b->slices[0]);
     if (!first) return 0;
-    int64_t limit = first->n_past >> kKvShift;
+    int64_t limit = first->n_past >> e->kv_shift;
     for (int i = 1; i < b->n; ++i) {
         const SliceState* st = e->pool.p.find(b->slices[(size_t)i]);
         if (!st) return 0;
-        if ((st->n_past >> kKvShift) < limit) limit = st->n_past >> kKvShift;
+        if ((st->n_past >> e->kv_shift) < limit) limit = st->n_past >> e->kv_shift;
     }
     if (limit > (int64_t)first->table.size()) limit = (int64_t)first->table.size();
     for (int i = 1; i < b->n && limit > 0; ++i) {
@@ -833,7 +848,7 @@ static int shared_prefix_pages(const nova_batch* b) {
         while (p < limit && st->table[(size_t)p] == first->table[(size_t)p]) ++p;
         limit = p;
     }
-    return limit >= 16 ? (int)limit : 0;        // below 256 shared tokens the extra launches cost more than they save
+    return (limit << e->kv_shift) >= 256 ? (int)limit : 0;        // below 256 shared tokens the extra launches cost more than they save
 }
 
 int nova_batch_set_cascade(nova_batch* b, int on) {
@@ -930,6 +945,7 @@ int nova_batch_prefill(nova_batch* b, int layer, int n_tokens, float* q, float* 
                        nova_stream_t s) {
     if (!b || !q || !k || !v || !out || layer < 0 || layer >= b->e->d.n_layers || n_tokens < 1) return NOVA_ERR_INVALID;
     if (n_tokens > nova_batch_prefill_max_tokens(b)) return NOVA_ERR_TOO_LARGE;
+    if (b->window > 0 && b->kernel != 1) return NOVA_ERR_UNSUPPORTED;      // the window is a tensor-core prefill feature
     nova_engine* e = b->e;
     for (int i = 0; i < b->n; ++i)
         if (!e->pool.p.find(b->slices[(size_t)i])) return NOVA_ERR_INVALID;
@@ -959,6 +975,7 @@ int nova_batch_prefill(nova_batch* b, int layer, int n_tokens, float* q, float* 
     at.q = q; at.out = out;
     at.layer0 = layer; at.n_layers = 1;
     at.n_q = n_tokens;
+    at.window = b->window;
     return run_attn(b, at, (cudaStream_t)s);
 }
 

@@ -61,14 +61,15 @@ __global__ void __launch_bounds__(256) rope_append_kernel(AppendLaunch a) {
     int64_t row = -1;   // element offset of this head's row in the pools
     if (!is_q) {
         const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
-        const int64_t lb = pos >> kKvShift;
+        const int kvs = a.kv_shift ? a.kv_shift : kKvShift;
+        const int64_t lb = pos >> kvs;
         int phys = -1;
         if (pos >= 0 && lb < a.table_stride) phys = __ldg(table + lb);
         if (phys < 0 || phys >= a.nb) {
             if (i == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
         } else {
-            const int slot = (int)(pos & (kKvBlock - 1));
-            row = (((int64_t)layer * a.nb + phys) * kKvBlock + slot) * (int64_t)NKV * HD + (int64_t)kvh * HD;
+            const int slot = (int)(pos & ((1 << kvs) - 1));
+            row = ((((int64_t)layer * a.nb + phys) << kvs) + slot) * (int64_t)NKV * HD + (int64_t)kvh * HD;
         }
     }
 

@@ -167,7 +167,7 @@ typedef struct {
     int32_t n_heads;        /* Model::NH                                          */
     int32_t n_kv_heads;     /* Model::NKV (NH % NKV == 0)                         */
     int32_t head_dim;       /* Model::HD; 128 only                                */
-    int32_t kv_block;       /* kKvBlock (code/graph/kv_pool_cfg.h:18); 16 only    */
+    int32_t kv_block;       /* kKvBlock = NOVA_KV_BLOCK (code/graph/kv_pool_cfg.h:12-26): 8, 16, 32 or 64 */
     int32_t kv_dtype;       /* NOVA_KV_F32 | NOVA_KV_F16                          */
     int32_t rope_theta;     /* Model::theta (1000000 / 500000 / 10000)            */
     int32_t rope_neox;      /* 1 = pairs (i, i+HD/2) (Qwen2), 0 = (2i, 2i+1)      */
@@ -362,6 +362,10 @@ int  nova_batch_advance(nova_batch* b, nova_stream_t s);
  * n_tokens <= nova_batch_prefill_max_tokens(b) per call; after the last layer call
  * nova_batch_advance_by(b, n_tokens). */
 int  nova_batch_prefill_max_tokens(const nova_batch* b);
+/* Sliding-window prefill (flash_paged_kernel<true>, src/kernel/attn.cu:317, MaskKind::CausalSWA): a query at
+ * position p sees keys (p - window_tokens, p].  0 = plain causal (every model of the reference).  Tensor-core
+ * kernel only; nova_batch_prefill returns NOVA_ERR_UNSUPPORTED otherwise. */
+int  nova_batch_set_window(nova_batch* b, int window_tokens);
 int  nova_batch_prefill(nova_batch* b, int layer, int n_tokens, float* q, float* k, const float* v, float* out,
                         nova_stream_t s);
 int  nova_batch_advance_by(nova_batch* b, int n_tokens, nova_stream_t s);

@@ -24,7 +24,7 @@ class Shape(C.Structure):
 
 
 _oracle = None
-_ref_host = None
+_ref_host: dict[int, C.CDLL] = {}
 _ref_gpu: dict[str, C.CDLL] = {}
 
 
@@ -55,7 +55,7 @@ def oracle() -> C.CDLL:
         o.oracle_attn_decode_paged_f64.restype = None
         o.oracle_attn_decode_paged_f64.argtypes = [P, vp, vp, vp, vp, i32, i32, i32, vp]
         o.oracle_attn_prefill_paged.restype = None
-        o.oracle_attn_prefill_paged.argtypes = [P, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+        o.oracle_attn_prefill_paged.argtypes = [P, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
         o.oracle_attn_partial_f64.restype = None
         o.oracle_attn_partial_f64.argtypes = [P, vp, vp, vp, vp, i32, i32, i32, i64, i64, vp]
         o.oracle_lse_combine.restype, o.oracle_lse_combine.argtypes = None, [vp, i32, i32, i32, vp]
@@ -67,11 +67,11 @@ def oracle() -> C.CDLL:
     return _oracle
 
 
-def ref_host() -> C.CDLL | None:
-    """The reference's own KvPool / kv_block / BlockRegistry behind a C shim, or None if unbuilt."""
-    global _ref_host
-    if _ref_host is None:
-        so = _build.build_ref_host()
+def ref_host(kv_block: int = 16) -> C.CDLL | None:
+    """The reference's own KvPool / kv_block / BlockRegistry behind a C shim (compiled with NOVA_KV_BLOCK =
+    kv_block), or None if unbuilt."""
+    if kv_block not in _ref_host:
+        so = _build.build_ref_host(kv_block=kv_block)
         if so is None:
             return None
         r = C.CDLL(so)
@@ -108,8 +108,8 @@ def ref_host() -> C.CDLL | None:
         r.ref_registry_find.restype, r.ref_registry_find.argtypes = i32, [vp, u64, u64, vp]
         r.ref_registry_live.restype, r.ref_registry_live.argtypes = i32, [vp]
         r.ref_registry_total.restype, r.ref_registry_total.argtypes = i32, [vp]
-        _ref_host = r
-    return _ref_host
+        _ref_host[kv_block] = r
+    return _ref_host[kv_block]
 
 
 def ref_gpu(model: str) -> C.CDLL | None:
@@ -142,8 +142,8 @@ def ref_gpu(model: str) -> C.CDLL | None:
 class RefPool:
     """The reference's KvPool, same method names as the product's PoolView."""
 
-    def __init__(self):
-        self.r = ref_host()
+    def __init__(self, kv_block: int = 16):
+        self.r = ref_host(kv_block)
         if self.r is None:
             raise RuntimeError("reference host library is not built")
         self.h = self.r.ref_pool_create()
@@ -253,12 +253,13 @@ def attn_decode_paged(sh, q, pool_k, pool_v, table, layer, nb, n_keys, exact=Fal
     return o
 
 
-def attn_prefill_paged(sh, q, pool_k, pool_v, table, layer, nb, n_q, n_past) -> np.ndarray:
-    """q [n_q][NH][HD] -> o, in the arithmetic order of the reference's flash_paged_kernel."""
+def attn_prefill_paged(sh, q, pool_k, pool_v, table, layer, nb, n_q, n_past, window=0) -> np.ndarray:
+    """q [n_q][NH][HD] -> o, in the arithmetic order of the reference's flash_paged_kernel; window > 0: its sliding-
+    window instantiation with that many visible keys (the reference fixes the window at kCtx)."""
     t = np.ascontiguousarray(table, dtype=np.int32)
     qq = np.ascontiguousarray(q, dtype=np.float32)
     o = np.empty_like(qq)
-    oracle().oracle_attn_prefill_paged(C.byref(sh), _p(qq), _p(pool_k), _p(pool_v), _p(t), layer, nb, n_q, n_past, _p(o))
+    oracle().oracle_attn_prefill_paged(C.byref(sh), _p(qq), _p(pool_k), _p(pool_v), _p(t), layer, nb, n_q, n_past, window, _p(o))
     return o
 
 

@@ -23,6 +23,7 @@ REF_OUT = os.path.join(HERE, "_ref")
 
 ORACLE_SO = os.path.join(BUILD, "libpaged_decode_oracle.so")
 REF_HOST_SO = os.path.join(REF_OUT, "libnova_ref_host.so")
+REF_HOST_BLOCKS = (16, 8, 32, 64)          # NOVA_KV_BLOCK variants of the reference's host headers
 # name -> the reference's compile-time switches: the model (include/nova/model/select.h) and, for the
 # page-size variants, NOVA_KV_BLOCK (code/graph/kv_pool_cfg.h:12-26)
 REF_GPU_MODELS = {
@@ -70,16 +71,22 @@ def build_oracle(force: bool = False) -> str:
     return ORACLE_SO
 
 
-def build_ref_host(force: bool = False) -> str | None:
+def ref_host_so(kv_block: int = 16) -> str:
+    return REF_HOST_SO if kv_block == 16 else os.path.join(REF_OUT, f"libnova_ref_host_kb{kv_block}.so")
+
+
+def build_ref_host(force: bool = False, kv_block: int = 16) -> str | None:
     ref = reference_dir()
     src = os.path.join(HERE, "ref_host_shim.cpp")
+    so = ref_host_so(kv_block)
     if ref is None:
-        return REF_HOST_SO if os.path.exists(REF_HOST_SO) else None
-    if not force and _newer(REF_HOST_SO, [src]):
-        return REF_HOST_SO
+        return so if os.path.exists(so) else None
+    if not force and _newer(so, [src]):
+        return so
     os.makedirs(REF_OUT, exist_ok=True)
-    _run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", f"-I{ref}/code", f"-I{ref}/include", src, "-o", REF_HOST_SO])
-    return REF_HOST_SO
+    _run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", f"-DNOVA_KV_BLOCK={kv_block}", f"-I{ref}/code", f"-I{ref}/include",
+          src, "-o", so])
+    return so
 
 
 def build_ref_gpu(force: bool = False) -> dict[str, str]:
@@ -111,7 +118,8 @@ def build_ref_gpu(force: bool = False) -> dict[str, str]:
 
 def build_all(force: bool = False) -> None:
     build_oracle(force)
-    build_ref_host(force)
+    for kb in REF_HOST_BLOCKS:
+        build_ref_host(force, kb)
     build_ref_gpu(force)
 
 

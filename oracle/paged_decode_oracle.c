@@ -307,11 +307,13 @@ void oracle_attn_decode_paged_f64(const oracle_shape* sh, const float* q, const 
         attn_head_f64(sh, q + (size_t)h * HD, pool_k, pool_v, table, layer, nb, n_keys, h / G, o + (size_t)h * HD);
 }
 
-/* ---- prefill attention, order-faithful: flash_paged_kernel<false>, src/kernel/attn.cu:292-357 ----
+/* ---- prefill attention, order-faithful: flash_paged_kernel<SWA>, src/kernel/attn.cu:292-357 ----
  * one warp per (head, query): every lane an fma chain over its 4 dims, the shuffle-tree sum, online
- * softmax over keys 0..n_past+qi in order, out = acc / l.  q, o: [n_q][NH][HD]. */
+ * softmax over keys start..n_past+qi in order, out = acc / l.  q, o: [n_q][NH][HD].
+ * window == 0: the causal instantiation (start = 0).  window > 0: the sliding-window one, attn.cu:317,
+ * start = max(0, pos - window + 1); the reference fixes the window at kCtx, here it is a parameter. */
 void oracle_attn_prefill_paged(const oracle_shape* sh, const float* q, const void* pool_k, const void* pool_v,
-                               const int32_t* table, int layer, int nb, int n_q, int n_past, float* o) {
+                               const int32_t* table, int layer, int nb, int n_q, int n_past, int window, float* o) {
     const int HD = sh->head_dim, NH = sh->n_heads, NKV = sh->n_kv_heads, KB = sh->kv_block, G = NH / NKV;
     const float scale = HD == 64 ? 0.125f : 0.08838834764831845f;
     int shift = 0;
@@ -324,7 +326,9 @@ void oracle_attn_prefill_paged(const oracle_shape* sh, const float* q, const voi
             const float* qp = q + ((size_t)qi * NH + h) * HD;
             float m = -INFINITY, l = 0.f, acc[128];
             for (int d = 0; d < HD; ++d) acc[d] = 0.f;
-            for (int p = 0; p <= n_past + qi; ++p) {
+            const int pos = n_past + qi;
+            const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+            for (int p = start; p <= pos; ++p) {
                 const int64_t row = (((int64_t)layer * nb + table[p >> shift]) * KB + (p & (KB - 1))) * (int64_t)NKV * HD + (int64_t)kvh * HD;
                 float lanes[32];
                 for (int lane = 0; lane < 32; ++lane) {

@@ -282,14 +282,15 @@ def test_other_rope_layouts_vs_reference_kernels(nv, ob, model):
         eng.close()
 
 
-def build_case(nv, ob, model, kvd, ctx_lens, L=2, seed=21, spare=0):
+def build_case(nv, ob, model, kvd, ctx_lens, L=2, seed=21, spare=0, kv_block=16, extra_ctx=40):
     """Engine + sessions with permuted tables and random cached context, mirrored in numpy pools."""
     NH, NKV = SHAPES[model]
     theta, neox = ROPE.get(model, (1000000, 1))
-    ctx = ((max(ctx_lens) + 40 + 15) // 16) * 16
-    eng = nv.Engine(L, NH, NKV, ctx=ctx, n_slices=len(ctx_lens) + spare, kv_dtype=kvd, rope_theta=theta, rope_neox=neox)
+    ctx = ((max(ctx_lens) + extra_ctx + 63) // 64) * 64
+    eng = nv.Engine(L, NH, NKV, ctx=ctx, n_slices=len(ctx_lens) + spare, kv_dtype=kvd, rope_theta=theta, rope_neox=neox,
+                    kv_block=kv_block)
     rng = np.random.default_rng(seed)
-    sh = ob.shape(L, NH, NKV, kvd, rope_neox=neox)
+    sh = ob.shape(L, NH, NKV, kvd, rope_neox=neox, kv_block=kv_block)
     pk, pv = ob.new_pools(sh, eng.nb)
     cs, sn = eng.rope_tables()
     shp = eng.shape()

@@ -85,14 +85,19 @@ def test_pool_errors_are_codes(nv):
     assert nv.PoolView(kv_block=32).init(2, 100) == 0
 
 
+@pytest.mark.parametrize("kv_block", [16, 8, 32, 64])
 @pytest.mark.parametrize("seed", range(8))
-def test_pool_vs_reference_live(nv, ob, seed):
-    if ob.ref_host() is None:
+def test_pool_vs_reference_live(nv, ob, seed, kv_block):
+    """Random operation sequences against the reference's KvPool compiled with the same NOVA_KV_BLOCK
+    (code/graph/kv_pool_cfg.h:12-26): every page size the reference allows."""
+    if ob.ref_host(kv_block) is None:
         pytest.skip("reference host library not built here")
-    rnd = random.Random(seed)
+    if kv_block != 16 and seed >= 4:
+        pytest.skip("four sequences per non-default page size")
+    rnd = random.Random(seed * 100 + kv_block)
     n_slices, ctx = rnd.randint(2, 7), rnd.choice([16, 48, 100, 160, 2048])
-    nblocks = (ctx + 15) // 16
-    mine, ref = nv.PoolView(), ob.RefPool()
+    nblocks = (ctx + kv_block - 1) // kv_block
+    mine, ref = nv.PoolView(kv_block=kv_block), ob.RefPool(kv_block)
     mine.init(n_slices, ctx)
     ref.init(n_slices, ctx)
     live = []
