@@ -236,7 +236,8 @@ def run_ours(args):
     PF_REPS = 3
     total_steps = 7 * (W + K) + (W + KE) + 8 + (PF_REPS + 1) * 512
     work = wl.Workload(w["model"], lens, seed=seed, steps=total_steps, device=local_rank,
-                       shared_prefix=w.get("prefix", 0), kv_dtype=nv.KV_F32 if args.kv == "f32" else nv.KV_F16)
+                       shared_prefix=w.get("prefix", 0), kv_dtype=nv.KV_F32 if args.kv == "f32" else nv.KV_F16,
+                       kv_block=args.page_tokens)
     eng, batch = work.eng, work.batch
     opt = configure_batch(nv, batch, args, prefix=bool(w.get("prefix", 0)))
     kernel, fused, cascade = opt["kernel"], opt["fused"], opt["cascade"]
@@ -332,7 +333,7 @@ def run_ours(args):
         prefill = prefill_sample(nv, work, stream, PF_REPS)
 
     ref_gpu = drop_in = None
-    if rank == 0 and world == 1 and not args.no_ref_gpu and args.workload in ("c1", "c2"):
+    if rank == 0 and world == 1 and not args.no_ref_gpu and args.workload in ("c1", "c2") and args.page_tokens == 16:
         ref_gpu, drop_in = reference_gpu_sample(nv, work)
 
     line = None
@@ -358,7 +359,7 @@ def run_ours(args):
             "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None,
             "dtype": args.kv, "data": "synthetic",
             "config": {"workload": f"{args.workload}: {w['text']}", "sessions_per_gpu": S,
-                       "context_tokens": lens, "layers": L, "kv_dtype": "fp16" if args.kv == "f16" else "fp32", "page_tokens": 16,
+                       "context_tokens": lens, "layers": L, "kv_dtype": "fp16" if args.kv == "f16" else "fp32", "page_tokens": args.page_tokens,
                        "launch": args.launch, "attention_kernel": "mma" if kernel == 1 else "simt", "fused_append": fused,
                        "pdl": opt["pdl"], "late_inputs": late_main,
                        "cascade_shared_pages": batch.shared_prefix_pages() if cascade else 0,
@@ -695,9 +696,9 @@ def cpu_baseline_sample(nv, work, lens, seed):
     eng = work.eng
     L, S = eng.L, len(work.sessions)
     sample_layers = 1
-    sh = ob.shape(sample_layers, eng.NH, eng.NKV, ob.KV_F16)
+    sh = ob.shape(sample_layers, eng.NH, eng.NKV, ob.KV_F16, kv_block=eng.desc.kv_block)
     n = eng.nb * eng.page_bytes // 2
-    shp = (sample_layers, eng.nb, 16, eng.NKV, eng.HD)
+    shp = (sample_layers, eng.nb, eng.desc.kv_block, eng.NKV, eng.HD)
     pk = nv.download_ptr(eng.k_base, np.float16, n).reshape(shp)
     pv = nv.download_ptr(eng.v_base, np.float16, n).reshape(shp)
     cs, sn = eng.rope_tables()
@@ -829,6 +830,8 @@ def main():
                     help="headline with q / new k / new v read only after the previous layer's kernels have finished")
     ap.add_argument("--kv", default="f16", choices=["f16", "f32"],
                     help="KV pool element type (f32 = the reference's own format)")
+    ap.add_argument("--page-tokens", type=int, default=16, choices=[8, 16, 32, 64],
+                    help="tokens per KV page (the reference's NOVA_KV_BLOCK; single-GPU workloads)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own kernels (sm_100a build)")
     ap.add_argument("--no-scaling-workloads", action="store_true", help="skip configurations 4 and 5 after the headline")

@@ -46,7 +46,7 @@ class Workload:
     """An engine, its sessions and one batch over them, with `ctx_lens[s]` cached tokens each."""
 
     def __init__(self, model: str, ctx_lens, *, seed: int, steps: int, kv_dtype=KV_F16, device=0, permute=True,
-                 spare_slices=0, fill=True, n_layers=None, zero_pages=0, shared_prefix=0, key_base=0):
+                 spare_slices=0, fill=True, n_layers=None, zero_pages=0, shared_prefix=0, key_base=0, kv_block=16):
         """ctx_lens[s] cached tokens per session.  shared_prefix > 0: one extra donor session holds that
         many tokens; every session attaches them (KvPool::attach_prefix: shared pages, the partly filled
         tail page included), un-shares the tail page on its first private write and appends
@@ -58,9 +58,10 @@ class Workload:
         self.ctx_lens = [int(c) for c in ctx_lens]
         self.shared_prefix = int(shared_prefix)
         S = len(self.ctx_lens)
-        ctx = ((max(self.ctx_lens) + steps + 15) // 16) * 16
+        self.kv_block = int(kv_block)
+        ctx = ((max(self.ctx_lens) + steps + kv_block - 1) // kv_block) * kv_block
         extra = (2 if shared_prefix else 0) + spare_slices        # donor + one slice of spare pages for COW
-        self.eng = Engine(L, NH, NKV, ctx=ctx, n_slices=S + extra, kv_dtype=kv_dtype,
+        self.eng = Engine(L, NH, NKV, ctx=ctx, n_slices=S + extra, kv_dtype=kv_dtype, kv_block=kv_block,
                           rope_positions=ctx, device=device, zero_pages=zero_pages, max_sessions=S + (1 if shared_prefix else 0))
         self.donor = None
         if shared_prefix:
@@ -168,7 +169,7 @@ class Workload:
         per_tok = 2 * e.NKV * e.HD * es * e.L
         if not self.shared_prefix:
             return self.kv_bytes_per_step(n_past)
-        full_pages = (self.shared_prefix // 16) * 16             # the tail page is private after its COW
+        full_pages = (self.shared_prefix // self.kv_block) * self.kv_block      # the tail page is private after its COW
         keys = full_pages + sum(n + 1 - full_pages for n in n_past)
         return keys * per_tok + len(self.sessions) * per_tok
 

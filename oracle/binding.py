@@ -139,6 +139,27 @@ def ref_gpu(model: str) -> C.CDLL | None:
     return _ref_gpu[model]
 
 
+_shim: dict[str, C.CDLL] = {}
+
+
+def shim_exec(model: str) -> C.CDLL | None:
+    """The reference's call sites bound to the product library through include/nova_b200_shim.h (oracle/shim_exec.cpp),
+    or None if unbuilt.  The product library must be loaded already (the package import does that)."""
+    if model not in _shim:
+        so = _build.shim_so(model)
+        if not os.path.exists(so):
+            so = _build.build_shim_exec().get(model)
+            if so is None:
+                return None
+        g = C.CDLL(so)
+        g.shim_shape.restype, g.shim_shape.argtypes = None, [c_i32p]
+        g.shim_rope_table.restype, g.shim_rope_table.argtypes = None, [vp, vp, vp]
+        g.shim_decode_layer.restype = None
+        g.shim_decode_layer.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i64, vp, vp, vp, vp, vp]
+        _shim[model] = g
+    return _shim[model]
+
+
 class RefPool:
     """The reference's KvPool, same method names as the product's PoolView."""
 

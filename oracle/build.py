@@ -116,11 +116,45 @@ def build_ref_gpu(force: bool = False) -> dict[str, str]:
     return out
 
 
+SHIM_MODELS = {"qwen25_7b": "NOVA_MODEL_QWEN25_7B", "r1_llama8b": "NOVA_MODEL_R1_LLAMA8B"}
+
+
+def shim_so(model: str) -> str:
+    return os.path.join(REF_OUT, f"libnova_shim_{model}.so")
+
+
+def build_shim_exec(force: bool = False) -> dict[str, str]:
+    """oracle/_ref/libnova_shim_<model>.so: the reference's call sites (include/nova/kernel.h) bound to the product
+    through include/nova_b200_shim.h, to be executed by the GPU tests.  Needs the reference tree, g++, the CUDA
+    headers and the built product library; elsewhere the prebuilt files are used."""
+    ref = reference_dir()
+    out: dict[str, str] = {}
+    src = os.path.join(HERE, "shim_exec.cpp")
+    lib_dir = os.path.join(REPO, "conflux-nova_b200")
+    cuda_inc = "/usr/local/cuda/include"
+    can_build = (ref is not None and shutil.which("g++") and os.path.isdir(cuda_inc)
+                 and os.path.exists(os.path.join(lib_dir, "libnova_b200.so")))
+    for model, macro in SHIM_MODELS.items():
+        so = shim_so(model)
+        if not can_build:
+            if os.path.exists(so):
+                out[model] = so
+            continue
+        if force or not _newer(so, [src, os.path.join(REPO, "include", "nova_b200_shim.h"), os.path.join(REPO, "include", "nova_b200.h")]):
+            os.makedirs(REF_OUT, exist_ok=True)
+            _run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", f"-D{macro}", f"-I{ref}/include", f"-I{ref}/code",
+                  f"-I{REPO}/include", f"-I{cuda_inc}", src, "-o", so, f"-L{lib_dir}", "-lnova_b200",
+                  "-Wl,-rpath,$ORIGIN/../../conflux-nova_b200"])
+        out[model] = so
+    return out
+
+
 def build_all(force: bool = False) -> None:
     build_oracle(force)
     for kb in REF_HOST_BLOCKS:
         build_ref_host(force, kb)
     build_ref_gpu(force)
+    build_shim_exec(force)
 
 
 if __name__ == "__main__":
