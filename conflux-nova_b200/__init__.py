@@ -112,7 +112,7 @@ SIGNATURES = {
     "nova_batch_size": (i32, [vp]), "nova_batch_sync_positions": (i32, [vp, vp]),
     "nova_batch_set_timeline": (i32, [vp, vp]),
     "nova_batch_set_pdl": (i32, [vp, i32]), "nova_batch_set_row_setup_pages": (i32, [vp, i32]),
-    "nova_batch_set_split_ctas": (i32, [vp, i32]), "nova_batch_set_window": (i32, [vp, i32]),
+    "nova_batch_set_split_ctas": (i32, [vp, i32]), "nova_batch_set_window": (i32, [vp, i32]), "nova_batch_set_prefill_kernel": (i32, [vp, i32]),
     "nova_batch_set_fused_append": (i32, [vp, i32]), "nova_batch_append_attn": (i32, [vp, i32, vp, vp, vp, vp, vp]),
     "nova_batch_set_kernel": (i32, [vp, i32]), "nova_batch_get_kernel": (i32, [vp]),
     "nova_batch_cow": (i32, [vp, vp]), "nova_batch_append": (i32, [vp, i32, vp, vp, vp, vp]),
@@ -474,6 +474,7 @@ class Batch:
     def set_kernel(self, which): return check(lib.nova_batch_set_kernel(self.h, which), "set_kernel")
     def set_fused_append(self, on): return check(lib.nova_batch_set_fused_append(self.h, int(on)), "set_fused_append")
     def set_pdl(self, on): return check(lib.nova_batch_set_pdl(self.h, int(on)), "set_pdl")
+    def set_prefill_kernel(self, which): return check(lib.nova_batch_set_prefill_kernel(self.h, int(which)), "set_prefill_kernel")
     def set_window(self, n): return check(lib.nova_batch_set_window(self.h, int(n)), "set_window")
     def set_split_ctas(self, n): return check(lib.nova_batch_set_split_ctas(self.h, int(n)), "set_split_ctas")
     def set_row_setup_pages(self, n): return check(lib.nova_batch_set_row_setup_pages(self.h, int(n)), "set_row_setup")

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnova_b200.so")
-SOURCES = ["hal.cu", "rope_append.cu", "attn_simt.cu", "attn_mma.cu", "attn_combine.cu", "attn_prefill.cu", "attn_static.cu", "synth.cu", "engine.cu", "host_capi.cpp"]
+SOURCES = ["hal.cu", "rope_append.cu", "attn_simt.cu", "attn_mma.cu", "attn_combine.cu", "attn_prefill.cu", "attn_prefill_tc5.cu", "attn_static.cu", "synth.cu", "engine.cu", "host_capi.cpp"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 

@@ -1,0 +1,392 @@
+// attn_prefill_tc5.cu — paged prefill attention on the fifth-generation tensor cores (tcgen05 + tensor memory).
+// Same contract as attn_prefill.cu (replaces flash_paged_kernel, src/kernel/attn.cu:292-357 of the reference, causal
+// and sliding-window), built for a contraction-bound shape: the scores S = Q.K^T and the outputs O += P.V are
+// tcgen05.mma instructions issued by one thread, their accumulators live in tensor memory, and the 128 threads of
+// the softmax warps each own one query row of them.
+//
+//   * One CTA = (session, kv head, tile of 128 / G query tokens): the (token, head) pairs that share the kv head are
+//     the M = 128 rows of the tile.  Q is converted once to fp16 (scaled by 1/sqrt(128) * log2 e) and laid out in
+//     shared memory in the K-major 128-byte-swizzle form the instruction reads (two slabs of 64 dims).
+//   * K/V arrive 64 keys at a time (four 16-key tiles of pages) through the same TMA boxes as everywhere else
+//     ([64 dims][16 slots][1 kv head], 128-byte swizzle): that layout IS the K-major form for K and the MN-major form
+//     for V, so the pages are consumed as they land, without a transpose.  Two stages of 32 KiB.
+//   * Per 64 keys: eight MMAs (M128 N64 K16) fill S in tensor memory (64 columns); the softmax warps read their row
+//     with tcgen05.ld, mask (causal / window), keep a running reference maximum that only moves when the row maximum
+//     grows by more than 2^8 (so the O accumulator is rescaled rarely), write P as fp16 into shared memory (K-major,
+//     swizzled); four MMAs (M128 N128 K16) add P.V to O (128 columns of tensor memory).
+//   * Two CTAs fit an SM (112 KiB of shared memory, 256 of the 512 tensor-memory columns each), so one CTA's softmax
+//     overlaps the other's MMAs.
+//   * Every mbarrier wait is bounded (NOVA_ERR_TIMEOUT in the status word); tensor memory is released on every path.
+#include "attn_plan.cuh"
+#include "mma_common.cuh"
+
+namespace novab {
+namespace {
+
+constexpr int kT5Rows = 128;                          // query rows of a CTA = M of the MMAs
+constexpr int kT5Keys = 64;                           // keys per K/V tile = N of S = Q.K^T
+constexpr int kT5Stages = 2;
+constexpr int kT5SlabBytes = kT5Keys * 128;           // 64 key rows x 128 B (64 dims): 8 KiB
+constexpr int kT5QSlabBytes = kT5Rows * 128;          // 128 query rows x 128 B: 16 KiB
+constexpr int kT5QBytes = 2 * kT5QSlabBytes;          // dims 0-63 | 64-127
+constexpr int kT5StageBytes = 4 * kT5SlabBytes;       // K dims lo | K dims hi | V dims lo | V dims hi: 32 KiB
+constexpr int kT5PBytes = kT5Rows * 128;              // P: 128 rows x 64 keys fp16
+constexpr int kT5OffStage = kT5QBytes;
+constexpr int kT5OffP = kT5OffStage + kT5Stages * kT5StageBytes;
+constexpr int kT5OffBar = kT5OffP + kT5PBytes;
+constexpr int kT5Smem = kT5OffBar + 128;              // 114816 B: two CTAs per SM
+constexpr int kT5TmemCols = 256;                      // S: columns 0-63, O: columns 128-255
+constexpr uint32_t kT5ColS = 0, kT5ColO = 128;
+constexpr float kRescaleStep = 8.f;                   // the reference maximum moves only when the row maximum grew by more (log2 units)
+
+// Instruction descriptors (kind::f16): fp32 accumulate (bit 4), fp16 A and B (formats 0), N >> 3 at bit 17,
+// M >> 4 at bit 24; bit 16 = B is MN-major (V: the 64 dims of a key row are contiguous).
+constexpr uint32_t kIdescS = (1u << 4) | ((uint32_t)(kT5Keys >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
+constexpr uint32_t kIdescPV = (1u << 4) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
+
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets (all >> 4),
+// descriptor version 1 (bit 46), layout type 2 = SWIZZLE_128B (bits 61-63).  Atoms are 8 rows x 128 B = 1024 B.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive columns of this thread's tensor-memory lane (the warp's 32 lanes = 32 rows of the tile)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+        "%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(160, 2)
+attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, int tq,
+                        int n_qtiles) {
+    // No static shared memory: the dynamic region then starts at the front of the CTA's window, 1024-byte aligned as the
+    // swizzled tiles need, without padding (the 112 KiB + 128 B are sized for two CTAs per SM).
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(smem_raw + kT5OffBar + 64);
+    volatile int& s_abort = *reinterpret_cast<volatile int*>(smem_raw + kT5OffBar + 68);
+
+    const int lane = (int)threadIdx.x & 31;
+    const int warp = (int)threadIdx.x >> 5;
+    const int G = a.n_heads / a.n_kv_heads;
+    const int NH = a.n_heads, NKV = a.n_kv_heads, NQ = a.n_q;
+    const PageGeom geo = page_geom(a.kv_shift);            // 16-key tiles (pages of 16, 32 or 64 tokens)
+    const int tpp_mask = (1 << geo.tpp_shift) - 1;
+    const uint32_t base = smem_u32(smem_raw);
+
+    // blockIdx.x -> (query tile, kv head, session); late tiles (most keys) first
+    int bid = (int)blockIdx.x;
+    const int qtile = n_qtiles - 1 - bid % n_qtiles;
+    bid /= n_qtiles;
+    const int kvh = bid % NKV;
+    const int s = bid / NKV;
+    const int t0 = qtile * tq;
+    const int t_cnt = NQ - t0 < tq ? NQ - t0 : tq;
+    const int n_past = a.n_past ? a.n_past[s] : a.keys_imm;
+    const int keys_all = n_past + a.keys_add + t0 + t_cnt - 1;          // keys seen by the tile's last query
+    const int first_key = a.window > 0 ? n_past + a.keys_add + t0 - a.window : 0;   // nothing before it is visible to any row
+    const int page_begin = first_key > 0 ? first_key >> 4 : 0;          // in 16-key tiles
+    const int page_end = (keys_all + 15) >> 4;
+    const int n_pages = page_end - page_begin;
+    const int n_tiles = (n_pages + 3) >> 2;                             // 64-key tiles
+    const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
+
+    const uint32_t bar_full0 = base + kT5OffBar, bar_sready = bar_full0 + 16, bar_pready = bar_full0 + 24, bar_pvdone = bar_full0 + 32;
+    if (threadIdx.x == 0) {
+        mbar_init(bar_full0, 1);
+        mbar_init(bar_full0 + 8, 1);
+        mbar_init(bar_sready, 1);
+        mbar_init(bar_pready, kT5Rows);
+        mbar_init(bar_pvdone, 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const bool bad_layout = (base & 1023u) != 0 || n_pages <= 0 || ((page_end + tpp_mask) >> geo.tpp_shift) > a.table_stride;
+    if (bad_layout) {                 // uniform over the CTA: nothing has been allocated yet
+        if (threadIdx.x == 0 && a.status && n_pages > 0) atomicCAS(a.status, 0, (base & 1023u) ? NOVA_ERR_UNSUPPORTED : NOVA_ERR_BAD_TABLE);
+        return;
+    }
+    if (warp == 0) {                  // tensor memory: 256 columns for this CTA, released below on every path
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"((uint32_t)kT5TmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    bool failed = false;
+
+    // pages 4i .. 4i+3 of the CTA's range into stage i & 1 (called by the one issuing thread)
+    auto load_tile = [&](int i) {
+        const int stage = i & 1;
+        const uint32_t dst = base + kT5OffStage + (uint32_t)stage * kT5StageBytes;
+        const uint32_t bar = bar_full0 + 8u * (uint32_t)stage;
+        const int p0 = 4 * i, cnt = n_pages - p0 < 4 ? n_pages - p0 : 4;
+        int phys[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) phys[j] = j < cnt ? __ldg(table + ((page_begin + p0 + j) >> geo.tpp_shift)) : 0;
+        mbar_expect_tx(bar, (uint32_t)cnt * 8192u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (j >= cnt) break;
+            int ph = phys[j];
+            if (ph < 0 || ph >= a.nb) {            // never follow a bad entry; the result is flagged invalid
+                if (a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
+                ph = 0;
+            }
+            const int c1 = (int)((((int64_t)a.layer0 * a.nb + ph) << geo.kv_shift) + (((page_begin + p0 + j) & tpp_mask) << 4));
+            const uint32_t d = dst + (uint32_t)j * 2048u;
+            tma_load_3d(d, &tmk, 0, c1, kvh, bar);
+            tma_load_3d(d + kT5SlabBytes, &tmk, 64, c1, kvh, bar);
+            tma_load_3d(d + 2 * kT5SlabBytes, &tmv, 0, c1, kvh, bar);
+            tma_load_3d(d + 3 * kT5SlabBytes, &tmv, 64, c1, kvh, bar);
+        }
+    };
+    if (warp == 4) {
+        // ------------------------------------------------------------- TMA + MMA issue: one thread
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
+            load_tile(0);
+            if (n_tiles > 1) load_tile(1);
+        }
+        __syncwarp();
+    }
+    // ---- Q -> shared memory (softmax threads: one row each), then everybody meets once
+    const int row = (int)threadIdx.x;                       // tile row of a softmax thread
+    int row_tok = 0, row_head = 0, row_lim = -1, row_lo = 0;
+    bool row_ok = false;
+    if (warp < 4) {
+        const int tk = row / G, g = row - tk * G;
+        row_ok = tk < t_cnt && tk < tq;
+        row_tok = t0 + tk;
+        row_head = kvh * G + g;
+        row_lim = row_ok ? n_past + a.keys_add + row_tok - 1 : -1;          // last visible key of the row
+        row_lo = (row_ok && a.window > 0) ? row_lim - a.window + 1 : 0;
+        constexpr float kQScale = kAttnScale * kLog2e;
+        const float* qp = a.q + (((int64_t)s * NQ + row_tok) * NH + row_head) * kHeadDim;
+#pragma unroll 4
+        for (int c = 0; c < 16; ++c) {                     // 16 chunks of 8 dims
+            float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+            if (row_ok) {
+                x0 = *reinterpret_cast<const float4*>(qp + 8 * c);
+                x1 = *reinterpret_cast<const float4*>(qp + 8 * c + 4);
+            }
+            const uint32_t w0 = pack_h2(x0.x * kQScale, x0.y * kQScale), w1 = pack_h2(x0.z * kQScale, x0.w * kQScale);
+            const uint32_t w2 = pack_h2(x1.x * kQScale, x1.y * kQScale), w3 = pack_h2(x1.z * kQScale, x1.w * kQScale);
+            const uint32_t addr = base + (uint32_t)((c >> 3) * kT5QSlabBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        if (lane == 0) {
+            const uint32_t q_lo = base, q_hi = base + kT5QSlabBytes, p_addr = base + kT5OffP;
+            for (int i = 0; i < n_tiles && !failed; ++i) {
+                const int stage = i & 1;
+                const uint32_t st_addr = base + kT5OffStage + (uint32_t)stage * kT5StageBytes;
+                if (!mbar_wait(bar_full0 + 8u * (uint32_t)stage, (uint32_t)(i >> 1) & 1u, &s_abort)) { failed = true; break; }
+                tc_fence_after();
+                // S = Q.K^T: eight K-steps of 16 dims; a step moves 32 bytes inside the swizzled 128-byte row
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint64_t ad = umma_desc((j < 4 ? q_lo : q_hi) + (uint32_t)(j & 3) * 32u, 16u, 1024u);
+                    const uint64_t bd = umma_desc(st_addr + (uint32_t)(j >> 2) * kT5SlabBytes + (uint32_t)(j & 3) * 32u, 16u, 1024u);
+                    umma_f16(tmem + kT5ColS, ad, bd, kIdescS, j > 0 ? 1u : 0u);
+                }
+                umma_commit(bar_sready);
+                if (!mbar_wait(bar_pready, (uint32_t)i & 1u, &s_abort)) { failed = true; break; }
+                tc_fence_after();
+                // O += P.V: four K-steps of 16 keys; V is MN-major: 16 key rows = two 1024-byte atoms (stride), the two
+                // halves of the 128 dims are a slab apart (leading offset)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint64_t ad = umma_desc(p_addr + (uint32_t)j * 32u, 16u, 1024u);
+                    const uint64_t bd = umma_desc(st_addr + 2u * kT5SlabBytes + (uint32_t)j * 2048u, (uint32_t)kT5SlabBytes, 1024u);
+                    umma_f16(tmem + kT5ColO, ad, bd, kIdescPV, (i > 0 || j > 0) ? 1u : 0u);
+                }
+                umma_commit(bar_pvdone);
+                if (i + 2 < n_tiles) {            // the stage is free once these MMAs have read it
+                    if (!mbar_wait(bar_pvdone, (uint32_t)i & 1u, &s_abort)) { failed = true; break; }
+                    load_tile(i + 2);
+                }
+            }
+            if (failed && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------- softmax warps: thread = one row of S and O
+        const uint32_t t_lane = tmem + ((uint32_t)(32 * warp) << 16);        // this warp's 32 lanes of tensor memory
+        const uint32_t p_row = base + kT5OffP + (uint32_t)row * 128u;
+        float m_ref = -INFINITY, l = 0.f;
+        for (int i = 0; i < n_tiles; ++i) {
+            // (the warp decides together: what follows is warp-collective)
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_sready, (uint32_t)i & 1u, &s_abort))) { failed = true; break; }
+            tc_fence_after();
+            uint32_t sv[2][32];
+            tmem_ld32(t_lane + kT5ColS, sv[0]);
+            tmem_ld32(t_lane + kT5ColS + 32, sv[1]);
+            tmem_wait_ld();
+            const int key0 = (page_begin + 4 * i) << 4;
+            const int kcount = keys_all - key0 < kT5Keys ? keys_all - key0 : kT5Keys;     // real keys in this tile
+            const int hi_k = (row_lim < key0 + kcount - 1 ? row_lim : key0 + kcount - 1) - key0;   // last visible column
+            const int lo_k = row_lo - key0;                                                        // first visible column
+            float mx = -INFINITY;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int col = 32 * h + c;
+                    float v = __uint_as_float(sv[h][c]);
+                    v = (col <= hi_k && col >= lo_k) ? v : -INFINITY;
+                    sv[h][c] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+            // reference maximum: moves only when the row maximum outgrew it by more than kRescaleStep
+            float scale = 1.f;
+            if (mx > m_ref + kRescaleStep || (m_ref == -INFINITY && mx > -INFINITY)) {
+                scale = m_ref == -INFINITY ? 0.f : ex2(m_ref - mx);
+                m_ref = mx;
+            }
+            const float ms = m_ref == -INFINITY ? 0.f : m_ref;          // nothing visible yet: keep exp arguments finite
+            uint32_t pk[32];
+            float psum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const int h = c >> 4, cc = (2 * c) & 31;
+                const uint32_t p2 = pack_h2(ex2(__uint_as_float(sv[h][cc]) - ms), ex2(__uint_as_float(sv[h][cc + 1]) - ms));
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&p2));
+                psum += f.x + f.y;                                       // the row sum uses the fp16-rounded weights that multiply V
+                pk[c] = p2;
+            }
+            l = fmaf(l, scale, psum);
+            // the previous tile's P.V must be done before P is overwritten and before O is rescaled
+            if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_pvdone, (uint32_t)(i - 1) & 1u, &s_abort))) { failed = true; break; }
+            if (i > 0 && __any_sync(0xffffffffu, scale != 1.f)) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t ov[32];
+                    tmem_ld32(t_lane + kT5ColO + 32u * (uint32_t)cc, ov);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * scale);
+                    tmem_st32(t_lane + kT5ColO + 32u * (uint32_t)cc, ov);
+                }
+                tmem_wait_st();
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c)                                  // chunk c = keys 8c .. 8c+7 of the row
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_row + (uint32_t)((c ^ (row & 7)) << 4)), "r"(pk[4 * c]),
+                             "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
+                             : "memory");
+            if (kcount < kT5Keys) {
+                // key rows past the last real key hold stale bytes: their weights are 0, but 0 * Inf/NaN would poison O
+                const uint32_t st_addr = base + kT5OffStage + (uint32_t)(i & 1) * kT5StageBytes + 2u * kT5SlabBytes;
+                for (int e = (int)threadIdx.x; e < (kT5Keys - kcount) * 16; e += kT5Rows) {
+                    const int r = kcount + (e >> 4), c = e & 15;
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(st_addr + (uint32_t)((c >> 3) * kT5SlabBytes + r * 128 + ((c & 7) << 4))),
+                                 "r"(0u)
+                                 : "memory");
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar_pready);
+        }
+        if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_pvdone, (uint32_t)(n_tiles - 1) & 1u, &s_abort))) failed = true;
+        if (failed) {
+            if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
+        } else {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float* op = a.out + (((int64_t)s * NQ + row_tok) * NH + row_head) * kHeadDim;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t ov[32];
+                tmem_ld32(t_lane + kT5ColO + 32u * (uint32_t)cc, ov);
+                tmem_wait_ld();
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4)
+                        *reinterpret_cast<float4*>(op + 32 * cc + c) =
+                            make_float4(__uint_as_float(ov[c]) * inv, __uint_as_float(ov[c + 1]) * inv, __uint_as_float(ov[c + 2]) * inv,
+                                        __uint_as_float(ov[c + 3]) * inv);
+                }
+            }
+        }
+    }
+    // ---- release the tensor memory (every path of every thread ends here)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kT5TmemCols) : "memory");
+}
+
+}  // namespace
+
+// Query tokens per CTA of the tcgen05 prefill: as many whole tokens as fit the 128-row tile.
+int attn_prefill_tc5_tile_tokens(int n_heads, int n_kv_heads) { return kT5Rows / (n_heads / n_kv_heads); }
+
+bool attn_prefill_tc5_supports(const AttnLaunch& a) {
+    const int kvs = a.kv_shift ? a.kv_shift : kKvShift;
+    return a.tmap_k1 && a.tmap_v1 && a.n_layers == 1 && a.n_q >= 1 && kvs >= 4 && a.n_heads % a.n_kv_heads == 0 &&
+           a.n_heads / a.n_kv_heads <= kT5Rows;
+}
+
+int launch_attn_prefill_tc5(const AttnLaunch& a, cudaStream_t s) {
+    if (!attn_prefill_tc5_supports(a)) return NOVA_ERR_UNSUPPORTED;
+    if (a.n_sessions <= 0) return NOVA_OK;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    NOVA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5Smem));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    const int tq = attn_prefill_tc5_tile_tokens(a.n_heads, a.n_kv_heads);
+    const int n_qtiles = (a.n_q + tq - 1) / tq;
+    const long long ctas = (long long)n_qtiles * a.n_kv_heads * a.n_sessions;
+    if (ctas > 0x7fffffffLL) return NOVA_ERR_TOO_LARGE;
+    const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k1);
+    const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v1);
+    attn_prefill_tc5_kernel<<<(unsigned)ctas, 160, kT5Smem, s>>>(a, *tk, *tv, tq, n_qtiles);
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+}  // namespace novab

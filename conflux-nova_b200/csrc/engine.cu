@@ -62,6 +62,7 @@ struct nova_batch {
                                      // they read their q / new k / new v only once the launches before them have finished
     int row_setup = 2;               // work-split weight of a row start, in pages (see AttnLaunch)
     int window = 0;                  // prefill: sliding window in tokens (0: plain causal)
+    int prefill_tc5 = 0;             // 1: prefill attention on tcgen05 + tensor memory (attn_prefill_tc5.cu)
     int split_ctas = 0;              // CTAs of a chained one-layer attention launch; 0: chosen from the work (pick_split_ctas)
     int cascade = 0;                 // 1: the shared leading pages of the batch's sessions are attended once for all
     int casc_pages = 0;              // shared leading pages found by the last nova_batch_cow (0: none worth it)
@@ -168,8 +169,11 @@ int pick_split_ctas(const nova_batch* b, const AttnLaunch& a);
 // Split kernel, then the merge of the rows that more than one CTA worked on.
 int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
     int rc, ctas;
-    if (b->kernel == 1 && a.n_q > 1 && a.n_layers == 1 && !a.write_partial_only)
-        return launch_attn_prefill(a, s);        // query-tiled prefill: every row complete in one CTA, no merge
+    if (b->kernel == 1 && a.n_q > 1 && a.n_layers == 1 && !a.write_partial_only) {
+        // query-tiled prefill: every row complete in one CTA, no merge
+        if (b->prefill_tc5 && attn_prefill_tc5_supports(a)) return launch_attn_prefill_tc5(a, s);
+        return launch_attn_prefill(a, s);
+    }
     if (b->kernel == 1 && b->cascade && b->casc_pages > 0 && a.n_layers == 1 && a.n_q <= 1 && !a.write_partial_only &&
         a.page_lo == 0 && a.page_hi < 0) {
         // Cascade over a shared prefix: (1) all sessions' queries against the shared pages, read once, as
@@ -800,6 +804,12 @@ int nova_batch_set_row_setup_pages(nova_batch* b, int pages) {
     if (!b || pages < 0 || pages > 64) return NOVA_ERR_INVALID;
     b->row_setup = pages;
     if (b->graph) { cudaGraphExecDestroy(b->graph); b->graph = nullptr; }
+    return NOVA_OK;
+}
+int nova_batch_set_prefill_kernel(nova_batch* b, int which) {
+    if (!b || which < 0 || which > 1) return NOVA_ERR_INVALID;
+    if (which == 1 && (b->e->d.kv_dtype != NOVA_KV_F16 || !b->e->tmaps_ok || b->e->kv_shift < 4)) return NOVA_ERR_UNSUPPORTED;
+    b->prefill_tc5 = which;
     return NOVA_OK;
 }
 int nova_batch_set_window(nova_batch* b, int window_tokens) {

@@ -368,7 +368,7 @@ def test_fullsize_14b_shape_sessions(nv, ob):
         work.close()
 
 
-@pytest.mark.parametrize("kernel", [1, 0])
+@pytest.mark.parametrize("kernel", [1, 3, 0])
 def test_fullsize_prefill_chunk(nv, ob, kernel):
     """Prefill at the size the benchmark runs it: 512 new tokens per session over 2-3k cached keys (7B shape, two
     sessions, two layers; many query tiles, many pages per ring).  One (layer, session) slice against the oracle's
@@ -383,7 +383,9 @@ def test_fullsize_prefill_chunk(nv, ob, kernel):
     cs, sn = eng.rope_tables()
     sh1 = ob.shape(1, NH, NKV, ob.KV_F16)
     try:
-        batch.set_kernel(kernel)
+        batch.set_kernel(min(kernel, 1))
+        if kernel == 3:
+            batch.set_prefill_kernel(1)            # tcgen05 + tensor memory
         assert batch.prefill_max_tokens() >= n_tok
         rng = np.random.default_rng(5)
         q = rng.standard_normal((L, S, n_tok, NH, 128)).astype(np.float32)

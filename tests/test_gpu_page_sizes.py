@@ -217,8 +217,9 @@ def test_page_sizes_cow_cascade_partials_prefill(nv, ob, kb):
     batch.sync_positions()
     # a prefill chunk on the same sessions (both kernels write the same rows; the second one re-writes them)
     n_tok = 37
-    for kernel in (1, 0):
-        batch.set_kernel(kernel)
+    for kernel in ((1, 3, 0) if kb >= 16 else (1, 0)):
+        batch.set_kernel(min(kernel, 1))
+        batch.set_prefill_kernel(1 if kernel == 3 else 0) if kernel else None
         q = rng.standard_normal((L, S, n_tok, NH, 128)).astype(np.float32)
         k = rng.standard_normal((L, S, n_tok, NKV, 128)).astype(np.float32)
         v = rng.standard_normal((L, S, n_tok, NKV, 128)).astype(np.float32)
@@ -242,8 +243,9 @@ def test_page_sizes_cow_cascade_partials_prefill(nv, ob, kb):
     eng.close()
 
 
+@pytest.mark.parametrize("tc5", [0, 1])
 @pytest.mark.parametrize("kb,window", [(16, 64), (16, 1000), (32, 100), (8, 50)])
-def test_sliding_window_prefill(nv, ob, kb, window):
+def test_sliding_window_prefill(nv, ob, kb, window, tc5):
     """Sliding-window prefill (MaskKind::CausalSWA, flash_paged_kernel<true>, src/kernel/attn.cu:317: a query at
     position p sees keys max(0, p - W + 1) .. p) against the oracle's restatement of that instantiation; sessions
     shorter and longer than the window, chunks that start inside and beyond it.  No model of the reference selects
@@ -253,6 +255,11 @@ def test_sliding_window_prefill(nv, ob, kb, window):
     L, S, NH, NKV = eng.L, 3, eng.NH, eng.NKV
     batch = eng.batch(ss)
     try_set_kernel(nv, batch, 1)
+    if tc5:
+        if kb < 16:
+            assert nv.lib.nova_batch_set_prefill_kernel(batch.h, 1) == nv.ERR_UNSUPPORTED     # 8-token pages stay on mma.sync
+            pytest.skip("the tcgen05 prefill takes pages of 16 tokens or more")
+        batch.set_prefill_kernel(1)
     batch.set_window(window)
     pos = [700, 20, 0]
     for n_tok in (45, 70):

@@ -36,13 +36,16 @@ def kernels_for(nv, kv_dtype):
 
 
 def try_set_kernel(nv, batch, which):
-    """0 = SIMT, 1 = tensor-core, 2 = tensor-core with RoPE+append fused into the attention launch."""
+    """0 = SIMT, 1 = tensor-core, 2 = tensor-core with RoPE+append fused into the attention launch,
+    3 = tensor-core with the prefill on tcgen05 + tensor memory."""
     rc = nv.lib.nova_batch_set_kernel(batch.h, min(which, 1))
     if rc == nv.ERR_UNSUPPORTED:
         pytest.skip("kernel not built for this dtype")
     assert rc == 0
     if which == 2:
         batch.set_fused_append(1)
+    if which == 3:
+        batch.set_prefill_kernel(1)
 
 
 # --------------------------------------------------------------------------------------------
@@ -1030,21 +1033,21 @@ def test_many_short_sessions_chained_launches(nv, ob, model, n_sessions, mode):
     eng.close()
 
 
-@pytest.mark.parametrize("kernel", [0, 1])
-@pytest.mark.parametrize("model", ["qwen25_1p5b", "qwen25_7b"])
+@pytest.mark.parametrize("kernel", [0, 1, 3])
+@pytest.mark.parametrize("model", ["qwen25_1p5b", "qwen25_7b", "qwen25_14b"])
 def test_prefill_vs_oracle_and_reference(nv, ob, model, kernel):
     """Paged prefill (multi-token RoPE+append, then causal attention of the new queries): pages bit-exact,
     attention against the oracle's restatement of flash_paged_kernel and, where the library is present, the
     reference's own launch_attn_prefill_paged on an fp32 pool with the same values; a chunked prefill followed by
     decode steps continues the same cache."""
-    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, nv.KV_F16, [37, 0], L=2, seed=31)
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, nv.KV_F16, [37, 0], L=2, seed=31, extra_ctx=300)
     L, S, NH, NKV = eng.L, 2, eng.NH, eng.NKV
     batch = eng.batch(ss)
     try_set_kernel(nv, batch, kernel)
     assert batch.prefill_max_tokens() >= 64
     pos = [37, 0]
     g = ob.ref_gpu(model)
-    for n_tok in (21, 5):
+    for n_tok in (21, 5, 150):
         q = rng.standard_normal((L, S, n_tok, NH, 128)).astype(np.float32)
         k = rng.standard_normal((L, S, n_tok, NKV, 128)).astype(np.float32)
         v = rng.standard_normal((L, S, n_tok, NKV, 128)).astype(np.float32)
