@@ -153,6 +153,8 @@ def configure_batch(nv, batch, args, prefix=False):
         batch.set_pdl(0 if args.no_pdl else 1)
     if args.row_setup >= 0:
         batch.set_row_setup_pages(args.row_setup)
+    if kernel == 1 and args.prefill_kernel >= 0:
+        nv.lib.nova_batch_set_prefill_kernel(batch.h, args.prefill_kernel)       # refused for page sizes it does not take
     cascade = bool(kernel == 1 and prefix and not args.no_cascade)
     if cascade:
         batch.set_cascade(1)          # shared prefix pages attended once for all sessions (per-layer launches)
@@ -832,6 +834,8 @@ def main():
                     help="KV pool element type (f32 = the reference's own format)")
     ap.add_argument("--page-tokens", type=int, default=16, choices=[8, 16, 32, 64],
                     help="tokens per KV page (the reference's NOVA_KV_BLOCK; single-GPU workloads)")
+    ap.add_argument("--prefill-kernel", type=int, default=-1,
+                    help="prefill attention: 0 mma.sync tiles, 1 tcgen05 + tensor memory, -1 the library's default")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own kernels (sm_100a build)")
     ap.add_argument("--no-scaling-workloads", action="store_true", help="skip configurations 4 and 5 after the headline")

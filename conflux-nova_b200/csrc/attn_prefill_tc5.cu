@@ -9,8 +9,10 @@
 //     shared memory in the K-major 128-byte-swizzle form the instruction reads (two slabs of 64 dims).
 //   * K/V arrive 64 keys at a time (four 16-key tiles of pages) through the same TMA boxes as everywhere else
 //     ([64 dims][16 slots][1 kv head], 128-byte swizzle): that layout IS the K-major form for K and the MN-major form
-//     for V, so the pages are consumed as they land, without a transpose.  Two stages of 32 KiB.
-//   * Per 64 keys: eight MMAs (M128 N64 K16) fill S in tensor memory (64 columns); the softmax warps read their row
+//     for V, so the pages are consumed as they land, without a transpose.  Two K stages and two V stages of 16 KiB:
+//     a K stage is free again once its scores have been read, a V stage once its P.V is done.
+//   * Per 64 keys: eight MMAs (M128 N64 K16) fill S in tensor memory (two buffers of 64 columns: the scores of the
+//     next 64 keys are computed while the softmax of these runs); the softmax warps read their row
 //     with tcgen05.ld, mask (causal / window), keep a running reference maximum that only moves when the row maximum
 //     grows by more than 2^8 (so the O accumulator is rescaled rarely), write P as fp16 into shared memory (K-major,
 //     swizzled); four MMAs (M128 N128 K16) add P.V to O (128 columns of tensor memory).
@@ -35,7 +37,7 @@ constexpr int kT5OffStage = kT5QBytes;
 constexpr int kT5OffP = kT5OffStage + kT5Stages * kT5StageBytes;
 constexpr int kT5OffBar = kT5OffP + kT5PBytes;
 constexpr int kT5Smem = kT5OffBar + 128;              // 114816 B: two CTAs per SM
-constexpr int kT5TmemCols = 256;                      // S: columns 0-63, O: columns 128-255
+constexpr int kT5TmemCols = 256;                      // S: columns 0-63 and 64-127 (two buffers), O: columns 128-255
 constexpr uint32_t kT5ColS = 0, kT5ColO = 128;
 constexpr float kRescaleStep = 8.f;                   // the reference maximum moves only when the row maximum grew by more (log2 units)
 
@@ -90,14 +92,25 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(160, 2)
+// Hand-overs between the warps of a CTA last a fraction of a microsecond: poll a while before reading the clock
+// (reading it costs more than such a wait lasts), then fall back to the bounded wait.
+__device__ __forceinline__ bool t5_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+        if (mbar_try(bar, parity)) return true;
+    return mbar_wait(bar, parity, abort_flag);
+}
+
+constexpr int kT5Threads = 192;       // 4 softmax warps, the MMA-issuing warp, the page-copy warp
+
+__global__ void __launch_bounds__(kT5Threads, 2)
 attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, int tq,
                         int n_qtiles) {
     // No static shared memory: the dynamic region then starts at the front of the CTA's window, 1024-byte aligned as the
     // swizzled tiles need, without padding (the 112 KiB + 128 B are sized for two CTAs per SM).
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(smem_raw + kT5OffBar + 64);
-    volatile int& s_abort = *reinterpret_cast<volatile int*>(smem_raw + kT5OffBar + 68);
+    uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(smem_raw + kT5OffBar + 96);
+    volatile int& s_abort = *reinterpret_cast<volatile int*>(smem_raw + kT5OffBar + 100);
 
     const int lane = (int)threadIdx.x & 31;
     const int warp = (int)threadIdx.x >> 5;
@@ -124,13 +137,16 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     const int n_tiles = (n_pages + 3) >> 2;                             // 64-key tiles
     const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
 
-    const uint32_t bar_full0 = base + kT5OffBar, bar_sready = bar_full0 + 16, bar_pready = bar_full0 + 24, bar_pvdone = bar_full0 + 32;
+    // barriers: K landed [2], V landed [2], scores ready [2], P written (all 128 softmax threads), P.V done [2].
+    // Every waiter waits for a phase whose successor on the same barrier cannot complete without that waiter's own next
+    // action (tiles alternate between the two barriers of a pair), so a parity can never be mistaken for a later one.
+    const uint32_t bar_kfull = base + kT5OffBar, bar_vfull = bar_kfull + 16, bar_sready = bar_kfull + 32, bar_pready = bar_kfull + 48,
+                   bar_pvdone = bar_kfull + 56;
     if (threadIdx.x == 0) {
-        mbar_init(bar_full0, 1);
-        mbar_init(bar_full0 + 8, 1);
-        mbar_init(bar_sready, 1);
+        for (int i = 0; i < 6; ++i) mbar_init(bar_kfull + 8u * (uint32_t)i, 1);
         mbar_init(bar_pready, kT5Rows);
         mbar_init(bar_pvdone, 1);
+        mbar_init(bar_pvdone + 8, 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -149,16 +165,16 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     const uint32_t tmem = s_tmem_base;
     bool failed = false;
 
-    // pages 4i .. 4i+3 of the CTA's range into stage i & 1 (called by the one issuing thread)
-    auto load_tile = [&](int i) {
+    // K (which = 0) or V (which = 1) rows of pages 4i .. 4i+3 of the CTA's range into stage i & 1 (called by the one
+    // copying thread; phys = the block-table entries of those pages).  Stage layout: K dims lo | K dims hi | V dims lo |
+    // V dims hi, 8 KiB each.
+    auto load_tile = [&](int i, int which, const int (&phys)[4]) {
         const int stage = i & 1;
-        const uint32_t dst = base + kT5OffStage + (uint32_t)stage * kT5StageBytes;
-        const uint32_t bar = bar_full0 + 8u * (uint32_t)stage;
+        const uint32_t dst = base + kT5OffStage + (uint32_t)stage * kT5StageBytes + (uint32_t)which * 2u * kT5SlabBytes;
+        const uint32_t bar = (which ? bar_vfull : bar_kfull) + 8u * (uint32_t)stage;
+        const CUtensorMap* tm = which ? &tmv : &tmk;
         const int p0 = 4 * i, cnt = n_pages - p0 < 4 ? n_pages - p0 : 4;
-        int phys[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) phys[j] = j < cnt ? __ldg(table + ((page_begin + p0 + j) >> geo.tpp_shift)) : 0;
-        mbar_expect_tx(bar, (uint32_t)cnt * 8192u);
+        mbar_expect_tx(bar, (uint32_t)cnt * 4096u);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             if (j >= cnt) break;
@@ -169,21 +185,29 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
             }
             const int c1 = (int)((((int64_t)a.layer0 * a.nb + ph) << geo.kv_shift) + (((page_begin + p0 + j) & tpp_mask) << 4));
             const uint32_t d = dst + (uint32_t)j * 2048u;
-            tma_load_3d(d, &tmk, 0, c1, kvh, bar);
-            tma_load_3d(d + kT5SlabBytes, &tmk, 64, c1, kvh, bar);
-            tma_load_3d(d + 2 * kT5SlabBytes, &tmv, 0, c1, kvh, bar);
-            tma_load_3d(d + 3 * kT5SlabBytes, &tmv, 64, c1, kvh, bar);
+            tma_load_3d(d, tm, 0, c1, kvh, bar);
+            tma_load_3d(d + kT5SlabBytes, tm, 64, c1, kvh, bar);
         }
     };
-    if (warp == 4) {
-        // ------------------------------------------------------------- TMA + MMA issue: one thread
-        if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
-            load_tile(0);
-            if (n_tiles > 1) load_tile(1);
+    auto fetch_phys = [&](int i, int (&phys)[4]) {       // block-table entries of tile i's pages (0 beyond the range)
+        const int p0 = 4 * i;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) phys[j] = p0 + j < n_pages ? __ldg(table + ((page_begin + p0 + j) >> geo.tpp_shift)) : 0;
+    };
+    int ph[4] = {0, 0, 0, 0}, ph_next[4] = {0, 0, 0, 0};       // the copying thread's block-table entries, a tile ahead
+    if (warp == 5 && lane == 0) {
+        // ------------------------------------------------------------- page copies: the first two tiles go out at once
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
+        fetch_phys(0, ph);
+        fetch_phys(1, ph_next);
+        load_tile(0, 0, ph);
+        load_tile(0, 1, ph);
+        if (n_tiles > 1) {
+            load_tile(1, 0, ph_next);
+            load_tile(1, 1, ph_next);
         }
-        __syncwarp();
+        fetch_phys(2, ph);
     }
     // ---- Q -> shared memory (softmax threads: one row each), then everybody meets once
     const int row = (int)threadIdx.x;                       // tile row of a softmax thread
@@ -214,23 +238,51 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     }
     __syncthreads();
 
-    if (warp == 4) {
+    if (warp == 5) {
+        // ------------------------------------------------------------- page copies: one thread, stage by stage
+        if (lane == 0) {
+            for (int t = 2; t < n_tiles; ++t) {
+                fetch_phys(t + 1, ph_next);
+                // K(t-2)'s stage is free once S(t-2) has been computed, V(t-2)'s once P.V(t-2) is done
+                if (!t5_wait(bar_sready + 8u * (uint32_t)(t & 1), (uint32_t)((t - 2) >> 1) & 1u, &s_abort)) break;
+                load_tile(t, 0, ph);
+                if (!t5_wait(bar_pvdone + 8u * (uint32_t)(t & 1), (uint32_t)((t - 2) >> 1) & 1u, &s_abort)) break;
+                load_tile(t, 1, ph);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ph[j] = ph_next[j];
+            }
+        }
+        __syncwarp();
+    } else if (warp == 4) {
+        // ------------------------------------------------------------- MMA issue: one thread
         if (lane == 0) {
             const uint32_t q_lo = base, q_hi = base + kT5QSlabBytes, p_addr = base + kT5OffP;
-            for (int i = 0; i < n_tiles && !failed; ++i) {
-                const int stage = i & 1;
+            // S(t) = Q.K(t)^T into score buffer t & 1: eight K-steps of 16 dims; a step moves 32 bytes inside the swizzled
+            // 128-byte row
+            auto issue_s = [&](int t) -> bool {
+                const int stage = t & 1;
                 const uint32_t st_addr = base + kT5OffStage + (uint32_t)stage * kT5StageBytes;
-                if (!mbar_wait(bar_full0 + 8u * (uint32_t)stage, (uint32_t)(i >> 1) & 1u, &s_abort)) { failed = true; break; }
+                if (!t5_wait(bar_kfull + 8u * (uint32_t)stage, (uint32_t)(t >> 1) & 1u, &s_abort)) return false;
                 tc_fence_after();
-                // S = Q.K^T: eight K-steps of 16 dims; a step moves 32 bytes inside the swizzled 128-byte row
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const uint64_t ad = umma_desc((j < 4 ? q_lo : q_hi) + (uint32_t)(j & 3) * 32u, 16u, 1024u);
                     const uint64_t bd = umma_desc(st_addr + (uint32_t)(j >> 2) * kT5SlabBytes + (uint32_t)(j & 3) * 32u, 16u, 1024u);
-                    umma_f16(tmem + kT5ColS, ad, bd, kIdescS, j > 0 ? 1u : 0u);
+                    umma_f16(tmem + kT5ColS + 64u * (uint32_t)stage, ad, bd, kIdescS, j > 0 ? 1u : 0u);
                 }
-                umma_commit(bar_sready);
-                if (!mbar_wait(bar_pready, (uint32_t)i & 1u, &s_abort)) { failed = true; break; }
+                umma_commit(bar_sready + 8u * (uint32_t)stage);
+                return true;
+            };
+            failed = !issue_s(0);
+            for (int i = 0; i < n_tiles && !failed; ++i) {
+                const int stage = i & 1;
+                const uint32_t st_addr = base + kT5OffStage + (uint32_t)stage * kT5StageBytes;
+                // The scores of the NEXT 64 keys first (their buffer was read two tiles ago): they are computed while the
+                // softmax warps work on tile i and are waiting for them when those warps come back.
+                if (i + 1 < n_tiles && !issue_s(i + 1)) { failed = true; break; }
+                // P(i) is written (the softmax has read S(i))
+                if (!t5_wait(bar_pready, (uint32_t)i & 1u, &s_abort)) { failed = true; break; }
+                if (!t5_wait(bar_vfull + 8u * (uint32_t)stage, (uint32_t)(i >> 1) & 1u, &s_abort)) { failed = true; break; }
                 tc_fence_after();
                 // O += P.V: four K-steps of 16 keys; V is MN-major: 16 key rows = two 1024-byte atoms (stride), the two
                 // halves of the 128 dims are a slab apart (leading offset)
@@ -240,11 +292,7 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
                     const uint64_t bd = umma_desc(st_addr + 2u * kT5SlabBytes + (uint32_t)j * 2048u, (uint32_t)kT5SlabBytes, 1024u);
                     umma_f16(tmem + kT5ColO, ad, bd, kIdescPV, (i > 0 || j > 0) ? 1u : 0u);
                 }
-                umma_commit(bar_pvdone);
-                if (i + 2 < n_tiles) {            // the stage is free once these MMAs have read it
-                    if (!mbar_wait(bar_pvdone, (uint32_t)i & 1u, &s_abort)) { failed = true; break; }
-                    load_tile(i + 2);
-                }
+                umma_commit(bar_pvdone + 8u * (uint32_t)stage);
             }
             if (failed && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
         }
@@ -256,27 +304,34 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
         float m_ref = -INFINITY, l = 0.f;
         for (int i = 0; i < n_tiles; ++i) {
             // (the warp decides together: what follows is warp-collective)
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_sready, (uint32_t)i & 1u, &s_abort))) { failed = true; break; }
+            if (!__all_sync(0xffffffffu, t5_wait(bar_sready + 8u * (uint32_t)(i & 1), (uint32_t)(i >> 1) & 1u, &s_abort))) { failed = true; break; }
             tc_fence_after();
             uint32_t sv[2][32];
-            tmem_ld32(t_lane + kT5ColS, sv[0]);
-            tmem_ld32(t_lane + kT5ColS + 32, sv[1]);
+            tmem_ld32(t_lane + kT5ColS + 64u * (uint32_t)(i & 1), sv[0]);
+            tmem_ld32(t_lane + kT5ColS + 64u * (uint32_t)(i & 1) + 32, sv[1]);
             tmem_wait_ld();
             const int key0 = (page_begin + 4 * i) << 4;
             const int kcount = keys_all - key0 < kT5Keys ? keys_all - key0 : kT5Keys;     // real keys in this tile
             const int hi_k = (row_lim < key0 + kcount - 1 ? row_lim : key0 + kcount - 1) - key0;   // last visible column
             const int lo_k = row_lo - key0;                                                        // first visible column
             float mx = -INFINITY;
+            if (__all_sync(0xffffffffu, hi_k >= kT5Keys - 1 && lo_k <= 0)) {      // every key of the tile is visible to the warp's rows
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int col = 32 * h + c;
-                    float v = __uint_as_float(sv[h][c]);
-                    v = (col <= hi_k && col >= lo_k) ? v : -INFINITY;
-                    sv[h][c] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
-                }
+                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[h][c]));
+            } else {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int col = 32 * h + c;
+                        float v = __uint_as_float(sv[h][c]);
+                        v = (col <= hi_k && col >= lo_k) ? v : -INFINITY;
+                        sv[h][c] = __float_as_uint(v);
+                        mx = fmaxf(mx, v);
+                    }
+            }
             // reference maximum: moves only when the row maximum outgrew it by more than kRescaleStep
             float scale = 1.f;
             if (mx > m_ref + kRescaleStep || (m_ref == -INFINITY && mx > -INFINITY)) {
@@ -296,7 +351,7 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
             }
             l = fmaf(l, scale, psum);
             // the previous tile's P.V must be done before P is overwritten and before O is rescaled
-            if (i > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_pvdone, (uint32_t)(i - 1) & 1u, &s_abort))) { failed = true; break; }
+            if (i > 0 && !__all_sync(0xffffffffu, t5_wait(bar_pvdone + 8u * (uint32_t)((i - 1) & 1), (uint32_t)((i - 1) >> 1) & 1u, &s_abort))) { failed = true; break; }
             if (i > 0 && __any_sync(0xffffffffu, scale != 1.f)) {
                 tc_fence_after();
 #pragma unroll 1
@@ -316,7 +371,9 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
                              "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
                              : "memory");
             if (kcount < kT5Keys) {
-                // key rows past the last real key hold stale bytes: their weights are 0, but 0 * Inf/NaN would poison O
+                // key rows past the last real key hold stale bytes: their weights are 0, but 0 * Inf/NaN would poison O.
+                // The V rows of this tile must have landed first (the copy of a partly filled page brings such rows too).
+                if (!__all_sync(0xffffffffu, t5_wait(bar_vfull + 8u * (uint32_t)(i & 1), (uint32_t)(i >> 1) & 1u, &s_abort))) { failed = true; break; }
                 const uint32_t st_addr = base + kT5OffStage + (uint32_t)(i & 1) * kT5StageBytes + 2u * kT5SlabBytes;
                 for (int e = (int)threadIdx.x; e < (kT5Keys - kcount) * 16; e += kT5Rows) {
                     const int r = kcount + (e >> 4), c = e & 15;
@@ -329,7 +386,7 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
             tc_fence_before();
             mbar_arrive(bar_pready);
         }
-        if (!failed && !__all_sync(0xffffffffu, mbar_wait(bar_pvdone, (uint32_t)(n_tiles - 1) & 1u, &s_abort))) failed = true;
+        if (!failed && !__all_sync(0xffffffffu, t5_wait(bar_pvdone + 8u * (uint32_t)((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u, &s_abort))) failed = true;
         if (failed) {
             if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
         } else {
@@ -384,7 +441,7 @@ int launch_attn_prefill_tc5(const AttnLaunch& a, cudaStream_t s) {
     if (ctas > 0x7fffffffLL) return NOVA_ERR_TOO_LARGE;
     const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k1);
     const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v1);
-    attn_prefill_tc5_kernel<<<(unsigned)ctas, 160, kT5Smem, s>>>(a, *tk, *tv, tq, n_qtiles);
+    attn_prefill_tc5_kernel<<<(unsigned)ctas, kT5Threads, kT5Smem, s>>>(a, *tk, *tv, tq, n_qtiles);
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }
