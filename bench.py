@@ -614,8 +614,9 @@ def prefill_sample(nv, work, stream, reps):
         b.free()
     return {"tokens_per_s": S * n_tok * reps / (ms / 1e3), "chunk_tokens_per_session": n_tok, "ms_per_chunk": ms / reps,
             "attention_tflops": flops / (ms / 1e3) / 1e12,
-            "note": "tensor-core kernel: query-tiled, K/V pages staged once per tile; SIMT kernel: one work-split row per "
-                    "query token"}
+            "note": "time of the whole chunk (RoPE+append and attention launches of every layer); fp16 pools with pages of 16 "
+                    "tokens or more: attention on tcgen05 + tensor memory unless --prefill-kernel 0 (mma.sync tiles); SIMT "
+                    "kernel: one work-split row per query token"}
 
 
 def reference_gpu_sample(nv, work):

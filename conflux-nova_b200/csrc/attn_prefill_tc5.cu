@@ -1,23 +1,26 @@
 // attn_prefill_tc5.cu — paged prefill attention on the fifth-generation tensor cores (tcgen05 + tensor memory).
 // Same contract as attn_prefill.cu (replaces flash_paged_kernel, src/kernel/attn.cu:292-357 of the reference, causal
 // and sliding-window), built for a contraction-bound shape: the scores S = Q.K^T and the outputs O += P.V are
-// tcgen05.mma instructions issued by one thread, their accumulators live in tensor memory, and the 128 threads of
+// tcgen05.mma instructions issued by one thread, their accumulators live in tensor memory, and the 256 threads of
 // the softmax warps each own one query row of them.
 //
-//   * One CTA = (session, kv head, tile of 128 / G query tokens): the (token, head) pairs that share the kv head are
-//     the M = 128 rows of the tile.  Q is converted once to fp16 (scaled by 1/sqrt(128) * log2 e) and laid out in
-//     shared memory in the K-major 128-byte-swizzle form the instruction reads (two slabs of 64 dims).
+//   * One CTA = (session, kv head, tile of 256 / G query tokens): the (token, head) pairs that share the kv head are
+//     the rows of the tile, handled as two halves of M = 128 rows that share every K/V page the CTA brings in (each
+//     byte fetched from L2 feeds twice the arithmetic a single half would; with one half per CTA the kernel was bound
+//     by those fetches).  Q is converted once to fp16 (scaled by 1/sqrt(128) * log2 e) and laid out in shared memory
+//     in the K-major 128-byte-swizzle form the instruction reads (per half, two slabs of 64 dims).
 //   * K/V arrive 64 keys at a time (four 16-key tiles of pages) through the same TMA boxes as everywhere else
 //     ([64 dims][16 slots][1 kv head], 128-byte swizzle): that layout IS the K-major form for K and the MN-major form
-//     for V, so the pages are consumed as they land, without a transpose.  Two K stages and two V stages of 16 KiB:
-//     a K stage is free again once its scores have been read, a V stage once its P.V is done.
-//   * Per 64 keys: eight MMAs (M128 N64 K16) fill S in tensor memory (two buffers of 64 columns: the scores of the
-//     next 64 keys are computed while the softmax of these runs); the softmax warps read their row
-//     with tcgen05.ld, mask (causal / window), keep a running reference maximum that only moves when the row maximum
-//     grows by more than 2^8 (so the O accumulator is rescaled rarely), write P as fp16 into shared memory (K-major,
-//     swizzled); four MMAs (M128 N128 K16) add P.V to O (128 columns of tensor memory).
-//   * Two CTAs fit an SM (112 KiB of shared memory, 256 of the 512 tensor-memory columns each), so one CTA's softmax
-//     overlaps the other's MMAs.
+//     for V, so the pages are consumed as they land, without a transpose.  Four stages of 16 KiB K + 16 KiB V: the K
+//     part is free again once both halves' scores are computed, the V part once both P.V products are done.
+//   * Per 64 keys and half: eight MMAs (M128 N64 K16) fill S in tensor memory (two buffers of 64 columns: the scores
+//     of the next 64 keys are computed while the softmax of these runs); the softmax warps read their row with
+//     tcgen05.ld, mask (causal / window), keep a running reference maximum that only moves when the row maximum grows
+//     by more than 2^8 (so the O accumulator is rescaled rarely) and write P as fp16 back into tensor memory over the
+//     scores they just read; four MMAs (M128 N128 K16, A = P from tensor memory) add P.V to O (128 columns).
+//   * One CTA per SM: 192 KiB of shared memory and all 512 tensor-memory columns (2 x 2 x 64 of scores, 2 x 128 of
+//     outputs).  Each half has its own MMA-issuing warp (one thread cannot issue MMAs of this size as fast as the
+//     pipe retires them); one half's softmax overlaps the other half's MMAs.
 //   * Every mbarrier wait is bounded (NOVA_ERR_TIMEOUT in the status word); tensor memory is released on every path.
 #include "attn_plan.cuh"
 #include "mma_common.cuh"
@@ -25,33 +28,37 @@
 namespace novab {
 namespace {
 
-constexpr int kT5Rows = 128;                          // query rows of a CTA = M of the MMAs
+constexpr int kT5Rows = 256;                          // query rows of a CTA
+constexpr int kT5Half = 128;                          // rows of one half = M of the MMAs
 constexpr int kT5Keys = 64;                           // keys per K/V tile = N of S = Q.K^T
-constexpr int kT5Stages = 2;
+constexpr int kT5Stages = 4;
 constexpr int kT5SlabBytes = kT5Keys * 128;           // 64 key rows x 128 B (64 dims): 8 KiB
-constexpr int kT5QSlabBytes = kT5Rows * 128;          // 128 query rows x 128 B: 16 KiB
-constexpr int kT5QBytes = 2 * kT5QSlabBytes;          // dims 0-63 | 64-127
+constexpr int kT5QSlabBytes = kT5Half * 128;          // 128 query rows x 128 B: 16 KiB
+constexpr int kT5QBytes = 4 * kT5QSlabBytes;          // half 0: dims 0-63 | 64-127, half 1: the same
 constexpr int kT5StageBytes = 4 * kT5SlabBytes;       // K dims lo | K dims hi | V dims lo | V dims hi: 32 KiB
-constexpr int kT5PBytes = kT5Rows * 128;              // P: 128 rows x 64 keys fp16
 constexpr int kT5OffStage = kT5QBytes;
-constexpr int kT5OffP = kT5OffStage + kT5Stages * kT5StageBytes;
-constexpr int kT5OffBar = kT5OffP + kT5PBytes;
-constexpr int kT5Smem = kT5OffBar + 128;              // 114816 B: two CTAs per SM
-constexpr int kT5TmemCols = 256;                      // S: columns 0-63 and 64-127 (two buffers), O: columns 128-255
-constexpr uint32_t kT5ColS = 0, kT5ColO = 128;
+constexpr int kT5OffBar = kT5OffStage + kT5Stages * kT5StageBytes;
+constexpr int kT5Smem = kT5OffBar + 256;              // 196864 B: one CTA per SM
+constexpr int kT5TmemCols = 512;                      // S of half h, buffer b: columns 128h + 64b (P overlays the first 32
+                                                      // of them); O of half h: columns 256 + 128h
+constexpr uint32_t kT5ColO = 256;
 constexpr float kRescaleStep = 8.f;                   // the reference maximum moves only when the row maximum grew by more (log2 units)
 
 // Instruction descriptors (kind::f16): fp32 accumulate (bit 4), fp16 A and B (formats 0), N >> 3 at bit 17,
 // M >> 4 at bit 24; bit 16 = B is MN-major (V: the 64 dims of a key row are contiguous).
-constexpr uint32_t kIdescS = (1u << 4) | ((uint32_t)(kT5Keys >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
-constexpr uint32_t kIdescPV = (1u << 4) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kT5Rows >> 4) << 24);
+constexpr uint32_t kIdescS = (1u << 4) | ((uint32_t)(kT5Keys >> 3) << 17) | ((uint32_t)(kT5Half >> 4) << 24);
+constexpr uint32_t kIdescPV = (1u << 4) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(kT5Half >> 4) << 24);
 
 // Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte offsets (all >> 4),
 // descriptor version 1 (bit 46), layout type 2 = SWIZZLE_128B (bits 61-63).  Atoms are 8 rows x 128 B = 1024 B.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
-           (1ull << 46) | (2ull << 61);
+// The issuing thread is one dependent instruction stream, so what it computes per MMA is what paces the tensor
+// pipe: the descriptor is split into a constant high word and a low word (address and leading offset, both >> 4) that
+// moves by a compile-time constant from one MMA to the next.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);      // stride 1024 B, version 1, SWIZZLE_128B
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
 }
+__device__ __forceinline__ uint64_t umma_desc_of(uint32_t lo) { return ((uint64_t)kDescHi << 32) | (uint64_t)lo; }
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t"
@@ -61,8 +68,24 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// The same with the A operand in tensor memory (M = 128: row r in lane r, two fp16 of consecutive K per 32-bit column).
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// One lane of a converged warp (the same one every time for a full mask).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -101,19 +124,27 @@ __device__ __forceinline__ bool t5_wait(uint32_t bar, uint32_t parity, volatile 
     return mbar_wait(bar, parity, abort_flag);
 }
 
-constexpr int kT5Threads = 192;       // 4 softmax warps, the MMA-issuing warp, the page-copy warp
+constexpr int kT5Threads = 352;       // 8 softmax warps (4 per half), an MMA-issuing warp per half, the page-copy warp
 
-__global__ void __launch_bounds__(kT5Threads, 2)
+#ifdef NOVA_TIMELINE       // profiling build: cycles spent inside a wait are added to a counter
+#define T5_TIMED(acc, expr) [&]() { const long long t_ = clock64(); const bool r_ = (expr); acc += clock64() - t_; return r_; }()
+#else
+#define T5_TIMED(acc, expr) (expr)
+#endif
+
+__global__ void __launch_bounds__(kT5Threads, 1)
 attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, int tq,
                         int n_qtiles) {
-    // No static shared memory: the dynamic region then starts at the front of the CTA's window, 1024-byte aligned as the
-    // swizzled tiles need, without padding (the 112 KiB + 128 B are sized for two CTAs per SM).
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(smem_raw + kT5OffBar + 96);
-    volatile int& s_abort = *reinterpret_cast<volatile int*>(smem_raw + kT5OffBar + 100);
+    // No static shared memory and no alignment attribute: the dynamic region then starts at the front of the CTA's
+    // window, which is 1024-byte aligned as the swizzled tiles need.  The kernel checks that and reports
+    // NOVA_ERR_UNSUPPORTED otherwise.
+    extern __shared__ unsigned char smem_raw[];
+    uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(smem_raw + kT5OffBar + 224);
+    volatile int& s_abort = *reinterpret_cast<volatile int*>(smem_raw + kT5OffBar + 228);
 
     const int lane = (int)threadIdx.x & 31;
-    const int warp = (int)threadIdx.x >> 5;
+    // (a shuffle result is warp-uniform for the compiler: the issuing warps then keep descriptors in uniform registers)
+    const int warp = __shfl_sync(0xffffffffu, (int)threadIdx.x >> 5, 0);
     const int G = a.n_heads / a.n_kv_heads;
     const int NH = a.n_heads, NKV = a.n_kv_heads, NQ = a.n_q;
     const PageGeom geo = page_geom(a.kv_shift);            // 16-key tiles (pages of 16, 32 or 64 tokens)
@@ -137,83 +168,95 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     const int n_tiles = (n_pages + 3) >> 2;                             // 64-key tiles
     const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
 
-    // barriers: K landed [2], V landed [2], scores ready [2], P written (all 128 softmax threads), P.V done [2].
+    // barriers (8 bytes each): K landed [4 stages], V landed [4], K part free [4], V part free [4], scores ready
+    // [half][buffer], P written [half][buffer] (the half's 128 threads), P.V done [half][buffer].
     // Every waiter waits for a phase whose successor on the same barrier cannot complete without that waiter's own next
-    // action (tiles alternate between the two barriers of a pair), so a parity can never be mistaken for a later one.
-    const uint32_t bar_kfull = base + kT5OffBar, bar_vfull = bar_kfull + 16, bar_sready = bar_kfull + 32, bar_pready = bar_kfull + 48,
-                   bar_pvdone = bar_kfull + 56;
+    // action, so a parity can never be mistaken for a later one.  (That is why "P written" has a barrier per buffer:
+    // a half's softmax may finish tile i + 1, whose scores are computed ahead, before the issuing thread has looked at
+    // tile i's barrier; tile i + 2's scores are only issued after it has.)
+    const uint32_t bar_kfull = base + kT5OffBar, bar_vfull = bar_kfull + 32, bar_kfree = bar_kfull + 64, bar_vfree = bar_kfull + 96,
+                   bar_sready = bar_kfull + 128, bar_pready = bar_kfull + 160, bar_pvdone = bar_kfull + 192;
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 6; ++i) mbar_init(bar_kfull + 8u * (uint32_t)i, 1);
-        mbar_init(bar_pready, kT5Rows);
-        mbar_init(bar_pvdone, 1);
-        mbar_init(bar_pvdone + 8, 1);
+        for (int i = 0; i < 8; ++i) mbar_init(bar_kfull + 8u * (uint32_t)i, 1);
+        for (int i = 0; i < 8; ++i) mbar_init(bar_kfree + 8u * (uint32_t)i, 2);        // both halves' issuers release a stage
+        for (int i = 0; i < 4; ++i) mbar_init(bar_sready + 8u * (uint32_t)i, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(bar_pready + 8u * (uint32_t)i, kT5Half);
+        for (int i = 0; i < 4; ++i) mbar_init(bar_pvdone + 8u * (uint32_t)i, 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+#ifdef NOVA_TIMELINE       // which SM ran this CTA, and when
+    if (a.timeline && threadIdx.x == 0 && blockIdx.x < 1700) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        a.timeline[(size_t)blockIdx.x * 4 + 0] = now_ns();
+        a.timeline[(size_t)blockIdx.x * 4 + 1] = smid;
+    }
+#endif
     const bool bad_layout = (base & 1023u) != 0 || n_pages <= 0 || ((page_end + tpp_mask) >> geo.tpp_shift) > a.table_stride;
     if (bad_layout) {                 // uniform over the CTA: nothing has been allocated yet
         if (threadIdx.x == 0 && a.status && n_pages > 0) atomicCAS(a.status, 0, (base & 1023u) ? NOVA_ERR_UNSUPPORTED : NOVA_ERR_BAD_TABLE);
         return;
     }
-    if (warp == 0) {                  // tensor memory: 256 columns for this CTA, released below on every path
+    if (warp == 0) {                  // tensor memory: all 512 columns (the CTA has the SM to itself), released below on every path
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"((uint32_t)kT5TmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = s_tmem_base;
+    const uint32_t tmem = __shfl_sync(0xffffffffu, s_tmem_base, 0);
     bool failed = false;
 
-    // K (which = 0) or V (which = 1) rows of pages 4i .. 4i+3 of the CTA's range into stage i & 1 (called by the one
-    // copying thread; phys = the block-table entries of those pages).  Stage layout: K dims lo | K dims hi | V dims lo |
-    // V dims hi, 8 KiB each.
-    auto load_tile = [&](int i, int which, const int (&phys)[4]) {
-        const int stage = i & 1;
-        const uint32_t dst = base + kT5OffStage + (uint32_t)stage * kT5StageBytes + (uint32_t)which * 2u * kT5SlabBytes;
-        const uint32_t bar = (which ? bar_vfull : bar_kfull) + 8u * (uint32_t)stage;
-        const CUtensorMap* tm = which ? &tmv : &tmk;
+    // Page copies: eight lanes of the copy warp, lane = (K or V, page j of the tile's four).  A lane brings page
+    // 4i + j of the CTA's range into stage i & 3 (two boxes: dims 0-63 and 64-127) and reads its own block-table
+    // entries two tiles ahead.  Stage layout: K dims lo | K dims hi | V dims lo | V dims hi, 8 KiB each; the first lane
+    // of each group posts the byte count (the other lanes' bytes may land before it: the phase cannot complete
+    // without that arrival).
+    const int cp_j = lane & 3, cp_which = (lane >> 2) & 1;
+    auto load_page = [&](int i, int ph) {
+        const int stage = i & (kT5Stages - 1);
+        const uint32_t dst = base + kT5OffStage + (uint32_t)stage * kT5StageBytes + (uint32_t)cp_which * 2u * kT5SlabBytes + (uint32_t)cp_j * 2048u;
+        const uint32_t bar = (cp_which ? bar_vfull : bar_kfull) + 8u * (uint32_t)stage;
         const int p0 = 4 * i, cnt = n_pages - p0 < 4 ? n_pages - p0 : 4;
-        mbar_expect_tx(bar, (uint32_t)cnt * 4096u);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (j >= cnt) break;
-            int ph = phys[j];
+        if (cp_j == 0) mbar_expect_tx(bar, (uint32_t)cnt * 4096u);
+        if (cp_j < cnt) {
             if (ph < 0 || ph >= a.nb) {            // never follow a bad entry; the result is flagged invalid
                 if (a.status) atomicCAS(a.status, 0, NOVA_ERR_BAD_TABLE);
                 ph = 0;
             }
-            const int c1 = (int)((((int64_t)a.layer0 * a.nb + ph) << geo.kv_shift) + (((page_begin + p0 + j) & tpp_mask) << 4));
-            const uint32_t d = dst + (uint32_t)j * 2048u;
-            tma_load_3d(d, tm, 0, c1, kvh, bar);
-            tma_load_3d(d + kT5SlabBytes, tm, 64, c1, kvh, bar);
+            const int c1 = (int)((((int64_t)a.layer0 * a.nb + ph) << geo.kv_shift) + (((page_begin + p0 + cp_j) & tpp_mask) << 4));
+            const CUtensorMap* tm = cp_which ? &tmv : &tmk;
+            tma_load_3d(dst, tm, 0, c1, kvh, bar);
+            tma_load_3d(dst + kT5SlabBytes, tm, 64, c1, kvh, bar);
         }
     };
-    auto fetch_phys = [&](int i, int (&phys)[4]) {       // block-table entries of tile i's pages (0 beyond the range)
-        const int p0 = 4 * i;
+    auto fetch_phys = [&](int i) -> int {       // this lane's block-table entry of tile i (0 beyond the range)
+        const int p = 4 * i + cp_j;
+        return p < n_pages ? __ldg(table + ((page_begin + p) >> geo.tpp_shift)) : 0;
+    };
+    int ph_a = 0, ph_b = 0;                     // entries of the next two tiles
+    if (warp == 10 && lane < 8) {
+        // ------------------------------------------------------------- every stage is filled at once
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
+        }
+        int e[kT5Stages];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) phys[j] = p0 + j < n_pages ? __ldg(table + ((page_begin + p0 + j) >> geo.tpp_shift)) : 0;
-    };
-    int ph[4] = {0, 0, 0, 0}, ph_next[4] = {0, 0, 0, 0};       // the copying thread's block-table entries, a tile ahead
-    if (warp == 5 && lane == 0) {
-        // ------------------------------------------------------------- page copies: the first two tiles go out at once
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmk) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmv) : "memory");
-        fetch_phys(0, ph);
-        fetch_phys(1, ph_next);
-        load_tile(0, 0, ph);
-        load_tile(0, 1, ph);
-        if (n_tiles > 1) {
-            load_tile(1, 0, ph_next);
-            load_tile(1, 1, ph_next);
-        }
-        fetch_phys(2, ph);
+        for (int t = 0; t < kT5Stages; ++t) e[t] = fetch_phys(t);
+        ph_a = fetch_phys(kT5Stages);
+        ph_b = fetch_phys(kT5Stages + 1);
+#pragma unroll
+        for (int t = 0; t < kT5Stages; ++t)
+            if (t < n_tiles) load_page(t, e[t]);
     }
     // ---- Q -> shared memory (softmax threads: one row each), then everybody meets once
     const int row = (int)threadIdx.x;                       // tile row of a softmax thread
+    const int half = row >> 7, hrow = row & (kT5Half - 1);
     int row_tok = 0, row_head = 0, row_lim = -1, row_lo = 0;
     bool row_ok = false;
-    if (warp < 4) {
+    if (warp < 8) {
         const int tk = row / G, g = row - tk * G;
         row_ok = tk < t_cnt && tk < tq;
         row_tok = t0 + tk;
@@ -231,84 +274,123 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
             }
             const uint32_t w0 = pack_h2(x0.x * kQScale, x0.y * kQScale), w1 = pack_h2(x0.z * kQScale, x0.w * kQScale);
             const uint32_t w2 = pack_h2(x1.x * kQScale, x1.y * kQScale), w3 = pack_h2(x1.z * kQScale, x1.w * kQScale);
-            const uint32_t addr = base + (uint32_t)((c >> 3) * kT5QSlabBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4));
+            const uint32_t addr = base + (uint32_t)((2 * half + (c >> 3)) * kT5QSlabBytes + hrow * 128 + (((c & 7) ^ (hrow & 7)) << 4));
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
 
-    if (warp == 5) {
-        // ------------------------------------------------------------- page copies: one thread, stage by stage
-        if (lane == 0) {
-            for (int t = 2; t < n_tiles; ++t) {
-                fetch_phys(t + 1, ph_next);
-                // K(t-2)'s stage is free once S(t-2) has been computed, V(t-2)'s once P.V(t-2) is done
-                if (!t5_wait(bar_sready + 8u * (uint32_t)(t & 1), (uint32_t)((t - 2) >> 1) & 1u, &s_abort)) break;
-                load_tile(t, 0, ph);
-                if (!t5_wait(bar_pvdone + 8u * (uint32_t)(t & 1), (uint32_t)((t - 2) >> 1) & 1u, &s_abort)) break;
-                load_tile(t, 1, ph);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) ph[j] = ph_next[j];
+    if (warp == 10) {
+        // ------------------------------------------------------------- page copies, stage by stage
+        if (lane < 8) {
+            for (int t = kT5Stages; t < n_tiles; ++t) {
+                const int stage = t & (kT5Stages - 1);
+                const uint32_t parity = (uint32_t)((t >> 2) - 1) & 1u;      // the stage's previous use (tile t - 4)
+                const int ph_c = fetch_phys(t + 2);
+                // the K part is free once both halves' scores of tile t - 4 are computed, the V part once both P.V are
+                if (!t5_wait((cp_which ? bar_vfree : bar_kfree) + 8u * (uint32_t)stage, parity, &s_abort)) break;
+                load_page(t, ph_a);
+                ph_a = ph_b;
+                ph_b = ph_c;
             }
         }
         __syncwarp();
-    } else if (warp == 4) {
-        // ------------------------------------------------------------- MMA issue: one thread
-        if (lane == 0) {
-            const uint32_t q_lo = base, q_hi = base + kT5QSlabBytes, p_addr = base + kT5OffP;
-            // S(t) = Q.K(t)^T into score buffer t & 1: eight K-steps of 16 dims; a step moves 32 bytes inside the swizzled
-            // 128-byte row
-            auto issue_s = [&](int t) -> bool {
-                const int stage = t & 1;
-                const uint32_t st_addr = base + kT5OffStage + (uint32_t)stage * kT5StageBytes;
-                if (!t5_wait(bar_kfull + 8u * (uint32_t)stage, (uint32_t)(t >> 1) & 1u, &s_abort)) return false;
-                tc_fence_after();
+    } else if (warp >= 8) {
+        // ------------------------------------------------------------- MMA issue: one warp per half, one elected lane
+        // A thread issues an MMA every ~80 cycles at best, more than a 64-key MMA takes: two issuers keep the pipe
+        // fed.  The whole warp runs the loop (uniform control flow and operands); one elected lane issues.  MMAs of one
+        // issuer execute in order, which is what the overlay of P on S relies on; the halves share only the stages.
+        const int h = warp - 8;
+#ifdef NOVA_TIMELINE
+        long long w_p = 0, w_v = 0, w_k = 0, w_is = 0, c0 = clock64();
+#else
+        int w_p = 0, w_v = 0, w_k = 0;
+        (void)w_p; (void)w_v; (void)w_k;
+#endif
+        const uint32_t q_lo0 = umma_desc_lo(base + (uint32_t)(2 * h) * kT5QSlabBytes, 16u), k_lo0 = umma_desc_lo(base + kT5OffStage, 16u),
+                       v_lo0 = umma_desc_lo(base + kT5OffStage + 2u * kT5SlabBytes, (uint32_t)kT5SlabBytes);
+        const uint32_t col_s = tmem + 128u * (uint32_t)h, col_o = tmem + kT5ColO + 128u * (uint32_t)h;
+        // S_h(t) = Q_h.K(t)^T into score buffer t & 1: eight K-steps of 16 dims (slab j >> 2 = dims 0-63 | 64-127; a
+        // step moves 32 bytes inside the swizzled 128-byte row)
+        auto issue_s = [&](int t) -> bool {
+            const int stage = t & (kT5Stages - 1);
+            const uint32_t k_lo = k_lo0 + (uint32_t)stage * (kT5StageBytes >> 4);
+            const uint32_t d_s = col_s + 64u * (uint32_t)(t & 1);
+            if (!__all_sync(0xffffffffu, T5_TIMED(w_k, t5_wait(bar_kfull + 8u * (uint32_t)stage, (uint32_t)(t >> 2) & 1u, &s_abort)))) return false;
+            tc_fence_after();
+#ifdef NOVA_TIMELINE
+            const long long ti = clock64();
+#endif
+            if (elect_one()) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint64_t ad = umma_desc((j < 4 ? q_lo : q_hi) + (uint32_t)(j & 3) * 32u, 16u, 1024u);
-                    const uint64_t bd = umma_desc(st_addr + (uint32_t)(j >> 2) * kT5SlabBytes + (uint32_t)(j & 3) * 32u, 16u, 1024u);
-                    umma_f16(tmem + kT5ColS + 64u * (uint32_t)stage, ad, bd, kIdescS, j > 0 ? 1u : 0u);
-                }
-                umma_commit(bar_sready + 8u * (uint32_t)stage);
-                return true;
-            };
-            failed = !issue_s(0);
-            for (int i = 0; i < n_tiles && !failed; ++i) {
-                const int stage = i & 1;
-                const uint32_t st_addr = base + kT5OffStage + (uint32_t)stage * kT5StageBytes;
-                // The scores of the NEXT 64 keys first (their buffer was read two tiles ago): they are computed while the
-                // softmax warps work on tile i and are waiting for them when those warps come back.
-                if (i + 1 < n_tiles && !issue_s(i + 1)) { failed = true; break; }
-                // P(i) is written (the softmax has read S(i))
-                if (!t5_wait(bar_pready, (uint32_t)i & 1u, &s_abort)) { failed = true; break; }
-                if (!t5_wait(bar_vfull + 8u * (uint32_t)stage, (uint32_t)(i >> 1) & 1u, &s_abort)) { failed = true; break; }
-                tc_fence_after();
-                // O += P.V: four K-steps of 16 keys; V is MN-major: 16 key rows = two 1024-byte atoms (stride), the two
-                // halves of the 128 dims are a slab apart (leading offset)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint64_t ad = umma_desc(p_addr + (uint32_t)j * 32u, 16u, 1024u);
-                    const uint64_t bd = umma_desc(st_addr + 2u * kT5SlabBytes + (uint32_t)j * 2048u, (uint32_t)kT5SlabBytes, 1024u);
-                    umma_f16(tmem + kT5ColO, ad, bd, kIdescPV, (i > 0 || j > 0) ? 1u : 0u);
-                }
-                umma_commit(bar_pvdone + 8u * (uint32_t)stage);
+                for (int j = 0; j < 8; ++j)
+                    umma_f16(d_s, umma_desc_of(q_lo0 + (uint32_t)((j >> 2) * (kT5QSlabBytes >> 4) + (j & 3) * 2)),
+                             umma_desc_of(k_lo + (uint32_t)((j >> 2) * (kT5SlabBytes >> 4) + (j & 3) * 2)), kIdescS, j > 0 ? 1u : 0u);
+                umma_commit(bar_sready + 8u * (uint32_t)(2 * h + (t & 1)));
+                umma_commit(bar_kfree + 8u * (uint32_t)stage);
             }
-            if (failed && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
+            __syncwarp();
+#ifdef NOVA_TIMELINE
+            w_is += clock64() - ti;
+#endif
+            return true;
+        };
+        failed = !issue_s(0);
+        for (int i = 0; i < n_tiles && !failed; ++i) {
+            const int stage = i & (kT5Stages - 1);
+            const uint32_t v_lo = v_lo0 + (uint32_t)stage * (kT5StageBytes >> 4);
+            const uint32_t p_col = col_s + 64u * (uint32_t)(i & 1);
+            const uint32_t acc0 = i > 0 ? 1u : 0u;
+            // The scores of the NEXT 64 keys first (their buffer was read two tiles ago): they are computed while the
+            // softmax warps work on tile i and are waiting for them when those warps come back.
+            if (i + 1 < n_tiles && !issue_s(i + 1)) { failed = true; break; }
+            if (!__all_sync(0xffffffffu, T5_TIMED(w_v, t5_wait(bar_vfull + 8u * (uint32_t)stage, (uint32_t)(i >> 2) & 1u, &s_abort)))) { failed = true; break; }
+            // P_h(i) is written (the half's softmax has read S_h(i))
+            if (!__all_sync(0xffffffffu, T5_TIMED(w_p, t5_wait(bar_pready + 8u * (uint32_t)(2 * h + (i & 1)), (uint32_t)(i >> 1) & 1u, &s_abort)))) { failed = true; break; }
+            tc_fence_after();
+            if (elect_one()) {
+                // O_h += P_h.V: four K-steps of 16 keys; P is read from tensor memory (16 keys = 8 columns); V is
+                // MN-major: 16 key rows = two 1024-byte atoms (stride), the two halves of the 128 dims are a slab apart
+                // (leading offset)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    umma_f16_ts(col_o, p_col + (uint32_t)(8 * j), umma_desc_of(v_lo + (uint32_t)(j * (2048 >> 4))), kIdescPV, j > 0 ? 1u : acc0);
+                umma_commit(bar_pvdone + 8u * (uint32_t)(2 * h + (i & 1)));
+                umma_commit(bar_vfree + 8u * (uint32_t)stage);
+            }
+            __syncwarp();
         }
-        __syncwarp();
+        if (failed && lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
+#ifdef NOVA_TIMELINE
+        if (a.timeline && blockIdx.x < 1700 && h == 0 && lane == 0) {       // cycles: total | K wait | P wait | V wait
+            unsigned long long* t = a.timeline + 1700 * 4 + (size_t)blockIdx.x * 4;
+            t[0] = (unsigned long long)(clock64() - c0);
+            t[1] = (unsigned long long)w_k;
+            t[2] = (unsigned long long)w_p;
+            t[3] = (unsigned long long)w_v;
+            a.timeline[(size_t)blockIdx.x * 4 + 3] = (unsigned long long)w_is;      // issuing the score MMAs
+        }
+#endif
     } else {
         // ------------------------------------------------------------- softmax warps: thread = one row of S and O
-        const uint32_t t_lane = tmem + ((uint32_t)(32 * warp) << 16);        // this warp's 32 lanes of tensor memory
-        const uint32_t p_row = base + kT5OffP + (uint32_t)row * 128u;
+        const uint32_t t_lane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);  // this warp's 32 lanes of tensor memory
+        const uint32_t col_s = 128u * (uint32_t)half, col_o = kT5ColO + 128u * (uint32_t)half;
+        const uint32_t my_sready = bar_sready + 16u * (uint32_t)half, my_pvdone = bar_pvdone + 16u * (uint32_t)half;
         float m_ref = -INFINITY, l = 0.f;
+#ifdef NOVA_TIMELINE
+        long long x_s = 0, x_pv = 0, x0 = clock64();
+#else
+        int x_s = 0, x_pv = 0;
+        (void)x_s; (void)x_pv;
+#endif
         for (int i = 0; i < n_tiles; ++i) {
             // (the warp decides together: what follows is warp-collective)
-            if (!__all_sync(0xffffffffu, t5_wait(bar_sready + 8u * (uint32_t)(i & 1), (uint32_t)(i >> 1) & 1u, &s_abort))) { failed = true; break; }
+            if (!__all_sync(0xffffffffu, T5_TIMED(x_s, t5_wait(my_sready + 8u * (uint32_t)(i & 1), (uint32_t)(i >> 1) & 1u, &s_abort)))) { failed = true; break; }
             tc_fence_after();
             uint32_t sv[2][32];
-            tmem_ld32(t_lane + kT5ColS + 64u * (uint32_t)(i & 1), sv[0]);
-            tmem_ld32(t_lane + kT5ColS + 64u * (uint32_t)(i & 1) + 32, sv[1]);
+            tmem_ld32(t_lane + col_s + 64u * (uint32_t)(i & 1), sv[0]);
+            tmem_ld32(t_lane + col_s + 64u * (uint32_t)(i & 1) + 32, sv[1]);
             tmem_wait_ld();
             const int key0 = (page_begin + 4 * i) << 4;
             const int kcount = keys_all - key0 < kT5Keys ? keys_all - key0 : kT5Keys;     // real keys in this tile
@@ -344,49 +426,58 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
                 const int h = c >> 4, cc = (2 * c) & 31;
-                const uint32_t p2 = pack_h2(ex2(__uint_as_float(sv[h][cc]) - ms), ex2(__uint_as_float(sv[h][cc + 1]) - ms));
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&p2));
-                psum += f.x + f.y;                                       // the row sum uses the fp16-rounded weights that multiply V
-                pk[c] = p2;
+                const float e0 = ex2(__uint_as_float(sv[h][cc]) - ms), e1 = ex2(__uint_as_float(sv[h][cc + 1]) - ms);
+                psum += e0 + e1;
+                pk[c] = pack_h2(e0, e1);                                 // keys 2c, 2c+1 of the tile
             }
             l = fmaf(l, scale, psum);
-            // the previous tile's P.V must be done before P is overwritten and before O is rescaled
-            if (i > 0 && !__all_sync(0xffffffffu, t5_wait(bar_pvdone + 8u * (uint32_t)((i - 1) & 1), (uint32_t)((i - 1) >> 1) & 1u, &s_abort))) { failed = true; break; }
             if (i > 0 && __any_sync(0xffffffffu, scale != 1.f)) {
+                // O is rescaled between two P.V products: the previous one must be done (the one before it is, since
+                // these scores were computed after it, so the barrier's parity cannot be mistaken)
+                if (!__all_sync(0xffffffffu, T5_TIMED(x_pv, t5_wait(my_pvdone + 8u * (uint32_t)((i - 1) & 1), (uint32_t)((i - 1) >> 1) & 1u, &s_abort)))) { failed = true; break; }
                 tc_fence_after();
 #pragma unroll 1
                 for (int cc = 0; cc < 4; ++cc) {
                     uint32_t ov[32];
-                    tmem_ld32(t_lane + kT5ColO + 32u * (uint32_t)cc, ov);
+                    tmem_ld32(t_lane + col_o + 32u * (uint32_t)cc, ov);
                     tmem_wait_ld();
 #pragma unroll
                     for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * scale);
-                    tmem_st32(t_lane + kT5ColO + 32u * (uint32_t)cc, ov);
+                    tmem_st32(t_lane + col_o + 32u * (uint32_t)cc, ov);
                 }
                 tmem_wait_st();
             }
-#pragma unroll
-            for (int c = 0; c < 8; ++c)                                  // chunk c = keys 8c .. 8c+7 of the row
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p_row + (uint32_t)((c ^ (row & 7)) << 4)), "r"(pk[4 * c]),
-                             "r"(pk[4 * c + 1]), "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3])
-                             : "memory");
+            // P (fp16) over the first 32 columns of the scores just read: the products issued before the next scores
+            // land in this buffer (tile i + 2) include the P.V that reads it
+            tmem_st32(t_lane + col_s + 64u * (uint32_t)(i & 1), pk);
+            tmem_wait_st();
             if (kcount < kT5Keys) {
                 // key rows past the last real key hold stale bytes: their weights are 0, but 0 * Inf/NaN would poison O.
                 // The V rows of this tile must have landed first (the copy of a partly filled page brings such rows too).
-                if (!__all_sync(0xffffffffu, t5_wait(bar_vfull + 8u * (uint32_t)(i & 1), (uint32_t)(i >> 1) & 1u, &s_abort))) { failed = true; break; }
-                const uint32_t st_addr = base + kT5OffStage + (uint32_t)(i & 1) * kT5StageBytes + 2u * kT5SlabBytes;
-                for (int e = (int)threadIdx.x; e < (kT5Keys - kcount) * 16; e += kT5Rows) {
+                // Each half does it before its own P.V (the two write the same zeros).
+                if (!__all_sync(0xffffffffu, t5_wait(bar_vfull + 8u * (uint32_t)(i & (kT5Stages - 1)), (uint32_t)(i >> 2) & 1u, &s_abort))) { failed = true; break; }
+                const uint32_t st_addr = base + kT5OffStage + (uint32_t)(i & (kT5Stages - 1)) * kT5StageBytes + 2u * kT5SlabBytes;
+                for (int e = hrow; e < (kT5Keys - kcount) * 16; e += kT5Half) {
                     const int r = kcount + (e >> 4), c = e & 15;
                     asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(st_addr + (uint32_t)((c >> 3) * kT5SlabBytes + r * 128 + ((c & 7) << 4))),
                                  "r"(0u)
                                  : "memory");
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
-            mbar_arrive(bar_pready);
+            mbar_arrive(bar_pready + 8u * (uint32_t)(2 * half + (i & 1)));
         }
-        if (!failed && !__all_sync(0xffffffffu, t5_wait(bar_pvdone + 8u * (uint32_t)((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u, &s_abort))) failed = true;
+#ifdef NOVA_TIMELINE
+        if (a.timeline && threadIdx.x == 0 && blockIdx.x < 1700) {       // cycles: softmax loop total | score wait | P.V wait | tiles
+            unsigned long long* t = a.timeline + 1700 * 8 + (size_t)blockIdx.x * 4;
+            t[0] = (unsigned long long)(clock64() - x0);
+            t[1] = (unsigned long long)x_s;
+            t[2] = (unsigned long long)x_pv;
+            t[3] = (unsigned long long)n_tiles;
+        }
+#endif
+        if (!failed && !__all_sync(0xffffffffu, t5_wait(my_pvdone + 8u * (uint32_t)((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u, &s_abort))) failed = true;
         if (failed) {
             if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
         } else {
@@ -396,7 +487,7 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
 #pragma unroll 1
             for (int cc = 0; cc < 4; ++cc) {
                 uint32_t ov[32];
-                tmem_ld32(t_lane + kT5ColO + 32u * (uint32_t)cc, ov);
+                tmem_ld32(t_lane + col_o + 32u * (uint32_t)cc, ov);
                 tmem_wait_ld();
                 if (row_ok) {
 #pragma unroll
@@ -411,6 +502,9 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     // ---- release the tensor memory (every path of every thread ends here)
     tc_fence_before();
     __syncthreads();
+#ifdef NOVA_TIMELINE
+    if (a.timeline && threadIdx.x == 0 && blockIdx.x < 1700) a.timeline[(size_t)blockIdx.x * 4 + 2] = now_ns();
+#endif
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kT5TmemCols) : "memory");
 }
 
@@ -433,6 +527,9 @@ int launch_attn_prefill_tc5(const AttnLaunch& a, cudaStream_t s) {
     NOVA_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5Smem));
+        // 192 KiB per CTA: the whole shared-memory carve-out
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           cudaSharedmemCarveoutMaxShared));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const int tq = attn_prefill_tc5_tile_tokens(a.n_heads, a.n_kv_heads);

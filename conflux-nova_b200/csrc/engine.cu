@@ -62,7 +62,7 @@ struct nova_batch {
                                      // they read their q / new k / new v only once the launches before them have finished
     int row_setup = 2;               // work-split weight of a row start, in pages (see AttnLaunch)
     int window = 0;                  // prefill: sliding window in tokens (0: plain causal)
-    int prefill_tc5 = 0;             // 1: prefill attention on tcgen05 + tensor memory (attn_prefill_tc5.cu)
+    int prefill_tc5 = 1;             // 1: prefill attention on tcgen05 + tensor memory where it applies (attn_prefill_tc5.cu), 0: mma.sync tiles
     int split_ctas = 0;              // CTAs of a chained one-layer attention launch; 0: chosen from the work (pick_split_ctas)
     int cascade = 0;                 // 1: the shared leading pages of the batch's sessions are attended once for all
     int casc_pages = 0;              // shared leading pages found by the last nova_batch_cow (0: none worth it)

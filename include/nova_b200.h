@@ -366,9 +366,10 @@ int  nova_batch_prefill_max_tokens(const nova_batch* b);
  * position p sees keys (p - window_tokens, p].  0 = plain causal (every model of the reference).  Tensor-core
  * kernel only; nova_batch_prefill returns NOVA_ERR_UNSUPPORTED otherwise. */
 int  nova_batch_set_window(nova_batch* b, int window_tokens);
-/* Which tensor-core prefill kernel nova_batch_prefill uses: 0 = mma.sync tiles of 64 rows, 1 = tcgen05 tiles of 128
+/* Which tensor-core prefill kernel nova_batch_prefill uses: 0 = mma.sync tiles of 64 rows, 1 = tcgen05 tiles of 256
  * rows with the accumulators in tensor memory (fp16 pools, pages of 16 tokens or more; NOVA_ERR_UNSUPPORTED
- * otherwise).  Both replace flash_paged_kernel (src/kernel/attn.cu:292-357). */
+ * otherwise).  1 is the default: a batch it does not apply to runs the mma.sync tiles.  Both replace
+ * flash_paged_kernel (src/kernel/attn.cu:292-357). */
 int  nova_batch_set_prefill_kernel(nova_batch* b, int which);
 int  nova_batch_prefill(nova_batch* b, int layer, int n_tokens, float* q, float* k, const float* v, float* out,
                         nova_stream_t s);

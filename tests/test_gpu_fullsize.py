@@ -384,8 +384,8 @@ def test_fullsize_prefill_chunk(nv, ob, kernel):
     sh1 = ob.shape(1, NH, NKV, ob.KV_F16)
     try:
         batch.set_kernel(min(kernel, 1))
-        if kernel == 3:
-            batch.set_prefill_kernel(1)            # tcgen05 + tensor memory
+        if kernel:
+            batch.set_prefill_kernel(1 if kernel == 3 else 0)      # tcgen05 + tensor memory | mma.sync tiles
         assert batch.prefill_max_tokens() >= n_tok
         rng = np.random.default_rng(5)
         q = rng.standard_normal((L, S, n_tok, NH, 128)).astype(np.float32)

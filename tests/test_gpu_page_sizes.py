@@ -260,6 +260,8 @@ def test_sliding_window_prefill(nv, ob, kb, window, tc5):
             assert nv.lib.nova_batch_set_prefill_kernel(batch.h, 1) == nv.ERR_UNSUPPORTED     # 8-token pages stay on mma.sync
             pytest.skip("the tcgen05 prefill takes pages of 16 tokens or more")
         batch.set_prefill_kernel(1)
+    else:
+        batch.set_prefill_kernel(0)
     batch.set_window(window)
     pos = [700, 20, 0]
     for n_tok in (45, 70):

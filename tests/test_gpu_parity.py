@@ -36,8 +36,8 @@ def kernels_for(nv, kv_dtype):
 
 
 def try_set_kernel(nv, batch, which):
-    """0 = SIMT, 1 = tensor-core, 2 = tensor-core with RoPE+append fused into the attention launch,
-    3 = tensor-core with the prefill on tcgen05 + tensor memory."""
+    """0 = SIMT, 1 = tensor-core (prefill on mma.sync tiles), 2 = tensor-core with RoPE+append fused into the attention
+    launch, 3 = tensor-core with the prefill on tcgen05 + tensor memory (the library's default where it applies)."""
     rc = nv.lib.nova_batch_set_kernel(batch.h, min(which, 1))
     if rc == nv.ERR_UNSUPPORTED:
         pytest.skip("kernel not built for this dtype")
@@ -46,6 +46,8 @@ def try_set_kernel(nv, batch, which):
         batch.set_fused_append(1)
     if which == 3:
         batch.set_prefill_kernel(1)
+    elif which >= 1:
+        batch.set_prefill_kernel(0)
 
 
 # --------------------------------------------------------------------------------------------
