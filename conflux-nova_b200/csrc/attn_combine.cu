@@ -630,7 +630,10 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
 #define NOVA_COMBINE_MAX_CTAS 76
 #endif
     // (a launch that covers several layers is not part of such a chain and takes up to 8 CTAs per SM)
-    const int64_t cap = (a.n_layers == 1 && a.pdl && a.pdl_spare) ? NOVA_COMBINE_MAX_CTAS : sm_count() * 8;
+    // (the cascade's merge, n_extra > 0, is part of such a chain too: its CTAs share the SMs of the split over the private
+    // pages - one beside each split CTA - because the shared-prefix tiles fill theirs)
+    int64_t cap = (a.n_layers == 1 && a.pdl && (a.pdl_spare || a.n_extra > 0)) ? NOVA_COMBINE_MAX_CTAS : sm_count() * 8;
+    if (a.n_layers == 1 && a.pdl && a.n_extra > 0 && n_ctas_split >= 8 && n_ctas_split < cap) cap = n_ctas_split;
     if (ctas > cap) ctas = cap;
     // Always a programmatic dependent of the split kernel launched just before it.
     const bool coop = a.n_extra == 0 && units <= NOVA_COMBINE_MAX_CTAS;      // few units: one CTA per unit

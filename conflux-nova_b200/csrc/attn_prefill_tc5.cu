@@ -132,9 +132,14 @@ constexpr int kT5Threads = 352;       // 8 softmax warps (4 per half), an MMA-is
 #define T5_TIMED(acc, expr) (expr)
 #endif
 
+// kPrefix = true is the shared-prefix form used by decode steps of sessions that share their first pages: the tile
+// rows are (session, head) pairs - each session's single query - the keys are chunk `bid / (row tiles * NKV)` of the
+// first prefix_pages 16-key tiles of the FIRST session's table, nothing is masked, q is rotated on the way in when
+// the append is fused, and the result is an un-normalised partial row per chunk (m, l, acc) for the merge kernel.
+template <bool kPrefix>
 __global__ void __launch_bounds__(kT5Threads, 1)
 attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, int tq,
-                        int n_qtiles) {
+                        int n_qtiles, int prefix_pages, int chunk_pages) {
     // No static shared memory and no alignment attribute: the dynamic region then starts at the front of the CTA's
     // window, which is 1024-byte aligned as the swizzled tiles need.  The kernel checks that and reports
     // NOVA_ERR_UNSUPPORTED otherwise.
@@ -156,14 +161,16 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     const int qtile = n_qtiles - 1 - bid % n_qtiles;
     bid /= n_qtiles;
     const int kvh = bid % NKV;
-    const int s = bid / NKV;
+    const int s = kPrefix ? 0 : bid / NKV;                              // prefix form: rows index sessions, the table is the first one's
+    const int chunk = kPrefix ? bid / NKV : 0;
     const int t0 = qtile * tq;
     const int t_cnt = NQ - t0 < tq ? NQ - t0 : tq;
-    const int n_past = a.n_past ? a.n_past[s] : a.keys_imm;
-    const int keys_all = n_past + a.keys_add + t0 + t_cnt - 1;          // keys seen by the tile's last query
-    const int first_key = a.window > 0 ? n_past + a.keys_add + t0 - a.window : 0;   // nothing before it is visible to any row
-    const int page_begin = first_key > 0 ? first_key >> 4 : 0;          // in 16-key tiles
-    const int page_end = (keys_all + 15) >> 4;
+    const int n_past = kPrefix ? 0 : (a.n_past ? a.n_past[s] : a.keys_imm);
+    const int first_key = (!kPrefix && a.window > 0) ? n_past + a.keys_add + t0 - a.window : 0;   // nothing before it is visible to any row
+    const int page_begin = kPrefix ? chunk * chunk_pages : (first_key > 0 ? first_key >> 4 : 0);   // in 16-key tiles
+    const int page_end = kPrefix ? (page_begin + chunk_pages < prefix_pages ? page_begin + chunk_pages : prefix_pages)
+                                 : (n_past + a.keys_add + t0 + t_cnt - 1 + 15) >> 4;
+    const int keys_all = kPrefix ? page_end << 4 : n_past + a.keys_add + t0 + t_cnt - 1;   // keys seen by the tile's last query
     const int n_pages = page_end - page_begin;
     const int n_tiles = (n_pages + 3) >> 2;                             // 64-key tiles
     const int32_t* table = a.table_base + (int64_t)(a.slice_ids ? a.slice_ids[s] : s) * a.table_stride;
@@ -176,6 +183,7 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     // tile i's barrier; tile i + 2's scores are only issued after it has.)
     const uint32_t bar_kfull = base + kT5OffBar, bar_vfull = bar_kfull + 32, bar_kfree = bar_kfull + 64, bar_vfree = bar_kfull + 96,
                    bar_sready = bar_kfull + 128, bar_pready = bar_kfull + 160, bar_pvdone = bar_kfull + 192;
+    if (kPrefix) pdl_launch_dependents();      // the split over the private pages shares nothing with this kernel
     if (threadIdx.x == 0) {
         for (int i = 0; i < 8; ++i) mbar_init(bar_kfull + 8u * (uint32_t)i, 1);
         for (int i = 0; i < 8; ++i) mbar_init(bar_kfree + 8u * (uint32_t)i, 2);        // both halves' issuers release a stage
@@ -186,7 +194,7 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 #ifdef NOVA_TIMELINE       // which SM ran this CTA, and when
-    if (a.timeline && threadIdx.x == 0 && blockIdx.x < 1700) {
+    if (a.timeline && threadIdx.x == 0 && blockIdx.x < (kPrefix ? 148 : 1700)) {
         unsigned smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
         a.timeline[(size_t)blockIdx.x * 4 + 0] = now_ns();
@@ -261,10 +269,54 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
         row_ok = tk < t_cnt && tk < tq;
         row_tok = t0 + tk;
         row_head = kvh * G + g;
-        row_lim = row_ok ? n_past + a.keys_add + row_tok - 1 : -1;          // last visible key of the row
-        row_lo = (row_ok && a.window > 0) ? row_lim - a.window + 1 : 0;
+        row_lim = kPrefix ? 0x7fffffff : (row_ok ? n_past + a.keys_add + row_tok - 1 : -1);          // last visible key of the row
+        row_lo = (!kPrefix && row_ok && a.window > 0) ? row_lim - a.window + 1 : 0;
         constexpr float kQScale = kAttnScale * kLog2e;
         const float* qp = a.q + (((int64_t)s * NQ + row_tok) * NH + row_head) * kHeadDim;
+        if (kPrefix && a.fuse_append) {
+            // q arrives un-rotated: rotate the NeoX pairs (d, d + 64) at the session's position with the same fused
+            // form as the append kernel, then scale and round
+            const int pos = row_ok ? a.n_past[row_tok] : 0;
+            const bool rot = row_ok && pos >= 0 && pos < a.rope_rows;
+            const float* cr = a.rope_cs + (int64_t)(rot ? pos : 0) * (kHeadDim / 2);
+            const float* sr = a.rope_sn + (int64_t)(rot ? pos : 0) * (kHeadDim / 2);
+#pragma unroll 4
+            for (int c = 0; c < 8; ++c) {                  // dims 8c .. 8c+7 and their partners 64 + 8c ..
+                float x0[8], x1[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x0[e] = x1[e] = 0.f;
+                if (row_ok) {
+                    *reinterpret_cast<float4*>(x0) = *reinterpret_cast<const float4*>(qp + 8 * c);
+                    *reinterpret_cast<float4*>(x0 + 4) = *reinterpret_cast<const float4*>(qp + 8 * c + 4);
+                    *reinterpret_cast<float4*>(x1) = *reinterpret_cast<const float4*>(qp + 64 + 8 * c);
+                    *reinterpret_cast<float4*>(x1 + 4) = *reinterpret_cast<const float4*>(qp + 64 + 8 * c + 4);
+                }
+                if (rot) {
+                    float cs[8], sn[8];
+                    *reinterpret_cast<float4*>(cs) = *reinterpret_cast<const float4*>(cr + 8 * c);
+                    *reinterpret_cast<float4*>(cs + 4) = *reinterpret_cast<const float4*>(cr + 8 * c + 4);
+                    *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sr + 8 * c);
+                    *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sr + 8 * c + 4);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float y0 = __fmaf_rn(x0[e], cs[e], -__fmul_rn(x1[e], sn[e]));
+                        const float y1 = __fmaf_rn(x0[e], sn[e], __fmul_rn(x1[e], cs[e]));
+                        x0[e] = y0;
+                        x1[e] = y1;
+                    }
+                }
+                const uint32_t sw = (uint32_t)(hrow * 128 + ((c ^ (hrow & 7)) << 4));
+                const uint32_t a0 = base + (uint32_t)(2 * half) * kT5QSlabBytes + sw, a1 = a0 + kT5QSlabBytes;
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a0), "r"(pack_h2(x0[0] * kQScale, x0[1] * kQScale)),
+                             "r"(pack_h2(x0[2] * kQScale, x0[3] * kQScale)), "r"(pack_h2(x0[4] * kQScale, x0[5] * kQScale)),
+                             "r"(pack_h2(x0[6] * kQScale, x0[7] * kQScale))
+                             : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a1), "r"(pack_h2(x1[0] * kQScale, x1[1] * kQScale)),
+                             "r"(pack_h2(x1[2] * kQScale, x1[3] * kQScale)), "r"(pack_h2(x1[4] * kQScale, x1[5] * kQScale)),
+                             "r"(pack_h2(x1[6] * kQScale, x1[7] * kQScale))
+                             : "memory");
+            }
+        } else {
 #pragma unroll 4
         for (int c = 0; c < 16; ++c) {                     // 16 chunks of 8 dims
             float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
@@ -277,9 +329,13 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
             const uint32_t addr = base + (uint32_t)((2 * half + (c >> 3)) * kT5QSlabBytes + hrow * 128 + (((c & 7) ^ (hrow & 7)) << 4));
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
         }
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+#ifdef NOVA_TIMELINE
+    if (kPrefix && a.timeline && threadIdx.x == 0 && blockIdx.x < 148) a.timeline[(size_t)blockIdx.x * 4 + 1] = now_ns();   // q staged
+#endif
 
     if (warp == 10) {
         // ------------------------------------------------------------- page copies, stage by stage
@@ -363,8 +419,8 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
         }
         if (failed && lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
 #ifdef NOVA_TIMELINE
-        if (a.timeline && blockIdx.x < 1700 && h == 0 && lane == 0) {       // cycles: total | K wait | P wait | V wait
-            unsigned long long* t = a.timeline + 1700 * 4 + (size_t)blockIdx.x * 4;
+        if (a.timeline && blockIdx.x < (kPrefix ? 148 : 1700) && h == 0 && lane == 0) {       // cycles: total | K wait | P wait | V wait
+            unsigned long long* t = a.timeline + (kPrefix ? 148 : 1700) * 4 + (size_t)blockIdx.x * 4;
             t[0] = (unsigned long long)(clock64() - c0);
             t[1] = (unsigned long long)w_k;
             t[2] = (unsigned long long)w_p;
@@ -469,8 +525,8 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
             mbar_arrive(bar_pready + 8u * (uint32_t)(2 * half + (i & 1)));
         }
 #ifdef NOVA_TIMELINE
-        if (a.timeline && threadIdx.x == 0 && blockIdx.x < 1700) {       // cycles: softmax loop total | score wait | P.V wait | tiles
-            unsigned long long* t = a.timeline + 1700 * 8 + (size_t)blockIdx.x * 4;
+        if (a.timeline && threadIdx.x == 0 && blockIdx.x < (kPrefix ? 148 : 1700)) {       // cycles: softmax loop total | score wait | P.V wait | tiles
+            unsigned long long* t = a.timeline + (kPrefix ? 148 : 1700) * 8 + (size_t)blockIdx.x * 4;
             t[0] = (unsigned long long)(clock64() - x0);
             t[1] = (unsigned long long)x_s;
             t[2] = (unsigned long long)x_pv;
@@ -478,9 +534,43 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
         }
 #endif
         if (!failed && !__all_sync(0xffffffffu, t5_wait(my_pvdone + 8u * (uint32_t)((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u, &s_abort))) failed = true;
-        if (failed) {
-            if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
-        } else {
+        if (failed && lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
+        if (kPrefix) {
+            // Partial rows (m, l, acc[128]) leave through shared memory: a thread owns a row, but the rows of a token
+            // are one contiguous run of G * 130 floats in the result, which the 256 threads then write together.
+            // Every MMA and page copy of the CTA is done once both halves are here (a failed wait has set the status
+            // word and passes through), so the staging area may start at the front of the shared memory.
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            tc_fence_after();
+            float* stage_rows = reinterpret_cast<float*>(smem_raw);
+            float* srow = stage_rows + row * kPartW;
+            *reinterpret_cast<float2*>(srow) = make_float2(m_ref * (1.f / kLog2e), l);
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t ov[32];
+                tmem_ld32(t_lane + col_o + 32u * (uint32_t)cc, ov);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c += 2)
+                    *reinterpret_cast<float2*>(srow + 2 + 32 * cc + c) = make_float2(__uint_as_float(ov[c]), __uint_as_float(ov[c + 1]));
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+#ifdef NOVA_TIMELINE
+            if (a.timeline && threadIdx.x == 0 && blockIdx.x < 148) a.timeline[148 * 8 + (size_t)blockIdx.x * 4 + 2] = now_ns();   // loop done
+#endif
+            // the chunk partials are re-used by every layer: the previous layer's final merge may still read them
+            pdl_wait();
+#ifdef NOVA_TIMELINE
+            if (a.timeline && threadIdx.x == 0 && blockIdx.x < 148) a.timeline[148 * 8 + (size_t)blockIdx.x * 4 + 3] = now_ns();   // dependency met
+#endif
+            const int seg = G * kPartW;                      // floats of one token's rows (even)
+            const int total2 = (t_cnt < tq ? t_cnt : tq) * seg / 2;
+            for (int e2 = (int)threadIdx.x; e2 < total2; e2 += kT5Rows) {
+                const int e = 2 * e2, tk = e / seg, r = e - tk * seg;
+                *reinterpret_cast<float2*>(a.out_part + (((int64_t)chunk * NQ + t0 + tk) * NH + kvh * G) * kPartW + r) =
+                    *reinterpret_cast<const float2*>(stage_rows + e);
+            }
+        } else if (!failed) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             float* op = a.out + (((int64_t)s * NQ + row_tok) * NH + row_head) * kHeadDim;
@@ -503,14 +593,14 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     tc_fence_before();
     __syncthreads();
 #ifdef NOVA_TIMELINE
-    if (a.timeline && threadIdx.x == 0 && blockIdx.x < 1700) a.timeline[(size_t)blockIdx.x * 4 + 2] = now_ns();
+    if (a.timeline && threadIdx.x == 0 && blockIdx.x < (kPrefix ? 148 : 1700)) a.timeline[(size_t)blockIdx.x * 4 + 2] = now_ns();
 #endif
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kT5TmemCols) : "memory");
 }
 
 }  // namespace
 
-// Query tokens per CTA of the tcgen05 prefill: as many whole tokens as fit the 128-row tile.
+// Query tokens per CTA of the tcgen05 prefill: as many whole tokens as fit the 256-row tile.
 int attn_prefill_tc5_tile_tokens(int n_heads, int n_kv_heads) { return kT5Rows / (n_heads / n_kv_heads); }
 
 bool attn_prefill_tc5_supports(const AttnLaunch& a) {
@@ -519,26 +609,82 @@ bool attn_prefill_tc5_supports(const AttnLaunch& a) {
            a.n_heads / a.n_kv_heads <= kT5Rows;
 }
 
-int launch_attn_prefill_tc5(const AttnLaunch& a, cudaStream_t s) {
-    if (!attn_prefill_tc5_supports(a)) return NOVA_ERR_UNSUPPORTED;
-    if (a.n_sessions <= 0) return NOVA_OK;
+namespace {
+int t5_set_attributes() {
     static bool attr_set[64] = {};
     int dev = 0;
     NOVA_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5Smem));
         // 192 KiB per CTA: the whole shared-memory carve-out
-        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5Smem));
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           cudaSharedmemCarveoutMaxShared));
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5Smem));
+        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_prefill_tc5_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                            cudaSharedmemCarveoutMaxShared));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
+    return NOVA_OK;
+}
+}  // namespace
+
+int launch_attn_prefill_tc5(const AttnLaunch& a, cudaStream_t s) {
+    if (!attn_prefill_tc5_supports(a)) return NOVA_ERR_UNSUPPORTED;
+    if (a.n_sessions <= 0) return NOVA_OK;
+    const int rc = t5_set_attributes();
+    if (rc != NOVA_OK) return rc;
     const int tq = attn_prefill_tc5_tile_tokens(a.n_heads, a.n_kv_heads);
     const int n_qtiles = (a.n_q + tq - 1) / tq;
     const long long ctas = (long long)n_qtiles * a.n_kv_heads * a.n_sessions;
     if (ctas > 0x7fffffffLL) return NOVA_ERR_TOO_LARGE;
     const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k1);
     const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v1);
-    attn_prefill_tc5_kernel<<<(unsigned)ctas, kT5Threads, kT5Smem, s>>>(a, *tk, *tv, tq, n_qtiles);
+    attn_prefill_tc5_kernel<false><<<(unsigned)ctas, kT5Threads, kT5Smem, s>>>(a, *tk, *tv, tq, n_qtiles, 0, 0);
+    NOVA_LAUNCH_CHECK();
+    return NOVA_OK;
+}
+
+// Chunks of the shared prefix (prefix_pages 16-key tiles) for the tcgen05 prefix launch: whole 64-key tiles per chunk,
+// at least four of them, and about a third of the SMs in all - the split over the private pages runs beside it.
+int attn_prefix_tc5_chunks(int n_sessions, int n_heads, int n_kv_heads, int prefix_pages, int* chunk_pages) {
+    const int tq = attn_prefill_tc5_tile_tokens(n_heads, n_kv_heads);
+    const int n_rt = (n_sessions + tq - 1) / tq;
+#ifndef NOVA_T5_PREFIX_EIGHTHS
+#define NOVA_T5_PREFIX_EIGHTHS 4
+#endif
+    int chunks = (sm_count() * NOVA_T5_PREFIX_EIGHTHS / 8) / (n_rt * n_kv_heads);
+    if (chunks > prefix_pages / 8) chunks = prefix_pages / 8;
+    if (chunks < 1) chunks = 1;
+    int per = (prefix_pages + chunks - 1) / chunks;
+    per = (per + 3) & ~3;
+    if (chunk_pages) *chunk_pages = per;
+    return (prefix_pages + per - 1) / per;
+}
+
+// Partials of every (session, head) row over the shared pages [0, prefix_pages) (in 16-key tiles) of the batch's
+// first session: a.out_part [chunks][n_sessions][NH][130], a.q [n_sessions][NH][128] (un-rotated when a.fuse_append),
+// one layer.  The tcgen05 counterpart of launch_attn_prefix.
+int launch_attn_prefix_tc5(const AttnLaunch& a_in, int prefix_pages, cudaStream_t s) {
+    if (a_in.n_sessions <= 0) return NOVA_OK;
+    AttnLaunch a = a_in;
+    a.n_q = a_in.n_sessions;             // the sessions are the query rows of one pseudo-session
+    if (!attn_prefill_tc5_supports(a) || !a.out_part || prefix_pages < 1) return NOVA_ERR_UNSUPPORTED;
+    if (a.fuse_append && (!a.n_past || !a.rope_cs || !a.rope_sn)) return NOVA_ERR_INVALID;
+    const int rc = t5_set_attributes();
+    if (rc != NOVA_OK) return rc;
+    int chunk_pages = 0;
+    const int chunks = attn_prefix_tc5_chunks(a_in.n_sessions, a.n_heads, a.n_kv_heads, prefix_pages, &chunk_pages);
+    const int tq = attn_prefill_tc5_tile_tokens(a.n_heads, a.n_kv_heads);
+    const int n_rt = (a.n_q + tq - 1) / tq;
+    const long long ctas = (long long)n_rt * a.n_kv_heads * chunks;
+    const CUtensorMap* tk = static_cast<const CUtensorMap*>(a.tmap_k1);
+    const CUtensorMap* tv = static_cast<const CUtensorMap*>(a.tmap_v1);
+    const cudaError_t le = launch_kernel_pdl(attn_prefill_tc5_kernel<true>, dim3((unsigned)ctas), dim3(kT5Threads), (size_t)kT5Smem, s,
+                                             a.pdl != 0, a, *tk, *tv, tq, n_rt, prefix_pages, chunk_pages);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "prefix attention launch (tcgen05)");
+        return NOVA_ERR_CUDA;
+    }
     NOVA_LAUNCH_CHECK();
     return NOVA_OK;
 }

@@ -172,6 +172,8 @@ int launch_attn_prefill(const AttnLaunch& a, cudaStream_t s);     // query-tiled
 int attn_prefill_tile_tokens(int n_heads, int n_kv_heads);
 int launch_attn_prefill_tc5(const AttnLaunch& a, cudaStream_t s);    // the same on tcgen05 + tensor memory (pages of >= 16 tokens)
 bool attn_prefill_tc5_supports(const AttnLaunch& a);
+int attn_prefix_tc5_chunks(int n_sessions, int n_heads, int n_kv_heads, int prefix_pages, int* chunk_pages);
+int launch_attn_prefix_tc5(const AttnLaunch& a, int prefix_pages, cudaStream_t s);   // shared-prefix partials on tcgen05
 // Shared-prefix form of the same kernel: decode queries of n_sessions sessions over the shared pages
 // [0, prefix_pages) of the first session's table, as partials a.out_part [chunks][n_sessions][NH][130].
 int attn_prefix_chunks(int n_sessions, int n_heads, int n_kv_heads, int prefix_pages, int* chunk_pages);

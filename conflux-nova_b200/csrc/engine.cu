@@ -181,11 +181,17 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
         // page on, also as partials; (3) the merge kernel: split-K slots, then the chunks, then the output.
         const int P = b->casc_pages << (b->e->kv_shift > 4 ? b->e->kv_shift - 4 : 0);      // the shared pages as 16-key tiles
         const int rows = b->n * a.n_heads;
-        const int chunks = attn_prefix_chunks(b->n, a.n_heads, a.n_kv_heads, P, nullptr);
+        // tcgen05 tiles (256 rows, a third of the SMs, the split runs beside them) where they apply, else mma.sync tiles
+        AttnLaunch ta = a;
+        ta.n_q = b->n;                // the sessions are the query rows of the prefix launch
+        const bool tc5 = b->prefill_tc5 && attn_prefill_tc5_supports(ta);
+        const int chunks = tc5 ? attn_prefix_tc5_chunks(b->n, a.n_heads, a.n_kv_heads, P, nullptr)
+                               : attn_prefix_chunks(b->n, a.n_heads, a.n_kv_heads, P, nullptr);
         if ((size_t)(chunks + 1) * rows * kPartW > b->casc_floats) return NOVA_ERR_TOO_LARGE;
         AttnLaunch pa = a;
         pa.out_part = b->casc_parts;
-        rc = launch_attn_prefix(pa, P, s);
+        if (pa.timeline) pa.timeline += 4 * (size_t)(kTimelineCtas * 12);       // profiling build: records 4-7 are the prefix launches
+        rc = tc5 ? launch_attn_prefix_tc5(pa, P, s) : launch_attn_prefix(pa, P, s);
         if (rc != NOVA_OK) return rc;
         AttnLaunch sa = a;
         sa.pdl_spare = 0;             // the chain here is prefix -> split -> merge -> final merge: early start only
@@ -195,6 +201,14 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
         sa.extra_parts = b->casc_parts;          // the merge kernel folds the chunks in and writes the output
         sa.n_extra = chunks;
         ctas = pick_split_ctas(b, sa);
+        if (tc5) {
+            // the prefix CTAs hold an SM each until they finish: the split takes the other SMs (an SM streams about as
+            // fast with either kernel, so the two finish together when the SMs are shared out by bytes)
+            const int tq5 = 256 / (a.n_heads / a.n_kv_heads);
+            const int prefix_ctas = ((b->n + tq5 - 1) / tq5) * a.n_kv_heads * chunks;
+            const int rest = sm_count() - prefix_ctas;
+            if (rest >= sm_count() / 4 && rest < ctas) ctas = rest;
+        }
         rc = launch_attn_mma(sa, b->e->d.kv_dtype, ctas, s);
         if (rc != NOVA_OK) return rc;
         return launch_attn_combine(sa, ctas, s);
@@ -868,7 +882,9 @@ int nova_batch_set_cascade(nova_batch* b, int on) {
     if (on && !b->casc_parts) {
         NOVA_CUDA_TRY(cudaSetDevice(e->d.device));
         // the chunk count never exceeds what a huge prefix would get (the per-CTA minimum of four pages only lowers it)
-        const int max_chunks = attn_prefix_chunks(b->n, e->d.n_heads, e->d.n_kv_heads, 1 << 24, nullptr);
+        int max_chunks = attn_prefix_chunks(b->n, e->d.n_heads, e->d.n_kv_heads, 1 << 24, nullptr);
+        const int tc5_chunks = attn_prefix_tc5_chunks(b->n, e->d.n_heads, e->d.n_kv_heads, 1 << 24, nullptr);
+        if (tc5_chunks > max_chunks) max_chunks = tc5_chunks;
         b->casc_floats = (size_t)(max_chunks + 1) * b->n * e->d.n_heads * kPartW;
         NOVA_CUDA_TRY(cudaMalloc((void**)&b->casc_parts, b->casc_floats * sizeof(float)));
     }

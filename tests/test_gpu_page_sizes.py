@@ -161,7 +161,7 @@ def test_page_sizes_cow_cascade_partials_prefill(nv, ob, kb):
         forks.append(f)
         eng.attach_prefix(f, donor, P)
     batch = eng.batch(forks)
-    try_set_kernel(nv, batch, 2)
+    try_set_kernel(nv, batch, 4 if kb >= 16 else 2)       # shared-prefix tiles on tcgen05 where the page size allows
     batch.set_cascade(1)
     batch.set_pdl(1)
     NH, NKV, S = eng.NH, eng.NKV, n_fork

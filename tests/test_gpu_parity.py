@@ -36,15 +36,16 @@ def kernels_for(nv, kv_dtype):
 
 
 def try_set_kernel(nv, batch, which):
-    """0 = SIMT, 1 = tensor-core (prefill on mma.sync tiles), 2 = tensor-core with RoPE+append fused into the attention
-    launch, 3 = tensor-core with the prefill on tcgen05 + tensor memory (the library's default where it applies)."""
+    """0 = SIMT, 1 = tensor-core (prefill and shared-prefix tiles on mma.sync), 2 = the same with RoPE+append fused into
+    the attention launch, 3 and 4 = 1 and 2 with the prefill and the shared-prefix tiles on tcgen05 + tensor memory (the
+    library's default where it applies)."""
     rc = nv.lib.nova_batch_set_kernel(batch.h, min(which, 1))
     if rc == nv.ERR_UNSUPPORTED:
         pytest.skip("kernel not built for this dtype")
     assert rc == 0
-    if which == 2:
+    if which in (2, 4):
         batch.set_fused_append(1)
-    if which == 3:
+    if which >= 3:
         batch.set_prefill_kernel(1)
     elif which >= 1:
         batch.set_prefill_kernel(0)
@@ -728,7 +729,7 @@ def test_cow_shared_prefix(nv, ob, kernel):
     eng.close()
 
 
-@pytest.mark.parametrize("kernel,mode", [(1, 1), (2, 1), (2, 2)])
+@pytest.mark.parametrize("kernel,mode", [(1, 1), (2, 1), (2, 2), (3, 1), (4, 1), (4, 2)])
 @pytest.mark.parametrize("model,n_fork,P", [("qwen25_7b", 12, 700), ("qwen25_14b", 5, 300), ("qwen25_1p5b", 10, 517)])
 def test_cascade_over_shared_prefix(nv, ob, model, n_fork, P, kernel, mode):
     """Sessions forked from one prefix (partly filled tail page), private suffixes of different lengths, then
@@ -747,7 +748,7 @@ def test_cascade_over_shared_prefix(nv, ob, model, n_fork, P, kernel, mode):
     batch = eng.batch(forks)
     try_set_kernel(nv, batch, kernel)
     batch.set_cascade(1)
-    batch.set_pdl(1 if kernel == 2 else 0)
+    batch.set_pdl(1 if kernel in (2, 4) else 0)
     NH, NKV, S = eng.NH, eng.NKV, n_fork
     out_d = nv.DevBuf(L * S * NH * 128 * 4)
     st = nv.Stream()
