@@ -104,8 +104,12 @@ constexpr int kCombineWarps = NOVA_COMBINE_WARPS;
 // kCoop = true (launches with few (row, head) units, e.g. one long session): a unit belongs to a whole CTA and its
 // contributors are dealt out to the warps 32 at a time, so a row that 136 CTAs worked on costs two memory round
 // trips instead of five; the warps' results meet in shared memory.
+// (Six warps of 128 registers for the cascade's merge were tried: such a CTA needs room in all four register-file
+// partitions and no longer starts beside a split CTA; 0.65 -> 0.86 ms per config-3 step.)
+constexpr int kFoldWarps = kCombineWarps;
 template <bool kFold, bool kCoop = false>
 __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLaunch a, int n_ctas_split) {
+    constexpr int kWarps = kCombineWarps;
     __shared__ int s_prefix[kMaxRowsSmem + 1];
     __shared__ float s_ml[kCoop ? 2 * kCombineWarps : 1];
     __shared__ float4 s_acc[kCoop ? kCombineWarps * 32 : 1];
@@ -143,8 +147,8 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
 
     const int64_t units = (int64_t)pv.rows_per_layer * a.n_layers * heads_per_row;
     const size_t stride_c = (size_t)heads_per_row * kSlotW;
-    for (int64_t u = kCoop ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kCombineWarps + warp; u < units;
-         u += kCoop ? (int64_t)gridDim.x : (int64_t)gridDim.x * kCombineWarps) {
+    for (int64_t u = kCoop ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kWarps + warp; u < units;
+         u += kCoop ? (int64_t)gridDim.x : (int64_t)gridDim.x * kWarps) {
         const int64_t v = u / heads_per_row;
         const int hr = (int)(u - v * heads_per_row);            // kv head in group * G + query head
         const int row = (int)(v % pv.rows_per_layer);
@@ -167,6 +171,77 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
         const int64_t head = ((int64_t)ll * S + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
         const float* base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
 
+        if constexpr (kFold) {
+            // The usual cascade row - a few split-K slots (or the one partial the split kernel left) and up to 16 chunk
+            // partials - in ONE memory round trip: every (m, l) pair and every accumulator is requested before
+            // anything is used.  (Piece by piece - slots, chunk maxima, chunks eight at a time - a row cost four
+            // dependent round trips, and a warp has several rows to finish.)
+            const int na = n == 1 ? 0 : n, nb = a.n_extra;
+            if (na <= 8 && nb <= 16) {
+                const size_t estride = (size_t)S * a.n_heads * kPartW;
+                const float* eb = a.extra_parts + head * kPartW;
+                const float* pr = a.out_part + head * kPartW;
+                float2 ml = make_float2(-INFINITY, 0.f);                 // lane = contributor: slots, chunks, lane 31 the lone partial
+                if (lane < na) ml = ld_cg_f2(base + (size_t)lane * stride_c);
+                else if (lane < na + nb) ml = ld_cg_f2(eb + (size_t)(lane - na) * estride);
+                else if (lane == 31 && n == 1) ml = ld_cg_f2(pr);
+                float4 xs[8];
+                float2 e0[16], e1[16], s0 = make_float2(0.f, 0.f), s1 = s0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    xs[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (i < na) xs[i] = ld_cg_f4(base + (size_t)i * stride_c + 4 + 4 * lane);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    e0[i] = e1[i] = make_float2(0.f, 0.f);
+                    if (i < nb) {
+                        const float* q = eb + (size_t)i * estride + 2 + 4 * lane;
+                        e0[i] = ld_cg_f2(q);
+                        e1[i] = ld_cg_f2(q + 2);
+                    }
+                }
+                if (n == 1) {
+                    s0 = ld_cg_f2(pr + 2 + 4 * lane);
+                    s1 = ld_cg_f2(pr + 4 + 4 * lane);
+                }
+                const float Mx = warp_max(ml.y > 0.f ? ml.x : -INFINITY);
+                const float w = (ml.y > 0.f && Mx > -INFINITY) ? __expf(ml.x - Mx) : 0.f;
+                const float Lx = warp_sum(ml.y * w);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float wi = __shfl_sync(0xffffffffu, w, i);
+                    if (i < na && wi != 0.f) {                 // a contributor with l == 0 carries no accumulator (and may hold anything)
+                        acc.x = fmaf(xs[i].x, wi, acc.x);
+                        acc.y = fmaf(xs[i].y, wi, acc.y);
+                        acc.z = fmaf(xs[i].z, wi, acc.z);
+                        acc.w = fmaf(xs[i].w, wi, acc.w);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float wi = __shfl_sync(0xffffffffu, w, (na + i) & 31);
+                    if (i < nb && wi != 0.f) {
+                        acc.x = fmaf(e0[i].x, wi, acc.x);
+                        acc.y = fmaf(e0[i].y, wi, acc.y);
+                        acc.z = fmaf(e1[i].x, wi, acc.z);
+                        acc.w = fmaf(e1[i].y, wi, acc.w);
+                    }
+                }
+                const float ws = __shfl_sync(0xffffffffu, w, 31);
+                if (n == 1 && ws != 0.f) {
+                    acc.x = fmaf(s0.x, ws, acc.x);
+                    acc.y = fmaf(s0.y, ws, acc.y);
+                    acc.z = fmaf(s1.x, ws, acc.z);
+                    acc.w = fmaf(s1.y, ws, acc.w);
+                }
+                const float inv = Lx > 0.f ? 1.f / Lx : 0.f;
+                *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =
+                    make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+                continue;
+            }
+        }
         // Contributors are taken 32 at a time: lane i holds (m, l) of contributor c0 + i while every
         // lane pulls its 4 dims of all 32 accumulators.  None of these loads depends on another, so a
         // chunk costs ONE memory round trip (a round trip is ~1 us here; a row usually fits one chunk).
@@ -625,7 +700,8 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
     // all of them to have started, and they must not pile up on the SMs the split kernel left free for
     // that next layer.  Measured (64 sessions x 8192 tokens, 14B shape): up to 74 CTAs 6.13 TB/s,
     // 120: 5.94, 148: 5.89.
-    int64_t ctas = (units + kCombineWarps - 1) / kCombineWarps;
+    const int warps = a.n_extra > 0 ? kFoldWarps : kCombineWarps;
+    int64_t ctas = (units + warps - 1) / warps;
 #ifndef NOVA_COMBINE_MAX_CTAS
 #define NOVA_COMBINE_MAX_CTAS 76
 #endif
@@ -639,7 +715,7 @@ int launch_attn_combine(const AttnLaunch& a, int n_ctas_split, cudaStream_t s) {
     const bool coop = a.n_extra == 0 && units <= NOVA_COMBINE_MAX_CTAS;      // few units: one CTA per unit
     if (coop) ctas = units;
     const cudaError_t le = a.n_extra > 0
-        ? launch_kernel_pdl(attn_combine_kernel<true>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split)
+        ? launch_kernel_pdl(attn_combine_kernel<true>, dim3((unsigned)ctas), dim3(32 * kFoldWarps), 0, s, true, a, n_ctas_split)
         : coop ? launch_kernel_pdl(attn_combine_kernel<false, true>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split)
                : launch_kernel_pdl(attn_combine_kernel<false>, dim3((unsigned)ctas), dim3(32 * kCombineWarps), 0, s, true, a, n_ctas_split);
     if (le != cudaSuccess) {

@@ -564,11 +564,14 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
             if (a.timeline && threadIdx.x == 0 && blockIdx.x < 148) a.timeline[148 * 8 + (size_t)blockIdx.x * 4 + 3] = now_ns();   // dependency met
 #endif
             const int seg = G * kPartW;                      // floats of one token's rows (even)
-            const int total2 = (t_cnt < tq ? t_cnt : tq) * seg / 2;
-            for (int e2 = (int)threadIdx.x; e2 < total2; e2 += kT5Rows) {
-                const int e = 2 * e2, tk = e / seg, r = e - tk * seg;
-                *reinterpret_cast<float2*>(a.out_part + (((int64_t)chunk * NQ + t0 + tk) * NH + kvh * G) * kPartW + r) =
-                    *reinterpret_cast<const float2*>(stage_rows + e);
+            const int total = (t_cnt < tq ? t_cnt : tq) * seg;
+            float* const obase = a.out_part + (((int64_t)chunk * NQ + t0) * NH + kvh * G) * kPartW;
+            const int64_t tok_stride = (int64_t)NH * kPartW;
+            int e = 2 * (int)threadIdx.x, tk = e / seg, r = e - tk * seg;       // float e of the staged rows = token tk, offset r
+            for (; e < total; e += 2 * kT5Rows) {
+                *reinterpret_cast<float2*>(obase + tk * tok_stride + r) = *reinterpret_cast<const float2*>(stage_rows + e);
+                r += 2 * kT5Rows;
+                while (r >= seg) { r -= seg; ++tk; }
             }
         } else if (!failed) {
             tc_fence_after();
