@@ -132,8 +132,6 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
     const int n_groups = a.n_kv_heads / KVG;
     const int heads_per_row = KVG * G;
     plan_build_prefix(a, s_prefix, n_groups);     // n_past: not written by the split kernel before us
-    pdl_wait();                                   // the split kernel's partials are complete from here on
-    if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[1]));
     PlanView pv;
     pv.prefix = s_prefix;
     const int S = a.n_sessions * plan_nq(a);        // units
@@ -142,55 +140,67 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
     pv.pages_per_layer = s_prefix[pv.rows_per_layer];
     pv.pages_total = pv.pages_per_layer * a.n_layers;
     pv.n_ctas = pv.pages_total < (int64_t)n_ctas_split ? (int)pv.pages_total : n_ctas_split;
-    plan_finish(pv);
-    if (pv.pages_total == 0) return;
+    if (pv.pages_total > 0) plan_finish(pv);
 
-    const int64_t units = (int64_t)pv.rows_per_layer * a.n_layers * heads_per_row;
+    const int64_t units = pv.pages_total > 0 ? (int64_t)pv.rows_per_layer * a.n_layers * heads_per_row : 0;
     const size_t stride_c = (size_t)heads_per_row * kSlotW;
-    for (int64_t u = kCoop ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kWarps + warp; u < units;
-         u += kCoop ? (int64_t)gridDim.x : (int64_t)gridDim.x * kWarps) {
+    // A (row, head) unit: where its split-K slots start, how many there are, which output row it is.  All of it
+    // follows from the positions alone, so a warp works it out for its first units BEFORE the dependency wait;
+    // what comes after the wait is on the layer's critical path.
+    struct Unit {
+        const float* base;
+        int64_t head;
+        int n;
+        bool todo;
+    };
+    auto describe = [&](int64_t u, Unit& d) {
         const int64_t v = u / heads_per_row;
         const int hr = (int)(u - v * heads_per_row);            // kv head in group * G + query head
         const int row = (int)(v % pv.rows_per_layer);
-        constexpr bool fold = kFold;                             // more parts to fold in: every row is ours to finish
         const bool no_pages = s_prefix[row + 1] == s_prefix[row];
-        if (no_pages && !fold) continue;                         // no pages: written by the split kernel
+        d.todo = false;
+        d.base = nullptr;
+        d.head = 0;
+        d.n = 0;
+        if (no_pages && !kFold) return;                          // no pages: written by the split kernel
         const int ll = (int)(v / pv.rows_per_layer);
         const int64_t row_begin = (int64_t)ll * pv.pages_per_layer + s_prefix[row];
         const int64_t row_end = (int64_t)ll * pv.pages_per_layer + s_prefix[row + 1];
-        int c_first, n;
-        if constexpr (kFold) {
+        int c_first;
+        if constexpr (kFold) {                                   // more parts to fold in: every row is ours to finish
             c_first = no_pages ? 0 : plan_owner(pv, row_begin);
-            n = no_pages ? 0 : plan_owner(pv, row_end - 1) - c_first + 1;
+            d.n = no_pages ? 0 : plan_owner(pv, row_end - 1) - c_first + 1;
         } else {
             c_first = plan_owner(pv, row_begin);
-            n = plan_owner(pv, row_end - 1) - c_first + 1;
-            if (n == 1) continue;                                 // written by the split kernel
+            d.n = plan_owner(pv, row_end - 1) - c_first + 1;
+            if (d.n == 1) return;                                 // written by the split kernel
         }
         const int s = row / n_groups, grp = row - s * n_groups;
-        const int64_t head = ((int64_t)ll * S + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
-        const float* base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
-
+        d.head = ((int64_t)ll * S + s) * a.n_heads + (int64_t)(grp * KVG) * G + hr;
+        d.base = a.part + ((size_t)(c_first + v) * heads_per_row + (size_t)hr) * kSlotW;
+        d.todo = true;
+    };
+    auto process = [&](const Unit& d) {
         if constexpr (kFold) {
             // The usual cascade row - a few split-K slots (or the one partial the split kernel left) and up to 16 chunk
             // partials - in ONE memory round trip: every (m, l) pair and every accumulator is requested before
             // anything is used.  (Piece by piece - slots, chunk maxima, chunks eight at a time - a row cost four
             // dependent round trips, and a warp has several rows to finish.)
-            const int na = n == 1 ? 0 : n, nb = a.n_extra;
+            const int na = d.n == 1 ? 0 : d.n, nb = a.n_extra;
             if (na <= 8 && nb <= 16) {
                 const size_t estride = (size_t)S * a.n_heads * kPartW;
-                const float* eb = a.extra_parts + head * kPartW;
-                const float* pr = a.out_part + head * kPartW;
+                const float* eb = a.extra_parts + d.head * kPartW;
+                const float* pr = a.out_part + d.head * kPartW;
                 float2 ml = make_float2(-INFINITY, 0.f);                 // lane = contributor: slots, chunks, lane 31 the lone partial
-                if (lane < na) ml = ld_cg_f2(base + (size_t)lane * stride_c);
+                if (lane < na) ml = ld_cg_f2(d.base + (size_t)lane * stride_c);
                 else if (lane < na + nb) ml = ld_cg_f2(eb + (size_t)(lane - na) * estride);
-                else if (lane == 31 && n == 1) ml = ld_cg_f2(pr);
+                else if (lane == 31 && d.n == 1) ml = ld_cg_f2(pr);
                 float4 xs[8];
                 float2 e0[16], e1[16], s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     xs[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (i < na) xs[i] = ld_cg_f4(base + (size_t)i * stride_c + 4 + 4 * lane);
+                    if (i < na) xs[i] = ld_cg_f4(d.base + (size_t)i * stride_c + 4 + 4 * lane);
                 }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -201,7 +211,7 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
                         e1[i] = ld_cg_f2(q + 2);
                     }
                 }
-                if (n == 1) {
+                if (d.n == 1) {
                     s0 = ld_cg_f2(pr + 2 + 4 * lane);
                     s1 = ld_cg_f2(pr + 4 + 4 * lane);
                 }
@@ -230,16 +240,16 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
                     }
                 }
                 const float ws = __shfl_sync(0xffffffffu, w, 31);
-                if (n == 1 && ws != 0.f) {
+                if (d.n == 1 && ws != 0.f) {
                     acc.x = fmaf(s0.x, ws, acc.x);
                     acc.y = fmaf(s0.y, ws, acc.y);
                     acc.z = fmaf(s1.x, ws, acc.z);
                     acc.w = fmaf(s1.y, ws, acc.w);
                 }
                 const float inv = Lx > 0.f ? 1.f / Lx : 0.f;
-                *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =
+                *reinterpret_cast<float4*>(a.out + d.head * kHeadDim + 4 * lane) =
                     make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-                continue;
+                return;
             }
         }
         // Contributors are taken 32 at a time: lane i holds (m, l) of contributor c0 + i while every
@@ -247,8 +257,8 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
         // chunk costs ONE memory round trip (a round trip is ~1 us here; a row usually fits one chunk).
         float M = -INFINITY, L = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if constexpr (kFold) if (n == 1) {            // the split kernel left this row's partial (m, l, acc) in out_part
-            const float* pr = a.out_part + head * kPartW;
+        if constexpr (kFold) if (d.n == 1) {            // the split kernel left this row's partial (m, l, acc) in out_part
+            const float* pr = a.out_part + d.head * kPartW;
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(pr));
             const float2 y0 = __ldcg(reinterpret_cast<const float2*>(pr + 2 + 4 * lane));
             const float2 y1 = __ldcg(reinterpret_cast<const float2*>(pr + 4 + 4 * lane));
@@ -258,8 +268,8 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
                 acc = make_float4(y0.x, y0.y, y1.x, y1.y);
             }
         }
-        for (int c0 = kCoop ? 32 * warp : 0; c0 < ((kFold && n == 1) ? 0 : n); c0 += kCoop ? 32 * kCombineWarps : 32)
-            fold_contributors(base + (size_t)c0 * stride_c, stride_c, n - c0 < 32 ? n - c0 : 32, lane, M, L, acc);
+        for (int c0 = kCoop ? 32 * warp : 0; c0 < ((kFold && d.n == 1) ? 0 : d.n); c0 += kCoop ? 32 * kCombineWarps : 32)
+            fold_contributors(d.base + (size_t)c0 * stride_c, stride_c, d.n - c0 < 32 ? d.n - c0 : 32, lane, M, L, acc);
         if constexpr (kCoop) {       // the warps' shares of the row meet here; warp 0 finishes the row
             if (lane == 0) { s_ml[2 * warp] = M; s_ml[2 * warp + 1] = L; }
             s_acc[warp * 32 + lane] = acc;
@@ -287,19 +297,19 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
                 M = Mx;
             }
             __syncthreads();
-            if (warp != 0) continue;
+            if (warp != 0) return;
         }
         if constexpr (kFold) {
             // the extra parts (a cascade's chunks over the shared pages), 32 (m, l) pairs and 8 accumulators at a time
             const size_t estride = (size_t)S * a.n_heads * kPartW;
-            const float* eb = a.extra_parts + head * kPartW;
+            const float* eb = a.extra_parts + d.head * kPartW;
             for (int e0 = 0; e0 < a.n_extra; e0 += 32) {
                 const int cnt = a.n_extra - e0 < 32 ? a.n_extra - e0 : 32;
                 float2 ml = make_float2(-INFINITY, 0.f);
                 if (lane < cnt) ml = __ldcg(reinterpret_cast<const float2*>(eb + (size_t)(e0 + lane) * estride));
                 const float mc = warp_max(ml.y > 0.f ? ml.x : -INFINITY);
                 const float Mn = fmaxf(M, mc);
-                if (Mn == -INFINITY) continue;
+                if (Mn == -INFINITY) return;
                 const float corr = __expf(M - Mn);
                 const float w = ml.y > 0.f ? __expf(ml.x - Mn) : 0.f;
                 L = fmaf(L, corr, warp_sum(ml.y * w));
@@ -329,10 +339,10 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
                 M = Mn;
             }
             const float inv = L > 0.f ? 1.f / L : 0.f;
-            *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =
+            *reinterpret_cast<float4*>(a.out + d.head * kHeadDim + 4 * lane) =
                 make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         } else if (a.write_partial_only) {
-            float* op = a.out_part + head * kPartW;
+            float* op = a.out_part + d.head * kPartW;
             if (lane == 0) { op[0] = M; op[1] = L; }
             op[2 + 4 * lane + 0] = acc.x;
             op[2 + 4 * lane + 1] = acc.y;
@@ -340,9 +350,31 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_kernel(AttnLa
             op[2 + 4 * lane + 3] = acc.w;
         } else {
             const float inv = L > 0.f ? 1.f / L : 0.f;
-            *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =
+            *reinterpret_cast<float4*>(a.out + d.head * kHeadDim + 4 * lane) =
                 make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         }
+    };
+    constexpr int kPre = (kFold && !kCoop) ? 6 : 1;
+    const int64_t u_step = kCoop ? (int64_t)gridDim.x : (int64_t)gridDim.x * kWarps;
+    int64_t u = kCoop ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kWarps + warp;
+    Unit pre[kPre];
+    int n_pre = 0;
+#pragma unroll
+    for (int i = 0; i < kPre; ++i)
+        if (u < units) {
+            describe(u, pre[i]);
+            ++n_pre;
+            u += u_step;
+        }
+    pdl_wait();                                   // the split kernel's partials are complete from here on
+    if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[1]));
+#pragma unroll
+    for (int i = 0; i < kPre; ++i)
+        if (i < n_pre && pre[i].todo) process(pre[i]);
+    for (; u < units; u += u_step) {
+        Unit d;
+        describe(u, d);
+        if (d.todo) process(d);
     }
     if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[3]));
 }
