@@ -712,6 +712,7 @@ __global__ void __launch_bounds__(32 * kCombineWarps) attn_combine_exchange_kern
             __syncthreads();
         }
         if (warp != 0) continue;
+        if (tl && threadIdx.x == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl[2]));     // (overwrites %smid) the rank's own row is ready
         if (!exchange_and_merge(ps, mine, region_bytes, n_ranks, my_rank, (int)head, epoch, timeout_ns, xstatus, M, L, acc)) continue;
         const float inv = L > 0.f ? 1.f / L : 0.f;
         *reinterpret_cast<float4*>(a.out + head * kHeadDim + 4 * lane) =

@@ -23,7 +23,8 @@ int nova_synth_normal(float* dst_dev, size_t n, uint64_t key, uint64_t first_ind
  * memory (launch i of the batch writes record i % 4), or NULL to switch off.  Every CTA leaves %globaltimer
  * stamps: [0] start, [1] work split known, [2] first page requested, [3] last page requested, [4] first page
  * landed, [5] last page consumed, [6] results written, [7] the SM it ran on (%smid); after those 148*8 values
- * the first 148 CTAs of the merge kernel leave four values each (start, dependency met, %smid, end).
+ * the first 148 CTAs of the merge kernel leave four values each (start, dependency met, %smid, end; the merge +
+ * exchange kernel of nova_batch_step_partial_peers leaves "own row ready" in place of %smid).
  * With the cascade on, four more records follow (launch i's shared-prefix tiles write record 4 + i % 4: per CTA start,
  * %smid, end).  The tcgen05 prefill kernel uses the buffer differently (3 x 1700 x 4 uint64, CTAs beyond 1700 leave nothing):
  * [cta][0..3] = start (ns), %smid, end (ns), cycles spent issuing score MMAs; then per CTA the first issuing warp's
