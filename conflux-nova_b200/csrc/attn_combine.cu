@@ -505,33 +505,30 @@ __device__ __forceinline__ bool exchange_and_merge(const PeerSlots& ps, const un
     unsigned long long t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     bool failed = false;
+    // Every peer in one round: all loads first, then the checks.  Lane p alone reads peer p's (m, l) word (the other
+    // lanes get the values by shuffle at the end), so a round is 2 loads per peer and lane, 64 registers in flight.
+    uint4 w0 = make_uint4(0u, 0u, 0u, 0u);
     while (__any_sync(0xffffffffu, pending != 0)) {
+        uint4 w1[kMaxPeerRanks], w2[kMaxPeerRanks], w0n = w0;
 #pragma unroll
-        for (int half = 0; half < kMaxPeerRanks; half += 4) {      // four peers at a time: all their loads first, then the checks
-            uint4 w0[4], w1[4], w2[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int p = half + j;
-                if (pending & (1u << p)) {
-                    const unsigned char* src = mine + (size_t)p * region_bytes + row_off;
-                    w0[j] = ll_load(src);                       // every lane needs (m, l)
-                    w1[j] = ll_load(src + 16 * (1 + 2 * lane));
-                    w2[j] = ll_load(src + 16 * (2 + 2 * lane));
-                }
+        for (int p = 0; p < kMaxPeerRanks; ++p) {
+            if (pending & (1u << p)) {
+                const unsigned char* src = mine + (size_t)p * region_bytes + row_off;
+                if (lane == p) w0n = ll_load(src);
+                w1[p] = ll_load(src + 16 * (1 + 2 * lane));
+                w2[p] = ll_load(src + 16 * (2 + 2 * lane));
             }
+        }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int p = half + j;
-                if (pending & (1u << p)) {
-                    const bool ok = w0[j].y == epoch && w0[j].w == epoch && w1[j].y == epoch && w1[j].w == epoch &&
-                                    w2[j].y == epoch && w2[j].w == epoch;
-                    if (ok) {
-                        pm[p] = __uint_as_float(w0[j].x);
-                        pl[p] = __uint_as_float(w0[j].z);
-                        pa[p] = make_float4(__uint_as_float(w1[j].x), __uint_as_float(w1[j].z), __uint_as_float(w2[j].x),
-                                            __uint_as_float(w2[j].z));
-                        pending &= ~(1u << p);
-                    }
+        for (int p = 0; p < kMaxPeerRanks; ++p) {
+            if (pending & (1u << p)) {
+                bool ok = w1[p].y == epoch && w1[p].w == epoch && w2[p].y == epoch && w2[p].w == epoch;
+                if (lane == p) ok = ok && w0n.y == epoch && w0n.w == epoch;
+                if (ok) {
+                    if (lane == p) w0 = w0n;
+                    pa[p] = make_float4(__uint_as_float(w1[p].x), __uint_as_float(w1[p].z), __uint_as_float(w2[p].x),
+                                        __uint_as_float(w2[p].z));
+                    pending &= ~(1u << p);
                 }
             }
         }
@@ -546,6 +543,15 @@ __device__ __forceinline__ bool exchange_and_merge(const PeerSlots& ps, const un
     if (failed) {
         if (lane == 0 && status) atomicCAS(status, 0, NOVA_ERR_TIMEOUT);
         return false;
+    }
+#pragma unroll
+    for (int p = 0; p < kMaxPeerRanks; ++p) {             // (m, l) of peer p from the lane that read it
+        const float m_p = __uint_as_float(__shfl_sync(0xffffffffu, w0.x, p));
+        const float l_p = __uint_as_float(__shfl_sync(0xffffffffu, w0.z, p));
+        if (p < n_ranks && p != my_rank) {
+            pm[p] = m_p;
+            pl[p] = l_p;
+        }
     }
 #pragma unroll
     for (int p = 0; p < kMaxPeerRanks; ++p) {             // this rank's own row sits at its place in the order
