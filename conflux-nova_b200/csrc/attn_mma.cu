@@ -25,6 +25,8 @@
 //     before) the kernel computes without waiting, parks finished segments in shared memory and
 //     waits for the previous kernels once, right before its first output write; such a launch
 //     leaves NOVA_ATTN_SPARE_SMS SMs without a CTA so that consecutive layers overlap.
+#include <type_traits>
+
 #include "attn_plan.cuh"
 #include "mma_common.cuh"
 
@@ -60,20 +62,30 @@ constexpr int kStages = NOVA_ATTN_STAGES;   // page sets in flight per CTA; more
 constexpr int kStashSlots = NOVA_ATTN_STASH;
 constexpr int kStashWords = 38;
 
-template <int KVG>
+// kF32: fp32 pools (the reference's own format).  The page copies then bring fp32 rows - boxes of [32 dims][16 slots]
+// [KVG], eight per page set, two page sets of 64 KiB in flight - and each consumer warp first converts its kv head's
+// 16 x 128 K and V values to fp16 into ONE shared page set laid out exactly like an fp16 stage (the raw stage is handed
+// back to the producer as soon as that is done); from there on the tile arithmetic is the fp16 kernel's.  K and V are
+// therefore rounded to fp16 on their way into the tensor cores (values beyond the fp16 range would saturate: the SIMT
+// kernel stays the default for fp32 pools); 16-token pages and 4-kv-head groups only in this form.  The fused append
+// stores the new token's fp32 rows into the pool and their fp16 roundings into the converted page set.
+template <int KVG, bool kF32 = false>
 struct MmaCfg {
-    static constexpr int kBoxBytes = KVG * 16 * 128;          // one [64 dims][16 slots][KVG] box
-    static constexpr int kStageBytes = 4 * kBoxBytes;          // K lo/hi dims + V lo/hi dims
+    static constexpr int kBoxBytes = KVG * 16 * 128;          // one [64 dims fp16 | 32 dims fp32][16 slots][KVG] box
+    static constexpr int kConvBytes = 4 * kBoxBytes;           // an fp16 page set: K lo/hi dims + V lo/hi dims
+    static constexpr int kStageBytes = kF32 ? 8 * kBoxBytes : kConvBytes;
+    static constexpr int kNStages = kF32 ? 2 : kStages;
     static constexpr int kStashBytes = kStashSlots * KVG * kStashWords * 128;   // finished segments parked until the first write
-    static constexpr int kSmemBytes = kStages * kStageBytes + kStashBytes + 1024;
+    static constexpr int kSmemBytes = kNStages * kStageBytes + (kF32 ? kConvBytes : 0) + kStashBytes + 1024;
     static constexpr int kThreads = 32 * (KVG + 1);
-    static constexpr int kCtasPerSm = 4 / KVG >= 1 ? 4 / KVG : 1;
+    static constexpr int kCtasPerSm = kF32 ? 1 : (4 / KVG >= 1 ? 4 / KVG : 1);
 };
 
-template <int KVG>
-__global__ void __launch_bounds__(MmaCfg<KVG>::kThreads, MmaCfg<KVG>::kCtasPerSm)
+template <int KVG, bool kF32 = false>
+__global__ void __launch_bounds__(MmaCfg<KVG, kF32>::kThreads, MmaCfg<KVG, kF32>::kCtasPerSm)
 attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv) {
-    using Cfg = MmaCfg<KVG>;
+    using Cfg = MmaCfg<KVG, kF32>;
+    constexpr int kNStages = Cfg::kNStages;
     extern __shared__ unsigned char smem_raw[];
     __shared__ int s_prefix[kMaxRowsSmem + 1];
     __shared__ int s_slice[kMaxRowsSmem];
@@ -107,8 +119,8 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         tl[0] = now_ns();
         tl[7] = smid;
     }
-    if (threadIdx.x == 32 * (MmaCfg<KVG>::kThreads / 32 - 1)) {      // the producer's lane 0; warp 0 is busy with the prefix scan
-        for (int i = 0; i < kStages; ++i) {
+    if (threadIdx.x == 32 * (Cfg::kThreads / 32 - 1)) {      // the producer's lane 0; warp 0 is busy with the prefix scan
+        for (int i = 0; i < kNStages; ++i) {
             mbar_init(smem_u32(&s_full[i]), 1);
             mbar_init(smem_u32(&s_empty[i]), KVG);
         }
@@ -123,7 +135,7 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         // 8-token pages fill only the first 8 of a stage's 16 key rows per kv head.  The other rows take part in the
         // tile arithmetic with weight zero, so they must hold finite values: clear the ring once; the page copies
         // never touch those rows afterwards.
-        for (uint32_t off = threadIdx.x * 16u; off < (uint32_t)(kStages * Cfg::kStageBytes); off += blockDim.x * 16u)
+        for (uint32_t off = threadIdx.x * 16u; off < (uint32_t)(kNStages * Cfg::kStageBytes); off += blockDim.x * 16u)
             asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(stage0 + off), "r"(0u) : "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -240,15 +252,15 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         while (cur.count > 0) {
             // Issue the first few pages of the batch before looking ahead, so that opening the next
             // segment (work split, prefetch hints) never delays copies that could already be in flight.
-            const int head_n = cur.count < kStages ? cur.count : kStages;
+            const int head_n = cur.count < kNStages ? cur.count : kNStages;
             Batch nxt;
             int phys_nxt = 0;
             for (int j = 0; j < cur.count; ++j, ++it) {
                 int phys = __shfl_sync(0xffffffffu, phys_cur, j);
                 int ok = 1;
                 if (lane == 0) {
-                    const int stage = (int)(it % kStages);
-                    const uint32_t round = it / kStages;
+                    const int stage = (int)(it % kNStages);
+                    const uint32_t round = it / kNStages;
                     if (round > 0 && !mbar_wait(smem_u32(&s_empty[stage]), (round - 1) & 1, &s_abort)) {
                         if (a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
                         ok = 0;
@@ -267,7 +279,21 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                         const uint32_t dst = stage0 + (uint32_t)stage * Cfg::kStageBytes;
                         const int c1 = (int)((((int64_t)cur.layer * a.nb + phys) << geo.kv_shift) + ((page & tpp_mask) << 4));
                         const int c2 = cur.group * KVG;
-                        if (geo.tile_keys < kTileKeysMax) {
+                        if constexpr (kF32) {
+                            // fp32 rows: four boxes of 32 dims for K, four for V
+                            mbar_expect_tx(bar, Cfg::kStageBytes);
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+#if NOVA_ATTN_EVICT_FIRST
+                                tma_load_3d_hint(dst + (uint32_t)(c * Cfg::kBoxBytes), &tmk, 32 * c, c1, c2, bar, kv_policy);
+                                tma_load_3d_hint(dst + (uint32_t)((4 + c) * Cfg::kBoxBytes), &tmv, 32 * c, c1, c2, bar, kv_policy);
+#else
+                                tma_load_3d(dst + (uint32_t)(c * Cfg::kBoxBytes), &tmk, 32 * c, c1, c2, bar);
+                                tma_load_3d(dst + (uint32_t)((4 + c) * Cfg::kBoxBytes), &tmv, 32 * c, c1, c2, bar);
+#endif
+                            }
+                            if (tl && it == 0) tl[2] = now_ns();
+                        } else if (geo.tile_keys < kTileKeysMax) {
                             // 8-token pages: the maps' boxes are [64 dims][8 slots][1 kv head]; each kv head's box goes
                             // to the first half of that head's 16 rows
                             mbar_expect_tx(bar, Cfg::kStageBytes / 2);
@@ -336,7 +362,9 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         dep_met = true;
     }
     int n_stashed = 0;
-    float* stash = reinterpret_cast<float*>(smem_raw + (stage0 - smem_u32(smem_raw)) + kStages * Cfg::kStageBytes);
+    const uint32_t conv0 = stage0 + (uint32_t)(kNStages * Cfg::kStageBytes);      // kF32: the converted (fp16) page set
+    float* stash = reinterpret_cast<float*>(smem_raw + (stage0 - smem_u32(smem_raw)) + kNStages * Cfg::kStageBytes +
+                                            (kF32 ? Cfg::kConvBytes : 0));
 
     // One finished segment -> memory: the row's output when this CTA covered the whole row, else
     // (m, l, acc) into this CTA's partial slot for the merge kernel.
@@ -428,15 +456,42 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
         for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = 0.f;
 
         for (int pg = 0; pg < sg.page_count; ++pg, ++it) {
-            const int stage = (int)(it % kStages);
-            const uint32_t round = it / kStages;
+            const int stage = (int)(it % kNStages);
+            const uint32_t round = it / kNStages;
             if (!mbar_wait(smem_u32(&s_full[stage]), round & 1, &s_abort)) {
                 if (lane == 0 && a.status) atomicCAS(a.status, 0, NOVA_ERR_TIMEOUT);
                 return;
             }
             if (tl && threadIdx.x == 0 && it == 0) tl[4] = now_ns();
             const int kcount = s_kcount[stage];
-            const uint32_t sk = stage0 + (uint32_t)stage * Cfg::kStageBytes;
+            uint32_t sk = stage0 + (uint32_t)stage * Cfg::kStageBytes;
+            if constexpr (kF32) {
+                // This kv head's 16 x 128 K and V values, fp32 -> fp16, from the raw stage into the fp16 page set (a
+                // lane takes 8 dims of a key at a time: two swizzled 16-byte pieces in, one out); then the raw stage
+                // goes back to the producer.
+                const uint32_t raw = sk;
+#pragma unroll
+                for (int which = 0; which < 2; ++which)
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int unit = lane + 32 * u, r = unit >> 4, ch = unit & 15;     // key row, 8-dim piece
+                        const uint32_t src = raw + (uint32_t)((4 * which + (ch >> 2)) * Cfg::kBoxBytes + (w * 16 + r) * 128);
+                        const uint32_t j0 = (uint32_t)((ch & 3) * 2);
+                        float4 x0, x1;
+                        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(x0.x), "=f"(x0.y), "=f"(x0.z), "=f"(x0.w)
+                                     : "r"(src + ((j0 ^ (uint32_t)(r & 7)) << 4)));
+                        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(x1.x), "=f"(x1.y), "=f"(x1.z), "=f"(x1.w)
+                                     : "r"(src + (((j0 + 1) ^ (uint32_t)(r & 7)) << 4)));
+                        const uint32_t dst = conv0 + (uint32_t)((2 * which + (ch >> 3)) * Cfg::kBoxBytes + w * 2048 + r * 128 +
+                                                                 (((ch & 7) ^ (r & 7)) << 4));
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(pack_h2(x0.x, x0.y)), "r"(pack_h2(x0.z, x0.w)),
+                                     "r"(pack_h2(x1.x, x1.y)), "r"(pack_h2(x1.z, x1.w))
+                                     : "memory");
+                    }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
+                sk = conv0;
+            }
             const uint32_t sv = sk + 2 * Cfg::kBoxBytes;
 
             if (kcount > 0) {
@@ -456,8 +511,9 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     const float* sr = a.rope_sn + (int64_t)pos_new * (kHeadDim / 2);
                     const int64_t grow = ((((int64_t)layer * a.nb + s_phys[stage]) << geo.kv_shift) + (pos_new & ((1 << geo.kv_shift) - 1))) *
                                              (int64_t)a.n_kv_heads * kHeadDim + (int64_t)kvh * kHeadDim;
-                    __half* gk = static_cast<__half*>(a.pool_k_w) + grow;
-                    __half* gv = static_cast<__half*>(a.pool_v_w) + grow;
+                    using PoolT = typename std::conditional<kF32, float, __half>::type;
+                    PoolT* gk = static_cast<PoolT*>(a.pool_k_w) + grow;
+                    PoolT* gv = static_cast<PoolT*>(a.pool_v_w) + grow;
                     const uint32_t srow = (uint32_t)(w * 2048 + slot * 128);
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
@@ -468,10 +524,16 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                         const float r1 = __fmaf_rn(x0, sn, __fmul_rn(x1, c));
                         kn[i] = r0;
                         kn[i + 64] = r1;
+                        const float vf0 = vn[i], vf1 = vn[i + 64];
                         const __half k0 = __float2half_rn(r0), k1 = __float2half_rn(r1);
-                        const __half v0 = __float2half_rn(vn[i]), v1 = __float2half_rn(vn[i + 64]);
-                        gk[i] = k0; gk[i + 64] = k1;
-                        gv[i] = v0; gv[i + 64] = v1;
+                        const __half v0 = __float2half_rn(vf0), v1 = __float2half_rn(vf1);
+                        if constexpr (kF32) {          // the pool keeps the fp32 values, the staged fp16 copy their roundings
+                            gk[i] = r0; gk[i + 64] = r1;
+                            gv[i] = vf0; gv[i + 64] = vf1;
+                        } else {
+                            gk[i] = k0; gk[i + 64] = k1;
+                            gv[i] = v0; gv[i + 64] = v1;
+                        }
                         const uint32_t off = srow + ((((uint32_t)i >> 3) ^ (uint32_t)(slot & 7)) << 4) + (((uint32_t)i & 7) << 1);
                         asm volatile("st.shared.u16 [%0], %1;" ::"r"(sk + off), "h"(__half_as_ushort(k0)) : "memory");
                         asm volatile("st.shared.u16 [%0], %1;" ::"r"(sk + (uint32_t)Cfg::kBoxBytes + off), "h"(__half_as_ushort(k1)) : "memory");
@@ -538,10 +600,10 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
                     mma_top(o[2 * jp][0], o[2 * jp][1], p0, p1, b[0], b[1], o[2 * jp][0], o[2 * jp][1]);
                     mma_top(o[2 * jp + 1][0], o[2 * jp + 1][1], p0, p1, b[2], b[3], o[2 * jp + 1][0], o[2 * jp + 1][1]);
                 }
-                if (kcount < geo.tile_keys || patched) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (!kF32 && (kcount < geo.tile_keys || patched)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
+            if (!kF32 && lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
         }
 
         // ---- segment done: row sums, then direct output or a partial slot
@@ -581,22 +643,22 @@ attn_mma_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, const __g
     }
 }
 
-template <int KVG>
+template <int KVG, bool kF32 = false>
 int launch_kvg(const AttnLaunch& a, int n_ctas, cudaStream_t s) {
-    using Cfg = MmaCfg<KVG>;
+    using Cfg = MmaCfg<KVG, kF32>;
     static bool attr_set[64] = {};          // the attribute is per device
     int dev = 0;
     NOVA_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        NOVA_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<KVG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           Cfg::kSmemBytes));
+        NOVA_CUDA_TRY((cudaFuncSetAttribute(attn_mma_kernel<KVG, kF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            Cfg::kSmemBytes)));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     // 8-token pages are fetched one kv head at a time (maps with [64][8][1] boxes)
     const bool per_head = (a.kv_shift ? a.kv_shift : kKvShift) < 4;
     const CUtensorMap* tk = static_cast<const CUtensorMap*>(per_head ? a.tmap_k1 : a.tmap_k);
     const CUtensorMap* tv = static_cast<const CUtensorMap*>(per_head ? a.tmap_v1 : a.tmap_v);
-    const cudaError_t le = launch_kernel_pdl(attn_mma_kernel<KVG>, dim3((unsigned)n_ctas), dim3(Cfg::kThreads),
+    const cudaError_t le = launch_kernel_pdl(attn_mma_kernel<KVG, kF32>, dim3((unsigned)n_ctas), dim3(Cfg::kThreads),
                                              (size_t)Cfg::kSmemBytes, s, a.pdl != 0, a, *tk, *tv);
     if (le != cudaSuccess) {
         set_cuda_error(le, "attention launch");
@@ -618,7 +680,7 @@ size_t attn_tmap_bytes() { return sizeof(CUtensorMap); }
 
 // Tensor map over one fp16 pool [rows = L*NB*page tokens][NKV][128]: dim0 = 128 dims, dim1 = slot rows
 // (stride NKV*256 B), dim2 = kv head (stride 256 B); box = [64][box_rows = 16 or 8][kv_group], 128-byte swizzle.
-int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group, int box_rows) {
+int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group, int box_rows, int elem_bytes) {
     static EncodeTiledFn encode = nullptr;
     if (!encode) {
         cudaDriverEntryPointQueryResult q;
@@ -631,12 +693,13 @@ int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads,
         encode = (EncodeTiledFn)fn;
     }
     if (slot_rows <= 0 || slot_rows > 0x7fffffffLL) return NOVA_ERR_TOO_LARGE;
-    if (box_rows != 8 && box_rows != 16) return NOVA_ERR_INVALID;
+    if ((box_rows != 8 && box_rows != 16) || (elem_bytes != 2 && elem_bytes != 4)) return NOVA_ERR_INVALID;
     const cuuint64_t dims[3] = {(cuuint64_t)kHeadDim, (cuuint64_t)slot_rows, (cuuint64_t)n_kv_heads};
-    const cuuint64_t strides[2] = {(cuuint64_t)n_kv_heads * kHeadDim * 2, (cuuint64_t)kHeadDim * 2};
-    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)kv_group};
+    const cuuint64_t strides[2] = {(cuuint64_t)n_kv_heads * kHeadDim * (cuuint64_t)elem_bytes, (cuuint64_t)kHeadDim * (cuuint64_t)elem_bytes};
+    const cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows, (cuuint32_t)kv_group};      // 128-byte lines
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = encode(static_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, pool, dims, strides,
+    const CUresult r = encode(static_cast<CUtensorMap*>(out_map), elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                              3, pool, dims, strides,
                               box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -653,7 +716,9 @@ int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
 }
 
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
-    if (kv_dtype != NOVA_KV_F16 || !a.tmap_k || !a.tmap_v) return NOVA_ERR_UNSUPPORTED;
+    if ((kv_dtype != NOVA_KV_F16 && kv_dtype != NOVA_KV_F32) || !a.tmap_k || !a.tmap_v) return NOVA_ERR_UNSUPPORTED;
+    // fp32 pools: converted to fp16 on the way in; 16-token pages and groups of four kv heads
+    if (kv_dtype == NOVA_KV_F32 && ((a.kv_shift ? a.kv_shift : kKvShift) != 4 || a.kv_group != 4)) return NOVA_ERR_UNSUPPORTED;
     if ((a.kv_shift ? a.kv_shift : kKvShift) < 4 && (!a.tmap_k1 || !a.tmap_v1)) return NOVA_ERR_UNSUPPORTED;
     if (a.fuse_append && a.n_q > 1) return NOVA_ERR_UNSUPPORTED;      // the fused append is a decode (one token) path
     if (a.fuse_append && (!a.n_past || !a.k_new || !a.v_new || !a.rope_cs || !a.rope_sn || !a.pool_k_w || !a.pool_v_w))
@@ -662,6 +727,7 @@ int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t 
     if (a.n_heads % a.n_kv_heads || a.n_kv_heads % a.kv_group) return NOVA_ERR_INVALID;
     if (a.n_heads / a.n_kv_heads > 8) return NOVA_ERR_UNSUPPORTED;
     if ((int64_t)a.n_sessions * (a.n_q > 1 ? a.n_q : 1) * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
+    if (kv_dtype == NOVA_KV_F32) return launch_kvg<4, true>(a, attn_split_ctas_mma(a, n_ctas), s);
     switch (a.kv_group) {
         case 4: return launch_kvg<4>(a, attn_split_ctas_mma(a, n_ctas), s);
         case 2: return launch_kvg<2>(a, attn_split_ctas_mma(a, n_ctas), s);

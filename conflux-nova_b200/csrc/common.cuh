@@ -167,7 +167,7 @@ int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t 
 int attn_default_ctas_simt(int n_kv_heads);
 int attn_default_ctas_mma();
 bool attn_mma_built();
-int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group, int box_rows);
+int attn_make_tmap(void* out_map, void* pool, int64_t slot_rows, int n_kv_heads, int kv_group, int box_rows, int elem_bytes);
 int launch_attn_prefill(const AttnLaunch& a, cudaStream_t s);     // query-tiled tensor-core prefill (n_q >= 1, one layer)
 int attn_prefill_tile_tokens(int n_heads, int n_kv_heads);
 int launch_attn_prefill_tc5(const AttnLaunch& a, cudaStream_t s);    // the same on tcgen05 + tensor memory (pages of >= 16 tokens)

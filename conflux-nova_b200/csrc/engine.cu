@@ -43,7 +43,8 @@ struct nova_engine {
     alignas(128) unsigned char tmap_v[128];
     alignas(128) unsigned char tmap_k1[128];  // one kv head per box (prefill)
     alignas(128) unsigned char tmap_v1[128];
-    bool tmaps_ok = false;
+    bool tmaps_ok = false;           // tmap_k / tmap_v (kv-group boxes) are valid: the tensor-core decode kernel can run
+    bool tmaps1_ok = false;          // tmap_k1 / tmap_v1 (one kv head per box) too: prefill tiles, 8-token pages
     std::vector<SessionRec> sess;
     std::mutex mu;
 };
@@ -159,8 +160,8 @@ void fill_attn(const nova_batch* b, AttnLaunch& a) {
     a.row_setup_pages = b->row_setup;
     a.tmap_k = e->tmaps_ok ? e->tmap_k : nullptr;
     a.tmap_v = e->tmaps_ok ? e->tmap_v : nullptr;
-    a.tmap_k1 = e->tmaps_ok ? e->tmap_k1 : nullptr;
-    a.tmap_v1 = e->tmaps_ok ? e->tmap_v1 : nullptr;
+    a.tmap_k1 = e->tmaps1_ok ? e->tmap_k1 : nullptr;
+    a.tmap_v1 = e->tmaps1_ok ? e->tmap_v1 : nullptr;
     a.timeline = b->timeline ? b->timeline + (size_t)(b->tl_seq++ % 4u) * (kTimelineCtas * 12) : nullptr;
 }
 
@@ -169,12 +170,13 @@ int pick_split_ctas(const nova_batch* b, const AttnLaunch& a);
 // Split kernel, then the merge of the rows that more than one CTA worked on.
 int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
     int rc, ctas;
-    if (b->kernel == 1 && a.n_q > 1 && a.n_layers == 1 && !a.write_partial_only) {
+    const bool f16 = b->e->d.kv_dtype == NOVA_KV_F16;
+    if (b->kernel == 1 && f16 && a.n_q > 1 && a.n_layers == 1 && !a.write_partial_only) {
         // query-tiled prefill: every row complete in one CTA, no merge
         if (b->prefill_tc5 && attn_prefill_tc5_supports(a)) return launch_attn_prefill_tc5(a, s);
         return launch_attn_prefill(a, s);
     }
-    if (b->kernel == 1 && b->cascade && b->casc_pages > 0 && a.n_layers == 1 && a.n_q <= 1 && !a.write_partial_only &&
+    if (b->kernel == 1 && f16 && b->cascade && b->casc_pages > 0 && a.n_layers == 1 && a.n_q <= 1 && !a.write_partial_only &&
         a.page_lo == 0 && a.page_hi < 0) {
         // Cascade over a shared prefix: (1) all sessions' queries against the shared pages, read once, as
         // partials per page chunk; (2) the usual split over each session's own pages from the first private
@@ -213,7 +215,7 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
         if (rc != NOVA_OK) return rc;
         return launch_attn_combine(sa, ctas, s);
     }
-    if (b->kernel == 1) {
+    if (b->kernel == 1 && (f16 || a.n_q <= 1)) {
         ctas = pick_split_ctas(b, a);
         rc = launch_attn_mma(a, b->e->d.kv_dtype, ctas, s);
     } else {
@@ -351,10 +353,16 @@ int nova_engine_create(const nova_engine_desc* desc, nova_engine** out) {
     if (d.kv_dtype == NOVA_KV_F16 && attn_mma_built()) {
         const int64_t slot_rows = (int64_t)d.n_layers * e->nb * d.kv_block;
         const int box_rows = d.kv_block < kTileKeysMax ? d.kv_block : kTileKeysMax;      // a tile of the page
-        e->tmaps_ok = attn_make_tmap(e->tmap_k, e->pool_k, slot_rows, d.n_kv_heads, e->kv_group, box_rows) == NOVA_OK &&
-                      attn_make_tmap(e->tmap_v, e->pool_v, slot_rows, d.n_kv_heads, e->kv_group, box_rows) == NOVA_OK &&
-                      attn_make_tmap(e->tmap_k1, e->pool_k, slot_rows, d.n_kv_heads, 1, box_rows) == NOVA_OK &&
-                      attn_make_tmap(e->tmap_v1, e->pool_v, slot_rows, d.n_kv_heads, 1, box_rows) == NOVA_OK;
+        e->tmaps_ok = attn_make_tmap(e->tmap_k, e->pool_k, slot_rows, d.n_kv_heads, e->kv_group, box_rows, 2) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_v, e->pool_v, slot_rows, d.n_kv_heads, e->kv_group, box_rows, 2) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_k1, e->pool_k, slot_rows, d.n_kv_heads, 1, box_rows, 2) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_v1, e->pool_v, slot_rows, d.n_kv_heads, 1, box_rows, 2) == NOVA_OK;
+        e->tmaps1_ok = e->tmaps_ok;
+    } else if (d.kv_dtype == NOVA_KV_F32 && attn_mma_built() && d.kv_block == kTileKeysMax && e->kv_group == 4) {
+        // fp32 pools through the tensor-core decode kernel (rows converted to fp16 on the way in): boxes of 32 dims
+        const int64_t slot_rows = (int64_t)d.n_layers * e->nb * d.kv_block;
+        e->tmaps_ok = attn_make_tmap(e->tmap_k, e->pool_k, slot_rows, d.n_kv_heads, e->kv_group, kTileKeysMax, 4) == NOVA_OK &&
+                      attn_make_tmap(e->tmap_v, e->pool_v, slot_rows, d.n_kv_heads, e->kv_group, kTileKeysMax, 4) == NOVA_OK;
     }
     int r = launch_rope_table(e->cs, e->sn, d.rope_positions, d.rope_theta, 0);   // Kernel::rope_table, model.cpp:119
     if (r == NOVA_OK && cudaDeviceSynchronize() != cudaSuccess) r = NOVA_ERR_CUDA;
@@ -791,7 +799,7 @@ int nova_batch_sync_positions(nova_batch* b, nova_stream_t s) {
 
 int nova_batch_set_kernel(nova_batch* b, int which) {
     if (!b || which < 0 || which > 1) return NOVA_ERR_INVALID;
-    if (which == 1 && (b->e->d.kv_dtype != NOVA_KV_F16 || !b->e->tmaps_ok)) return NOVA_ERR_UNSUPPORTED;
+    if (which == 1 && !b->e->tmaps_ok) return NOVA_ERR_UNSUPPORTED;      // (fp32 pools: 4-kv-head groups of 16-token pages only)
     b->kernel = which;
     if (which != 1) b->fused = 0;
     return NOVA_OK;
