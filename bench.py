@@ -401,6 +401,12 @@ def run_ours(args):
     work.close()
     if args.workload == "c2" and not args.no_scaling_workloads:
         sw = {}
+        if world == 1 and args.kv == "f16" and line is not None:
+            # the reference's own pool format (fp32) through the same batched per-layer calls: the tensor-core kernel
+            # converts the rows to fp16 in shared memory (the SIMT kernel where that form does not apply)
+            f32 = sharded_measure(cx, args, "c2", steps=32, warm=3, kv_dtype=nv.KV_F32)
+            line["fp32_pools"] = {k: f32[k] for k in ("workload", "steps", "ms_per_step", "value", "unit", "kv_gbs", "frac_per_gpu",
+                                                      "launch", "attention_kernel", "pdl")}
         sw["c4"] = sharded_measure(cx, args, "c4", steps=8, warm=3)
         if world > 1:
             c5 = long_context_measure(cx, args, 16, 3, "p2p")
@@ -419,16 +425,18 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def sharded_measure(cx, args, name, steps, warm):
+def sharded_measure(cx, args, name, steps, warm, kv_dtype=None):
     """One configuration whose sessions are divided over the GPUs (no collective), per-layer launches in the
-    engine's order: ms per step (max over ranks), whole-job KV GB/s and the per-GPU roofline fraction."""
+    engine's order: ms per step (max over ranks), whole-job KV GB/s and the per-GPU roofline fraction.
+    kv_dtype: the pools' element type when it is not the fp16 of the bench configurations."""
     nv, wl = cx.nv, cx.wl
     w = WORKLOADS[name]
     seed = BASE_SEED + w["cfg"] + 1000 * cx.rank
     n_sess = w["sessions"] if w["scaling"] == "weak" else max(1, w["sessions"] // cx.world)
     lens = wl.context_lengths(seed, n_sess, *w["ctx"])
     work = wl.Workload(w["model"], lens, seed=seed, steps=2 * (warm + steps) + 8, device=cx.local_rank,
-                       shared_prefix=w.get("prefix", 0), key_base=cx.rank * n_sess)
+                       shared_prefix=w.get("prefix", 0), key_base=cx.rank * n_sess,
+                       kv_dtype=nv.KV_F16 if kv_dtype is None else kv_dtype)
     try:
         opt = configure_batch(nv, work.batch, args, prefix=bool(w.get("prefix", 0)))
         stream = nv.Stream()
