@@ -67,7 +67,7 @@ constexpr int kStashWords = 38;
 // 16 x 128 K and V values to fp16 into ONE shared page set laid out exactly like an fp16 stage (the raw stage is handed
 // back to the producer as soon as that is done); from there on the tile arithmetic is the fp16 kernel's.  K and V are
 // therefore rounded to fp16 on their way into the tensor cores (values beyond the fp16 range would saturate: the SIMT
-// kernel stays the default for fp32 pools); 16-token pages and 4-kv-head groups only in this form.  The fused append
+// kernel stays the default for fp32 pools); 16-token pages only in this form.  The fused append
 // stores the new token's fp32 rows into the pool and their fp16 roundings into the converted page set.
 template <int KVG, bool kF32 = false>
 struct MmaCfg {
@@ -78,7 +78,7 @@ struct MmaCfg {
     static constexpr int kStashBytes = kStashSlots * KVG * kStashWords * 128;   // finished segments parked until the first write
     static constexpr int kSmemBytes = kNStages * kStageBytes + (kF32 ? kConvBytes : 0) + kStashBytes + 1024;
     static constexpr int kThreads = 32 * (KVG + 1);
-    static constexpr int kCtasPerSm = kF32 ? 1 : (4 / KVG >= 1 ? 4 / KVG : 1);
+    static constexpr int kCtasPerSm = 4 / KVG >= 1 ? 4 / KVG : 1;
 };
 
 template <int KVG, bool kF32 = false>
@@ -717,8 +717,8 @@ int attn_split_ctas_mma(const AttnLaunch& a, int n_ctas) {
 
 int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t s) {
     if ((kv_dtype != NOVA_KV_F16 && kv_dtype != NOVA_KV_F32) || !a.tmap_k || !a.tmap_v) return NOVA_ERR_UNSUPPORTED;
-    // fp32 pools: converted to fp16 on the way in; 16-token pages and groups of four kv heads
-    if (kv_dtype == NOVA_KV_F32 && ((a.kv_shift ? a.kv_shift : kKvShift) != 4 || a.kv_group != 4)) return NOVA_ERR_UNSUPPORTED;
+    // fp32 pools: converted to fp16 on the way in; 16-token pages only
+    if (kv_dtype == NOVA_KV_F32 && (a.kv_shift ? a.kv_shift : kKvShift) != 4) return NOVA_ERR_UNSUPPORTED;
     if ((a.kv_shift ? a.kv_shift : kKvShift) < 4 && (!a.tmap_k1 || !a.tmap_v1)) return NOVA_ERR_UNSUPPORTED;
     if (a.fuse_append && a.n_q > 1) return NOVA_ERR_UNSUPPORTED;      // the fused append is a decode (one token) path
     if (a.fuse_append && (!a.n_past || !a.k_new || !a.v_new || !a.rope_cs || !a.rope_sn || !a.pool_k_w || !a.pool_v_w))
@@ -727,7 +727,14 @@ int launch_attn_mma(const AttnLaunch& a, int kv_dtype, int n_ctas, cudaStream_t 
     if (a.n_heads % a.n_kv_heads || a.n_kv_heads % a.kv_group) return NOVA_ERR_INVALID;
     if (a.n_heads / a.n_kv_heads > 8) return NOVA_ERR_UNSUPPORTED;
     if ((int64_t)a.n_sessions * (a.n_q > 1 ? a.n_q : 1) * (a.n_kv_heads / a.kv_group) > kMaxRowsSmem) return NOVA_ERR_TOO_LARGE;
-    if (kv_dtype == NOVA_KV_F32) return launch_kvg<4, true>(a, attn_split_ctas_mma(a, n_ctas), s);
+    if (kv_dtype == NOVA_KV_F32) {
+        switch (a.kv_group) {
+            case 4: return launch_kvg<4, true>(a, attn_split_ctas_mma(a, n_ctas), s);
+            case 2: return launch_kvg<2, true>(a, attn_split_ctas_mma(a, n_ctas), s);
+            case 1: return launch_kvg<1, true>(a, attn_split_ctas_mma(a, n_ctas), s);
+            default: return NOVA_ERR_UNSUPPORTED;
+        }
+    }
     switch (a.kv_group) {
         case 4: return launch_kvg<4>(a, attn_split_ctas_mma(a, n_ctas), s);
         case 2: return launch_kvg<2>(a, attn_split_ctas_mma(a, n_ctas), s);

@@ -358,7 +358,7 @@ int nova_engine_create(const nova_engine_desc* desc, nova_engine** out) {
                       attn_make_tmap(e->tmap_k1, e->pool_k, slot_rows, d.n_kv_heads, 1, box_rows, 2) == NOVA_OK &&
                       attn_make_tmap(e->tmap_v1, e->pool_v, slot_rows, d.n_kv_heads, 1, box_rows, 2) == NOVA_OK;
         e->tmaps1_ok = e->tmaps_ok;
-    } else if (d.kv_dtype == NOVA_KV_F32 && attn_mma_built() && d.kv_block == kTileKeysMax && e->kv_group == 4) {
+    } else if (d.kv_dtype == NOVA_KV_F32 && attn_mma_built() && d.kv_block == kTileKeysMax) {
         // fp32 pools through the tensor-core decode kernel (rows converted to fp16 on the way in): boxes of 32 dims
         const int64_t slot_rows = (int64_t)d.n_layers * e->nb * d.kv_block;
         e->tmaps_ok = attn_make_tmap(e->tmap_k, e->pool_k, slot_rows, d.n_kv_heads, e->kv_group, kTileKeysMax, 4) == NOVA_OK &&
@@ -799,7 +799,7 @@ int nova_batch_sync_positions(nova_batch* b, nova_stream_t s) {
 
 int nova_batch_set_kernel(nova_batch* b, int which) {
     if (!b || which < 0 || which > 1) return NOVA_ERR_INVALID;
-    if (which == 1 && !b->e->tmaps_ok) return NOVA_ERR_UNSUPPORTED;      // (fp32 pools: 4-kv-head groups of 16-token pages only)
+    if (which == 1 && !b->e->tmaps_ok) return NOVA_ERR_UNSUPPORTED;      // (fp32 pools: 16-token pages only)
     b->kernel = which;
     if (which != 1) b->fused = 0;
     return NOVA_OK;

@@ -307,7 +307,7 @@ int  nova_batch_size(const nova_batch* b);
 int  nova_batch_sync_positions(nova_batch* b, nova_stream_t s);
 /* Select the attention kernel: 0 = SIMT (the default; fp32 arithmetic on the pool's own values), 1 = tensor-core
  * (mma + bulk-copy pipeline).  On fp16 pools 1 applies to every shape and page size.  On fp32 pools - the
- * reference's format - it applies to 16-token pages and kv heads in groups of four; the K/V rows are rounded to
+ * reference's format - it applies to 16-token pages; the K/V rows are rounded to
  * fp16 in shared memory on their way into the tensor cores (results agree with the exact softmax to about 3e-4
  * relative, values beyond the fp16 range would saturate), the pool itself keeps fp32.  NOVA_ERR_UNSUPPORTED
  * otherwise. */

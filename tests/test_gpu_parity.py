@@ -329,8 +329,7 @@ def test_decode_steps_vs_oracle(nv, ob, model, dtype, kernel):
     """Sessions of ragged lengths (a fresh one, page-boundary cases, a long one), three decode steps
     per-layer and all-layers: pages bit-exact, attention within tolerance of the exact softmax."""
     kvd = nv.KV_F16 if dtype == "f16" else nv.KV_F32
-    # (kernels 1 and 2 on fp32 pools: the tensor-core kernel converts the rows to fp16 on the way in; 4-kv-head groups
-    # only, other shapes answer NOVA_ERR_UNSUPPORTED and are skipped by try_set_kernel)
+    # (kernels 1 and 2 on fp32 pools: the tensor-core kernel converts the rows to fp16 on the way in)
     ctx_lens = [0, 1, 15, 16, 17, 31, 33, 100, 255, 1024, 1500]
     eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, model, kvd, ctx_lens)
     NH, NKV, L, S = eng.NH, eng.NKV, eng.L, len(ss)
