@@ -233,6 +233,8 @@ def run_ours(args):
         return
     seed = BASE_SEED + w["cfg"] + 1000 * rank          # every GPU holds its own sessions
     n_sess = w["sessions"] if w["scaling"] == "weak" else max(1, w["sessions"] // world)
+    if args.sessions > 0:
+        n_sess = args.sessions            # a cut-down case for profiler captures
     lens = wl.context_lengths(seed, n_sess, *w["ctx"])
     K, W, KE = args.steps, args.warmup, args.e2e_steps
     PF_REPS = 3
@@ -849,6 +851,7 @@ def main():
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own kernels (sm_100a build)")
     ap.add_argument("--no-scaling-workloads", action="store_true", help="skip configurations 4 and 5 after the headline")
     ap.add_argument("--quick-prefill", action="store_true", help="only the prefill sample (for profiler captures)")
+    ap.add_argument("--sessions", type=int, default=0, help="override the workload's session count (cut-down cases for profiler captures)")
     ap.add_argument("--quick", action="store_true",
                     help="only the main timed region (for profiler captures): no other modes, e2e or CPU baseline")
     args = ap.parse_args()
