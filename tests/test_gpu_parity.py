@@ -729,7 +729,8 @@ def test_cow_shared_prefix(nv, ob, kernel):
 
 
 @pytest.mark.parametrize("kernel,mode", [(1, 1), (2, 1), (2, 2), (3, 1), (4, 1), (4, 2)])
-@pytest.mark.parametrize("model,n_fork,P", [("qwen25_7b", 12, 700), ("qwen25_14b", 5, 300), ("qwen25_1p5b", 10, 517)])
+@pytest.mark.parametrize("model,n_fork,P", [("qwen25_7b", 12, 700), ("qwen25_14b", 5, 300), ("qwen25_1p5b", 10, 517),
+                                            ("qwen25_7b", 40, 700)])       # 40 sessions x 7 heads: two 256-row tiles per kv head
 def test_cascade_over_shared_prefix(nv, ob, model, n_fork, P, kernel, mode):
     """Sessions forked from one prefix (partly filled tail page), private suffixes of different lengths, then
     decode steps with the cascade switched on: the shared full pages are attended once for all sessions, each
