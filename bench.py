@@ -660,7 +660,17 @@ def reference_gpu_sample(nv, work):
     st = nv.Stream()
     sh32 = nv.KvShape(NH, NKV, 128, 16, nv.KV_F32, 1)
 
+    # one C call per pass on either side (per session: RopeKvOp then AttnOp): a Python loop over the launchers would
+    # measure the interpreter (about 35 us per call), not the GPU
+    tab_arr = (C.c_void_p * S)(*tabs)
+    pos_arr = (C.c_int64 * S)(*pos)
+    c_loops = hasattr(g, "ref_gpu_decode_layer_sessions")
+
     def ref_pass():
+        if c_loops:
+            g.ref_gpu_decode_layer_sessions(S, pk.ptr, pv.ptr, tab_arr, 0, eng.nb, pos_arr, q.ptr, k.ptr, v.ptr, NH * 128, NKV * 128,
+                                            cs, sn, o.ptr, scr.ptr, st.h)
+            return
         for i in range(S):
             qi, ki, vi = q.ptr + i * NH * 512, k.ptr + i * NKV * 512, v.ptr + i * NKV * 512
             g.ref_gpu_rope_batch(qi, ki, 1, pos[i], cs, sn, st.h)
@@ -669,6 +679,10 @@ def reference_gpu_sample(nv, work):
                                         scr.ptr, st.h)
 
     def ours_pass():
+        if c_loops:
+            nv.check(nv.lib.nova_launch_decode_layer_sessions(C.byref(sh32), S, pk.ptr, pv.ptr, tab_arr, 0, eng.nb, pos_arr, q.ptr, k.ptr,
+                                                              v.ptr, NH * 128, NKV * 128, cs, sn, o.ptr, scr.ptr, st.h))
+            return
         for i in range(S):
             qi, ki, vi = q.ptr + i * NH * 512, k.ptr + i * NKV * 512, v.ptr + i * NKV * 512
             nv.lib.nova_launch_rope_append_paged(C.byref(sh32), pk.ptr, pv.ptr, tabs[i], 0, eng.nb, 1, pos[i], qi, ki, vi,
@@ -690,14 +704,23 @@ def reference_gpu_sample(nv, work):
     ms_ref, reps = time_pass(ref_pass)
     ok = g.ref_gpu_last_error() == 0
     ms_ours, _ = time_pass(ours_pass)
+    ms_ours_tc = None
+    if nv.lib.nova_launcher_set_kernel(1) == nv.OK:          # the same launchers on the tensor-core kernel
+        ms_ours_tc, _ = time_pass(ours_pass)
+        nv.lib.nova_launcher_set_kernel(0)
     for b in (pk, pv, q, k, v, o, scr):
         b.free()
     sample = (f"{reps} x one layer of {eng.L}, all {S} sessions, fp32 pools, the reference's call order (per session and "
-              f"layer); time scaled by {eng.L}")
+              f"layer){', each pass one C call' if c_loops else ''}; time scaled by {eng.L}")
     ref = {"value": S / (ms_ref * eng.L / 1e3), "unit": UNIT, "ms_per_step": ms_ref * eng.L, "ok": ok,
            "launches_per_session_layer": 4, "sample": sample}
     ours = {"value": S / (ms_ours * eng.L / 1e3), "unit": UNIT, "ms_per_step": ms_ours * eng.L,
-            "launches_per_session_layer": 3, "speedup_vs_reference_kernels": ms_ref / ms_ours, "sample": sample}
+            "launches_per_session_layer": 3, "speedup_vs_reference_kernels": ms_ref / ms_ours, "sample": sample,
+            "kernel": "SIMT (fp32 arithmetic, the launchers' default)",
+            "tensor_core_kernel": None if ms_ours_tc is None else {
+                "ms_per_step": ms_ours_tc * eng.L, "value": S / (ms_ours_tc * eng.L / 1e3),
+                "speedup_vs_reference_kernels": ms_ref / ms_ours_tc,
+                "note": "nova_launcher_set_kernel(1): K/V rows rounded to fp16 on their way into the tensor cores"}}
     return ref, ours
 
 

@@ -110,7 +110,8 @@ SIGNATURES = {
     "nova_synth_key": (u64, [u64, u64, u64, u64]), "nova_synth_normal": (i32, [vp, sz, u64, u64, vp]),
     "nova_batch_create": (i32, [vp, c_i32p, i32, C.POINTER(vp)]), "nova_batch_destroy": (None, [vp]),
     "nova_batch_size": (i32, [vp]), "nova_batch_sync_positions": (i32, [vp, vp]),
-    "nova_batch_set_timeline": (i32, [vp, vp]),
+    "nova_batch_set_timeline": (i32, [vp, vp]), "nova_launcher_set_kernel": (i32, [i32]),
+    "nova_launch_decode_layer_sessions": (i32, [vp, i32, vp, vp, vp, i32, i32, vp, vp, vp, vp, C.c_size_t, C.c_size_t, vp, vp, vp, vp, vp]),
     "nova_batch_set_pdl": (i32, [vp, i32]), "nova_batch_set_row_setup_pages": (i32, [vp, i32]),
     "nova_batch_set_split_ctas": (i32, [vp, i32]), "nova_batch_set_window": (i32, [vp, i32]), "nova_batch_set_prefill_kernel": (i32, [vp, i32]),
     "nova_batch_set_fused_append": (i32, [vp, i32]), "nova_batch_append_attn": (i32, [vp, i32, vp, vp, vp, vp, vp]),

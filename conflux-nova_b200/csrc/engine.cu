@@ -5,6 +5,7 @@
 // the raw launcher entry points (include/nova/kernel.h:44-49,62-64) and the batched
 // per-layer / all-layer decode calls that replace the per-session loop of
 // Engine::decode_batch (src/model.cpp:281-290).
+#include <atomic>
 #include <cstring>
 #include <limits>
 #include <mutex>
@@ -646,6 +647,44 @@ size_t nova_attn_scratch_floats(const nova_kv_shape* sh) {
     return sh ? (size_t)sh->n_heads * 32 * (size_t)(sh->head_dim + 2) : 0;
 }
 
+// The literal launchers have no engine behind them, so the tensor maps of the pools they are given are kept here,
+// one per (pool, element type, kv heads, rows covered): a map is encoded once and found again by a short scan.
+namespace {
+struct RawMap {
+    const void* pool;
+    int kv_dtype, n_kv_heads, kv_group;
+    int64_t slot_rows;
+    alignas(128) unsigned char map[128];
+};
+std::mutex g_raw_mu;
+std::vector<RawMap*> g_raw_maps;
+std::atomic<int> g_raw_kernel{0};
+
+const void* raw_tmap(const void* pool, int kv_dtype, int n_kv_heads, int kv_group, int64_t slot_rows) {
+    std::lock_guard<std::mutex> lk(g_raw_mu);
+    for (RawMap* m : g_raw_maps)
+        if (m->pool == pool && m->kv_dtype == kv_dtype && m->n_kv_heads == n_kv_heads && m->kv_group == kv_group && m->slot_rows >= slot_rows)
+            return m->map;
+    if (g_raw_maps.size() >= 4096) return nullptr;          // a caller that keeps changing pools: stay on the SIMT kernel
+    RawMap* m = new (std::nothrow) RawMap;
+    if (!m) return nullptr;
+    m->pool = pool; m->kv_dtype = kv_dtype; m->n_kv_heads = n_kv_heads; m->kv_group = kv_group; m->slot_rows = slot_rows;
+    if (attn_make_tmap(m->map, const_cast<void*>(pool), slot_rows, n_kv_heads, kv_group, kTileKeysMax, kv_dtype == NOVA_KV_F16 ? 2 : 4) != NOVA_OK) {
+        delete m;
+        return nullptr;
+    }
+    g_raw_maps.push_back(m);
+    return m->map;
+}
+}  // namespace
+
+int nova_launcher_set_kernel(int which) {
+    if (which < 0 || which > 1) return NOVA_ERR_INVALID;
+    if (which == 1 && !attn_mma_built()) return NOVA_ERR_UNSUPPORTED;
+    g_raw_kernel.store(which);
+    return NOVA_OK;
+}
+
 int nova_launch_attn_decode_paged(const nova_kv_shape* sh, const float* q, const void* pool_k, const void* pool_v,
                                   const int32_t* table, int layer, int nb, int n_keys, float* o, float* scratch,
                                   nova_stream_t s) {
@@ -668,12 +707,45 @@ int nova_launch_attn_decode_paged(const nova_kv_shape* sh, const float* q, const
     const int heads_per_row = a.kv_group * (sh->n_heads / sh->n_kv_heads);
     const int rows = sh->n_kv_heads / a.kv_group;
     int ctas = (int)(nova_attn_scratch_floats(sh) / ((size_t)heads_per_row * kSlotW)) - rows;
+    if (ctas < 1) return NOVA_ERR_UNSUPPORTED;
+    if (g_raw_kernel.load() == 1 && a.kv_shift == 4 && sh->n_heads / sh->n_kv_heads <= 8) {
+        // tensor-core kernel (nova_launcher_set_kernel): the pools' maps cover the rows up to this layer's last page
+        const int64_t slot_rows = (int64_t)(layer + 1) * nb * sh->kv_block;
+        a.tmap_k = raw_tmap(pool_k, sh->kv_dtype, sh->n_kv_heads, a.kv_group, slot_rows);
+        a.tmap_v = raw_tmap(pool_v, sh->kv_dtype, sh->n_kv_heads, a.kv_group, slot_rows);
+        if (a.tmap_k && a.tmap_v) {
+            const int all = attn_split_ctas_mma(a, 0);
+            const int c = ctas < all ? ctas : all;
+            int rc = launch_attn_mma(a, sh->kv_dtype, c, (cudaStream_t)s);
+            if (rc == NOVA_OK) return launch_attn_combine(a, c, (cudaStream_t)s);
+            if (rc != NOVA_ERR_UNSUPPORTED) return rc;
+        }
+        a.tmap_k = a.tmap_v = nullptr;
+    }
     const int want = attn_default_ctas_simt(sh->n_kv_heads);
     if (ctas > want) ctas = want;
-    if (ctas < 1) return NOVA_ERR_UNSUPPORTED;
     int rc = launch_attn_simt(a, sh->kv_dtype, ctas, (cudaStream_t)s);
     if (rc != NOVA_OK) return rc;
     return launch_attn_combine(a, ctas, (cudaStream_t)s);
+}
+
+// Declared in nova_b200_testing.h: the two literal launchers for n sessions of a layer, in the reference's call order.
+int nova_launch_decode_layer_sessions(const nova_kv_shape* sh, int n, void* pool_k, void* pool_v, const int32_t* const* tables,
+                                      int layer, int nb, const int64_t* pos, float* q, float* k, const float* v, size_t q_stride,
+                                      size_t kv_stride, const float* cs, const float* sn, float* o, float* scratch,
+                                      nova_stream_t s) {
+    if (!sh || n < 0 || !tables || !pos || !q || !k || !v || !o) return NOVA_ERR_INVALID;
+    for (int i = 0; i < n; ++i) {
+        float* qi = q + (size_t)i * q_stride;
+        float* ki = k + (size_t)i * kv_stride;
+        int rc = nova_launch_rope_append_paged(sh, pool_k, pool_v, tables[i], layer, nb, 1, pos[i], qi, ki, v + (size_t)i * kv_stride,
+                                               cs, sn, s);
+        if (rc != NOVA_OK) return rc;
+        rc = nova_launch_attn_decode_paged(sh, qi, pool_k, pool_v, tables[i], layer, nb, (int)pos[i] + 1, o + (size_t)i * q_stride,
+                                           scratch, s);
+        if (rc != NOVA_OK) return rc;
+    }
+    return NOVA_OK;
 }
 
 int nova_lse_combine(const float* parts, int n_parts, int n_rows, int head_dim, float* out, nova_stream_t s) {

@@ -276,6 +276,13 @@ int nova_launch_attn_decode_paged(const nova_kv_shape* sh, const float* q,
                                   const int32_t* table, int layer, int nb, int n_keys,
                                   float* o, float* scratch, nova_stream_t s);
 
+/* No counterpart in the reference.  Which kernel nova_launch_attn_decode_paged runs, process-wide: 0 = SIMT (the
+ * default: fp32 arithmetic on the pool's own values), 1 = the tensor-core kernel where it applies (16-token pages,
+ * at most 8 query heads per kv head; fp32 pools are rounded to fp16 on their way into the tensor cores, see
+ * nova_batch_set_kernel) with the SIMT kernel for everything else.  The launcher keeps one tensor map per pool it
+ * has been given (encoded on first use). */
+int nova_launcher_set_kernel(int which);
+
 /* No counterpart in the reference.  The same attention as nova_launch_attn_decode_paged for callers
  * that cannot provide scratch memory because they may not allocate on the device at all (an engine
  * whose start-up arena is spoken for and whose operators must not call cudaMalloc, code inside a

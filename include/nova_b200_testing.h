@@ -31,6 +31,15 @@ int nova_synth_normal(float* dst_dev, size_t n, uint64_t key, uint64_t first_ind
  * cycles (total, K wait, P wait, V wait); then the first softmax thread's (total, score wait, P.V wait, tiles). */
 int nova_batch_set_timeline(nova_batch* b, void* dev_buf);
 
+/* The literal drop-in launchers (nova_launch_rope_append_paged, nova_launch_attn_decode_paged) for n sessions of one
+ * layer in the reference's call order (per session: RopeKvOp then AttnOp, code/graph/dense.h:75-95), issued from
+ * one C call: a loop in an interpreter is bound by the interpreter, not by the GPU.  q / k / v / o rows of session i
+ * at i * q_stride / i * kv_stride floats; tables[i] = that session's device block table; pos[i] = its n_past. */
+int nova_launch_decode_layer_sessions(const nova_kv_shape* sh, int n, void* pool_k, void* pool_v,
+                                      const int32_t* const* tables, int layer, int nb, const int64_t* pos,
+                                      float* q, float* k, const float* v, size_t q_stride, size_t kv_stride,
+                                      const float* cs, const float* sn, float* o, float* scratch, nova_stream_t s);
+
 #ifdef __cplusplus
 }
 #endif

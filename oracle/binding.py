@@ -134,6 +134,9 @@ def ref_gpu(model: str) -> C.CDLL | None:
         if hasattr(g, "ref_gpu_attn_prefill_paged"):
             g.ref_gpu_attn_prefill_paged.restype = None
             g.ref_gpu_attn_prefill_paged.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
+        if hasattr(g, "ref_gpu_decode_layer_sessions"):
+            g.ref_gpu_decode_layer_sessions.restype = None
+            g.ref_gpu_decode_layer_sessions.argtypes = [i32, vp, vp, vp, i32, i32, vp, vp, vp, vp, C.c_size_t, C.c_size_t, vp, vp, vp, vp, vp]
         g.ref_gpu_last_error.restype = i32
         _ref_gpu[model] = g
     return _ref_gpu[model]

@@ -47,6 +47,22 @@ void ref_gpu_attn_decode(const float* q, const float* kc, const float* vc, float
                          float* scratch, void* stream) {
     nova::launch_attn_decode(q, kc, vc, o, n_past, scratch, (cudaStream_t)stream);
 }
+// One decode step of n sessions in one layer in the reference's order (per session: rope_batch, kv_store_paged,
+// attn_decode_paged = RopeKvOp then AttnOp, code/graph/dense.h:75-95), issued from one C call so that a timing of it
+// is not bound by an interpreter's loop.  Rows of session i at i * q_stride / i * kv_stride floats.
+void ref_gpu_decode_layer_sessions(int n, float* pool_k, float* pool_v, const int32_t* const* tables, int layer, int nb,
+                                   const int64_t* pos, float* q, float* k, const float* v, size_t q_stride, size_t kv_stride,
+                                   const float* cs, const float* sn, float* o, float* scratch, void* stream) {
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int i = 0; i < n; ++i) {
+        float* qi = q + (size_t)i * q_stride;
+        float* ki = k + (size_t)i * kv_stride;
+        const float* vi = v + (size_t)i * kv_stride;
+        nova::launch_rope_batch(qi, ki, 1, pos[i], cs, sn, s);
+        nova::launch_kv_store_paged(pool_k, pool_v, tables[i], layer, nb, 1, pos[i], ki, vi, s);
+        nova::launch_attn_decode_paged(qi, pool_k, pool_v, tables[i], layer, nb, (int)pos[i] + 1, o + (size_t)i * q_stride, scratch, s);
+    }
+}
 int ref_gpu_last_error(void) { return (int)cudaGetLastError(); }
 
 }  // extern "C"

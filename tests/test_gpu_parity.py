@@ -420,6 +420,50 @@ def test_attention_vs_reference_kernels(nv, ob, model):
         eng.close()
 
 
+def test_decode_layer_sessions_from_c(nv, ob):
+    """The two C loops the bench times for the literal drop-in (one call = RopeKvOp + AttnOp of every session of a
+    layer, code/graph/dense.h:75-95): this library's launchers and the reference's, on fp32 pools with the same
+    contents - appended rows bit-identical, outputs within float reordering."""
+    g = ob.ref_gpu("qwen25_7b")
+    if g is None or not hasattr(g, "ref_gpu_decode_layer_sessions"):
+        pytest.skip("reference CUDA library not built")
+    ctx_lens = [5, 100, 1030]
+    eng, ss, sh, pk, pv, cs, sn, rng = build_case(nv, ob, "qwen25_7b", nv.KV_F32, ctx_lens, L=2, seed=77)
+    NH, NKV, S, layer = eng.NH, eng.NKV, len(ss), 1
+    rk, rv = nv.to_device(pk), nv.to_device(pv)                    # the reference works on its own copy of the pools
+    q = rng.standard_normal((S, NH, 128)).astype(np.float32)
+    k = rng.standard_normal((S, NKV, 128)).astype(np.float32)
+    v = rng.standard_normal((S, NKV, 128)).astype(np.float32)
+    tabs = (C.c_void_p * S)(*[nv.lib.nova_kv_table_slot(eng.h, eng.session_slice(s)) for s in ss])
+    pos = (C.c_int64 * S)(*ctx_lens)
+    dcs, dsn = nv.lib.nova_rope_cos(eng.h), nv.lib.nova_rope_sin(eng.h)
+    scr = nv.DevBuf(NH * 32 * 130 * 4)
+    outs = []
+    for which in (0, 1, 2):
+        dq, dk, dv, do = nv.to_device(q), nv.to_device(k), nv.to_device(v), nv.DevBuf(q.nbytes)
+        if which in (0, 2):       # 2: the same launchers with the tensor-core kernel switched on (the append finds its rows in place)
+            shp = eng.shape()
+            assert nv.lib.nova_launcher_set_kernel(1 if which == 2 else 0) == 0
+            nv.check(nv.lib.nova_launch_decode_layer_sessions(C.byref(shp), S, eng.k_base, eng.v_base, tabs, layer, eng.nb, pos, dq.ptr,
+                                                              dk.ptr, dv.ptr, NH * 128, NKV * 128, dcs, dsn, do.ptr, scr.ptr, None))
+            assert nv.lib.nova_launcher_set_kernel(0) == 0
+        else:
+            g.ref_gpu_decode_layer_sessions(S, rk.ptr, rv.ptr, tabs, layer, eng.nb, pos, dq.ptr, dk.ptr, dv.ptr, NH * 128, NKV * 128,
+                                            dcs, dsn, do.ptr, scr.ptr, None)
+        nv.check(nv.lib.dev_sync())
+        outs.append((do.download(np.float32).reshape(S, NH, 128), dq.download(np.float32), dk.download(np.float32)))
+    assert g.ref_gpu_last_error() == 0
+    gk, gv = eng.read_pools()
+    assert np.array_equal(bits(gk), bits(rk.download(np.float32).reshape(gk.shape)))
+    assert np.array_equal(bits(gv), bits(rv.download(np.float32).reshape(gv.shape)))
+    assert np.array_equal(bits(outs[0][1]), bits(outs[1][1])) and np.array_equal(bits(outs[0][2]), bits(outs[1][2]))   # rotated q, k
+    for i in range(S):
+        assert_attn_close(outs[0][0][i], outs[1][0][i], f"session {i}")
+        assert_attn_close(outs[2][0][i], outs[1][0][i], f"session {i}, tensor-core launcher")
+    assert np.array_equal(bits(outs[2][2]), bits(outs[1][2]))
+    eng.close()
+
+
 def test_gpu_misc_known_answers(nv):
     """tests/gpu_misc.cu of the reference: RoPE at position 0 is the identity; one key -> V[0]."""
     eng = nv.Engine(1, 12, 2, ctx=64, n_slices=1, kv_dtype=nv.KV_F32)
