@@ -402,10 +402,14 @@ def test_attention_vs_reference_kernels(nv, ob, model):
         # raw launcher (caller scratch, separate merge)
         shp = eng.shape()
         o = nv.DevBuf(NH * 128 * 4)
-        nv.check(nv.lib.nova_launch_attn_decode_paged(C.byref(shp), dq.ptr, eng.k_base, eng.v_base, tab, layer, eng.nb,
-                                                      n_ctx, o.ptr, scr.ptr, None))
-        nv.check(nv.lib.dev_sync())
-        assert_attn_close(o.download(np.float32).reshape(NH, 128), ref, f"raw n={n_ctx}")
+        for launcher_kernel in (0, 1):           # SIMT (default), then the tensor-core kernel behind the same launcher
+            assert nv.lib.nova_launcher_set_kernel(launcher_kernel) == 0
+            o.zero()
+            nv.check(nv.lib.nova_launch_attn_decode_paged(C.byref(shp), dq.ptr, eng.k_base, eng.v_base, tab, layer, eng.nb,
+                                                          n_ctx, o.ptr, scr.ptr, None))
+            nv.check(nv.lib.dev_sync())
+            assert_attn_close(o.download(np.float32).reshape(NH, 128), ref, f"raw n={n_ctx} launcher kernel {launcher_kernel}")
+        assert nv.lib.nova_launcher_set_kernel(0) == 0
         # batched path, both kernels; n_keys = n_past + 1 so step back by one
         eng.set_n_past(ss[0], n_ctx - 1)
         batch = eng.batch(ss)
