@@ -505,38 +505,81 @@ __device__ __forceinline__ bool exchange_and_merge(const PeerSlots& ps, const un
     unsigned long long t0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     bool failed = false;
-    // Every peer in one round: all loads first, then the checks.  Lane p alone reads peer p's (m, l) word (the other
-    // lanes get the values by shuffle at the end), so a round is 2 loads per peer and lane, 64 registers in flight.
+    // Two forms of the same poll, each measured where it is used.  Up to four ranks: every peer in one round, two loads
+    // per peer and lane, the (m, l) word read by lane p alone and handed round by shuffle afterwards (config 5 on 4 GPUs:
+    // 0.527 -> 0.507 ms per step).  More ranks: four peers at a time with every lane reading (m, l) itself - polling
+    // all seven peers per round was 10 % slower on 8 GPUs (0.389 -> 0.427 ms).
     uint4 w0 = make_uint4(0u, 0u, 0u, 0u);
-    while (__any_sync(0xffffffffu, pending != 0)) {
-        uint4 w1[kMaxPeerRanks], w2[kMaxPeerRanks], w0n = w0;
+    const bool few = n_ranks <= 4;
+    if (few) {
+        while (__any_sync(0xffffffffu, pending != 0)) {
+            uint4 w1[kMaxPeerRanks], w2[kMaxPeerRanks], w0n = w0;
 #pragma unroll
-        for (int p = 0; p < kMaxPeerRanks; ++p) {
-            if (pending & (1u << p)) {
-                const unsigned char* src = mine + (size_t)p * region_bytes + row_off;
-                if (lane == p) w0n = ll_load(src);
-                w1[p] = ll_load(src + 16 * (1 + 2 * lane));
-                w2[p] = ll_load(src + 16 * (2 + 2 * lane));
-            }
-        }
-#pragma unroll
-        for (int p = 0; p < kMaxPeerRanks; ++p) {
-            if (pending & (1u << p)) {
-                bool ok = w1[p].y == epoch && w1[p].w == epoch && w2[p].y == epoch && w2[p].w == epoch;
-                if (lane == p) ok = ok && w0n.y == epoch && w0n.w == epoch;
-                if (ok) {
-                    if (lane == p) w0 = w0n;
-                    pa[p] = make_float4(__uint_as_float(w1[p].x), __uint_as_float(w1[p].z), __uint_as_float(w2[p].x),
-                                        __uint_as_float(w2[p].z));
-                    pending &= ~(1u << p);
+            for (int p = 0; p < kMaxPeerRanks; ++p) {
+                if (pending & (1u << p)) {
+                    const unsigned char* src = mine + (size_t)p * region_bytes + row_off;
+                    if (lane == p) w0n = ll_load(src);
+                    w1[p] = ll_load(src + 16 * (1 + 2 * lane));
+                    w2[p] = ll_load(src + 16 * (2 + 2 * lane));
                 }
             }
+#pragma unroll
+            for (int p = 0; p < kMaxPeerRanks; ++p) {
+                if (pending & (1u << p)) {
+                    bool ok = w1[p].y == epoch && w1[p].w == epoch && w2[p].y == epoch && w2[p].w == epoch;
+                    if (lane == p) ok = ok && w0n.y == epoch && w0n.w == epoch;
+                    if (ok) {
+                        if (lane == p) w0 = w0n;
+                        pa[p] = make_float4(__uint_as_float(w1[p].x), __uint_as_float(w1[p].z), __uint_as_float(w2[p].x),
+                                            __uint_as_float(w2[p].z));
+                        pending &= ~(1u << p);
+                    }
+                }
+            }
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (__any_sync(0xffffffffu, t1 - t0 > timeout_ns)) {     // a peer never got there: report, merge nothing
+                failed = pending != 0;
+                break;
+            }
         }
-        unsigned long long t1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        if (__any_sync(0xffffffffu, t1 - t0 > timeout_ns)) {     // a peer never got there: report, merge nothing
-            failed = pending != 0;
-            break;
+    } else {
+        while (__any_sync(0xffffffffu, pending != 0)) {
+#pragma unroll
+            for (int half = 0; half < kMaxPeerRanks; half += 4) {      // four peers at a time: all their loads first, then the checks
+                uint4 v0[4], w1[4], w2[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int p = half + j;
+                    if (pending & (1u << p)) {
+                        const unsigned char* src = mine + (size_t)p * region_bytes + row_off;
+                        v0[j] = ll_load(src);                       // every lane needs (m, l)
+                        w1[j] = ll_load(src + 16 * (1 + 2 * lane));
+                        w2[j] = ll_load(src + 16 * (2 + 2 * lane));
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int p = half + j;
+                    if (pending & (1u << p)) {
+                        const bool ok = v0[j].y == epoch && v0[j].w == epoch && w1[j].y == epoch && w1[j].w == epoch &&
+                                        w2[j].y == epoch && w2[j].w == epoch;
+                        if (ok) {
+                            pm[p] = __uint_as_float(v0[j].x);
+                            pl[p] = __uint_as_float(v0[j].z);
+                            pa[p] = make_float4(__uint_as_float(w1[j].x), __uint_as_float(w1[j].z), __uint_as_float(w2[j].x),
+                                                __uint_as_float(w2[j].z));
+                            pending &= ~(1u << p);
+                        }
+                    }
+                }
+            }
+            unsigned long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (__any_sync(0xffffffffu, t1 - t0 > timeout_ns)) {     // a peer never got there: report, merge nothing
+                failed = pending != 0;
+                break;
+            }
         }
     }
     failed = __any_sync(0xffffffffu, failed);
@@ -544,13 +587,15 @@ __device__ __forceinline__ bool exchange_and_merge(const PeerSlots& ps, const un
         if (lane == 0 && status) atomicCAS(status, 0, NOVA_ERR_TIMEOUT);
         return false;
     }
+    if (few) {
 #pragma unroll
-    for (int p = 0; p < kMaxPeerRanks; ++p) {             // (m, l) of peer p from the lane that read it
-        const float m_p = __uint_as_float(__shfl_sync(0xffffffffu, w0.x, p));
-        const float l_p = __uint_as_float(__shfl_sync(0xffffffffu, w0.z, p));
-        if (p < n_ranks && p != my_rank) {
-            pm[p] = m_p;
-            pl[p] = l_p;
+        for (int p = 0; p < kMaxPeerRanks; ++p) {             // (m, l) of peer p from the lane that read it
+            const float m_p = __uint_as_float(__shfl_sync(0xffffffffu, w0.x, p));
+            const float l_p = __uint_as_float(__shfl_sync(0xffffffffu, w0.z, p));
+            if (p < n_ranks && p != my_rank) {
+                pm[p] = m_p;
+                pl[p] = l_p;
+            }
         }
     }
 #pragma unroll

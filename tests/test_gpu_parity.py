@@ -543,16 +543,17 @@ def ll_encode(rows, epoch):
     return w
 
 
-def test_peer_exchange_on_one_gpu(nv, ob):
+@pytest.mark.parametrize("n_ranks", [4, 8])      # the kernel polls up to four ranks and more than four in different ways
+def test_peer_exchange_on_one_gpu(nv, ob, n_ranks):
     """nova_lse_merge_peers: every rank stores its partial rows into the peers' exchange buffers, waits until the
-    peers' rows have arrived in its own, and merges in rank order.  Here the 'ranks' are four buffers of this one GPU
+    peers' rows have arrived in its own, and merges in rank order.  Here the 'ranks' are buffers of this one GPU
     and run one after the other (kernels that wait on one another never share a GPU): rank r finds the rows of the
     ranks before it where THEIR kernels stored them, and the rows of the ranks after it where the test put them
     beforehand.  Same result as nova_lse_combine on the stacked rows and as the oracle's merge for every rank, over
     two epochs (both slots); what each rank stored is checked word for word.  Then the bounded wait: rows that never
     arrive -> NOVA_ERR_TIMEOUT in the status word, output left alone."""
     rng = np.random.default_rng(31)
-    n_ranks, n_rows = 4, 56
+    n_rows = 56
     slot_bytes = int(nv.lib.nova_peer_slot_bytes(n_rows))
     region = slot_bytes // 8
     assert slot_bytes % 128 == 0 and region >= n_rows * 65 * 16
