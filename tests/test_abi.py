@@ -34,6 +34,8 @@ def test_status_strings_and_host_only_calls(nv):
     sh = nv.KvShape(28, 4, 128, 16, nv.KV_F32, 1)
     assert nv.lib.nova_attn_scratch_floats(ctypes.byref(sh)) == 28 * 32 * 130   # src/model.cpp:148
     assert nv.synth_key(1, 2, 3, 4) != nv.synth_key(1, 2, 3, 5)
+    assert nv.lib.nova_launcher_set_kernel(2) == nv.ERR_INVALID and nv.lib.nova_launcher_set_kernel(-1) == nv.ERR_INVALID
+    assert nv.lib.nova_launcher_set_kernel(1) == nv.OK and nv.lib.nova_launcher_set_kernel(0) == nv.OK      # a switch, no GPU work
 
 
 def test_no_product_path_into_oracle():
