@@ -161,7 +161,8 @@ attn_prefill_tc5_kernel(AttnLaunch a, const __grid_constant__ CUtensorMap tmk, c
     const int qtile = n_qtiles - 1 - bid % n_qtiles;
     bid /= n_qtiles;
     const int kvh = bid % NKV;
-    const int s = kPrefix ? 0 : bid / NKV;                              // prefix form: rows index sessions, the table is the first one's
+    // prefix form: rows index sessions, the table is the first one's; prefill: sessions in the host's order (longest first)
+    const int s = kPrefix ? 0 : (a.n_order > 0 && bid / NKV < a.n_order ? (int)a.sess_order[bid / NKV] : bid / NKV);
     const int chunk = kPrefix ? bid / NKV : 0;
     const int t0 = qtile * tq;
     const int t_cnt = NQ - t0 < tq ? NQ - t0 : tq;

@@ -100,6 +100,8 @@ struct AttnLaunch {
     const void* pool_v;
     int32_t kv_shift;            // log2(tokens per page): 3..6; 0 is read as 4 (16-token pages)
     int32_t window;              // prefill only: > 0 = sliding window, query at position p sees keys (p - window, p]
+    int32_t n_order;             // tcgen05 prefill only: > 0 = the CTAs take the sessions in the order sess_order[0..n_order)
+    unsigned char sess_order[64];   //   (longest context first, so that the last CTAs of the launch are the short ones)
     const int32_t* table_base;   // device block tables, one per slice
     int64_t table_stride;        // entries per slice table (nblocks)
     const int32_t* slice_ids;    // [S] slice of each batch entry; nullptr: entry s uses table_base + s*stride

@@ -5,6 +5,7 @@
 // the raw launcher entry points (include/nova/kernel.h:44-49,62-64) and the batched
 // per-layer / all-layer decode calls that replace the per-session loop of
 // Engine::decode_batch (src/model.cpp:281-290).
+#include <algorithm>
 #include <atomic>
 #include <cstring>
 #include <limits>
@@ -174,7 +175,23 @@ int run_attn(const nova_batch* b, const AttnLaunch& a, cudaStream_t s) {
     const bool f16 = b->e->d.kv_dtype == NOVA_KV_F16;
     if (b->kernel == 1 && f16 && a.n_q > 1 && a.n_layers == 1 && !a.write_partial_only) {
         // query-tiled prefill: every row complete in one CTA, no merge
-        if (b->prefill_tc5 && attn_prefill_tc5_supports(a)) return launch_attn_prefill_tc5(a, s);
+        if (b->prefill_tc5 && attn_prefill_tc5_supports(a)) {
+            // Longest context first: a CTA's work grows with its session's context, and the launch ends with the CTAs
+            // that were handed out last (host positions, the same ones pick_split_ctas reads).
+            AttnLaunch pa = a;
+            const PagePool& pp = b->e->pool.p;
+            if (b->n >= 2 && b->n <= 64 && a.n_sessions == b->n) {
+                int64_t len[64];
+                for (int i = 0; i < b->n; ++i) {
+                    const SliceState* st = pp.find(b->slices[i]);
+                    len[i] = st ? st->n_past : 0;
+                    pa.sess_order[i] = (unsigned char)i;
+                }
+                std::stable_sort(pa.sess_order, pa.sess_order + b->n, [&](unsigned char x, unsigned char y) { return len[x] > len[y]; });
+                pa.n_order = b->n;
+            }
+            return launch_attn_prefill_tc5(pa, s);
+        }
         return launch_attn_prefill(a, s);
     }
     if (b->kernel == 1 && f16 && b->cascade && b->casc_pages > 0 && a.n_layers == 1 && a.n_q <= 1 && !a.write_partial_only &&
