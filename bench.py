@@ -153,6 +153,8 @@ def configure_batch(nv, batch, args, prefix=False):
         batch.set_pdl(0 if args.no_pdl else 1)
     if args.row_setup >= 0:
         batch.set_row_setup_pages(args.row_setup)
+    if args.split_ctas > 0 and kernel == 1:
+        batch.set_split_ctas(args.split_ctas)
     if kernel == 1 and args.prefill_kernel >= 0:
         nv.lib.nova_batch_set_prefill_kernel(batch.h, args.prefill_kernel)       # refused for page sizes it does not take
     cascade = bool(kernel == 1 and prefix and not args.no_cascade)
@@ -860,6 +862,7 @@ def main():
     ap.add_argument("--no-fused-append", action="store_true",
                     help="keep RoPE+append as its own launch instead of doing it inside the attention launch")
     ap.add_argument("--row-setup", type=int, default=-1, help="work-split weight of a session start, in pages")
+    ap.add_argument("--split-ctas", type=int, default=0, help="CTAs of a tensor-core attention launch (0 = the library's choice)")
     ap.add_argument("--no-cascade", action="store_true", help="config 3: attend the shared prefix per session, as the plain path does")
     ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch between layers")
     ap.add_argument("--late-inputs", action="store_true",

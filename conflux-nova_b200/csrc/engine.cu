@@ -271,6 +271,14 @@ int pick_split_ctas(const nova_batch* b, const AttnLaunch& a) {
     const int half = (sm_count() / 2) * per_sm, third = (sm_count() / 3) * per_sm;
     // measured on one 7B-shaped session (per layer): 1024 pages 8.7-9.4 us with 37-56 CTAs, 9.5 with 74, 11.8 with 136;
     // 2048 pages 14.3 with 74 or 136; 4096 pages 24.5 with 74, 23.0 with 136
+    // a handful of pages (one short session): a CTA per four pages, at least eight - the merge then has few partial slots
+    // to fold (1.5B shape, 1 x 1024 tokens = 64 pages per layer: 0.180 ms per step with 64 CTAs, 0.167 with 16)
+    if (pages <= 128) {
+        int few = (int)(pages / 4);
+        if (few < 8) few = 8;
+        if (few > third) few = third;
+        return few < all ? few : all;
+    }
     if (pages < (int64_t)all * 8) return third < all ? third : all;
     return pages < (int64_t)all * 16 ? (half < all ? half : all) : all;
 }
